@@ -1,0 +1,81 @@
+// Rotary position encoding of q and k (NeoX pairing) fused with the append of k and v to
+// the paged cache.
+//
+// qkv is one row per token: [q heads | k heads | v heads], each head head_dim wide.
+// For i < rotary_dim/2:  ang = pos * inv_freq[i];  (a, b) = (x[i], x[i + rotary_dim/2]);
+// x[i] = a cos - b sin;  x[i + half] = a sin + b cos.  Dimensions >= rotary_dim and v are
+// untouched (crates/kernels/src/cu/ops.cu:488-523; crates/kernels/src/cpu/mod.rs:275-314).
+// The reference then stores k and v in a second kernel (ops.cu:661-685) and scatters a slot
+// table in a third (:693-701); here the page of a token is looked up in the request's block
+// table: page = table[entry][pos / page_size], row = pos % page_size.
+//
+// Angles, sine and cosine are 32-bit with the accurate sincosf.  inv_freq comes from the
+// host, so the device's pow never enters.
+#include "common.cuh"
+
+namespace {
+
+template <typename T>
+__global__ void rope_cache_kernel(T* __restrict__ qkv, int row_stride, const int* __restrict__ positions,
+                                  const int* __restrict__ tok_entry, const int* __restrict__ block_table,
+                                  int max_blocks, const float* __restrict__ inv_freq, int rotary_dim,
+                                  T* __restrict__ k_cache, T* __restrict__ v_cache, int page_size,
+                                  int n_heads, int n_kv, int head_dim, int write_cache) {
+    const int t = blockIdx.x;
+    const int h = blockIdx.y;                 // [0,n_heads): q   [n_heads, +n_kv): k   then v
+    const int pos = positions[t];
+    T* row = qkv + (size_t)t * row_stride + (size_t)h * head_dim;
+    const int half = rotary_dim >> 1;
+    const bool is_q = h < n_heads;
+    const bool is_k = !is_q && h < n_heads + n_kv;
+    T* dst = nullptr;
+    if (!is_q) {
+        if (!write_cache) return;
+        const int kvh = is_k ? h - n_heads : h - n_heads - n_kv;
+        const int page = block_table[(size_t)tok_entry[t] * max_blocks + pos / page_size];
+        if (page < 0) return;     // never for a token of this step; guards a bad table
+        T* base = is_k ? k_cache : v_cache;
+        dst = base + (((size_t)page * n_kv + kvh) * page_size + (pos % page_size)) * head_dim;
+    }
+    if (is_q || is_k) {
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            float s, c;
+            sincosf((float)pos * inv_freq[i], &s, &c);
+            const float a = to_f32(row[i]), b = to_f32(row[i + half]);
+            const T ra = from_f32<T>(a * c - b * s), rb = from_f32<T>(a * s + b * c);
+            if (is_q) { row[i] = ra; row[i + half] = rb; }
+            else      { dst[i] = ra; dst[i + half] = rb; }
+        }
+        if (is_k)
+            for (int i = rotary_dim + threadIdx.x; i < head_dim; i += blockDim.x) dst[i] = row[i];
+    } else {
+        for (int i = threadIdx.x; i < head_dim; i += blockDim.x) dst[i] = row[i];
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+int infero_rope_cache(void* qkv, int dtype, int row_stride, const int* positions, const int* tok_entry,
+                      const int* block_table, int max_blocks, const float* inv_freq, int rotary_dim,
+                      void* k_cache, void* v_cache, int page_size, int n_tokens, int n_heads, int n_kv,
+                      int head_dim, int write_cache, cudaStream_t stream) {
+    if (n_tokens == 0) return 0;
+    INFERO_REQUIRE(rotary_dim >= 0 && rotary_dim % 2 == 0 && rotary_dim <= head_dim,
+                   "rope_cache: rotary_dim %d must be even and <= head_dim %d", rotary_dim, head_dim);
+    INFERO_REQUIRE(n_heads + 2 * n_kv <= 65535, "rope_cache: too many heads (%d)", n_heads + 2 * n_kv);
+    dim3 grid(n_tokens, n_heads + 2 * n_kv);
+    const int threads = head_dim >= 128 ? 64 : 32;
+    if (dtype == INFERO_F32)
+        rope_cache_kernel<float><<<grid, threads, 0, stream>>>((float*)qkv, row_stride, positions, tok_entry,
+            block_table, max_blocks, inv_freq, rotary_dim, (float*)k_cache, (float*)v_cache, page_size,
+            n_heads, n_kv, head_dim, write_cache);
+    else
+        rope_cache_kernel<bf16><<<grid, threads, 0, stream>>>((bf16*)qkv, row_stride, positions, tok_entry,
+            block_table, max_blocks, inv_freq, rotary_dim, (bf16*)k_cache, (bf16*)v_cache, page_size,
+            n_heads, n_kv, head_dim, write_cache);
+    return infero_check_launch("rope_cache");
+}
+
+}  // extern "C"

@@ -1,0 +1,46 @@
+// Error record shared by every launcher, and small device queries.
+#include "common.cuh"
+#include <cstdarg>
+#include <cstdio>
+
+static thread_local char g_error[1024] = {0};
+
+void infero_set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+// Launch errors only (invalid configuration and the like); asynchronous faults surface
+// at the caller's next synchronisation.
+int infero_check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        infero_set_error("%s: %s", what, cudaGetErrorString(e));
+        return 1;
+    }
+    return 0;
+}
+
+extern "C" {
+
+const char* infero_last_error() { return g_error; }
+
+int infero_abi_version() { return 1; }
+
+int infero_device_info(int device, int* sm_count, int* cc_major, int* cc_minor, int* smem_optin) {
+    cudaDeviceProp p;
+    cudaError_t e = cudaGetDeviceProperties(&p, device);
+    if (e != cudaSuccess) {
+        infero_set_error("device_info: %s", cudaGetErrorString(e));
+        return 1;
+    }
+    *sm_count = p.multiProcessorCount;
+    *cc_major = p.major;
+    *cc_minor = p.minor;
+    *smem_optin = (int)p.sharedMemPerBlockOptin;
+    return 0;
+}
+
+}  // extern "C"

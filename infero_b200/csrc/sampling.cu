@@ -1,0 +1,269 @@
+// Turning rows of logits into tokens on the device.
+//
+// The distribution is the reference's (crates/model/src/sampling.rs:169-235):
+//   repetition penalty (divide a positive logit, multiply a negative one)
+//   -> keep the top_k largest -> sort descending -> w = exp((z - max) / max(T, 1e-5))
+//   -> top_p: shortest prefix whose mass reaches top_p * total (top_p clamped to [1e-4, 1])
+//   -> r = u * total; the first candidate at which the running remainder is <= 0.
+// Greedy is a strict '>' scan, so ties keep the lowest index (sampling.rs:302-310;
+// crates/kernels/src/cu/sample.cu:42-47).  The uniform draw u comes from the host, one per
+// row, as in the reference (crates/server/src/scheduler.rs:1279-1299), so a host sampler
+// fed the same u picks the same token.
+//
+// One block per row.  The selection is a 4-pass radix select over order-preserving 32-bit
+// keys with integer histograms, ties at the threshold taken in ascending index, so the
+// result is a deterministic function of the row.  At most SAMPLE_MAX_K candidates survive
+// the top-k stage; a larger (or disabled) top_k is clamped to that.
+#include "common.cuh"
+#include <math_constants.h>
+
+namespace {
+
+constexpr int SAMPLE_THREADS = 1024;
+constexpr int SAMPLE_MAX_K = 1024;
+
+__device__ __forceinline__ uint32_t order_key(float v) {
+    // larger float -> larger unsigned key; NaN sorts lowest
+    if (v != v) return 0u;
+    uint32_t b = __float_as_uint(v);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float key_value(uint32_t k) {
+    uint32_t b = (k & 0x80000000u) ? (k & 0x7fffffffu) : ~k;
+    return __uint_as_float(b);
+}
+
+// (token, exponent) pairs: logits[row, token] is divided (if positive) or multiplied by
+// penalty^exponent.  Pairs with token < 0 are padding.
+__global__ void apply_penalty_kernel(float* __restrict__ logits, int vocab, const int* __restrict__ pen_tokens,
+                                     const int* __restrict__ pen_counts, int pen_stride,
+                                     const float* __restrict__ penalty) {
+    const int row = blockIdx.x;
+    const float p = penalty[row];
+    if (p == 1.0f) return;
+    for (int i = threadIdx.x; i < pen_stride; i += blockDim.x) {
+        const int tok = pen_tokens[(size_t)row * pen_stride + i];
+        if (tok < 0 || tok >= vocab) continue;
+        const int c = pen_counts[(size_t)row * pen_stride + i];
+        float* z = logits + (size_t)row * vocab + tok;
+        float v = *z;
+        for (int k = 0; k < c; ++k) v = v > 0.f ? v / p : v * p;
+        *z = v;
+    }
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out) {
+    __shared__ float bv[32];
+    __shared__ int bi[32];
+    const float* z = logits + (size_t)blockIdx.x * vocab;
+    float best = -CUDART_INF_F;
+    int idx = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float v = z[i];
+        if (v > best) { best = v; idx = i; }       // ascending i per thread: lowest index wins ties
+    }
+    // reduce (value desc, index asc)
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { bv[warp] = best; bi[warp] = idx; }
+    __syncthreads();
+    if (warp == 0) {
+        best = bv[lane]; idx = bi[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+        }
+        if (lane == 0) out[blockIdx.x] = (idx == 0x7fffffff) ? 0 : idx;   // all -inf/NaN: token 0, as the scan from (0,-inf)
+    }
+}
+
+// Exclusive prefix sum of one int per thread over the block; returns the total too.
+__device__ __forceinline__ int block_exclusive_scan(int v, int* total, int* warp_sums) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += n;
+    }
+    __syncthreads();
+    if (lane == 31) warp_sums[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        int w = warp_sums[lane];
+        int winc = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int n = __shfl_up_sync(0xffffffffu, winc, o);
+            if (lane >= o) winc += n;
+        }
+        warp_sums[lane] = winc - w;
+        if (lane == 31) warp_sums[32] = winc;
+    }
+    __syncthreads();
+    *total = warp_sums[32];
+    return warp_sums[warp] + inc - v;
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
+              const int* __restrict__ top_k, const float* __restrict__ top_p,
+              const double* __restrict__ draw, int* __restrict__ out) {
+    __shared__ int hist[256];
+    __shared__ int scan_ws[33];
+    __shared__ unsigned long long cand[SAMPLE_MAX_K];   // (key << 32) | ~index : descending sort = value desc, index asc
+    __shared__ uint32_t s_prefix;
+    __shared__ int s_need;
+    const int row = blockIdx.x;
+    const float* z = logits + (size_t)row * vocab;
+    int k = top_k[row];
+    if (k <= 0 || k > SAMPLE_MAX_K) k = SAMPLE_MAX_K;
+    if (k > vocab) k = vocab;
+
+    // ---- radix select: the key of the k-th largest element ----------------------------------
+    if (threadIdx.x == 0) { s_prefix = 0u; s_need = k; }
+    __syncthreads();
+    for (int pass = 0; pass < 4; ++pass) {
+        const int shift = 24 - 8 * pass;
+        const uint32_t mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+        for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
+        __syncthreads();
+        const uint32_t prefix = s_prefix;
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+            const uint32_t key = order_key(z[i]);
+            if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255], 1);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int need = s_need, b = 255;
+            for (; b > 0; --b) {
+                if (hist[b] >= need) break;
+                need -= hist[b];
+            }
+            s_prefix = prefix | ((uint32_t)b << shift);
+            s_need = need;
+        }
+        __syncthreads();
+    }
+    const uint32_t thr = s_prefix;     // key of the k-th largest
+    const int need_eq = s_need;        // how many elements equal to thr are taken (lowest indices)
+
+    // ---- collect survivors in index order (contiguous range per thread) -----------------------
+    const int per = (vocab + blockDim.x - 1) / blockDim.x;
+    const int lo = threadIdx.x * per, hi = min(vocab, lo + per);
+    int n_gt = 0, n_eq = 0;
+    for (int i = lo; i < hi; ++i) {
+        const uint32_t key = order_key(z[i]);
+        n_gt += key > thr;
+        n_eq += key == thr;
+    }
+    int tot_gt, tot_eq;
+    int off_gt = block_exclusive_scan(n_gt, &tot_gt, scan_ws);
+    int off_eq = block_exclusive_scan(n_eq, &tot_eq, scan_ws);
+    for (int i = threadIdx.x; i < SAMPLE_MAX_K; i += blockDim.x) cand[i] = 0ull;   // sorts last
+    __syncthreads();
+    for (int i = lo; i < hi; ++i) {
+        const uint32_t key = order_key(z[i]);
+        if (key > thr) {
+            cand[off_gt++] = ((unsigned long long)key << 32) | (uint32_t)(~(uint32_t)i);
+        } else if (key == thr) {
+            if (off_eq < need_eq) cand[tot_gt + off_eq] = ((unsigned long long)key << 32) | (uint32_t)(~(uint32_t)i);
+            ++off_eq;
+        }
+    }
+    __syncthreads();
+    const int n_cand = tot_gt + min(need_eq, tot_eq);    // == k
+
+    // ---- bitonic sort, descending, over SAMPLE_MAX_K slots ------------------------------------
+    for (int size = 2; size <= SAMPLE_MAX_K; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            const int i = threadIdx.x;
+            const int j = i ^ stride;
+            if (i < SAMPLE_MAX_K && j > i) {
+                const bool desc = (i & size) == 0;
+                const unsigned long long a = cand[i], b = cand[j];
+                if ((a < b) == desc) { cand[i] = b; cand[j] = a; }
+            }
+            __syncthreads();
+        }
+    }
+
+    // ---- weights in parallel, then nucleus and pick in the reference's sequential order -------
+    __shared__ double wd[SAMPLE_MAX_K];
+    {
+        const float t = fmaxf(temperature[row], 1e-5f);
+        const float inv_t = 1.0f / t;
+        const float zmax = key_value((uint32_t)(cand[0] >> 32));
+        for (int i = threadIdx.x; i < n_cand; i += blockDim.x) {
+            const float zi = key_value((uint32_t)(cand[i] >> 32));
+            wd[i] = exp((double)((zi - zmax) * inv_t));
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        // the total is summed from the double weights; afterwards each weight is its float rounding
+        double total = 0.0;
+        for (int i = 0; i < n_cand; ++i) total += wd[i];
+        int keep = n_cand;
+        float tp = top_p[row];
+        if (tp < 1.0f) {
+            tp = fminf(fmaxf(tp, 1e-4f), 1.0f);
+            const double target = total * (double)tp;
+            double acc = 0.0;
+            keep = 0;
+            for (int i = 0; i < n_cand; ++i) {
+                acc += (double)(float)wd[i];
+                ++keep;
+                if (acc >= target) break;
+            }
+            if (keep < 1) keep = 1;
+            total = 0.0;
+            for (int i = 0; i < keep; ++i) total += (double)(float)wd[i];
+        }
+        double r = draw[row] * total;
+        int pick = keep - 1;
+        for (int i = 0; i < keep; ++i) {
+            r -= (double)(float)wd[i];
+            if (r <= 0.0) { pick = i; break; }
+        }
+        out[row] = (int)(~(uint32_t)(cand[pick] & 0xffffffffull));
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+int infero_apply_penalty(float* logits, int n_rows, int vocab, const int* pen_tokens, const int* pen_counts,
+                         int pen_stride, const float* penalty, cudaStream_t stream) {
+    if (n_rows == 0 || pen_stride == 0) return 0;
+    apply_penalty_kernel<<<n_rows, 128, 0, stream>>>(logits, vocab, pen_tokens, pen_counts, pen_stride, penalty);
+    return infero_check_launch("apply_penalty");
+}
+
+int infero_argmax(const float* logits, int n_rows, int vocab, int* out, cudaStream_t stream) {
+    if (n_rows == 0) return 0;
+    INFERO_REQUIRE(vocab > 0, "argmax: empty vocabulary");
+    argmax_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, vocab, out);
+    return infero_check_launch("argmax");
+}
+
+int infero_sample(const float* logits, int n_rows, int vocab, const float* temperature, const int* top_k,
+                  const float* top_p, const double* draw, int* out, cudaStream_t stream) {
+    if (n_rows == 0) return 0;
+    INFERO_REQUIRE(vocab > 0, "sample: empty vocabulary");
+    sample_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, vocab, temperature, top_k, top_p, draw, out);
+    return infero_check_launch("sample");
+}
+
+int infero_sample_max_k() { return SAMPLE_MAX_K; }
+
+}  // extern "C"

@@ -1,0 +1,212 @@
+"""The step function: run one batch of (request, its next tokens) from the cache.
+
+A step holds any mix of prompt portions and single decoded tokens, cut anywhere; it runs
+only the tokens it is given, as one flat batch, against what earlier steps left in the
+cache, and returns 32-bit logits at the wanted places.  The reference's counterpart is
+``forward_batch_rows`` (crates/model/src/lib.rs:3423-4243): same flat layout
+(token_ids, seq_of, positions; :3483-3557), same constraints (a sequence at most once,
+:3464-3475; a token budget, :3445-3449), but logits only for the last rows of an item,
+where this step takes arbitrary positions.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache import CacheManager, CacheStorage, OutOfPages, RequestCache
+from ..config.engine_config import EngineConfig
+from ..models.decoder import DecoderModel
+
+
+class StepError(ValueError):
+    """A batch the step function refuses (nothing was run, nothing was reserved)."""
+
+
+@dataclass
+class StepEntry:
+    rid: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+class StepContext:
+    """What the parts see of a step."""
+
+    def __init__(self, runner: "ModelRunner"):
+        self._runner = runner
+        self.act_dtype: torch.dtype = runner.act_dtype
+        self.device = runner.device
+        self.n_tokens = 0
+        self.n_entries = 0
+        # device int32
+        self.token_ids: torch.Tensor = None
+        self.positions: torch.Tensor = None
+        self.tok_entry: torch.Tensor = None
+        self.entry_q_start: torch.Tensor = None
+        self.entry_q_len: torch.Tensor = None
+        self.entry_pos0: torch.Tensor = None
+        self.entry_slot: torch.Tensor = None
+        self._tables: List[torch.Tensor] = []
+        # host copies
+        self.h_q_start: np.ndarray = None
+        self.h_q_len: np.ndarray = None
+        self.h_pos0: np.ndarray = None
+        self.h_slot: np.ndarray = None
+        self.decode_only = False
+        self.max_q_len = 0
+        self.max_kv_len = 0
+        self._empty_f32 = None
+
+    def kv_cache(self, slot: int):
+        return self._runner.storage.layer_kv(slot)
+
+    def state(self, slot: int) -> torch.Tensor:
+        """[max_requests, *shape]; row ``entry_slot[e]`` belongs to entry e."""
+        return self._runner.storage.state(slot)
+
+    def block_table(self, group: int) -> torch.Tensor:
+        return self._tables[group]
+
+    def zero_inv_freq(self, device) -> torch.Tensor:
+        if self._empty_f32 is None:
+            self._empty_f32 = torch.empty(0, dtype=torch.float32, device=device)
+        return self._empty_f32
+
+
+class ModelRunner:
+    """Owns the cache (bookkeeping + device arrays) and runs steps of one model."""
+
+    def __init__(self, model: DecoderModel, cfg: EngineConfig, device=None):
+        self.model = model
+        self.cfg = cfg
+        self.device = torch.device(device or cfg.device)
+        self.act_dtype = torch.bfloat16 if cfg.dtype == "bfloat16" else torch.float32
+        self.page_size = cfg.page_size
+        self.num_pages = cfg.resolved_num_pages()
+        self.max_blocks = max(1, -(-cfg.ctx // cfg.page_size))
+        self.storage = CacheStorage(model.kv_specs, model.state_specs, self.num_pages, cfg.page_size,
+                                    cfg.max_seqs, self.act_dtype, self.device)
+        self.manager = CacheManager(self.storage.bookkeeping_groups(), self.num_pages, cfg.page_size,
+                                    cfg.max_seqs, max_blocks=self.max_blocks)
+        self.steps_run = 0
+        self.tokens_run = 0
+
+    # ---- requests --------------------------------------------------------------------------
+    def open(self, rid: Hashable) -> RequestCache:
+        return self.manager.open(rid)
+
+    def close(self, rid: Hashable) -> None:
+        self.manager.close(rid)
+
+    def length(self, rid: Hashable) -> int:
+        return self.manager.get(rid).length
+
+    # ---- the step ----------------------------------------------------------------------------
+    def _validate(self, entries: Sequence[StepEntry]) -> List[RequestCache]:
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        seen = set()
+        rcs = []
+        total = 0
+        rows = 0
+        vocab = self.model.spec.vocab_size
+        for e in entries:
+            if e.rid in seen:
+                raise StepError(f"request {e.rid!r} appears twice in one step")
+            seen.add(e.rid)
+            if e.rid not in self.manager.requests:
+                raise StepError(f"request {e.rid!r} is not open")
+            n = len(e.tokens)
+            if n == 0:
+                raise StepError(f"request {e.rid!r} brings no tokens")
+            rc = self.manager.get(e.rid)
+            if rc.length + n > self.cfg.ctx:
+                raise StepError(f"request {e.rid!r} would reach {rc.length + n} tokens, context is {self.cfg.ctx}")
+            for w in e.want:
+                if not (0 <= int(w) < n):
+                    raise StepError(f"request {e.rid!r}: wanted place {w} outside its {n} tokens")
+            for tkn in e.tokens:
+                if not (0 <= int(tkn) < vocab):
+                    raise StepError(f"request {e.rid!r}: token id {tkn} outside the vocabulary of {vocab}")
+            total += n
+            rows += len(e.want)
+            rcs.append(rc)
+        if total > self.cfg.max_batch_tokens:
+            raise StepError(f"step of {total} tokens exceeds the budget of {self.cfg.max_batch_tokens}")
+        if rows > self.cfg.max_logit_rows:
+            raise StepError(f"step wants {rows} rows of logits, at most {self.cfg.max_logit_rows}")
+        return rcs
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run the batch; returns float32 logits [rows wanted, vocab] on the device, in the
+        order of the entries and of each entry's ``want`` (None if nothing is wanted).
+        Raises OutOfPages (nothing reserved, nothing run) when the cache cannot hold it."""
+        rcs = self._validate(entries)
+        done: List[RequestCache] = []
+        try:
+            for rc, e in zip(rcs, entries):
+                self.manager.reserve(rc, len(e.tokens))
+                done.append(rc)
+        except OutOfPages:
+            for rc in done:
+                self.manager.abort_reservation(rc)
+            raise
+        try:
+            ctx, rows = self._build_context(entries, rcs)
+            for rc in rcs:
+                if rc.fresh and self.storage.states:
+                    self.storage.zero_state(rc.slot)
+            logits = self.model.forward(ctx, ctx.token_ids, rows)
+        except Exception:
+            for rc in rcs:
+                self.manager.abort_reservation(rc)
+            raise
+        for rc, e in zip(rcs, entries):
+            self.manager.commit(rc, len(e.tokens))
+        self.steps_run += 1
+        self.tokens_run += ctx.n_tokens
+        return logits
+
+    def _build_context(self, entries: Sequence[StepEntry], rcs: Sequence[RequestCache]):
+        E = len(entries)
+        lens = np.fromiter((len(e.tokens) for e in entries), dtype=np.int32, count=E)
+        T = int(lens.sum())
+        q_start = np.zeros(E, dtype=np.int32)
+        np.cumsum(lens[:-1], out=q_start[1:])
+        pos0 = np.fromiter((rc.length for rc in rcs), dtype=np.int32, count=E)
+        slots = np.fromiter((rc.slot for rc in rcs), dtype=np.int32, count=E)
+        token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+        tok_entry = np.repeat(np.arange(E, dtype=np.int32), lens)
+        positions = np.arange(T, dtype=np.int32) - np.repeat(q_start, lens) + np.repeat(pos0, lens)
+        want_rows = [q_start[i] + np.asarray(e.want, dtype=np.int32) for i, e in enumerate(entries) if len(e.want)]
+        rows = np.concatenate(want_rows).astype(np.int32) if want_rows else np.zeros(0, dtype=np.int32)
+        n_groups = len(self.manager.groups)
+        tables = [self.manager.block_table_array(g, rcs, self.max_blocks) for g in range(n_groups)]
+
+        # one pinned staging buffer, one host-to-device copy
+        parts = [token_ids, positions, tok_entry, q_start, lens, pos0, slots, rows] + [t.reshape(-1) for t in tables]
+        sizes = [p.size for p in parts]
+        total = int(sum(sizes))
+        staging = torch.empty(total, dtype=torch.int32, pin_memory=(self.device.type == "cuda"))
+        np.concatenate(parts, out=staging.numpy())
+        dev = staging.to(self.device, non_blocking=True)
+        views = []
+        off = 0
+        for s in sizes:
+            views.append(dev[off:off + s])
+            off += s
+
+        ctx = StepContext(self)
+        ctx.n_tokens, ctx.n_entries = T, E
+        (ctx.token_ids, ctx.positions, ctx.tok_entry, ctx.entry_q_start, ctx.entry_q_len, ctx.entry_pos0,
+         ctx.entry_slot, d_rows) = views[:8]
+        ctx._tables = [views[8 + g].view(E, self.max_blocks) for g in range(n_groups)]
+        ctx.h_q_start, ctx.h_q_len, ctx.h_pos0, ctx.h_slot = q_start, lens, pos0, slots
+        ctx.decode_only = bool((lens == 1).all())
+        ctx.max_q_len = int(lens.max())
+        ctx.max_kv_len = int((pos0 + lens).max())
+        ctx._staging = staging          # keep the pinned buffer alive until the copy has run
+        return ctx, (d_rows if rows.size else None)

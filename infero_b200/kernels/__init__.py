@@ -1,0 +1,204 @@
+"""Python face of the CUDA library: thin wrappers that check tensors and call the exported
+C launchers on the current torch stream.
+
+There is no CPU path and no library model code behind these names: if the shared library
+cannot be built or loaded, or a tensor is not on a CUDA device, the call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int, c_float, c_void_p, c_char_p, POINTER
+from typing import Optional
+
+import torch
+
+from .build import ensure_built, BuildError
+
+F32, BF16 = 0, 1
+_LIB = None
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def lib():
+    """The loaded shared library (built on first use)."""
+    global _LIB
+    if _LIB is None:
+        path = ensure_built()
+        try:
+            L = ctypes.CDLL(path)
+        except OSError as e:
+            raise KernelError(f"cannot load {path}: {e}") from None
+        L.infero_last_error.restype = c_char_p
+        L.infero_abi_version.restype = c_int
+        _LIB = L
+    return _LIB
+
+
+def loaded_library_path() -> Optional[str]:
+    return None if _LIB is None else _LIB._name
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"unsupported tensor dtype {t.dtype} (float32 or bfloat16 only)")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
+    if t is None:
+        return c_void_p(0)
+    if not t.is_cuda:
+        raise KernelError("tensor is not on a CUDA device; this engine has no CPU path")
+    return c_void_p(t.data_ptr())
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise KernelError(lib().infero_last_error().decode("utf-8", "replace"))
+
+
+def _i32(t: torch.Tensor, name: str) -> torch.Tensor:
+    if t.dtype != torch.int32 or not t.is_contiguous():
+        raise KernelError(f"{name} must be a contiguous int32 tensor")
+    return t
+
+
+# ---- embedding, norms, elementwise ---------------------------------------------------------
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out_x: torch.Tensor, scale: float = 1.0) -> None:
+    """out_x[t,:] = table[ids[t],:] * scale, out_x float32 [T, d]."""
+    T, d = out_x.shape
+    assert out_x.dtype == torch.float32 and out_x.is_contiguous() and table.is_contiguous()
+    assert table.shape[1] == d and ids.numel() == T
+    _check(lib().infero_embed_gather(_ptr(table), c_int(_dt(table)), _ptr(_i32(ids, "ids")), _ptr(out_x),
+                                     c_int(T), c_int(d), c_int(table.shape[0]), c_float(scale), _stream()))
+
+
+def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+    """x += delta (if given; 32-bit), out = rmsnorm(x) * weight.  With ``rows`` only those
+    rows are normalised (out has len(rows) rows) and x is left as it is."""
+    d = x.shape[1]
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous()
+    assert weight.numel() == d and out.shape[1] == d
+    n = out.shape[0]
+    if rows is None:
+        assert n == x.shape[0]
+    else:
+        assert rows.numel() == n
+    if delta is not None:
+        assert delta.shape == x.shape and delta.is_contiguous()
+    _check(lib().infero_add_rmsnorm(_ptr(x), _ptr(delta), c_int(_dt(delta) if delta is not None else F32),
+                                    _ptr(weight), c_int(_dt(weight)), c_float(eps), _ptr(out), c_int(_dt(out)),
+                                    _ptr(None if rows is None else _i32(rows, "rows")), c_int(n), c_int(d),
+                                    _stream()))
+
+
+def residual_add(x: torch.Tensor, delta: torch.Tensor) -> None:
+    assert x.dtype == torch.float32 and x.shape == delta.shape and x.is_contiguous() and delta.is_contiguous()
+    _check(lib().infero_residual_add(_ptr(x), _ptr(delta), c_int(_dt(delta)), c_int(x.shape[0]),
+                                     c_int(x.shape[1]), _stream()))
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, j] = silu(gate_up[t, j]) * gate_up[t, ff + j]."""
+    T, ff = out.shape
+    assert gate_up.shape == (T, 2 * ff) and gate_up.dtype == out.dtype
+    assert gate_up.is_contiguous() and out.is_contiguous()
+    _check(lib().infero_swiglu(_ptr(gate_up), _ptr(out), c_int(_dt(out)), c_int(T), c_int(ff), _stream()))
+
+
+# ---- matrix products ------------------------------------------------------------------------
+def gemm_tiled(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out[M,N] = a[M,K] @ w[N,K]^T (+ bias); 32-bit accumulation in ascending k."""
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.shape == (M, N) and w.is_contiguous()
+    assert a.stride(1) == 1 and out.stride(1) == 1
+    _check(lib().infero_gemm_tiled(_ptr(a), c_int(_dt(a)), _ptr(w), c_int(_dt(w)), _ptr(bias),
+                                   c_int(_dt(bias) if bias is not None else F32), _ptr(out), c_int(_dt(out)),
+                                   c_int(M), c_int(N), c_int(K), c_int(a.stride(0)), c_int(out.stride(0)),
+                                   _stream()))
+
+
+def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """bf16 x bf16 for 1..4 rows of a."""
+    M, K = a.shape
+    N = w.shape[0]
+    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous()
+    assert w.shape[1] == K and out.shape == (M, N) and a.stride(1) == 1 and out.stride(1) == 1
+    _check(lib().infero_gemm_skinny(_ptr(a), _ptr(w), _ptr(bias), c_int(_dt(bias) if bias is not None else F32),
+                                    _ptr(out), c_int(_dt(out)), c_int(M), c_int(N), c_int(K),
+                                    c_int(a.stride(0)), c_int(out.stride(0)), _stream()))
+
+
+# ---- position encoding + cache append, attention --------------------------------------------
+def rope_cache(qkv: torch.Tensor, positions: torch.Tensor, tok_entry: torch.Tensor, block_table: torch.Tensor,
+               inv_freq: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, n_heads: int, n_kv: int,
+               head_dim: int, page_size: int, write_cache: bool = True) -> None:
+    """Rotate q (in place) and k, append k and v to their pages.  qkv [T, (H + 2 Hkv) * D];
+    caches [pages, Hkv, page_size, D] of qkv's dtype; block_table [entries, max_blocks]."""
+    T = qkv.shape[0]
+    assert qkv.stride(1) == 1 and qkv.shape[1] == (n_heads + 2 * n_kv) * head_dim
+    assert k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype
+    assert k_cache.is_contiguous() and v_cache.is_contiguous() and block_table.dim() == 2
+    assert inv_freq.dtype == torch.float32
+    rotary = 2 * inv_freq.numel()
+    _check(lib().infero_rope_cache(_ptr(qkv), c_int(_dt(qkv)), c_int(qkv.stride(0)), _ptr(_i32(positions, "positions")),
+                                   _ptr(_i32(tok_entry, "tok_entry")), _ptr(_i32(block_table, "block_table")),
+                                   c_int(block_table.shape[1]), _ptr(inv_freq), c_int(rotary), _ptr(k_cache),
+                                   _ptr(v_cache), c_int(page_size), c_int(T), c_int(n_heads), c_int(n_kv),
+                                   c_int(head_dim), c_int(1 if write_cache else 0), _stream()))
+
+
+def attention_generic(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                      block_table: torch.Tensor, tok_entry: torch.Tensor, positions: torch.Tensor,
+                      n_heads: int, n_kv: int, head_dim: int, page_size: int, window: Optional[int],
+                      scale: float) -> None:
+    """q: [T, >= H*D] view (row stride free), out [T, H*D]."""
+    T = q.shape[0]
+    assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_cache.dtype
+    _check(lib().infero_attention_generic(_ptr(q), c_int(q.stride(0)), _ptr(out), c_int(out.stride(0)),
+                                          _ptr(k_cache), _ptr(v_cache), c_int(_dt(q)),
+                                          _ptr(_i32(block_table, "block_table")), c_int(block_table.shape[1]),
+                                          _ptr(_i32(tok_entry, "tok_entry")), _ptr(_i32(positions, "positions")),
+                                          c_int(T), c_int(n_heads), c_int(n_kv), c_int(head_dim),
+                                          c_int(page_size), c_int(window or 0), c_float(scale), _stream()))
+
+
+# ---- sampling --------------------------------------------------------------------------------
+def apply_penalty(logits: torch.Tensor, pen_tokens: torch.Tensor, pen_counts: torch.Tensor,
+                  penalty: torch.Tensor) -> None:
+    R, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.is_contiguous() and penalty.dtype == torch.float32
+    assert pen_tokens.shape == pen_counts.shape and pen_tokens.shape[0] == R
+    _check(lib().infero_apply_penalty(_ptr(logits), c_int(R), c_int(V), _ptr(_i32(pen_tokens, "pen_tokens")),
+                                      _ptr(_i32(pen_counts, "pen_counts")), c_int(pen_tokens.shape[1]),
+                                      _ptr(penalty), _stream()))
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    R, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.is_contiguous() and out.numel() >= R
+    _check(lib().infero_argmax(_ptr(logits), c_int(R), c_int(V), _ptr(_i32(out, "out")), _stream()))
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           draw: torch.Tensor, out: torch.Tensor) -> None:
+    R, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    assert temperature.dtype == torch.float32 and top_p.dtype == torch.float32 and draw.dtype == torch.float64
+    _check(lib().infero_sample(_ptr(logits), c_int(R), c_int(V), _ptr(temperature), _ptr(_i32(top_k, "top_k")),
+                               _ptr(top_p), _ptr(draw), _ptr(_i32(out, "out")), _stream()))
+
+
+def sample_max_k() -> int:
+    return int(lib().infero_sample_max_k())

@@ -1,0 +1,3 @@
+from .decoder import DecoderModel
+
+__all__ = ["DecoderModel"]

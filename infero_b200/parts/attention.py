@@ -1,0 +1,85 @@
+"""Grouped-query attention over the paged cache."""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import kernels as K
+from ..config.spec import MixerSpec
+from ..registry import part_class
+from .base import KvCacheSpec, Mixer, TensorDecl
+from .linear import Linear
+
+
+class GqaAttention(Mixer):
+    """q,k,v = h Wq^T + bq, ...; rotary on q and k; append k,v to the cache; causal (and
+    windowed) softmax attention with kv head = head // group; delta = attn Wo^T
+    (crates/model/src/lib.rs:5628-5663, :5895-5913, :5979-5993, :6996-7047).
+
+    q, k and v are one stacked product [H*D + 2*Hkv*D, d] with a stacked bias; the reference
+    stacks them only for its quantised formats (crates/model/src/weights.rs:2704-2735).
+    """
+
+    def __init__(self, spec: MixerSpec, prefix: str):
+        if spec.num_kv_heads <= 0 or spec.num_heads % spec.num_kv_heads:
+            raise ValueError(f"{spec.num_heads} heads are not a multiple of {spec.num_kv_heads} kv heads")
+        if spec.head_dim % 2 or not (2 <= spec.head_dim <= 256):
+            raise ValueError(f"head_dim {spec.head_dim} must be even and at most 256")
+        self.spec = spec
+        self.prefix = prefix
+        self.rope = None
+        if spec.position is not None:
+            self.rope = part_class("position", spec.position.kind)(spec.position)
+        self.qkv: Linear = None
+        self.out: Linear = None
+
+    def _n(self, leaf: str) -> str:
+        return f"{self.prefix}.self_attn.{leaf}"
+
+    def cache_spec(self) -> Optional[KvCacheSpec]:
+        return KvCacheSpec(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window)
+
+    def declare(self) -> List[TensorDecl]:
+        s = self.spec
+        da, dkv = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
+        out = [TensorDecl(self._n("q_proj.weight"), (da, s.hidden)),
+               TensorDecl(self._n("k_proj.weight"), (dkv, s.hidden)),
+               TensorDecl(self._n("v_proj.weight"), (dkv, s.hidden)),
+               TensorDecl(self._n("o_proj.weight"), (s.hidden, da))]
+        if s.qkv_bias:
+            out += [TensorDecl(self._n("q_proj.bias"), (da,), role="bias"),
+                    TensorDecl(self._n("k_proj.bias"), (dkv,), role="bias"),
+                    TensorDecl(self._n("v_proj.bias"), (dkv,), role="bias")]
+        if s.out_bias:
+            out.append(TensorDecl(self._n("o_proj.bias"), (s.hidden,), role="bias"))
+        return out
+
+    @staticmethod
+    def _stack(ts):
+        if len({t.dtype for t in ts}) > 1:
+            ts = [t.float() for t in ts]
+        return torch.cat(ts, dim=0)
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        s = self.spec
+        w = self._stack([tensors[self._n(f"{p}_proj.weight")] for p in "qkv"])
+        b = self._stack([tensors[self._n(f"{p}_proj.bias")] for p in "qkv"]) if s.qkv_bias else None
+        self.qkv = Linear(w, b, self._n("qkv_proj"))
+        ob = tensors[self._n("o_proj.bias")] if s.out_bias else None
+        self.out = Linear(tensors[self._n("o_proj.weight")], ob, self._n("o_proj"))
+
+    def forward(self, ctx, h, slot):
+        s = self.spec
+        T = h.shape[0]
+        H, Hkv, D = s.num_heads, s.num_kv_heads, s.head_dim
+        qkv = self.qkv.forward(h)                              # [T, (H + 2 Hkv) D]
+        kv = ctx.kv_cache(slot.cache)                          # keys, values, group
+        table = ctx.block_table(kv.group)
+        inv = self.rope.inv_freq(h.device) if self.rope is not None else ctx.zero_inv_freq(h.device)
+        K.rope_cache(qkv, ctx.positions, ctx.tok_entry, table, inv, kv.k, kv.v, H, Hkv, D,
+                     kv.page_size, write_cache=slot.write_cache)
+        attn = torch.empty((T, H * D), dtype=h.dtype, device=h.device)
+        from ..kernels import attention as A
+        A.paged_attention(ctx, qkv, attn, kv, table, H, Hkv, D, s.window, s.scale)
+        return self.out.forward(attn)

@@ -1,0 +1,47 @@
+"""out = a @ W^T (+ bias): the one place that picks a matrix-product kernel.
+
+Weights stay [out_features, in_features] as stored (crates/model/src/weights.rs:2276-2277).
+Choice, in the spirit of the reference's ``matmul_pre`` (crates/model/src/lib.rs:8462-8505):
+
+  float32 weights or activations -> gemm_tiled (true 32-bit, order-fixed accumulation)
+  bf16 x bf16                    -> the tcgen05 kernel when the shape allows it,
+                                    gemm_skinny for 1..4 rows otherwise,
+                                    gemm_tiled as the any-shape fallback.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import kernels as K
+
+
+class Linear:
+    def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, name: str = ""):
+        assert weight.dim() == 2
+        self.weight = weight.contiguous()
+        self.bias = bias
+        self.name = name
+        self.out_features, self.in_features = weight.shape
+
+    def forward(self, a: torch.Tensor, out: Optional[torch.Tensor] = None,
+                out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        M = a.shape[0]
+        if out is None:
+            out = torch.empty((M, self.out_features), dtype=out_dtype or a.dtype, device=a.device)
+        if M == 0:
+            return out
+        w = self.weight
+        if a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+            from ..kernels import tc_gemm
+            if tc_gemm.supported(a, w, out):
+                tc_gemm.gemm(a, w, self.bias, out)
+                return out
+            if (M <= 16 and self.in_features % 8 == 0 and a.stride(0) % 8 == 0
+                    and a.data_ptr() % 16 == 0):
+                for m0 in range(0, M, 4):
+                    K.gemm_skinny(a[m0:m0 + 4], w, self.bias, out[m0:m0 + 4])
+                return out
+        K.gemm_tiled(a, w, self.bias, out)
+        return out

@@ -1,0 +1,123 @@
+"""The engine against the plain implementation under every way of cutting the work."""
+import numpy as np
+import pytest
+
+import replay_util as R
+from engine_fixtures import TOL, make_requests, make_runner, model_dir, plain_logits
+from tiny_configs import CONFIGS
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"A": [40, 1, 17, 33, 64, 90], "B": [120, 3, 70, 49, 97, 130], "C": [150, 31, 66]}
+CASES = [(n, d) for n in ("A", "B", "C") for d in ("float32", "bfloat16")]
+
+
+def _check(name, dtype, steps, reqs, mdir, max_tokens=None, page_size=16):
+    plain = plain_logits(mdir, reqs)
+    n = max_tokens or R.max_live_tokens(steps, reqs)
+    runner = make_runner(mdir, dtype, n, page_size=page_size)
+    got = R.replay_inprocess(runner, steps)
+    assert got, "the trace asked for no logits"
+    err, where = R.compare(got, plain)
+    assert err <= TOL[dtype], f"{name} {dtype}: relative error {err:.3e} at {where}"
+    assert not runner.manager.requests
+    for a in runner.manager.allocators:
+        assert a.num_free == a.num_pages
+    return runner, err
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_each_request_alone_and_whole(name, dtype):
+    mdir = model_dir(name)
+    reqs = make_requests(name, LENGTHS[name], seed=1)
+    _check(name, dtype, R.steps_whole(reqs), reqs, mdir)
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_last_32_tokens_one_by_one(name, dtype):
+    mdir = model_dir(name)
+    reqs = make_requests(name, LENGTHS[name], seed=2)
+    _check(name, dtype, R.steps_tail_decode(reqs, 32), reqs, mdir)
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_portions_of_changing_size(name, dtype):
+    mdir = model_dir(name)
+    reqs = make_requests(name, LENGTHS[name], seed=3)
+    _check(name, dtype, R.steps_chunked(reqs, seed=5), reqs, mdir)
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+@pytest.mark.parametrize("seed", [0, 1])
+def test_mixed_batches_with_page_reuse(name, dtype, seed):
+    mdir = model_dir(name)
+    lengths = LENGTHS[name] + [l + 5 for l in LENGTHS[name]]
+    reqs = make_requests(name, lengths, seed=10 + seed)
+    steps = R.steps_mixed(reqs, seed=seed, max_live=4)
+    runner, _ = _check(name, dtype, steps, reqs, mdir)
+    assert runner.manager.pages_reused > 0, "the pool was large enough that no page was used twice"
+    if CONFIGS[name].get("use_sliding_window"):
+        assert runner.manager.pages_reclaimed > 0, "no page of the window group came back early"
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_sharp_attention(name, dtype):
+    """Scaled q/k projections make single keys dominate, so a wrong or missing key shows."""
+    mdir = model_dir(name, qk_gain=6.0)
+    reqs = make_requests(name, LENGTHS[name][:4], seed=7)
+    _check(name, dtype, R.steps_mixed(reqs, seed=3, max_live=3), reqs, mdir)
+    _check(name, dtype, R.steps_tail_decode(reqs, 32), reqs, mdir)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("page_size", [32, 64])
+def test_other_page_sizes(dtype, page_size):
+    mdir = model_dir("B")
+    reqs = make_requests("B", [130, 70, 65, 100, 127], seed=4)
+    steps = R.steps_mixed(reqs, seed=9, max_live=3)
+    _check("B", dtype, steps, reqs, mdir, page_size=page_size)
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_long_decoding(name, dtype):
+    """One prompt token, then every further token alone: hundreds of single-token steps."""
+    mdir = model_dir(name)
+    n = {"A": 250, "B": 400, "C": 300}[name]
+    reqs = make_requests(name, [n], seed=11)
+    steps = R.steps_tail_decode(reqs, tail=n - 1)
+    _check(name, dtype, steps, reqs, mdir)
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_first_tokens_of_a_sequence(name, dtype):
+    mdir = model_dir(name)
+    reqs = make_requests(name, [1, 2, 3, 4], seed=12)
+    steps = R.steps_whole(reqs)
+    _check(name, dtype, steps, reqs, mdir)
+    steps = R.steps_tail_decode(reqs, tail=8)
+    _check(name, dtype, steps, reqs, mdir)
+
+
+def test_float32_cuts_agree_bitwise():
+    """On the 32-bit path a token's arithmetic does not depend on the cut at all."""
+    mdir = model_dir("B")
+    reqs = make_requests("B", [90, 61], seed=13)
+    a = R.replay_inprocess(make_runner(mdir, "float32", 256), R.steps_whole(reqs))
+    b = R.replay_inprocess(make_runner(mdir, "float32", 256), R.steps_chunked(reqs, seed=2))
+    c = R.replay_inprocess(make_runner(mdir, "float32", 256), R.steps_mixed(reqs, seed=4, max_live=2))
+    for key, row in a.items():
+        assert np.array_equal(row, b[key]), f"chunked differs at {key}"
+        if key in c:
+            assert np.array_equal(row, c[key]), f"mixed differs at {key}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(tmp_path, dtype):
+    """The same through bin/trace_run over a pipe."""
+    mdir = model_dir("B")
+    reqs = make_requests("B", [80, 45, 100, 33], seed=14)
+    steps = R.steps_mixed(reqs, seed=6, max_live=3)
+    n = R.max_live_tokens(steps, reqs)
+    got = R.replay_subprocess(mdir, dtype, steps, n, str(tmp_path / "out"), CONFIGS["B"]["vocab_size"])
+    err, where = R.compare(got, plain_logits(mdir, reqs))
+    assert err <= TOL[dtype], f"trace_run {dtype}: relative error {err:.3e} at {where}"
