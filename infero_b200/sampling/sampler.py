@@ -1,0 +1,72 @@
+"""Device sampling for the rows of a step.
+
+The pipeline and its order are the reference's (crates/model/src/sampling.rs:108-235): the
+uniform draw is taken on the host from the request's own generator and handed to the
+kernel, so only the selection runs on the device (crates/server/src/scheduler.rs:1279-1299).
+Greedy rows go through the argmax kernel; the repetition penalty is applied to the logits
+in place first (once per distinct token for greedy, once per occurrence otherwise, exactly
+as sampling.rs:240-310 does).
+"""
+from __future__ import annotations
+
+from collections import Counter
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import kernels as K
+from .params import SamplingParams
+
+
+class RowSampler:
+    """Host-side state of one request's sampler: parameters and generator."""
+
+    def __init__(self, params: SamplingParams):
+        self.params = params
+        self.rng = np.random.Generator(np.random.PCG64(params.seed))
+
+    def next_draw(self) -> float:
+        return float(self.rng.random())
+
+    def penalty_pairs(self, history: Sequence[int]):
+        p = self.params
+        if p.repetition_penalty == 1.0 or not history:
+            return []
+        recent = history[-p.repetition_window:] if p.repetition_window > 0 else []
+        if p.is_greedy():
+            return [(t, 1) for t in sorted(set(recent))]
+        return sorted(Counter(recent).items())
+
+
+def sample_rows(logits: torch.Tensor, samplers: Sequence[RowSampler],
+                histories: Sequence[Sequence[int]]) -> List[int]:
+    """Pick one token per row of ``logits`` [R, vocab] (float32, device; modified in place
+    when a repetition penalty applies).  Returns host ints (one device-to-host copy)."""
+    R, V = logits.shape
+    assert len(samplers) == R and len(histories) == R
+    dev = logits.device
+    pairs = [s.penalty_pairs(h) for s, h in zip(samplers, histories)]
+    width = max((len(p) for p in pairs), default=0)
+    if width:
+        toks = np.full((R, width), -1, dtype=np.int32)
+        cnts = np.zeros((R, width), dtype=np.int32)
+        for r, p in enumerate(pairs):
+            for i, (t, c) in enumerate(p):
+                toks[r, i], cnts[r, i] = t, c
+        pen = np.array([s.params.repetition_penalty for s in samplers], dtype=np.float32)
+        K.apply_penalty(logits, torch.from_numpy(toks).to(dev), torch.from_numpy(cnts).to(dev),
+                        torch.from_numpy(pen).to(dev))
+    greedy = [s.params.is_greedy() for s in samplers]
+    out = torch.empty(2 * R, dtype=torch.int32, device=dev)
+    K.argmax(logits, out[:R])
+    if not all(greedy):
+        temp = np.array([max(s.params.temperature, 0.0) for s in samplers], dtype=np.float32)
+        topk = np.array([s.params.top_k for s in samplers], dtype=np.int32)
+        topp = np.array([s.params.top_p for s in samplers], dtype=np.float32)
+        # a draw is taken for every row, greedy or not, as the reference does (sampling.rs:113-121)
+        draw = np.array([s.next_draw() for s in samplers], dtype=np.float64)
+        K.sample(logits, torch.from_numpy(temp).to(dev), torch.from_numpy(topk).to(dev),
+                 torch.from_numpy(topp).to(dev), torch.from_numpy(draw).to(dev), out[R:])
+    host = out.cpu().numpy()
+    return [int(host[r] if greedy[r] else host[R + r]) for r in range(R)]

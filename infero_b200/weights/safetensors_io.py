@@ -14,6 +14,7 @@ import json
 import mmap
 import os
 import struct
+import warnings
 from dataclasses import dataclass
 from typing import Dict, Iterable, Iterator, List, Tuple
 
@@ -87,7 +88,9 @@ class SafetensorsFile:
             n *= s
         if n == 0:
             return torch.empty(ent.shape, dtype=ent.dtype)
-        t = torch.frombuffer(self._mm, dtype=ent.dtype, count=n, offset=ent.begin)
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore", UserWarning)     # the mapping is read-only by design
+            t = torch.frombuffer(self._mm, dtype=ent.dtype, count=n, offset=ent.begin)
         return t.view(ent.shape)
 
     def close(self):

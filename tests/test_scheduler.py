@@ -1,0 +1,221 @@
+"""Scheduler decisions with a fake step function (no GPU)."""
+import random
+
+import pytest
+
+from infero_b200.cache import CacheManager, GroupSpec
+from infero_b200.engine.scheduler import Request, Scheduler
+from infero_b200.sampling import SamplingParams
+
+
+class FakeExecutor:
+    """Reserves and commits pages like the real step function; the 'model' returns
+    (sum of the request's tokens so far + position) % vocab, so outputs are checkable."""
+
+    def __init__(self, manager, vocab=100):
+        self.manager = manager
+        self.vocab = vocab
+        self.batches = []
+        self.seen = {}
+
+    def __call__(self, items):
+        self.batches.append([(it.run.req.rid, len(it.tokens), it.is_decode, it.samples) for it in items])
+        out = []
+        for it in items:
+            self.manager.reserve(it.run.rc, len(it.tokens))
+        for it in items:
+            self.manager.commit(it.run.rc, len(it.tokens))
+            hist = self.seen.setdefault(it.run.req.rid, [])
+            assert it.run.rc.length - len(it.tokens) == len(hist) or it.run.preemptions, "tokens fed out of order"
+            if it.run.rc.length - len(it.tokens) == 0:
+                hist.clear()
+            hist.extend(it.tokens)
+            if it.samples:
+                out.append((sum(hist) + len(hist)) % self.vocab)
+        self.manager.check()
+        return out
+
+
+def expected_output(prompt, n, vocab=100, eos=()):
+    seq, out = list(prompt), []
+    for _ in range(n):
+        t = (sum(seq) + len(seq)) % vocab
+        if t in eos:
+            break
+        out.append(t)
+        seq.append(t)
+    return out
+
+
+def make(num_pages=64, page_size=16, max_seqs=4, budget=64, ctx=512, groups=None, chunk=None):
+    m = CacheManager(groups or [GroupSpec(None)], num_pages=num_pages, page_size=page_size, max_requests=max_seqs)
+    ex = FakeExecutor(m)
+    return Scheduler(m, ex, max_seqs=max_seqs, max_batch_tokens=budget, ctx=ctx, max_prefill_chunk=chunk), ex, m
+
+
+def run_all(s, limit=5000):
+    out, reasons = {}, {}
+    for _ in range(limit):
+        if s.is_idle():
+            break
+        for ev in s.step():
+            if ev.token is not None:
+                out.setdefault(ev.rid, []).append(ev.token)
+            if ev.finished:
+                reasons[ev.rid] = (ev.reason, ev.message)
+    assert s.is_idle(), "scheduler did not drain"
+    return out, reasons
+
+
+def req(rid, prompt, n=8, **kw):
+    return Request(rid, list(prompt), SamplingParams.greedy(), max_new_tokens=n, **kw)
+
+
+def test_prompt_is_cut_under_the_token_budget_and_decodes_go_first():
+    s, ex, m = make(budget=32)
+    s.enqueue(req("a", range(1, 71), n=3))
+    out, reasons = run_all(s)
+    assert [b[0][1] for b in ex.batches[:3]] == [32, 32, 6]
+    assert [b[0][3] for b in ex.batches[:3]] == [False, False, True]
+    assert out["a"] == expected_output(range(1, 71), 3) and reasons["a"][0] == "length"
+    # a second request joins while the first decodes: decode item first, prompt portion after
+    s, ex, m = make(budget=16)
+    s.enqueue(req("a", [1, 2, 3], n=6))
+    s.step()
+    s.enqueue(req("b", range(40), n=2))
+    s.step()
+    assert ex.batches[1][0] == ("a", 1, True, True) and ex.batches[1][1] == ("b", 15, False, False)
+    out, _ = run_all(s)
+    assert m.free_pages(0) == 64
+
+
+def test_several_prompts_share_a_step():
+    s, ex, m = make(budget=64)
+    s.enqueue(req("a", range(20), n=1))
+    s.enqueue(req("b", range(30), n=1))
+    s.enqueue(req("c", range(30), n=1))
+    s.step()
+    assert ex.batches[0] == [("a", 20, False, True), ("b", 30, False, True), ("c", 14, False, False)]
+
+
+def test_eos_stops_without_appending_and_frees():
+    prompt = [5, 6, 7]
+    full = expected_output(prompt, 10)
+    eos = full[4]
+    s, ex, m = make()
+    s.enqueue(req("a", prompt, n=10, eos_token_ids=(eos,)))
+    out, reasons = run_all(s)
+    assert out["a"] == full[:full.index(eos)] and reasons["a"][0] == "stop"
+    assert m.free_pages(0) == 64 and not m.requests
+    s.enqueue(req("b", prompt, n=10, eos_token_ids=(eos,), ignore_eos=True))
+    out, reasons = run_all(s)
+    assert out["b"] == full and reasons["b"][0] == "length"
+
+
+def test_bad_requests_are_refused_up_front():
+    s, ex, m = make(ctx=32, num_pages=2)
+    s.enqueue(req("empty", []))
+    s.enqueue(req("long", range(40)))
+    s.enqueue(req("fits_ctx_not_pool", range(31)))          # 32 tokens = 2 pages: fits exactly
+    out, reasons = run_all(s)
+    assert reasons["empty"] == ("error", "empty prompt")
+    assert reasons["long"][0] == "error" and "context" in reasons["long"][1]
+    assert reasons["fits_ctx_not_pool"][0] == "length"
+    s, ex, m = make(ctx=512, num_pages=2)
+    s.enqueue(req("never", range(60)))
+    out, reasons = run_all(s)
+    assert reasons["never"][0] == "error" and "pool" in reasons["never"][1]
+
+
+def test_admission_waits_for_pages_and_keeps_fifo_order():
+    s, ex, m = make(num_pages=6, budget=128, max_seqs=4)
+    s.enqueue(req("a", range(60), n=4))      # 4 pages
+    s.enqueue(req("b", range(40), n=4))      # 3 pages: does not fit beside a
+    s.enqueue(req("c", range(5), n=4))       # would fit, but waits behind b
+    first = s.step()
+    assert [r.req.rid for r in s.running] == ["a"] and len(s.waiting) == 2
+    out, reasons = run_all(s)
+    out["a"] = [ev.token for ev in first if ev.token is not None] + out["a"]
+    assert out["a"] == expected_output(range(60), 4)
+    assert out["b"] == expected_output(range(40), 4)
+    assert out["c"] == expected_output(range(5), 4)
+    first_seen = [next(i for i, b in enumerate(ex.batches) if any(x[0] == r for x in b)) for r in "abc"]
+    assert first_seen == sorted(first_seen)
+
+
+def test_max_seqs_bounds_the_running_set():
+    s, ex, m = make(max_seqs=2)
+    for i in range(5):
+        s.enqueue(req(i, [i + 1, 2, 3], n=3))
+    for _ in range(200):
+        if s.is_idle():
+            break
+        s.step()
+        assert len(s.running) <= 2
+    assert s.stats["finished"] == 5
+
+
+def test_when_pages_run_out_the_youngest_is_recomputed_and_outputs_do_not_change():
+    # three requests that fit at admission but outgrow an 8-page pool while decoding
+    s, ex, m = make(num_pages=8, budget=64, max_seqs=3)
+    prompts = {"a": list(range(1, 31)), "b": list(range(2, 33)), "c": list(range(3, 30))}
+    for k, p in prompts.items():
+        s.enqueue(req(k, p, n=40))
+    out, reasons = run_all(s)
+    assert s.stats["preemptions"] > 0
+    for k, p in prompts.items():
+        assert out[k] == expected_output(p, 40), k
+        assert reasons[k][0] == "length"
+    assert m.free_pages(0) == 8 and not m.requests
+
+
+def test_a_request_that_holds_the_whole_pool_ends_with_length():
+    s, ex, m = make(num_pages=2, budget=64)
+    s.enqueue(req("a", range(20), n=100))
+    out, reasons = run_all(s)
+    assert reasons["a"] == ("length", "cache exhausted")
+    assert out["a"] == expected_output(range(20), 100)[:len(out["a"])] and 10 <= len(out["a"]) <= 13
+    assert m.free_pages(0) == 2
+
+
+def test_context_limit_ends_with_length():
+    s, ex, m = make(ctx=24)
+    s.enqueue(req("a", range(20), n=100))
+    out, reasons = run_all(s)
+    assert reasons["a"][0] == "length" and len(out["a"]) == 4
+
+
+def test_prefill_chunk_cap():
+    s, ex, m = make(budget=64, chunk=10)
+    s.enqueue(req("a", range(25), n=1))
+    run_all(s)
+    assert [b[0][1] for b in ex.batches] == [10, 10, 5]
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_load_with_a_window_group_drains_and_matches(seed):
+    rng = random.Random(seed)
+    s, ex, m = make(num_pages=rng.randint(10, 20), page_size=16, max_seqs=4, budget=rng.choice([16, 48, 96]),
+                    groups=[GroupSpec(None), GroupSpec(32)])
+    prompts = {}
+    for i in range(12):
+        prompts[i] = [rng.randrange(100) for _ in range(rng.randint(1, 70))]
+    pending = list(prompts.items())
+    out, reasons = {}, {}
+    for _ in range(5000):
+        while pending and rng.random() < 0.3:
+            k, p = pending.pop(0)
+            s.enqueue(req(k, p, n=rng.randint(1, 30)))
+        if s.is_idle() and not pending:
+            break
+        for ev in s.step():
+            if ev.token is not None:
+                out.setdefault(ev.rid, []).append(ev.token)
+            if ev.finished:
+                reasons[ev.rid] = ev.reason
+        m.check()
+    assert s.is_idle() and not pending
+    for k, p in prompts.items():
+        assert reasons[k] == "length"
+        assert out[k] == expected_output(p, len(out[k]))
+    assert all(a.num_free == a.num_pages for a in m.allocators)
