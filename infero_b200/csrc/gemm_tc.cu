@@ -1,0 +1,510 @@
+// bf16 matrix product on the 5th-generation tensor cores: out[M,N] = X[M,K] * W[N,K]^T (+ bias).
+//
+// One CTA computes one 128 x BN tile of D = A * B^T over a range of K, where A and B are both
+// K-major row-major matrices (activations [M,K] and weights [N,K] are stored exactly so):
+//   * TMA (cp.async.bulk.tensor, 128-byte swizzle) brings 128x64 and BNx64 bf16 tiles into a
+//     ring of shared-memory stages, signalled through mbarriers;
+//   * one elected thread issues tcgen05.mma (M=128, N=BN, K=16) four times per stage; the
+//     accumulator lives in tensor memory (128 lanes x BN 32-bit columns);
+//   * tcgen05.commit hands finished stages back to the loader and the finished accumulator
+//     to four epilogue warps, which read it with tcgen05.ld and write the result.
+// Warp roles: 0 loads, 1 owns TMEM and issues MMAs, 2..5 run the epilogue.
+//
+// Which matrix is "A" is the launcher's choice:
+//   many tokens (M > 256): A = activations, B = weights; an epilogue thread owns one token
+//     row and writes BN consecutive features (ROW mode).
+//   few tokens (decode, small chunks): A = weights, B = activations, so that the 128-wide
+//     side of the MMA is always full and the token side is as narrow as 16.  The CTAs then
+//     number N/128 x splits of K, enough to keep every SM streaming weights; with more than
+//     one split each CTA writes a 32-bit partial result [split, M, N] that the consumer
+//     (reduce_partials here, or a fused norm / activation kernel) sums in a fixed order
+//     (PARTIAL mode); with one split it writes the result itself (COL mode).
+// The reference takes cuBLAS for the same products above a row threshold and its own
+// mat-vec below (crates/model/src/lib.rs:8462-8505).
+//
+// Sizes: any M and N; K a multiple of 8 (rows must start on 16-byte boundaries for TMA);
+// edges are zero-filled by TMA on the way in and masked on the way out.
+#include "tc_common.cuh"
+#include <cudaTypedefs.h>
+#include <mutex>
+#include <unordered_map>
+#include <cstring>
+
+namespace {
+
+using namespace tc;
+
+constexpr int TILE_A = 128;
+constexpr int TILE_K = 64;
+constexpr int UMMA_K = 16;
+constexpr int GEMM_THREADS = 192;
+constexpr int A_STAGE_BYTES = TILE_A * TILE_K * 2;
+
+enum : int { EPI_ROW = 0, EPI_COL = 1, EPI_PARTIAL = 2 };
+
+template <int BN, int STAGES>
+struct SmemPlan {
+    static constexpr int B_STAGE_BYTES = BN * TILE_K * 2;
+    static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+    static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+    static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;      // barriers + slack for 1024-byte alignment
+};
+
+template <typename OutT>
+__device__ __forceinline__ void store16(OutT* dst, const float* v, bool vec_ok);
+template <>
+__device__ __forceinline__ void store16<float>(float* dst, const float* v, bool vec_ok) {
+    if (vec_ok) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) dst[i] = v[i];
+    }
+}
+template <>
+__device__ __forceinline__ void store16<bf16>(bf16* dst, const float* v, bool vec_ok) {
+    if (vec_ok) {
+        uint32_t p[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            p[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        reinterpret_cast<uint4*>(dst)[0] = make_uint4(p[0], p[1], p[2], p[3]);
+        reinterpret_cast<uint4*>(dst)[1] = make_uint4(p[4], p[5], p[6], p[7]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) dst[i] = __float2bfloat16_rn(v[i]);
+    }
+}
+
+template <int BN, int STAGES, int EPI, typename OutT>
+__global__ void __launch_bounds__(GEMM_THREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               OutT* __restrict__ out, const void* __restrict__ bias, int bias_dtype,
+               int RA, int RB, int K, int ktiles_per_split, long long ldc, int a_evict_first,
+               int* __restrict__ err_flag) {
+    using Plan = SmemPlan<BN, STAGES>;
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Plan::BAR_OFFSET);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* accum_bar = empty_bar + STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* never_flag = abort_flag + 1;           // stays 0: for waits that must not be cut short
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int a0 = blockIdx.x * TILE_A, b0 = blockIdx.y * BN;
+    const int total_kt = (K + TILE_K - 1) / TILE_K;
+    const int kt_begin = blockIdx.z * ktiles_per_split;
+    const int kt_end = min(total_kt, kt_begin + ktiles_per_split);
+    const int n_kt = kt_end - kt_begin;
+
+    if (threadIdx.x == 0) {
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(accum_bar, 1);
+        *abort_flag = 0;
+        *never_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---- loader --------------------------------------------------------------------------
+        if (elect_one()) {
+            // few-token path: A is the weight matrix, read once (evict first); B the activations,
+            // read by every CTA (evict last)
+            const uint64_t pol_a = policy_evict_first();
+            const uint64_t pol_b = policy_evict_last();
+            int issued = 0;
+            bool ok = true;
+            for (int i = 0; i < n_kt; ++i) {
+                const int s = i % STAGES;
+                const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
+                if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+                uint8_t* sa = smem + s * Plan::STAGE_BYTES;
+                mbar_expect_tx(&full_bar[s], Plan::STAGE_BYTES);
+                const int kx = (kt_begin + i) * TILE_K;
+                if (a_evict_first) {
+                    tma_load_2d_hint(sa, &map_a, kx, a0, &full_bar[s], pol_a);
+                    tma_load_2d_hint(sa + A_STAGE_BYTES, &map_b, kx, b0, &full_bar[s], pol_b);
+                } else {
+                    tma_load_2d(sa, &map_a, kx, a0, &full_bar[s]);
+                    tma_load_2d(sa + A_STAGE_BYTES, &map_b, kx, b0, &full_bar[s]);
+                }
+                issued = i + 1;
+            }
+            if (!ok) {
+                *abort_flag = 1;
+                atomicExch(err_flag, 1);
+            }
+            if (*abort_flag) {
+                // someone gave up: let the copies that are still in flight land before the
+                // block (and its shared memory) goes away
+                for (int i = max(0, issued - STAGES); i < issued; ++i)
+                    mbar_wait(&full_bar[i % STAGES], (uint32_t)(i / STAGES) & 1u, never_flag);
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issue -----------------------------------------------------------------------
+        if (elect_one()) {
+            constexpr uint32_t idesc = idesc_bf16_f32(TILE_A, BN);
+            bool ok = true;
+            for (int i = 0; i < n_kt; ++i) {
+                const int s = i % STAGES;
+                const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
+                if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t sa = smem_u32(smem + s * Plan::STAGE_BYTES);
+                const uint64_t da = smem_desc_k_sw128(sa);
+                const uint64_t db = smem_desc_k_sw128(sa + A_STAGE_BYTES);
+#pragma unroll
+                for (int k = 0; k < TILE_K / UMMA_K; ++k) {
+                    // 16 elements along K = 32 bytes = 2 units of the descriptor's address field
+                    umma_bf16(tmem_base, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
+                              (i > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(&empty_bar[s]);
+            }
+            if (ok) {
+                umma_commit(accum_bar);
+            } else {
+                *abort_flag = 1;
+                atomicExch(err_flag, 2);
+            }
+        }
+    } else {
+        // ---- epilogue ------------------------------------------------------------------------
+        const int q = warp & 3;                              // the TMEM lane quarter this warp may read
+        const int ra = a0 + q * 32 + lane;
+        const bool ok = mbar_wait(accum_bar, 0, abort_flag);
+        tc_fence_after_sync();
+        if (ok) {
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                if (b0 + c0 >= RB) break;                    // uniform over the block
+                __syncwarp();
+                float v[16];
+                tmem_ld16(lane_addr + (uint32_t)c0, v);
+                if (ra >= RA) continue;
+                const int rb = b0 + c0;
+                if (EPI == EPI_ROW) {
+                    // out[ra, rb .. rb+15] (+ bias[rb ..])
+                    OutT* dst = out + (size_t)ra * ldc + rb;
+                    const bool full = rb + 16 <= RB;
+                    if (bias) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            if (rb + i < RB) v[i] += load_any(bias, bias_dtype, rb + i);
+                    }
+                    if (full) {
+                        const bool vec_ok = ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0);
+                        store16<OutT>(dst, v, vec_ok);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            if (rb + i < RB) dst[i] = from_f32<OutT>(v[i]);
+                    }
+                } else if (EPI == EPI_COL) {
+                    // out[rb + i, ra] (+ bias[ra]): lanes walk consecutive features
+                    const float bv = bias ? load_any(bias, bias_dtype, ra) : 0.f;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        if (rb + i < RB) out[(size_t)(rb + i) * ldc + ra] = from_f32<OutT>(v[i] + bv);
+                } else {
+                    // partial[split, rb + i, ra], 32-bit
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        if (rb + i < RB)
+                            out[((size_t)blockIdx.z * RB + (rb + i)) * (size_t)RA + ra] = from_f32<OutT>(v[i]);
+                }
+            }
+        } else if (lane == 0) {
+            *abort_flag = 1;
+            atomicExch(err_flag, 3);
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// out[t, n] = sum_s partial[s, t, n] (+ bias[n]); the sum runs over s in ascending order.
+template <typename OutT>
+__global__ void reduce_partials_kernel(const float* __restrict__ partial, int splits, const void* __restrict__ bias,
+                                       int bias_dtype, OutT* __restrict__ out, int M, int N, long long ldc) {
+    const size_t total = (size_t)M * N;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int t = (int)(i / N), n = (int)(i - (size_t)t * N);
+        float acc = partial[i];
+        for (int s = 1; s < splits; ++s) acc += partial[(size_t)s * total + i];
+        if (bias) acc += load_any(bias, bias_dtype, n);
+        out[(size_t)t * ldc + n] = from_f32<OutT>(acc);
+    }
+}
+
+// ---- host: tensor maps -----------------------------------------------------------------------
+PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+std::mutex g_mutex;
+
+struct MapKey {
+    const void* ptr;
+    int rows, cols, ld, box_rows;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = std::hash<const void*>()(k.ptr);
+        h = h * 1000003u ^ (size_t)k.rows;
+        h = h * 1000003u ^ (size_t)k.cols;
+        h = h * 1000003u ^ (size_t)k.ld;
+        h = h * 1000003u ^ (size_t)k.box_rows;
+        return h;
+    }
+};
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+
+int load_encoder() {
+    if (g_encode) return 0;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) {
+        infero_set_error("gemm_tc: the driver does not offer cuTensorMapEncodeTiled (%s)", cudaGetErrorString(e));
+        return 1;
+    }
+    g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+    return 0;
+}
+
+// A [rows, cols] bf16 matrix with row stride ld (elements), tiles of box_rows x 64.
+int get_map(const void* ptr, int rows, int cols, int ld, int box_rows, CUtensorMap* out) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (load_encoder()) return 1;
+    MapKey key{ptr, rows, cols, ld, box_rows};
+    auto it = g_maps.find(key);
+    if (it != g_maps.end()) {
+        *out = it->second;
+        return 0;
+    }
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)TILE_K, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUtensorMap m;
+    CUresult r = g_encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        infero_set_error("gemm_tc: cuTensorMapEncodeTiled failed (%d) for a [%d, %d] matrix, row stride %d, box %d",
+                         (int)r, rows, cols, ld, box_rows);
+        return 1;
+    }
+    if (g_maps.size() > 8192) g_maps.clear();
+    g_maps.emplace(key, m);
+    *out = m;
+    return 0;
+}
+
+int* g_err_flag = nullptr;
+int err_flag_ptr(int** out) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (!g_err_flag) {
+        cudaError_t e = cudaMalloc(&g_err_flag, sizeof(int));
+        if (e == cudaSuccess) e = cudaMemset(g_err_flag, 0, sizeof(int));
+        if (e != cudaSuccess) {
+            g_err_flag = nullptr;
+            infero_set_error("gemm_tc: cannot allocate the error flag: %s", cudaGetErrorString(e));
+            return 1;
+        }
+    }
+    *out = g_err_flag;
+    return 0;
+}
+
+template <int BN, int STAGES, int EPI, typename OutT>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, const void* bias, int bias_dtype, int RA,
+           int RB, int K, int ktiles_per_split, int splits, long long ldc, int a_evict_first, int* err,
+           cudaStream_t stream) {
+    using Plan = SmemPlan<BN, STAGES>;
+    auto kern = gemm_tc_kernel<BN, STAGES, EPI, OutT>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::TOTAL);
+        if (e != cudaSuccess) {
+            infero_set_error("gemm_tc: cannot get %d bytes of shared memory: %s", Plan::TOTAL, cudaGetErrorString(e));
+            return 1;
+        }
+        configured = true;
+    }
+    dim3 grid((RA + TILE_A - 1) / TILE_A, (RB + BN - 1) / BN, splits);
+    kern<<<grid, GEMM_THREADS, Plan::TOTAL, stream>>>(ma, mb, (OutT*)out, bias, bias_dtype, RA, RB, K,
+                                                     ktiles_per_split, ldc, a_evict_first, err);
+    return infero_check_launch("gemm_tc");
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+
+extern "C" {
+
+// Can the tensor-core kernel take this product?  (bf16 operands are the caller's business.)
+int infero_gemm_tc_supported(const void* x, const void* w, int M, int N, int K, int ldx) {
+    return M > 0 && N > 0 && K >= 8 && K % 8 == 0 && ldx % 8 == 0 && ldx >= K && aligned16(x) && aligned16(w);
+}
+
+// How the few-token path would cut the work: the number of splits of K and the bytes of
+// 32-bit partials it needs (0 when one split writes the result directly).
+int infero_gemm_tc_plan(int M, int N, int K, int sm_count, int* splits, int* ktiles_per_split,
+                        long long* workspace_bytes) {
+    const int total_kt = (K + TILE_K - 1) / TILE_K;
+    int s = 1, per = total_kt;
+    if (M <= 256) {
+        const int tiles = (N + TILE_A - 1) / TILE_A;
+        const int target = 2 * (sm_count > 0 ? sm_count : 148);
+        s = target / tiles;
+        if (s < 1) s = 1;
+        if (s > 16) s = 16;
+        const int min_kt = 4;                              // a split shorter than this is all start-up
+        if (s > total_kt / min_kt) s = total_kt / min_kt > 0 ? total_kt / min_kt : 1;
+        per = (total_kt + s - 1) / s;
+        s = (total_kt + per - 1) / per;
+    }
+    *splits = s;
+    *ktiles_per_split = per;
+    *workspace_bytes = s > 1 ? (long long)s * M * N * 4 : 0;
+    return 0;
+}
+
+// 32-bit partial products of the few-token path: partial[s, t, n] for s < splits.
+// x [M, K] (row stride ldx) and w [N, K] are bf16; M <= 256.
+int infero_gemm_tc_partials(const void* x, const void* w, float* partial, int M, int N, int K, int ldx,
+                            int splits, int ktiles_per_split, cudaStream_t stream) {
+    INFERO_REQUIRE(infero_gemm_tc_supported(x, w, M, N, K, ldx), "gemm_tc: shape M=%d N=%d K=%d ldx=%d not supported", M, N, K, ldx);
+    INFERO_REQUIRE(M <= 256, "gemm_tc_partials: M=%d above 256", M);
+    INFERO_REQUIRE(splits >= 1 && ktiles_per_split >= 1 && (long long)(splits - 1) * ktiles_per_split * TILE_K < K,
+                   "gemm_tc_partials: %d splits of %d k-tiles do not fit K=%d", splits, ktiles_per_split, K);
+    int* err;
+    if (err_flag_ptr(&err)) return 1;
+    const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+    CUtensorMap mw, mx;
+    if (get_map(w, N, K, K, TILE_A, &mw)) return 1;
+    if (get_map(x, M, K, ldx, bn, &mx)) return 1;
+#define GO(BN_, ST_) return launch<BN_, ST_, EPI_PARTIAL, float>(mw, mx, partial, nullptr, 0, N, M, K, ktiles_per_split, splits, 0, 1, err, stream)
+    switch (bn) {
+        case 16: GO(16, 6);
+        case 32: GO(32, 5);
+        case 64: GO(64, 4);
+        case 128: GO(128, 3);
+        default: GO(256, 4);
+    }
+#undef GO
+}
+
+int infero_reduce_partials(const float* partial, int splits, const void* bias, int bias_dtype, void* out,
+                           int out_dtype, int M, int N, int ldc, cudaStream_t stream) {
+    if (M == 0 || N == 0) return 0;
+    const size_t total = (size_t)M * N;
+    const unsigned blocks = (unsigned)((total + 255) / 256 > 4096 ? 4096 : (total + 255) / 256);
+    if (out_dtype == INFERO_F32)
+        reduce_partials_kernel<float><<<blocks, 256, 0, stream>>>(partial, splits, bias, bias_dtype, (float*)out, M, N, ldc);
+    else
+        reduce_partials_kernel<bf16><<<blocks, 256, 0, stream>>>(partial, splits, bias, bias_dtype, (bf16*)out, M, N, ldc);
+    return infero_check_launch("reduce_partials");
+}
+
+// out[M, N] (bf16 or float, row stride ldc) = x[M, K] * w[N, K]^T (+ bias), bf16 operands.
+// workspace: what infero_gemm_tc_plan asked for (may be null when it asked for nothing).
+// tile_n: 0 = default, else 128 or 256 for the many-token path.
+int infero_gemm_tc(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int out_dtype,
+                   int M, int N, int K, int ldx, int ldc, void* workspace, long long workspace_bytes,
+                   int sm_count, int tile_n, cudaStream_t stream) {
+    if (M == 0 || N == 0) return 0;
+    INFERO_REQUIRE(infero_gemm_tc_supported(x, w, M, N, K, ldx), "gemm_tc: shape M=%d N=%d K=%d ldx=%d not supported", M, N, K, ldx);
+    INFERO_REQUIRE(ldc >= N, "gemm_tc: ldc=%d below N=%d", ldc, N);
+    int* err;
+    if (err_flag_ptr(&err)) return 1;
+    if (M <= 256) {
+        int splits, per;
+        long long need;
+        infero_gemm_tc_plan(M, N, K, sm_count, &splits, &per, &need);
+        if (splits > 1) {
+            INFERO_REQUIRE(workspace && workspace_bytes >= need, "gemm_tc: workspace of %lld bytes needed, %lld given", need, workspace_bytes);
+            if (infero_gemm_tc_partials(x, w, (float*)workspace, M, N, K, ldx, splits, per, stream)) return 1;
+            return infero_reduce_partials((const float*)workspace, splits, bias, bias_dtype, out, out_dtype, M, N, ldc, stream);
+        }
+        const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+        CUtensorMap mw, mx;
+        if (get_map(w, N, K, K, TILE_A, &mw)) return 1;
+        if (get_map(x, M, K, ldx, bn, &mx)) return 1;
+#define GO(BN_, ST_)                                                                                              \
+    do {                                                                                                          \
+        if (out_dtype == INFERO_F32)                                                                              \
+            return launch<BN_, ST_, EPI_COL, float>(mw, mx, out, bias, bias_dtype, N, M, K, per, 1, ldc, 1, err, stream); \
+        return launch<BN_, ST_, EPI_COL, bf16>(mw, mx, out, bias, bias_dtype, N, M, K, per, 1, ldc, 1, err, stream);      \
+    } while (0)
+        switch (bn) {
+            case 16: GO(16, 6);
+            case 32: GO(32, 5);
+            case 64: GO(64, 4);
+            case 128: GO(128, 3);
+            default: GO(256, 4);
+        }
+#undef GO
+    }
+    const int total_kt = (K + TILE_K - 1) / TILE_K;
+    const int bn = tile_n == 128 ? 128 : 256;
+    CUtensorMap mx, mw;
+    if (get_map(x, M, K, ldx, TILE_A, &mx)) return 1;
+    if (get_map(w, N, K, K, bn, &mw)) return 1;
+    if (bn == 128) {
+        if (out_dtype == INFERO_F32)
+            return launch<128, 3, EPI_ROW, float>(mx, mw, out, bias, bias_dtype, M, N, K, total_kt, 1, ldc, 0, err, stream);
+        return launch<128, 3, EPI_ROW, bf16>(mx, mw, out, bias, bias_dtype, M, N, K, total_kt, 1, ldc, 0, err, stream);
+    }
+    if (out_dtype == INFERO_F32)
+        return launch<256, 4, EPI_ROW, float>(mx, mw, out, bias, bias_dtype, M, N, K, total_kt, 1, ldc, 0, err, stream);
+    return launch<256, 4, EPI_ROW, bf16>(mx, mw, out, bias, bias_dtype, M, N, K, total_kt, 1, ldc, 0, err, stream);
+}
+
+// Reads (and clears) the flag a tensor-core kernel raises when one of its waits ran out.
+// Synchronises the device.  0 = no error.
+int infero_tc_error_flag() {
+    int* err;
+    if (err_flag_ptr(&err)) return -1;
+    int v = 0;
+    cudaError_t e = cudaMemcpy(&v, err, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) {
+        infero_set_error("tc_error_flag: %s", cudaGetErrorString(e));
+        return -1;
+    }
+    if (v) cudaMemset(err, 0, sizeof(int));
+    return v;
+}
+
+}  // extern "C"

@@ -1,10 +1,111 @@
-"""Choice of attention kernel for a step."""
+"""Choice of attention kernel for a step.
+
+float32 (the true 32-bit path), head sizes the tensor-core kernels have no instance for, and
+page sizes that are no multiple of 16 go to the generic kernel (one warp per token and head).
+bf16 steps are split in two: the leading run of single-token requests goes to the split-context
+decode kernel, everything after it (prompt portions, and single tokens that follow one) to the
+tiled prefill kernel.  The scheduler puts decodes first, as the reference's does
+(crates/server/src/scheduler.rs:1037-1041), so that split is the common case.
+"""
 from __future__ import annotations
 
-from . import attention_generic
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from . import KernelError, _check, _dt, _i32, _ptr, _stream, attention_generic, lib
+
+PREFILL_ROWS = 64          # query rows per CTA of the prefill kernel
+DECODE_MIN_CHUNK = 64      # keys per split, at least
+TARGET_CTAS = 4 * 148      # decode CTAs wanted in flight
+
+
+def mma_supported(head_dim: int, page_size: int) -> bool:
+    return bool(lib().infero_attn_mma_supported(c_int(head_dim), c_int(page_size)))
+
+
+def plan_decode(n_tok: int, n_kv: int, group: int, max_visible: int) -> Tuple[int, int]:
+    """(keys per split, number of splits) so that the splits cover ``max_visible`` keys and the
+    grid has about TARGET_CTAS blocks."""
+    ctas_per_split = max(1, n_tok * n_kv * (-(-group // 16)))
+    want = max(1, TARGET_CTAS // ctas_per_split)
+    max_visible = max(16, max_visible)
+    chunk = -(-max_visible // want)
+    chunk = max(DECODE_MIN_CHUNK, -(-chunk // 16) * 16)
+    splits = -(-max_visible // chunk)
+    return chunk, splits
+
+
+def decode(q, out, k_cache, v_cache, table, tok_entry, positions, tok_first: int, n_tok: int, n_heads: int,
+           n_kv: int, head_dim: int, page_size: int, window: Optional[int], scale: float, chunk: int,
+           n_splits: int) -> None:
+    need = int(lib_scratch(n_tok, n_heads, head_dim, n_splits))
+    scratch = torch.empty(need // 4, dtype=torch.float32, device=q.device)
+    _check(lib().infero_attn_decode(_ptr(q), c_int(q.stride(0)), _ptr(out), c_int(out.stride(0)), _ptr(k_cache),
+                                    _ptr(v_cache), _ptr(_i32(table, "block_table")), c_int(table.shape[1]),
+                                    _ptr(_i32(tok_entry, "tok_entry")), _ptr(_i32(positions, "positions")),
+                                    c_int(tok_first), c_int(n_tok), c_int(n_heads), c_int(n_kv), c_int(head_dim),
+                                    c_int(page_size), c_int(window or 0), c_float(scale), c_int(chunk),
+                                    c_int(n_splits), _ptr(scratch), _stream()))
+
+
+def lib_scratch(n_tok, n_heads, head_dim, n_splits) -> int:
+    f = lib().infero_attn_decode_scratch
+    f.restype = c_longlong
+    return f(c_int(n_tok), c_int(n_heads), c_int(head_dim), c_int(n_splits))
+
+
+def prefill(q, out, k_cache, v_cache, table, entry_q_start, entry_q_len, entry_pos0, n_entries: int,
+            first_entry: int, n_tiles: int, n_heads: int, n_kv: int, head_dim: int, page_size: int,
+            window: Optional[int], scale: float) -> None:
+    _check(lib().infero_attn_prefill(_ptr(q), c_int(q.stride(0)), _ptr(out), c_int(out.stride(0)), _ptr(k_cache),
+                                     _ptr(v_cache), _ptr(_i32(table, "block_table")), c_int(table.shape[1]),
+                                     _ptr(_i32(entry_q_start, "entry_q_start")), _ptr(_i32(entry_q_len, "entry_q_len")),
+                                     _ptr(_i32(entry_pos0, "entry_pos0")), c_int(n_entries), c_int(first_entry),
+                                     c_int(n_tiles), c_int(n_heads), c_int(n_kv), c_int(head_dim), c_int(page_size),
+                                     c_int(window or 0), c_float(scale), _stream()))
+
+
+def attention_any(q, out, k_cache, v_cache, table, tok_entry, positions, n_heads: int, n_kv: int, head_dim: int,
+                  page_size: int, window: Optional[int], scale: float, q_lens: Sequence[int], pos0: Sequence[int],
+                  entry_q_start=None, entry_q_len=None, entry_pos0=None, kv_bound: Optional[int] = None) -> None:
+    """q: [T, >= H*D] view with rotated queries in front (row stride free); out [T, H*D].
+    ``q_lens`` / ``pos0`` are the host copies of each request's new-token count and cached
+    length; the device copies are made here when the caller has none.  ``kv_bound``: plan the
+    decode splits for this many visible keys instead of what the batch holds now (a captured
+    step is replayed while its requests grow)."""
+    if q.dtype != torch.bfloat16 or not mma_supported(head_dim, page_size):
+        attention_generic(q, out, k_cache, v_cache, table, tok_entry, positions, n_heads, n_kv, head_dim,
+                          page_size, window, scale)
+        return
+    E = len(q_lens)
+    n_dec = 0
+    while n_dec < E and q_lens[n_dec] == 1:
+        n_dec += 1
+    if n_dec:
+        vis = max(int(pos0[i]) + 1 for i in range(n_dec)) if kv_bound is None else int(kv_bound)
+        if window:
+            vis = min(vis, window + 15)
+        chunk, splits = plan_decode(n_dec, n_kv, n_heads // n_kv, vis)
+        decode(q, out, k_cache, v_cache, table, tok_entry, positions, 0, n_dec, n_heads, n_kv, head_dim,
+               page_size, window, scale, chunk, splits)
+    if n_dec < E:
+        if entry_q_len is None:
+            dev = q.device
+            starts = [0]
+            for n in q_lens[:-1]:
+                starts.append(starts[-1] + int(n))
+            entry_q_start = torch.tensor(starts, dtype=torch.int32, device=dev)
+            entry_q_len = torch.tensor([int(n) for n in q_lens], dtype=torch.int32, device=dev)
+            entry_pos0 = torch.tensor([int(p) for p in pos0], dtype=torch.int32, device=dev)
+        n_tiles = sum(-(-int(n) // PREFILL_ROWS) for n in q_lens[n_dec:])
+        prefill(q, out, k_cache, v_cache, table, entry_q_start, entry_q_len, entry_pos0, E, n_dec, n_tiles,
+                n_heads, n_kv, head_dim, page_size, window, scale)
 
 
 def paged_attention(ctx, qkv, out, kv, table, n_heads, n_kv, head_dim, window, scale) -> None:
     """qkv: [T, (H + 2 Hkv) D] with rotated queries in front; out [T, H*D]."""
-    attention_generic(qkv, out, kv.k, kv.v, table, ctx.tok_entry, ctx.positions, n_heads, n_kv,
-                      head_dim, kv.page_size, window, scale)
+    attention_any(qkv, out, kv.k, kv.v, table, ctx.tok_entry, ctx.positions, n_heads, n_kv, head_dim,
+                  kv.page_size, window, scale, ctx.h_q_len, ctx.h_pos0, ctx.entry_q_start, ctx.entry_q_len,
+                  ctx.entry_pos0, kv_bound=getattr(ctx, "kv_bound", None))

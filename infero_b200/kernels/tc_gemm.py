@@ -1,12 +1,81 @@
-"""Tensor-core (tcgen05 / TMEM / TMA) matrix product for bf16 operands."""
+"""Tensor-core (tcgen05 / TMEM / TMA) matrix product for bf16 operands.
+
+``gemm`` computes out = a @ w^T (+ bias).  With few rows (<= 256) the weights take the
+128-wide side of the MMA and K is cut into splits so that every SM streams weights; the
+32-bit partial products go through a workspace and are summed in a fixed order.
+``partials`` exposes those partial products to consumers that fold the sum into their own
+pass (norm, activation, rotary + cache append).
+"""
 from __future__ import annotations
+
+from ctypes import POINTER, byref, c_int, c_longlong, c_void_p
+from typing import Optional, Tuple
 
 import torch
 
+from . import BF16, F32, KernelError, _check, _dt, _ptr, _stream, lib
 
-def supported(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
-    return False
+_SM_COUNT = {}
 
 
-def gemm(a, w, bias, out) -> None:
-    raise NotImplementedError
+def sm_count(device) -> int:
+    idx = torch.device(device).index or 0
+    if idx not in _SM_COUNT:
+        _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _SM_COUNT[idx]
+
+
+def supported(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> bool:
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not w.is_contiguous() or a.stride(1) != 1:
+        return False
+    M, K = a.shape
+    return bool(lib().infero_gemm_tc_supported(_ptr(a), _ptr(w), c_int(M), c_int(w.shape[0]), c_int(K),
+                                               c_int(a.stride(0))))
+
+
+def plan(M: int, N: int, K: int, device) -> Tuple[int, int, int]:
+    """(splits, k-tiles per split, workspace bytes) of the few-row path."""
+    s, per, ws = c_int(0), c_int(0), c_longlong(0)
+    lib().infero_gemm_tc_plan(c_int(M), c_int(N), c_int(K), c_int(sm_count(device)), byref(s), byref(per), byref(ws))
+    return s.value, per.value, ws.value
+
+
+def gemm(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+         tile_n: int = 0) -> None:
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.shape == (M, N) and out.stride(1) == 1
+    ws = None
+    ws_bytes = 0
+    if M <= 256:
+        _, _, ws_bytes = plan(M, N, K, a.device)
+        if ws_bytes:
+            ws = torch.empty(ws_bytes // 4, dtype=torch.float32, device=a.device)
+    _check(lib().infero_gemm_tc(_ptr(a), _ptr(w), _ptr(bias), c_int(_dt(bias) if bias is not None else F32),
+                                _ptr(out), c_int(_dt(out)), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)),
+                                c_int(out.stride(0)), _ptr(ws), c_longlong(ws_bytes), c_int(sm_count(a.device)),
+                                c_int(tile_n), _stream()))
+
+
+def partials(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """float32 [splits, M, N] whose sum over the first axis is a @ w^T (M <= 256)."""
+    M, K = a.shape
+    N = w.shape[0]
+    s, per, _ = plan(M, N, K, a.device)
+    out = torch.empty((s, M, N), dtype=torch.float32, device=a.device)
+    _check(lib().infero_gemm_tc_partials(_ptr(a), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K),
+                                         c_int(a.stride(0)), c_int(s), c_int(per), _stream()))
+    return out
+
+
+def reduce_partials(partial: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    S, M, N = partial.shape
+    assert partial.is_contiguous() and partial.dtype == torch.float32 and out.shape == (M, N)
+    _check(lib().infero_reduce_partials(_ptr(partial), c_int(S), _ptr(bias),
+                                        c_int(_dt(bias) if bias is not None else F32), _ptr(out), c_int(_dt(out)),
+                                        c_int(M), c_int(N), c_int(out.stride(0)), _stream()))
+
+
+def error_flag() -> int:
+    """Synchronises; non-zero if a tensor-core kernel gave up on one of its waits."""
+    return int(lib().infero_tc_error_flag())

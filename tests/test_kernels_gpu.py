@@ -1,0 +1,342 @@
+"""Each CUDA kernel alone against a plain PyTorch float32/float64 statement of the same op,
+at sizes other than the engine's tiny configurations."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def _rand(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g, dtype=torch.float32) * scale).to(dtype).to(DEV)
+
+
+# ---- matrix products ---------------------------------------------------------------------------
+def _gemm_ref(a, w, bias):
+    out = a.double().cpu() @ w.double().cpu().T
+    if bias is not None:
+        out += bias.double().cpu()
+    return out
+
+
+def _rel_err(got, ref):
+    return float((got.double().cpu() - ref).abs().max() / (ref.abs().max() + 1e-30))
+
+
+GEMM_TC_SHAPES = [
+    # M, N, K  (few rows: weights on the wide side, K in splits; many rows: tokens on the wide side)
+    (1, 128, 64), (1, 3584, 3584), (8, 4608, 3584), (8, 3584, 18944), (3, 1000, 96), (16, 777, 224),
+    (17, 512, 64), (33, 300, 176), (64, 1152, 896), (65, 2048, 1024), (130, 640, 520), (256, 384, 200),
+    (257, 512, 128), (300, 777, 224), (512, 1000, 96), (1024, 4608, 3584), (2048, 1280, 4864), (384, 96, 256),
+]
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_TC_SHAPES)
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_tensor_core(M, N, K, out_dtype):
+    from infero_b200.kernels import tc_gemm
+    a = _rand((M, K), torch.bfloat16, 1)
+    w = _rand((N, K), torch.bfloat16, 2, 0.05)
+    bias = _rand((N,), torch.bfloat16, 3)
+    assert tc_gemm.supported(a, w)
+    for b in (None, bias):
+        out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+        tc_gemm.gemm(a, w, b, out)
+        assert tc_gemm.error_flag() == 0
+        err = _rel_err(out, _gemm_ref(a, w, b))
+        tol = 1e-5 if out_dtype == torch.float32 else 6e-3       # bf16 output rounds to 2^-9
+        assert err <= tol, f"M={M} N={N} K={K} bias={b is not None}: {err:.3e}"
+
+
+@pytest.mark.parametrize("tile_n", [128, 256])
+def test_gemm_tensor_core_tiles_and_strides(tile_n):
+    from infero_b200.kernels import tc_gemm
+    M, N, K = 700, 900, 1096
+    big = _rand((M, K + 40), torch.bfloat16, 4)
+    a = big[:, 8:8 + K]                                 # a strided view: rows 16-byte aligned, stride K + 40
+    w = _rand((N, K), torch.bfloat16, 5, 0.05)
+    out_big = torch.zeros((M, N + 24), dtype=torch.bfloat16, device=DEV)
+    out = out_big[:, :N]
+    assert tc_gemm.supported(a, w)
+    tc_gemm.gemm(a, w, None, out, tile_n=tile_n)
+    assert tc_gemm.error_flag() == 0
+    assert _rel_err(out, _gemm_ref(a, w, None)) <= 6e-3
+    assert float(out_big[:, N:].abs().max()) == 0.0, "wrote outside its columns"
+
+
+def test_gemm_tensor_core_partials_sum_in_fixed_order():
+    from infero_b200.kernels import tc_gemm
+    M, N, K = 8, 3584, 18944
+    a = _rand((M, K), torch.bfloat16, 6)
+    w = _rand((N, K), torch.bfloat16, 7, 0.02)
+    p1 = tc_gemm.partials(a, w)
+    p2 = tc_gemm.partials(a, w)
+    assert p1.shape[0] > 1, "this shape was meant to be cut along K"
+    assert torch.equal(p1, p2)
+    out = torch.empty((M, N), dtype=torch.float32, device=DEV)
+    tc_gemm.reduce_partials(p1, None, out)
+    assert _rel_err(out, _gemm_ref(a, w, None)) <= 1e-5
+    assert tc_gemm.error_flag() == 0
+
+
+def test_gemm_tensor_core_refuses_what_it_cannot_take():
+    from infero_b200.kernels import tc_gemm
+    a = _rand((4, 100), torch.bfloat16, 1)               # K = 100 is no multiple of 8
+    w = _rand((32, 100), torch.bfloat16, 2)
+    assert not tc_gemm.supported(a, w)
+    a = _rand((4, 104), torch.bfloat16, 1)[:, 1:97]      # misaligned start
+    assert not tc_gemm.supported(a, _rand((32, 96), torch.bfloat16, 2))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (5, 130, 67), (70, 65, 129), (3, 1000, 96)])
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_gemm_tiled(M, N, K, dt):
+    from infero_b200 import kernels as Kn
+    a, w, bias = _rand((M, K), dt, 1), _rand((N, K), dt, 2, 0.1), _rand((N,), dt, 3)
+    out = torch.empty((M, N), dtype=torch.float32, device=DEV)
+    Kn.gemm_tiled(a, w, bias, out)
+    assert _rel_err(out, _gemm_ref(a, w, bias)) <= 2e-6
+
+
+def test_gemm_tiled_rows_do_not_depend_on_the_batch():
+    from infero_b200 import kernels as Kn
+    a, w = _rand((77, 200), torch.float32, 1), _rand((90, 200), torch.float32, 2)
+    full = torch.empty((77, 90), dtype=torch.float32, device=DEV)
+    Kn.gemm_tiled(a, w, None, full)
+    for rows in ([5], [0, 76], list(range(60, 70))):
+        sub = a[rows].contiguous()
+        out = torch.empty((len(rows), 90), dtype=torch.float32, device=DEV)
+        Kn.gemm_tiled(sub, w, None, out)
+        assert torch.equal(out, full[rows])
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 4])
+def test_gemm_skinny(M):
+    from infero_b200 import kernels as Kn
+    N, K = 1003, 520
+    a, w, bias = _rand((M, K), torch.bfloat16, 1), _rand((N, K), torch.bfloat16, 2, 0.1), _rand((N,), torch.float32, 3)
+    out = torch.empty((M, N), dtype=torch.float32, device=DEV)
+    Kn.gemm_skinny(a, w, bias, out)
+    assert _rel_err(out, _gemm_ref(a, w, bias)) <= 1e-5
+
+
+# ---- embedding, norm, activation ---------------------------------------------------------------
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_embed_gather(dt):
+    from infero_b200 import kernels as Kn
+    table = _rand((301, 136), dt, 1)
+    ids = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32, device=DEV)
+    x = torch.empty((5, 136), dtype=torch.float32, device=DEV)
+    Kn.embed_gather(table, ids, x, 1.0)
+    assert torch.equal(x, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("d", [40, 1000, 3584])
+@pytest.mark.parametrize("eps", [1e-6, 1e-3])
+@pytest.mark.parametrize("act", [torch.float32, torch.bfloat16])
+def test_add_rmsnorm(d, eps, act):
+    from infero_b200 import kernels as Kn
+    T = 7
+    x = _rand((T, d), torch.float32, 1)
+    delta = _rand((T, d), act, 2)
+    w = _rand((d,), act, 3) + 1
+    x0 = x.clone()
+    out = torch.empty((T, d), dtype=act, device=DEV)
+    Kn.add_rmsnorm(x, delta, w, eps, out)
+    v = x0.double() + delta.double()
+    ref = v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps) * w.double()
+    assert torch.allclose(x.double(), v.float().double(), atol=0, rtol=0)
+    tol = 1e-6 if act == torch.float32 else 5e-3
+    assert float((out.double() - ref).abs().max() / ref.abs().max()) <= tol
+    # selected rows, no write-back
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    x1 = x0.clone()
+    out2 = torch.empty((3, d), dtype=act, device=DEV)
+    Kn.add_rmsnorm(x1, delta, w, eps, out2, rows)
+    assert torch.equal(x1, x0)
+    assert torch.equal(out2, out[rows.long()])
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_swiglu(dt):
+    from infero_b200 import kernels as Kn
+    T, ff = 5, 333
+    gu = _rand((T, 2 * ff), dt, 1, 3.0)
+    out = torch.empty((T, ff), dtype=dt, device=DEV)
+    Kn.swiglu(gu, out)
+    g, u = gu[:, :ff].double(), gu[:, ff:].double()
+    ref = g / (1 + torch.exp(-g)) * u
+    tol = 1e-6 if dt == torch.float32 else 5e-3
+    assert float((out.double() - ref).abs().max() / ref.abs().max()) <= tol
+
+
+# ---- rotary + cache append, attention ----------------------------------------------------------
+def _rope_ref(x, pos, theta, rotary):
+    half = rotary // 2
+    inv = theta ** (-2.0 * torch.arange(half, dtype=torch.float64) / rotary)
+    ang = pos.double()[:, None] * inv[None, :]
+    c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    out = x.clone()
+    a, b = x[..., :half], x[..., half:rotary]
+    out[..., :half] = a * c - b * s
+    out[..., half:rotary] = a * s + b * c
+    return out
+
+
+@pytest.mark.parametrize("H,Hkv,D,rotary", [(6, 3, 48, 48), (5, 5, 80, 40), (7, 1, 128, 128)])
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_rope_and_cache_append(H, Hkv, D, rotary, dt):
+    from infero_b200 import kernels as Kn
+    P, pages, T = 16, 12, 9
+    theta = 50000.0
+    qkv = _rand((T, (H + 2 * Hkv) * D), dt, 1)
+    qkv0 = qkv.clone()
+    # two requests: entry 0 at positions 30..34 (pages 1 and 2 of its table), entry 1 at 0..3
+    positions = torch.tensor([30, 31, 32, 33, 34, 0, 1, 2, 3], dtype=torch.int32, device=DEV)
+    entry = torch.tensor([0] * 5 + [1] * 4, dtype=torch.int32, device=DEV)
+    table = torch.tensor([[7, 3, 9, -1], [11, -1, -1, -1]], dtype=torch.int32, device=DEV)
+    kc = torch.zeros((pages, Hkv, P, D), dtype=dt, device=DEV)
+    vc = torch.zeros_like(kc)
+    half = rotary // 2
+    inv = torch.from_numpy((np.float64(theta) ** (-2.0 * np.arange(half) / rotary)).astype(np.float32)).to(DEV)
+    Kn.rope_cache(qkv, positions, entry, table, inv, kc, vc, H, Hkv, D, P)
+    q0 = qkv0[:, :H * D].double().cpu().view(T, H, D)
+    k0 = qkv0[:, H * D:(H + Hkv) * D].double().cpu().view(T, Hkv, D)
+    v0 = qkv0[:, (H + Hkv) * D:].cpu().view(T, Hkv, D)
+    qr, kr = _rope_ref(q0, positions.cpu(), theta, rotary), _rope_ref(k0, positions.cpu(), theta, rotary)
+    tol = 2e-6 if dt == torch.float32 else 8e-3
+    assert float((qkv[:, :H * D].double().cpu().view(T, H, D) - qr).abs().max()) <= tol * float(qr.abs().max())
+    tb = table.cpu()
+    for t in range(T):
+        p, e = int(positions[t]), int(entry[t])
+        page, row = int(tb[e, p // P]), p % P
+        assert float((kc[page, :, row].double().cpu() - kr[t]).abs().max()) <= tol * float(kr.abs().max())
+        assert torch.equal(vc[page, :, row].cpu(), v0[t])
+    assert int((kc != 0).any(-1).sum()) == T * Hkv, "keys were written to rows that belong to no token"
+
+
+def _attention_ref(q, keys, values, scale, window):
+    """q [H, D] at the last position of keys [L, Hkv, D]."""
+    H, D = q.shape
+    L, Hkv, _ = keys.shape
+    g = H // Hkv
+    lo = max(0, L - window) if window else 0
+    out = torch.zeros(H, D, dtype=torch.float64)
+    for h in range(H):
+        s = (keys[lo:, h // g] @ q[h]) * scale
+        p = torch.softmax(s, dim=0)
+        out[h] = p @ values[lo:, h // g]
+    return out
+
+
+@pytest.mark.parametrize("H,Hkv,D", [(6, 3, 48), (7, 1, 128), (4, 4, 80), (10, 2, 64)])
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [None, 40])
+def test_attention_over_pages(H, Hkv, D, dt, window):
+    """Mixed batch: a long prompt portion, a decode token far into its request, a fresh request.
+    One key per request gets a large score so that a lost or misplaced key shows."""
+    from infero_b200 import kernels as Kn
+    from infero_b200.kernels import attention as A
+    P, pages = 16, 40
+    lens = [(0, 70), (133, 1), (50, 23), (0, 1)]          # (tokens already cached, new tokens)
+    rng = np.random.default_rng(0)
+    perm = rng.permutation(pages)
+    table = torch.full((len(lens), 12), -1, dtype=torch.int32)
+    nxt = 0
+    K_all, V_all = [], []
+    kc = torch.zeros((pages, Hkv, P, D), dtype=dt, device=DEV)
+    vc = torch.zeros_like(kc)
+    for e, (old, new) in enumerate(lens):
+        L = old + new
+        k = _rand((L, Hkv, D), dt, 10 + e)
+        v = _rand((L, Hkv, D), dt, 20 + e)
+        K_all.append(k)
+        V_all.append(v)
+        for b in range(-(-L // P)):
+            table[e, b] = int(perm[nxt]); nxt += 1
+            n = min(P, L - b * P)
+            kc[table[e, b], :, :n] = k[b * P:b * P + n].transpose(0, 1)
+            vc[table[e, b], :, :n] = v[b * P:b * P + n].transpose(0, 1)
+    T = sum(n for _, n in lens)
+    q = _rand((T, H * D), dt, 3)
+    scale = 1.0 / math.sqrt(D)
+    # make key 5 of request 0 and key 100 of request 1 stand out for head 0
+    q3 = q.view(T, H, D)
+    for e, j in ((0, 5), (1, 100)):
+        t0 = sum(n for _, n in lens[:e])
+        kk = K_all[e][j, 0].float()
+        q3[t0:t0 + lens[e][1], 0] = (kk * (6.0 / scale / float(kk @ kk))).to(dt)
+    positions = torch.tensor([old + i for old, n in lens for i in range(n)], dtype=torch.int32, device=DEV)
+    entry = torch.tensor([e for e, (_, n) in enumerate(lens) for _ in range(n)], dtype=torch.int32, device=DEV)
+    out = torch.empty((T, H * D), dtype=dt, device=DEV)
+    A.attention_any(q, out, kc, vc, table.to(DEV), entry, positions, H, Hkv, D, P, window, scale,
+                    q_lens=[n for _, n in lens], pos0=[o for o, _ in lens])
+    t = 0
+    worst = 0.0
+    for e, (old, new) in enumerate(lens):
+        for i in range(new):
+            L = old + i + 1
+            ref = _attention_ref(q3[t].double().cpu(), K_all[e][:L].double().cpu(), V_all[e][:L].double().cpu(),
+                                 scale, window)
+            got = out[t].double().cpu().view(H, D)
+            worst = max(worst, float((got - ref).abs().max() / ref.abs().max()))
+            t += 1
+    assert worst <= (3e-6 if dt == torch.float32 else 1.5e-2), f"{worst:.3e}"
+
+
+# ---- sampling ------------------------------------------------------------------------------------
+def test_argmax_lowest_index_wins_ties():
+    from infero_b200 import kernels as Kn
+    V = 152_064 + 3
+    z = _rand((3, V), torch.float32, 1)
+    z[0, 77] = z[0, 150_000] = 9.0
+    z[1, V - 1] = 11.0
+    z[2] = -float("inf")
+    out = torch.empty(3, dtype=torch.int32, device=DEV)
+    Kn.argmax(z, out)
+    assert out.tolist() == [77, V - 1, 0]
+
+
+def _host_sample(z, temp, top_k, top_p, u):
+    """crates/model/src/sampling.rs:169-235 restated on the host in 64-bit."""
+    idx = np.argsort(-z, kind="stable")[:top_k]
+    zz = z[idx].astype(np.float64)
+    w = np.exp((zz - zz[0]) / max(temp, 1e-5))
+    total = w.sum()
+    p = min(max(top_p, 1e-4), 1.0)
+    keep = len(w)
+    acc = 0.0
+    for i, wi in enumerate(w):
+        acc += wi
+        if acc >= p * total:
+            keep = i + 1
+            break
+    w = w[:keep]
+    r = u * w.sum()
+    for i, wi in enumerate(w):
+        r -= wi
+        if r <= 0:
+            return int(idx[i])
+    return int(idx[keep - 1])
+
+
+def test_sample_matches_host_statement():
+    from infero_b200 import kernels as Kn
+    V, R = 5003, 24
+    rng = np.random.default_rng(5)
+    z = torch.from_numpy(rng.normal(size=(R, V)).astype(np.float32) * 3).to(DEV)
+    temp = torch.tensor([0.7, 1.0, 0.3] * 8, dtype=torch.float32, device=DEV)
+    top_k = torch.tensor([20, 50, 5, 1000] * 6, dtype=torch.int32, device=DEV)
+    top_p = torch.tensor([0.8, 1.0, 0.5, 0.95, 0.9, 0.3] * 4, dtype=torch.float32, device=DEV)
+    draw = torch.from_numpy(rng.random(R)).to(DEV)
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    Kn.sample(z, temp, top_k, top_p, draw, out)
+    zh = z.cpu().numpy()
+    for r in range(R):
+        want = _host_sample(zh[r], float(temp[r]), int(top_k[r]), float(top_p[r]), float(draw[r]))
+        assert int(out[r]) == want, f"row {r}"
