@@ -1,0 +1,345 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine at Qwen2.5-7B layer sizes, random weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+One JSON line on standard output.  A "step" is one decode step of the whole batch: the
+host-to-device copy of the step's inputs, the model's forward pass from the cache (a
+captured CUDA graph once the shape has been seen twice) and the argmax kernel.
+
+  value     decoded tokens per second at batch 8 with about 4,096 tokens of context each,
+            timed on the device with CUDA events around exactly K steps; the tokens fed are
+            drawn beforehand, so no step waits for the host
+  e2e       the same through ``Engine.add_request`` / ``Engine.step``: host token ids in,
+            sampled token ids back on the host every step
+  prefill   one step of 2,048 prompt tokens (flops / time / peak)
+  roofline  bytes a decode step has to read (every weight it uses once, and the cache of
+            the live requests) / its time, against the measured copy bandwidth
+  points    decoded tokens per second at batch 1 and 64
+
+This engine runs on one GPU; with --gpus above 1 it says so and exits with 2.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import random
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: Qwen2.5-7B shape
+QWEN25_7B = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 28, "hidden_size": 3584, "num_attention_heads": 28, "num_key_value_heads": 4,
+    "head_dim": 128, "intermediate_size": 18944, "vocab_size": 152064, "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "use_sliding_window": False,
+    "max_position_embeddings": 32768, "hidden_act": "silu",
+}
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """Reads SM clock and throttle reasons through NVML every 20 ms while ``on`` is set.
+    Reading only: nothing about the GPU is changed."""
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
+               0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting"}
+
+    def __init__(self, index: int = 0):
+        self.samples, self.reasons, self.on, self._stop = [], set(), False, False
+        self.max_mhz = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._run, daemon=True)
+            self.thread.start()
+        except Exception as e:          # noqa: BLE001
+            self.nv = None
+            self.error = str(e)
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop:
+            if self.on:
+                try:
+                    self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                    mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+                    for bit, name in self.REASONS.items():
+                        if mask & bit:
+                            self.reasons.add(name)
+                except Exception:       # noqa: BLE001
+                    pass
+            time.sleep(0.02)
+
+    def summary(self):
+        self._stop = True
+        if self.nv is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "error": getattr(self, "error", "")}
+        s = sorted(self.samples)
+        return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+def matmul_params_per_layer(c):
+    d, ff = c["hidden_size"], c["intermediate_size"]
+    da = c["num_attention_heads"] * c["head_dim"]
+    dkv = c["num_key_value_heads"] * c["head_dim"]
+    return d * (da + 2 * dkv) + da * d + 3 * d * ff
+
+
+def decode_bytes(c, layers, batch, kv_tokens_total, esize=2):
+    """Bytes one decode step has to read: every matrix and vector it uses once, the embedding
+    rows of its tokens, and the cached keys and values of the live requests."""
+    d, V = c["hidden_size"], c["vocab_size"]
+    da = c["num_attention_heads"] * c["head_dim"]
+    dkv = c["num_key_value_heads"] * c["head_dim"]
+    per_layer = matmul_params_per_layer(c) + (da + 2 * dkv) + 2 * d          # + biases + two norms
+    weights = (layers * per_layer + V * d + d) * esize
+    kv = kv_tokens_total * layers * 2 * dkv * esize
+    return weights + kv + batch * d * esize
+
+
+def prefill_flops(c, layers, T):
+    gemm = 2.0 * T * layers * matmul_params_per_layer(c) + 2.0 * c["vocab_size"] * c["hidden_size"]
+    attn = layers * 2.0 * T * T * c["num_attention_heads"] * c["head_dim"]    # causal: half of 4 T^2 H D
+    return gemm + attn
+
+
+def random_prompt(rng, vocab, n):
+    return [rng.randrange(vocab) for _ in range(n)]
+
+
+def fill_cache(runner, rids, length, vocab, rng, chunk):
+    """Bring each request to ``length`` cached tokens by prompt portions without logits."""
+    from infero_b200.engine import StepEntry
+    for rid in rids:
+        runner.open(rid)
+        done = 0
+        while done < length:
+            n = min(chunk, length - done)
+            runner.step([StepEntry(rid, random_prompt(rng, vocab, n), [])])
+            done += n
+
+
+def time_decode(model, cfg_json, layers, batch, steps, warmup, clocks, page_size):
+    """Device-timed decode steps at ``batch`` requests of about CONTEXT tokens each."""
+    import torch
+    from infero_b200 import kernels as K
+    from infero_b200.config import EngineConfig
+    from infero_b200.engine import ModelRunner, StepEntry
+    vocab = cfg_json["vocab_size"]
+    rng = random.Random(1000 + batch)
+    start_len = CONTEXT - (steps + warmup) - 1
+    ecfg = EngineConfig(dtype="bfloat16", page_size=page_size, num_pages=batch * (-(-CONTEXT // page_size)),
+                        max_seqs=batch, ctx=CONTEXT, max_batch_tokens=PREFILL_TOKENS, max_logit_rows=max(batch, 8),
+                        cuda_graphs=True)
+    runner = ModelRunner(model, ecfg)
+    rids = [f"b{batch}_{i}" for i in range(batch)]
+    fill_cache(runner, rids, start_len, vocab, rng, PREFILL_TOKENS)
+    feed = [[rng.randrange(vocab) for _ in range(batch)] for _ in range(steps + warmup)]
+    picked = torch.empty(batch, dtype=torch.int32, device="cuda")
+
+    def one(i):
+        logits = runner.step([StepEntry(rid, [feed[i][j]], [0]) for j, rid in enumerate(rids)])
+        K.argmax(logits, picked)
+
+    for i in range(warmup):
+        one(i)
+    torch.cuda.synchronize()
+    launches0, replays0 = K.launch_count(), runner.graph_replays
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    clocks.on = True
+    e0.record()
+    for i in range(warmup, warmup + steps):
+        one(i)
+    e1.record()
+    torch.cuda.synchronize()
+    clocks.on = False
+    ms = e0.elapsed_time(e1) / steps
+    graph_nodes = max((g.n_kernels for g in runner._graphs.values()), default=0)
+    launches = (K.launch_count() - launches0) + (runner.graph_replays - replays0) * graph_nodes
+    kv_tokens = sum(runner.length(r) for r in rids)
+    out = {"ms_per_step": ms, "tok_s": batch / (ms / 1e3), "launches": int(launches),
+           "bytes": decode_bytes(cfg_json, layers, batch, kv_tokens), "h2d": runner.last_h2d_bytes,
+           "graph_replays": runner.graph_replays - replays0, "kv_tokens": kv_tokens}
+    for r in rids:
+        runner.close(r)
+    del runner
+    torch.cuda.empty_cache()
+    return out
+
+
+def time_prefill(model, cfg_json, layers, reps, warmup, clocks, page_size):
+    import torch
+    from infero_b200.config import EngineConfig
+    from infero_b200.engine import ModelRunner, StepEntry
+    vocab = cfg_json["vocab_size"]
+    rng = random.Random(77)
+    ecfg = EngineConfig(dtype="bfloat16", page_size=page_size, num_pages=2 * (-(-PREFILL_TOKENS // page_size)),
+                        max_seqs=2, ctx=PREFILL_TOKENS, max_batch_tokens=PREFILL_TOKENS, cuda_graphs=False)
+    runner = ModelRunner(model, ecfg)
+    times = []
+    for i in range(warmup + reps):
+        prompt = random_prompt(rng, vocab, PREFILL_TOKENS)
+        runner.open("p")
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if i >= warmup:
+            clocks.on = True
+        e0.record()
+        runner.step([StepEntry("p", prompt, [PREFILL_TOKENS - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        clocks.on = False
+        if i >= warmup:
+            times.append(e0.elapsed_time(e1))
+        runner.close("p")
+    del runner
+    torch.cuda.empty_cache()
+    times.sort()
+    ms = times[len(times) // 2]
+    return {"ms": ms, "flops": prefill_flops(cfg_json, layers, PREFILL_TOKENS)}
+
+
+def time_e2e(model, cfg_json, batch, steps, warmup, clocks, page_size):
+    """Through the Engine: requests in as host token ids, sampled ids out on the host each step."""
+    import torch
+    from infero_b200.engine import Engine
+    from infero_b200.sampling import SamplingParams
+    vocab = cfg_json["vocab_size"]
+    rng = random.Random(2000 + batch)
+    start_len = CONTEXT - (steps + warmup) - 2
+    eng = Engine(model=model, dtype="bfloat16", ctx=CONTEXT, max_seqs=batch, kv_slots=batch * CONTEXT,
+                 max_batch_tokens=PREFILL_TOKENS, page_size=page_size, cuda_graphs=True)
+    start_len -= 4 * batch                   # requests that finish their prompt early decode meanwhile
+    pure_argmax = SamplingParams(temperature=0.0, repetition_penalty=1.0)
+    for _ in range(batch):
+        eng.add_request(random_prompt(rng, vocab, start_len), pure_argmax,
+                        max_new_tokens=CONTEXT, ignore_eos=True)
+    got = 0
+    while got < batch:                       # prompts, in portions, until every request has its first token
+        got += sum(1 for ev in eng.step() if ev.token is not None)
+    for _ in range(warmup):
+        eng.step()
+    torch.cuda.synchronize()
+    clocks.on = True
+    t0 = time.perf_counter()
+    tokens = 0
+    for _ in range(steps):
+        tokens += sum(1 for ev in eng.step() if ev.token is not None)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    clocks.on = False
+    h2d = eng.runner.last_h2d_bytes
+    d2h = 2 * batch * 4                      # sample_rows reads back two int32 per row
+    eng.abort_all("bench done")
+    del eng
+    torch.cuda.empty_cache()
+    return {"tok_s": tokens / dt, "ms_per_step": dt * 1e3 / steps, "h2d": h2d, "d2h": d2h, "tokens": tokens}
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
+    ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--skip-prefill", action="store_true")
+    args = ap.parse_args(argv)
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference",
+                          "unavailable": "jackwangfeng/infero is a Rust workspace (no setup.py / pyproject.toml; "
+                                         "pip: 'not installable') and this image has no cargo or rustc"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not built")
+        return 2
+    steps, warmup = max(1, args.steps), max(3, args.warmup)
+
+    import torch
+    from infero_b200 import kernels as K
+    from infero_b200.loading import random_model
+    K.lib()
+    cfg_json = dict(QWEN25_7B)
+    full_layers = cfg_json["num_hidden_layers"]
+    layers = args.layers or full_layers
+    cfg_json["num_hidden_layers"] = layers
+    pk = peaks()
+    clocks = ClockSampler(0)
+    t_start = time.time()
+    model, _ = random_model(cfg_json, seed=0, dtype="bfloat16", device="cuda:0", generate_on_device=True)
+    torch.cuda.synchronize()
+
+    main_pt = time_decode(model, cfg_json, layers, args.batch, steps, warmup, clocks, args.page_size)
+    main_clocks = clocks.summary()
+    quiet = ClockSampler.__new__(ClockSampler)
+    quiet.on = False
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            r = time_decode(model, cfg_json, layers, b, min(steps, 50), warmup, quiet, args.page_size)
+            points[f"decode_b{b}"] = round(r["tok_s"], 1)
+            points[f"decode_b{b}_hbm_frac"] = round(r["bytes"] / (r["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"], 3)
+    prefill = None
+    if not args.skip_prefill:
+        r = time_prefill(model, cfg_json, layers, 5, 3, quiet, args.page_size)
+        prefill = {"value": round(PREFILL_TOKENS / (r["ms"] / 1e3), 1), "tokens": PREFILL_TOKENS,
+                   "ms": round(r["ms"], 3),
+                   "frac": round(r["flops"] / (r["ms"] / 1e3) / 1e12 / pk["bf16_tflops"], 4)}
+    e2e = None
+    if not args.skip_e2e:
+        r = time_e2e(model, cfg_json, args.batch, steps, warmup, quiet, args.page_size)
+        e2e = {"value": round(r["tok_s"], 1), "unit": "tok/s", "h2d_bytes_per_step": r["h2d"],
+               "d2h_bytes_per_step": r["d2h"], "ms_per_step": round(r["ms_per_step"], 4)}
+
+    achieved = main_pt["bytes"] / (main_pt["ms_per_step"] / 1e3) / 1e9
+    line = {
+        "metric": "decode tok/s at batch 8 (4K ctx), Qwen2.5-7B shape",
+        "value": round(main_pt["tok_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": round(main_pt["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic: random weights N(0,0.02) from a seed, uniform random token ids",
+        "impl": "ours",
+        "config": {"model": "Qwen2.5-7B shape", "global_batch": args.batch, "seq_len": CONTEXT,
+                   "parallelism": "single GPU", "layers": layers, "layers_of_configuration": full_layers,
+                   "hidden": cfg_json["hidden_size"], "heads": cfg_json["num_attention_heads"],
+                   "kv_heads": cfg_json["num_key_value_heads"], "head_dim": cfg_json["head_dim"],
+                   "intermediate": cfg_json["intermediate_size"], "vocab": cfg_json["vocab_size"],
+                   "page_size": args.page_size, "l2": "inputs larger than L2 (weights and cache)",
+                   "peaks": pk["source"], "prefill_tokens": PREFILL_TOKENS},
+        "e2e": e2e, "gpu_launches": main_pt["launches"], "clocks": main_clocks,
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+        "wall_s": round(time.time() - t_start, 1),
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -3,7 +3,10 @@
 #include <cstdarg>
 #include <cstdio>
 
+#include <atomic>
+
 static thread_local char g_error[1024] = {0};
+static std::atomic<long long> g_launches{0};
 
 void infero_set_error(const char* fmt, ...) {
     va_list ap;
@@ -15,6 +18,7 @@ void infero_set_error(const char* fmt, ...) {
 // Launch errors only (invalid configuration and the like); asynchronous faults surface
 // at the caller's next synchronisation.
 int infero_check_launch(const char* what) {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         infero_set_error("%s: %s", what, cudaGetErrorString(e));
@@ -28,6 +32,10 @@ extern "C" {
 const char* infero_last_error() { return g_error; }
 
 int infero_abi_version() { return 1; }
+
+// Kernels launched by this library since it was loaded (one per successful or failed launch
+// check; a launch recorded into a CUDA graph counts once, at capture).
+long long infero_launch_count() { return g_launches.load(std::memory_order_relaxed); }
 
 int infero_device_info(int device, int* sm_count, int* cc_major, int* cc_minor, int* smem_optin) {
     cudaDeviceProp p;

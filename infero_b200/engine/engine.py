@@ -93,13 +93,18 @@ class Engine:
         try:
             return self.scheduler.step()
         except Exception as e:                      # noqa: BLE001
-            events = self.scheduler.abort_all(f"step failed: {e}")
-            for rid in list(self.runner.manager.requests):
-                self.runner.manager.close(rid)
+            events = self.abort_all(f"step failed: {e}")
             if not events:
                 raise
             self.last_error = e
             return events
+
+    def abort_all(self, message: str = "aborted") -> List[Event]:
+        """End every running and waiting request now and give back what they hold."""
+        events = self.scheduler.abort_all(message)
+        for rid in list(self.runner.manager.requests):
+            self.runner.manager.close(rid)
+        return events
 
     def is_idle(self) -> bool:
         return self.scheduler.is_idle()

@@ -58,6 +58,7 @@ class StepContext:
         self.decode_only = False
         self.max_q_len = 0
         self.max_kv_len = 0
+        self.kv_bound: Optional[int] = None     # plan decode attention for this many keys (captured steps)
         self._empty_f32 = None
 
     def kv_cache(self, slot: int):
@@ -93,6 +94,14 @@ class ModelRunner:
                                     cfg.max_seqs, max_blocks=self.max_blocks)
         self.steps_run = 0
         self.tokens_run = 0
+        # captured decode steps: (entries, key bound) -> _DecodeGraph; a shape is run eagerly the
+        # first time it is seen, captured the second time and replayed from then on (the
+        # reference does the same per (pool, tokens, kv bucket), crates/model/src/lib.rs:3887-3981)
+        self._graphs: Dict[tuple, "_DecodeGraph"] = {}
+        self._graph_seen: Dict[tuple, int] = {}
+        self.graph_replays = 0
+        self.graph_captures = 0
+        self.last_h2d_bytes = 0
 
     # ---- requests --------------------------------------------------------------------------
     def open(self, rid: Hashable) -> RequestCache:
@@ -155,11 +164,19 @@ class ModelRunner:
                 self.manager.abort_reservation(rc)
             raise
         try:
-            ctx, rows = self._build_context(entries, rcs)
             for rc in rcs:
                 if rc.fresh and self.storage.states:
                     self.storage.zero_state(rc.slot)
-            logits = self.model.forward(ctx, ctx.token_ids, rows)
+            logits = None
+            key = self._graph_key(entries, rcs)
+            if key is not None:
+                logits = self._graph_step(key, entries, rcs)
+            if key is None or logits is None:
+                ctx, rows = self._build_context(entries, rcs)
+                logits = self.model.forward(ctx, ctx.token_ids, rows)
+                n_tokens = ctx.n_tokens
+            else:
+                n_tokens = len(entries)
         except Exception:
             for rc in rcs:
                 self.manager.abort_reservation(rc)
@@ -167,10 +184,14 @@ class ModelRunner:
         for rc, e in zip(rcs, entries):
             self.manager.commit(rc, len(e.tokens))
         self.steps_run += 1
-        self.tokens_run += ctx.n_tokens
+        self.tokens_run += n_tokens
         return logits
 
-    def _build_context(self, entries: Sequence[StepEntry], rcs: Sequence[RequestCache]):
+    # ---- device inputs of a step ---------------------------------------------------------------
+    def _host_arrays(self, entries: Sequence[StepEntry], rcs: Sequence[RequestCache]):
+        """The int32 arrays a step needs, in the order they lie in the device buffer:
+        token ids, positions, token -> entry, then per entry first row, row count, cached
+        length and state slot, the rows whose logits are wanted, and one block table per group."""
         E = len(entries)
         lens = np.fromiter((len(e.tokens) for e in entries), dtype=np.int32, count=E)
         T = int(lens.sum())
@@ -178,35 +199,127 @@ class ModelRunner:
         np.cumsum(lens[:-1], out=q_start[1:])
         pos0 = np.fromiter((rc.length for rc in rcs), dtype=np.int32, count=E)
         slots = np.fromiter((rc.slot for rc in rcs), dtype=np.int32, count=E)
-        token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
-        tok_entry = np.repeat(np.arange(E, dtype=np.int32), lens)
-        positions = np.arange(T, dtype=np.int32) - np.repeat(q_start, lens) + np.repeat(pos0, lens)
+        if T == E:
+            token_ids = np.fromiter((e.tokens[0] for e in entries), dtype=np.int32, count=E)
+            tok_entry = np.arange(E, dtype=np.int32)
+            positions = pos0
+        else:
+            token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+            tok_entry = np.repeat(np.arange(E, dtype=np.int32), lens)
+            positions = np.arange(T, dtype=np.int32) - np.repeat(q_start, lens) + np.repeat(pos0, lens)
         want_rows = [q_start[i] + np.asarray(e.want, dtype=np.int32) for i, e in enumerate(entries) if len(e.want)]
         rows = np.concatenate(want_rows).astype(np.int32) if want_rows else np.zeros(0, dtype=np.int32)
         n_groups = len(self.manager.groups)
         tables = [self.manager.block_table_array(g, rcs, self.max_blocks) for g in range(n_groups)]
-
-        # one pinned staging buffer, one host-to-device copy
         parts = [token_ids, positions, tok_entry, q_start, lens, pos0, slots, rows] + [t.reshape(-1) for t in tables]
-        sizes = [p.size for p in parts]
-        total = int(sum(sizes))
-        staging = torch.empty(total, dtype=torch.int32, pin_memory=(self.device.type == "cuda"))
-        np.concatenate(parts, out=staging.numpy())
-        dev = staging.to(self.device, non_blocking=True)
+        return parts, (q_start, lens, pos0, slots)
+
+    def _context_from(self, dev: torch.Tensor, sizes: Sequence[int], host, E: int, T: int):
         views = []
         off = 0
-        for s in sizes:
-            views.append(dev[off:off + s])
-            off += s
-
+        for n in sizes:
+            views.append(dev[off:off + n])
+            off += n
+        q_start, lens, pos0, slots = host
         ctx = StepContext(self)
         ctx.n_tokens, ctx.n_entries = T, E
         (ctx.token_ids, ctx.positions, ctx.tok_entry, ctx.entry_q_start, ctx.entry_q_len, ctx.entry_pos0,
          ctx.entry_slot, d_rows) = views[:8]
-        ctx._tables = [views[8 + g].view(E, self.max_blocks) for g in range(n_groups)]
+        ctx._tables = [views[8 + g].view(E, self.max_blocks) for g in range(len(self.manager.groups))]
         ctx.h_q_start, ctx.h_q_len, ctx.h_pos0, ctx.h_slot = q_start, lens, pos0, slots
         ctx.decode_only = bool((lens == 1).all())
         ctx.max_q_len = int(lens.max())
         ctx.max_kv_len = int((pos0 + lens).max())
+        return ctx, (d_rows if sizes[7] else None)
+
+    def _build_context(self, entries: Sequence[StepEntry], rcs: Sequence[RequestCache]):
+        parts, host = self._host_arrays(entries, rcs)
+        sizes = [p.size for p in parts]
+        # one pinned staging buffer, one host-to-device copy
+        staging = torch.empty(int(sum(sizes)), dtype=torch.int32, pin_memory=(self.device.type == "cuda"))
+        np.concatenate(parts, out=staging.numpy())
+        dev = staging.to(self.device, non_blocking=True)
+        self.last_h2d_bytes = staging.numel() * 4
+        ctx, rows = self._context_from(dev, sizes, host, len(entries), int(host[1].sum()))
         ctx._staging = staging          # keep the pinned buffer alive until the copy has run
-        return ctx, (d_rows if rows.size else None)
+        return ctx, rows
+
+    # ---- captured decode steps -------------------------------------------------------------------
+    def _graph_key(self, entries: Sequence[StepEntry], rcs: Sequence[RequestCache]):
+        """(entries, key bound) if this step can run as a captured graph: single tokens only,
+        each wanting its own logits.  The bound is the smallest 256 * 2^k that holds every
+        request's keys, so a graph serves a request while it grows to twice its length."""
+        if not self.cfg.cuda_graphs or self.device.type != "cuda" or len(entries) > self.MAX_GRAPH_ENTRIES:
+            return None
+        for e in entries:
+            if len(e.tokens) != 1 or len(e.want) != 1 or int(e.want[0]) != 0:
+                return None
+        need = max(rc.length for rc in rcs) + 1
+        bound = 256
+        while bound < need:
+            bound *= 2
+        return (len(entries), min(bound, self.max_blocks * self.page_size))
+
+    MAX_GRAPH_ENTRIES = 256
+
+    def _graph_step(self, key, entries, rcs) -> Optional[torch.Tensor]:
+        seen = self._graph_seen.get(key, 0)
+        self._graph_seen[key] = seen + 1
+        g = self._graphs.get(key)
+        if g is None:
+            if seen == 0:
+                return None          # first sight runs eagerly: it warms what is set up lazily
+            g = _DecodeGraph(self, key, entries, rcs)
+            self._graphs[key] = g
+            self.graph_captures += 1
+        g.load(entries, rcs)
+        g.graph.replay()
+        self.graph_replays += 1
+        return g.logits
+
+    def drop_graphs(self) -> None:
+        self._graphs.clear()
+        self._graph_seen.clear()
+
+
+class _DecodeGraph:
+    """One captured decode step.  Its inputs live in a device buffer of fixed address that is
+    refilled from pinned host memory before every replay; two staging buffers alternate so
+    that the host never writes one whose copy may still be in flight."""
+
+    def __init__(self, runner: ModelRunner, key, entries, rcs):
+        self.runner = runner
+        E, bound = key
+        parts, host = runner._host_arrays(entries, rcs)
+        self.sizes = [p.size for p in parts]
+        n = int(sum(self.sizes))
+        self.dev = torch.zeros(n, dtype=torch.int32, device=runner.device)
+        self.staging = [torch.empty(n, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self.copied = [None, None]
+        self.turn = 0
+        self.load(entries, rcs, parts)
+        ctx, rows = runner._context_from(self.dev, self.sizes, host, E, E)
+        ctx.kv_bound = bound
+        ctx.max_kv_len = bound
+        self.ctx = ctx
+        torch.cuda.current_stream(runner.device).synchronize()
+        from .. import kernels as K
+        before = K.launch_count()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.logits = runner.model.forward(ctx, ctx.token_ids, rows)
+        self.n_kernels = K.launch_count() - before
+
+    def load(self, entries, rcs, parts=None) -> None:
+        if parts is None:
+            parts, _ = self.runner._host_arrays(entries, rcs)
+        i = self.turn
+        self.turn ^= 1
+        if self.copied[i] is not None:
+            self.copied[i].synchronize()
+        np.concatenate(parts, out=self.staging[i].numpy())
+        self.dev.copy_(self.staging[i], non_blocking=True)
+        self.runner.last_h2d_bytes = self.dev.numel() * 4
+        ev = torch.cuda.Event()
+        ev.record()
+        self.copied[i] = ev

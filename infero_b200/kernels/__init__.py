@@ -37,6 +37,14 @@ def lib():
     return _LIB
 
 
+def launch_count() -> int:
+    """Kernels launched through this library so far (a launch recorded into a CUDA graph
+    counts once, when it is captured)."""
+    f = lib().infero_launch_count
+    f.restype = ctypes.c_longlong
+    return int(f())
+
+
 def loaded_library_path() -> Optional[str]:
     return None if _LIB is None else _LIB._name
 

@@ -127,3 +127,57 @@ def test_trace_run_program(tmp_path, dtype):
     got = R.replay_subprocess(mdir, dtype, steps, n, str(tmp_path / "out"), CONFIGS["B"]["vocab_size"])
     err, where = R.compare(got, plain_logits(mdir, reqs))
     assert err <= TOL[dtype], f"trace_run {dtype}: relative error {err:.3e} at {where}"
+
+
+@pytest.mark.parametrize("name,dtype", [("B", "bfloat16"), ("C", "bfloat16"), ("B", "float32")])
+def test_captured_decode_steps_equal_eager_ones(name, dtype):
+    """Decode steps replayed from a captured CUDA graph give the logits of eager steps, while
+    requests grow across pages and the batch changes size."""
+    import torch
+    from infero_b200.engine import StepEntry
+    mdir = model_dir(name)
+    reqs = make_requests(name, [70, 40, 55], seed=21)
+    plain = plain_logits(mdir, reqs)
+    runner = make_runner(mdir, dtype, 512, cuda_graphs=True)
+    head = 20
+    for rid, toks in reqs.items():
+        runner.open(rid)
+        runner.step([StepEntry(rid, toks[:head], [])])
+    worst = 0.0
+    for p in range(head, 70):
+        live = [rid for rid, toks in reqs.items() if p < len(toks)]
+        logits = runner.step([StepEntry(rid, [reqs[rid][p]], [0]) for rid in live])
+        got = logits.float().cpu().numpy()
+        for i, rid in enumerate(live):
+            ref = plain[rid][p]
+            worst = max(worst, float(np.abs(got[i] - ref).max() / np.abs(plain[rid]).max()))
+    assert runner.graph_captures >= 2 and runner.graph_replays > 40
+    assert worst <= TOL[dtype], f"{name} {dtype}: relative error {worst:.3e}"
+    torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_entry_point(name, dtype):
+    """Engine.generate (scheduler, prompt portions, captured decode steps, device argmax)
+    against the plain implementation's argmax continuation."""
+    import plain_qwen2
+    from engine_fixtures import plain_model
+    from infero_b200.engine import Engine
+    from infero_b200.sampling import SamplingParams
+    # wider weights than 0.02 so that the largest logit leads by more than bf16 rounding
+    mdir = model_dir(name, seed=77, qk_gain=1.5)
+    cfg, w = plain_model(mdir)
+    reqs = make_requests(name, [9, 30, 3, 21], seed=31)
+    n_new = 10
+    want = [plain_qwen2.greedy_generate(cfg, w, toks, n_new) for toks in reqs.values()]
+    eng = Engine(mdir, dtype=dtype, ctx=128, max_seqs=3, kv_slots=256, max_batch_tokens=32)
+    got = eng.generate(list(reqs.values()), SamplingParams(temperature=0.0, repetition_penalty=1.0),
+                       max_new_tokens=n_new, ignore_eos=True)
+    if dtype == "float32":
+        assert got == want
+    else:
+        same = sum(int(a == b) for g, x in zip(got, want) for a, b in zip(g, x))
+        assert same >= 4 * n_new - 4 and all(g[0] == x[0] for g, x in zip(got, want)), (got, want)
+    assert eng.runner.graph_replays > 0
+    assert not eng.runner.manager.requests
