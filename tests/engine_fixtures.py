@@ -59,7 +59,8 @@ def make_requests(name: str, lengths, seed: int = 0) -> Dict[str, List[int]]:
     return {f"r{i}": [rng.randrange(V) for _ in range(n)] for i, n in enumerate(lengths)}
 
 
-def make_runner(mdir: str, dtype: str, max_tokens: int, page_size: int = 16, max_seqs: int = 8, **kw):
+def make_runner(mdir: str, dtype: str, max_tokens: int, page_size: int = 16, max_seqs: int = 8,
+                cuda_graphs: bool = False, **kw):
     from infero_b200.config import EngineConfig
     from infero_b200.engine import ModelRunner
     from infero_b200.loading import load_model
@@ -67,5 +68,5 @@ def make_runner(mdir: str, dtype: str, max_tokens: int, page_size: int = 16, max
     pages = -(-max_tokens // page_size)
     cfg = EngineConfig(dtype=dtype, page_size=page_size, num_pages=pages, max_seqs=max_seqs,
                        ctx=pages * page_size, max_batch_tokens=max(64, pages * page_size),
-                       max_logit_rows=max(64, pages * page_size), cuda_graphs=False, **kw)
+                       max_logit_rows=max(64, pages * page_size), cuda_graphs=cuda_graphs, **kw)
     return ModelRunner(model, cfg)

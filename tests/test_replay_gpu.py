@@ -177,7 +177,15 @@ def test_greedy_generation_through_the_entry_point(name, dtype):
     if dtype == "float32":
         assert got == want
     else:
-        same = sum(int(a == b) for g, x in zip(got, want) for a, b in zip(g, x))
-        assert same >= 4 * n_new - 4 and all(g[0] == x[0] for g, x in zip(got, want)), (got, want)
+        # bfloat16 may pick another token only where the plain logits nearly tie; from there on
+        # the two continuations are different sequences and are not compared
+        for toks, g, x in zip(reqs.values(), got, want):
+            assert len(g) == n_new
+            for i in range(n_new):
+                if g[i] != x[i]:
+                    row = plain_qwen2.forward(cfg, w, list(toks) + x[:i])[-1]
+                    gap = float(row.max() - row[g[i]]) / float(row.abs().max())
+                    assert gap <= TOL[dtype], f"token {i}: picked {g[i]}, plain {x[i]}, gap {gap:.3e}"
+                    break
     assert eng.runner.graph_replays > 0
     assert not eng.runner.manager.requests
