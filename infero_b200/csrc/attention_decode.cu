@@ -1,0 +1,306 @@
+// Decode attention over the paged cache, fed by TMA.
+//
+// One CTA = one token, one kv head (its group of query heads fills the 16 rows of the MMA,
+// 16 at a time) and one split of the context.  Each of the four warps walks its own 16-key
+// slices (warp w takes slices w, w + 4, ...) through a ring of shared-memory stages of its
+// own: lane 0 looks the slice's page up in the block table and issues tiled TMA loads
+// (cp.async.bulk.tensor, 128-byte swizzle) for the slice's keys and values, which complete
+// on an mbarrier; the warp waits for the stage, runs the 16-key step of the online softmax
+// on mma.sync (s = q k^T, p = 2^(s - m), o += p v) and refills the stage.  Nothing but the
+// TMA issue touches addresses, so the loop is a few hundred instructions per 8 KB of cache.
+// The four warps are merged in shared memory and the CTA writes an unnormalised partial
+// result (o, m, l) per query head; attn_combine merges the splits.
+//
+// The cache of one layer is seen as a matrix [pages * kv_heads * page_size, head_dim]; a slice
+// of 16 keys is 16 consecutive rows of it (page_size is a multiple of 16).  Head sizes: 64 and
+// 128 (whole 128-byte swizzle blocks); other sizes stay with the cp.async kernel in
+// attention_mma.cu.  Reference: crates/kernels/src/cu/ops.cu:1773-2075 (fused decode attention
+// with split context), :1465-1494 (merge).
+#include "attn_common.cuh"
+#include "tc_common.cuh"
+
+namespace {
+
+using namespace attn;
+
+constexpr int TD_WARPS = 4, TD_THREADS = TD_WARPS * 32;
+
+template <int D>
+struct TdPlan {
+    static constexpr int STAGES = D == 128 ? 3 : 4;
+    static constexpr int HALF_BYTES = 16 * D * 2;                 // keys (or values) of one slice
+    static constexpr int STAGE_BYTES = 2 * HALF_BYTES;
+    static constexpr int WARP_BYTES = STAGES * STAGE_BYTES;
+    static constexpr int TILES_BYTES = TD_WARPS * WARP_BYTES;
+    static constexpr int RED_BYTES = TD_WARPS * 16 * (D + 2) * 4;
+    static constexpr int DATA_BYTES = TILES_BYTES > RED_BYTES ? TILES_BYTES : RED_BYTES;
+    static constexpr int BAR_OFFSET = DATA_BYTES;
+    static constexpr int TOTAL = DATA_BYTES + TD_WARPS * STAGES * 8 + 16 + 1024;
+};
+
+// partial_o [n_tok, n_heads, n_splits, D] float (unnormalised), partial_ml [n_tok, n_heads, n_splits, 2].
+template <int D>
+__global__ void __launch_bounds__(TD_THREADS)
+attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                       const bf16* __restrict__ q, int q_stride, const int* __restrict__ block_table,
+                       int max_blocks, const int* __restrict__ tok_entry, const int* __restrict__ positions,
+                       int tok_first, int n_heads, int n_kv, int page_size, int window, float scale_log2,
+                       int chunk, int n_splits, float* __restrict__ partial_o, float* __restrict__ partial_ml,
+                       int* __restrict__ err_flag) {
+    using Plan = TdPlan<D>;
+    using Layout = Swizzled128<D, 16>;
+    constexpr int STAGES = Plan::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = tc::smem_u32(smem_raw);
+    uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Plan::BAR_OFFSET);       // [warp][stage]
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + TD_WARPS * STAGES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+    const int split = blockIdx.x;
+    const int group = n_heads / n_kv;
+    const int gtiles = (group + 15) / 16;
+    const int kvh = blockIdx.y / gtiles, gt = blockIdx.y % gtiles;
+    const int ti = blockIdx.z;
+    const int t = tok_first + ti;
+    const int pos = positions[t];
+    const int* table = block_table + (size_t)tok_entry[t] * max_blocks;
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int base = (lo / KEYS16) * KEYS16;
+    const int k_begin = base + split * chunk;
+    const int k_end = min(pos + 1, k_begin + chunk);                  // exclusive
+    const int h0 = kvh * group + gt * 16;
+    const int valid = min(16, group - gt * 16);
+    float* po = partial_o + (((size_t)ti * n_heads + h0) * n_splits + split) * D;
+    float* pml = partial_ml + (((size_t)ti * n_heads + h0) * n_splits + split) * 2;
+    if (k_begin >= k_end) {
+        // nothing in this split: leave (m, l) = (-inf, 0) so the merge skips it
+        for (int r = threadIdx.x; r < valid; r += TD_THREADS) {
+            pml[(size_t)r * n_splits * 2] = -CUDART_INF_F;
+            pml[(size_t)r * n_splits * 2 + 1] = 0.f;
+        }
+        return;
+    }
+    if (threadIdx.x == 0) {
+        tc::prefetch_tensormap(&map_k);
+        tc::prefetch_tensormap(&map_v);
+        for (int i = 0; i < TD_WARPS * STAGES; ++i) tc::mbar_init(&bars[i], 1);
+        *abort_flag = 0;
+        tc::fence_barrier_init();
+        tc::fence_proxy_async();
+    }
+    __syncthreads();
+
+    uint8_t* my = smem + (size_t)warp * Plan::WARP_BYTES;
+    uint64_t* my_bar = bars + warp * STAGES;
+
+    uint32_t qf[D / 16][4];
+    load_q<D>(qf, q + (size_t)t * q_stride + (size_t)h0 * D, (size_t)D, valid, lane);
+    float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+    const int n_slices = (k_end - k_begin + KEYS16 - 1) / KEYS16;
+    const int my_slices = n_slices > warp ? (n_slices - warp + TD_WARPS - 1) / TD_WARPS : 0;
+    const uint64_t policy = tc::policy_evict_first();                 // the cache is read once per step
+    // lane 0 issues the loads of the warp's i-th slice into stage i % STAGES
+    auto issue = [&](int i) {
+        if (i < my_slices && lane == 0) {
+            const int key0 = k_begin + (warp + i * TD_WARPS) * KEYS16;
+            const int page = table[key0 / page_size];
+            const int row = (page < 0 ? 0 : (page * n_kv + kvh) * page_size) + key0 % page_size;
+            uint8_t* st = my + (size_t)(i % STAGES) * Plan::STAGE_BYTES;
+            uint64_t* bar = &my_bar[i % STAGES];
+            tc::mbar_expect_tx(bar, Plan::STAGE_BYTES);
+#pragma unroll
+            for (int b = 0; b < D / 64; ++b) {
+                tc::tma_load_2d_hint(st + b * 2048, &map_k, b * 64, row, bar, policy);
+                tc::tma_load_2d_hint(st + Plan::HALF_BYTES + b * 2048, &map_v, b * 64, row, bar, policy);
+            }
+        }
+    };
+#pragma unroll
+    for (int i = 0; i < STAGES - 1; ++i) issue(i);
+    bool ok = true;
+    int waited = 0;
+    for (int i = 0; i < my_slices; ++i) {
+        issue(i + STAGES - 1);                                        // the stage the last iteration left
+        if (!tc::mbar_wait(&my_bar[i % STAGES], (uint32_t)(i / STAGES) & 1u, abort_flag)) { ok = false; break; }
+        waited = i + 1;
+        const bf16* kt = reinterpret_cast<const bf16*>(my + (size_t)(i % STAGES) * Plan::STAGE_BYTES);
+        const bf16* vt = kt + 16 * D;
+        const int kb = k_begin + (warp + i * TD_WARPS) * KEYS16;
+        slice16<D, Layout>(qf, kt, vt, 0, kb, lo, pos, lo, pos, scale_log2, m, l, o, lane);
+        __syncwarp();
+    }
+    if (!ok) {
+        // a load never arrived: report, and let what is still in flight land before the block
+        // (and its shared memory) goes away
+        if (lane == 0) {
+            *abort_flag = 1;
+            atomicExch(err_flag, 4);
+        }
+        volatile int never = 0;
+        const int issued = min(my_slices, waited + STAGES);
+        for (int i = waited; i < issued; ++i)
+            tc::mbar_wait(&my_bar[i % STAGES], (uint32_t)(i / STAGES) & 1u, &never);
+    }
+    // ---- merge the four warps ----------------------------------------------------------------------
+    float l0 = l[0], l1 = l[1];
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    __syncthreads();                                   // every warp is done with its stages
+    float* red_o = reinterpret_cast<float*>(smem);                    // [4 warps][16 rows][D]
+    float* red_ml = red_o + TD_WARPS * 16 * D;                        // [4 warps][16 rows][2]
+#pragma unroll
+    for (int nt = 0; nt < D / 8; ++nt) {
+        const int d = nt * 8 + c * 2;
+        float* r0 = red_o + ((size_t)warp * 16 + g) * D + d;
+        float* r1 = red_o + ((size_t)warp * 16 + g + 8) * D + d;
+        r0[0] = o[nt][0]; r0[1] = o[nt][1];
+        r1[0] = o[nt][2]; r1[1] = o[nt][3];
+    }
+    if (c == 0) {
+        red_ml[((size_t)warp * 16 + g) * 2] = m[0];
+        red_ml[((size_t)warp * 16 + g) * 2 + 1] = l0;
+        red_ml[((size_t)warp * 16 + g + 8) * 2] = m[1];
+        red_ml[((size_t)warp * 16 + g + 8) * 2 + 1] = l1;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < valid * D; idx += TD_THREADS) {
+        const int r = idx / D, d = idx - r * D;
+        float mm = -CUDART_INF_F;
+#pragma unroll
+        for (int w = 0; w < TD_WARPS; ++w) mm = fmaxf(mm, red_ml[((size_t)w * 16 + r) * 2]);
+        float acc = 0.f, ll = 0.f;
+#pragma unroll
+        for (int w = 0; w < TD_WARPS; ++w) {
+            const float mw = red_ml[((size_t)w * 16 + r) * 2];
+            const float f = mw == -CUDART_INF_F ? 0.f : exp2f(mw - mm);
+            acc += red_o[((size_t)w * 16 + r) * D + d] * f;
+            ll += red_ml[((size_t)w * 16 + r) * 2 + 1] * f;
+        }
+        po[(size_t)r * n_splits * D + d] = acc;
+        if (d == 0) {
+            pml[(size_t)r * n_splits * 2] = mm;
+            pml[(size_t)r * n_splits * 2 + 1] = ll;
+        }
+    }
+}
+
+// out[t, h, :] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), M = max_s m_s; splits in
+// ascending order.  One warp per (token, head): the weights of the splits are worked out once
+// (lanes over splits), then every lane sums its columns with the loads of all splits in flight.
+constexpr int COMBINE_MAX_SPLITS = 256;
+__global__ void __launch_bounds__(128)
+attn_combine_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
+                    bf16* __restrict__ out, int out_stride, int tok_first, int n_tok, int n_heads,
+                    int n_splits, int head_dim) {
+    __shared__ float wsm[4][COMBINE_MAX_SPLITS];
+    const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = blockIdx.x * 4 + wib;
+    if (warp >= n_tok * n_heads) return;
+    const int ti = warp / n_heads, h = warp % n_heads;
+    const float* ml = partial_ml + (size_t)warp * n_splits * 2;
+    const float* po = partial_o + (size_t)warp * n_splits * head_dim;
+    float* wgt = wsm[wib];
+    float M = -CUDART_INF_F;
+    for (int s = lane; s < n_splits; s += 32) M = fmaxf(M, ml[s * 2]);
+    M = warp_max(M);
+    for (int s = lane; s < n_splits; s += 32) {
+        const float ms = ml[s * 2];
+        wgt[s] = ms == -CUDART_INF_F ? 0.f : exp2f(ms - M);
+    }
+    __syncwarp();
+    float L = 0.f;
+    for (int s = 0; s < n_splits; ++s) L += ml[s * 2 + 1] * wgt[s];    // ascending, same in every lane
+    const float inv = 1.0f / L;
+    bf16* orow = out + (size_t)(tok_first + ti) * out_stride + (size_t)h * head_dim;
+    for (int d = lane * 2; d < head_dim; d += 64) {
+        float a0 = 0.f, a1 = 0.f;
+#pragma unroll 8
+        for (int s = 0; s < n_splits; ++s) {
+            const float2 v = *reinterpret_cast<const float2*>(po + (size_t)s * head_dim + d);
+            a0 = fmaf(v.x, wgt[s], a0);
+            a1 = fmaf(v.y, wgt[s], a1);
+        }
+        *reinterpret_cast<uint32_t*>(orow + d) = pack_bf16(a0 * inv, a1 * inv);
+    }
+}
+
+template <int D>
+int launch_tma(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, int q_stride, const int* block_table,
+               int max_blocks, const int* tok_entry, const int* positions, int tok_first, int n_tok, int n_heads,
+               int n_kv, int page_size, int window, float scale_log2, int chunk, int n_splits, float* po, float* pml,
+               int* err, cudaStream_t stream) {
+    using Plan = TdPlan<D>;
+    auto kern = attn_decode_tma_kernel<D>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::TOTAL);
+        if (e != cudaSuccess) {
+            infero_set_error("attn_decode_tma: cannot get %d bytes of shared memory: %s", Plan::TOTAL, cudaGetErrorString(e));
+            return 1;
+        }
+        configured = true;
+    }
+    const int group = n_heads / n_kv;
+    dim3 grid(n_splits, n_kv * ((group + 15) / 16), n_tok);
+    kern<<<grid, TD_THREADS, Plan::TOTAL, stream>>>(mk, mv, (const bf16*)q, q_stride, block_table, max_blocks, tok_entry,
+                                                    positions, tok_first, n_heads, n_kv, page_size, window, scale_log2,
+                                                    chunk, n_splits, po, pml, err);
+    return infero_check_launch("attn_decode_tma");
+}
+
+}  // namespace
+
+extern "C" {
+
+int infero_attn_decode_tma_supported(int head_dim, int page_size) {
+    return (head_dim == 64 || head_dim == 128) && page_size % 16 == 0;
+}
+
+// The same contract as infero_attn_decode (attention_mma.cu), plus num_pages: the caches are
+// [num_pages, n_kv, page_size, head_dim] bf16, contiguous and 16-byte aligned.  n_splits is
+// at most 256.  scratch: infero_attn_decode_scratch bytes.
+int infero_attn_decode_tma(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
+                           const void* v_cache, int num_pages, const int* block_table, int max_blocks,
+                           const int* tok_entry, const int* positions, int tok_first, int n_tok, int n_heads,
+                           int n_kv, int head_dim, int page_size, int window, float scale, int chunk, int n_splits,
+                           void* scratch, cudaStream_t stream) {
+    if (n_tok == 0) return 0;
+    INFERO_REQUIRE(infero_attn_decode_tma_supported(head_dim, page_size),
+                   "attn_decode_tma: head_dim %d / page_size %d not supported", head_dim, page_size);
+    INFERO_REQUIRE(n_kv > 0 && n_heads % n_kv == 0, "attn_decode_tma: bad head counts %d / %d", n_heads, n_kv);
+    INFERO_REQUIRE(chunk > 0 && chunk % 16 == 0 && n_splits >= 1 && n_splits <= COMBINE_MAX_SPLITS,
+                   "attn_decode_tma: bad split plan chunk=%d splits=%d", chunk, n_splits);
+    INFERO_REQUIRE(n_tok <= 65535 && (long long)num_pages * n_kv * page_size < (1ll << 31),
+                   "attn_decode_tma: %d tokens / %d pages in one call", n_tok, num_pages);
+    INFERO_REQUIRE(q_stride % 2 == 0 && out_stride % 2 == 0, "attn_decode_tma: odd row stride");
+    CUtensorMap mk, mv;
+    const int rows = num_pages * n_kv * page_size;
+    if (infero_tensor_map_bf16(k_cache, rows, head_dim, head_dim, 16, &mk)) return 1;
+    if (infero_tensor_map_bf16(v_cache, rows, head_dim, head_dim, 16, &mv)) return 1;
+    int* err;
+    if (infero_tc_err_flag(&err)) return 1;
+    const float sl2 = scale * 1.4426950408889634f;
+    float* po = (float*)scratch;
+    float* pml = po + (size_t)n_tok * n_heads * n_splits * head_dim;
+    int rc;
+    if (head_dim == 128)
+        rc = launch_tma<128>(mk, mv, q, q_stride, block_table, max_blocks, tok_entry, positions, tok_first, n_tok,
+                             n_heads, n_kv, page_size, window, sl2, chunk, n_splits, po, pml, err, stream);
+    else
+        rc = launch_tma<64>(mk, mv, q, q_stride, block_table, max_blocks, tok_entry, positions, tok_first, n_tok,
+                            n_heads, n_kv, page_size, window, sl2, chunk, n_splits, po, pml, err, stream);
+    if (rc) return rc;
+    const int warps = n_tok * n_heads;
+    attn_combine_kernel<<<(warps + 3) / 4, 128, 0, stream>>>(po, pml, (bf16*)out, out_stride, tok_first, n_tok,
+                                                             n_heads, n_splits, head_dim);
+    return infero_check_launch("attn_combine");
+}
+
+}  // extern "C"

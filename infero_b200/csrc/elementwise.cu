@@ -22,13 +22,42 @@ __global__ void embed_gather_kernel(const TE* __restrict__ table, const int* __r
     for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_f32(row[i]) * scale;
 }
 
+// 4 consecutive elements as 32-bit values (p must be aligned to 4 elements).
+__device__ __forceinline__ void load4(const float* p, float* v) {
+    const float4 f = *reinterpret_cast<const float4*>(p);
+    v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+}
+__device__ __forceinline__ void load4(const bf16* p, float* v) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+    v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+}
+__device__ __forceinline__ void load4_any(const void* p, int dtype, size_t i, float* v) {
+    if (dtype == INFERO_F32) load4(reinterpret_cast<const float*>(p) + i, v);
+    else load4(reinterpret_cast<const bf16*>(p) + i, v);
+}
+__device__ __forceinline__ void store4(float* p, const float* v) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(bf16* p, const float* v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 u;
+    u.x = *reinterpret_cast<uint32_t*>(&a);
+    u.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = u;
+}
+
 // One block per output row.
 //   src row  = rows ? rows[blockIdx.x] : blockIdx.x
-//   v        = x[src] (+ delta[src])            (32-bit)
-//   if !rows: x[src] = v                        (the residual stream moves on)
+//   v        = x[src] + sum_s delta[s][src] (+ dbias)      (32-bit; s ascending)
+//   if !rows: x[src] = v                                   (the residual stream moves on)
 //   out[blockIdx.x] = v * rsqrt(mean(v^2)+eps) * w
-template <typename TD, typename TO>
-__global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta,
+// delta may come as several 32-bit partial sums (the split-K products of the few-token
+// matrix kernel), split_stride elements apart.  VEC = 4 needs d % 4 == 0.
+template <typename TD, typename TO, int VEC>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int splits,
+                                   long long split_stride, const void* __restrict__ dbias, int dbias_dtype,
                                    const void* __restrict__ w, int wdtype, float eps,
                                    TO* __restrict__ out, const int* __restrict__ rows, int d) {
     __shared__ float red[32];
@@ -39,31 +68,90 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
     TO* orow = out + (size_t)r * d;
     extern __shared__ float vbuf[];      // d floats: the summed row, read twice
     float ss = 0.f;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        float v = xr[i];
-        if (dr) v += to_f32(dr[i]);
-        vbuf[i] = v;
-        if (!rows && dr) xr[i] = v;
-        ss = fmaf(v, v, ss);
+    if (VEC == 4) {
+        for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
+            float v[4];
+            load4(xr + i, v);
+            if (dr) {
+                for (int s = 0; s < splits; ++s) {
+                    float t[4];
+                    load4(dr + (size_t)s * split_stride + i, t);
+                    v[0] += t[0]; v[1] += t[1]; v[2] += t[2]; v[3] += t[3];
+                }
+                if (dbias) {
+                    float t[4];
+                    load4_any(dbias, dbias_dtype, i, t);
+                    v[0] += t[0]; v[1] += t[1]; v[2] += t[2]; v[3] += t[3];
+                }
+                if (!rows) store4(xr + i, v);
+            }
+            store4(vbuf + i, v);
+            ss = fmaf(v[0], v[0], ss); ss = fmaf(v[1], v[1], ss); ss = fmaf(v[2], v[2], ss); ss = fmaf(v[3], v[3], ss);
+        }
+    } else {
+        for (int i = threadIdx.x; i < d; i += blockDim.x) {
+            float v = xr[i];
+            if (dr) {
+                for (int s = 0; s < splits; ++s) v += to_f32(dr[(size_t)s * split_stride + i]);
+                if (dbias) v += load_any(dbias, dbias_dtype, i);
+                if (!rows) xr[i] = v;
+            }
+            vbuf[i] = v;
+            ss = fmaf(v, v, ss);
+        }
     }
     ss = block_sum(ss, red);
-    const float s = 1.0f / sqrtf(ss / (float)d + eps);
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        float v = vbuf[i] * s;
-        orow[i] = from_f32<TO>(v * load_any(w, wdtype, i));
+    const float sc = 1.0f / sqrtf(ss / (float)d + eps);
+    if (VEC == 4) {
+        for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
+            float v[4], ww[4];
+            load4(vbuf + i, v);
+            load4_any(w, wdtype, i, ww);
+            v[0] = v[0] * sc * ww[0]; v[1] = v[1] * sc * ww[1]; v[2] = v[2] * sc * ww[2]; v[3] = v[3] * sc * ww[3];
+            store4(orow + i, v);
+        }
+    } else {
+        for (int i = threadIdx.x; i < d; i += blockDim.x) {
+            float v = vbuf[i] * sc;
+            orow[i] = from_f32<TO>(v * load_any(w, wdtype, i));
+        }
     }
 }
 
-template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int ff, size_t total) {
-    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+// out[t, j] = silu(g) * u with g = sum_s gu[s][t, j], u = sum_s gu[s][t, ff + j] (s ascending).
+template <typename T, int VEC>
+__global__ void swiglu_kernel(const T* __restrict__ gu, int splits, long long split_stride, T* __restrict__ out_same,
+                              bf16* __restrict__ out_bf16, int ff, size_t total) {
+    size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     if (i >= total) return;
     size_t t = i / ff;
     int j = (int)(i - t * ff);
-    float g = to_f32(gu[t * 2 * (size_t)ff + j]);
-    float u = to_f32(gu[t * 2 * (size_t)ff + ff + j]);
-    float h = g / (1.0f + expf(-g)) * u;
-    out[i] = from_f32<T>(h);
+    const T* row = gu + t * 2 * (size_t)ff;
+    float g[VEC], u[VEC], h[VEC];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) g[k] = u[k] = 0.f;
+    for (int s = 0; s < splits; ++s) {
+        const T* rs = row + (size_t)s * split_stride;
+        if (VEC == 4) {
+            float a[4], b[4];
+            load4(rs + j, a);
+            load4(rs + ff + j, b);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { g[k] += a[k]; u[k] += b[k]; }
+        } else {
+            g[0] += to_f32(rs[j]);
+            u[0] += to_f32(rs[ff + j]);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) h[k] = g[k] / (1.0f + expf(-g[k])) * u[k];
+    if (VEC == 4) {
+        if (out_bf16) store4(out_bf16 + i, h);
+        else store4(out_same + i, h);
+    } else {
+        if (out_bf16) out_bf16[i] = __float2bfloat16_rn(h[0]);
+        else out_same[i] = from_f32<T>(h[0]);
+    }
 }
 
 // x[t,:] += delta[t,:]   (used when no norm follows)
@@ -90,20 +178,37 @@ int infero_embed_gather(const void* table, int table_dtype, const int* ids, floa
 }
 
 // delta may be null (plain norm); rows may be null (all rows, residual written back).
-int infero_add_rmsnorm(float* x, const void* delta, int delta_dtype, const void* w, int w_dtype,
+// delta: delta_splits arrays of [rows of x, d], split_stride elements apart, summed in
+// ascending order, plus dbias (nullable) -- the few-token matrix kernel's partial products.
+int infero_add_rmsnorm(float* x, const void* delta, int delta_dtype, int delta_splits, long long split_stride,
+                       const void* dbias, int dbias_dtype, const void* w, int w_dtype,
                        float eps, void* out, int out_dtype, const int* rows, int n_rows, int d,
                        cudaStream_t stream) {
     if (n_rows == 0) return 0;
     INFERO_REQUIRE(d > 0 && (size_t)d * 4 <= 160 * 1024, "add_rmsnorm: width %d not supported (1..40960)", d);
+    INFERO_REQUIRE(delta_splits >= 1, "add_rmsnorm: %d splits", delta_splits);
     const size_t smem = (size_t)d * sizeof(float);
-    const int threads = 256;
+    auto al = [](const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; };
+    const bool vec = d % 4 == 0 && al(x, 16) && al(out, 16) && al(w, 16) && (!delta || al(delta, 16)) &&
+                     (!dbias || al(dbias, 16)) && split_stride % 4 == 0;
+    int threads = vec ? (d / 4 + 31) / 32 * 32 : 256;
+    if (threads > 1024) threads = 1024;
+    if (threads < 32) threads = 32;
 #define LAUNCH(TD, TO)                                                                          \
     do {                                                                                        \
-        auto k = add_rmsnorm_kernel<TD, TO>;                                                    \
-        if (smem > 48 * 1024)                                                                   \
-            cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
-        k<<<n_rows, threads, smem, stream>>>(x, (const TD*)delta, w, w_dtype, eps, (TO*)out,    \
-                                             rows, d);                                          \
+        if (vec) {                                                                              \
+            auto k = add_rmsnorm_kernel<TD, TO, 4>;                                             \
+            if (smem > 48 * 1024)                                                               \
+                cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            k<<<n_rows, threads, smem, stream>>>(x, (const TD*)delta, delta_splits, split_stride, dbias,  \
+                                                 dbias_dtype, w, w_dtype, eps, (TO*)out, rows, d);       \
+        } else {                                                                                \
+            auto k = add_rmsnorm_kernel<TD, TO, 1>;                                             \
+            if (smem > 48 * 1024)                                                               \
+                cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            k<<<n_rows, threads, smem, stream>>>(x, (const TD*)delta, delta_splits, split_stride, dbias,  \
+                                                 dbias_dtype, w, w_dtype, eps, (TO*)out, rows, d);       \
+        }                                                                                       \
     } while (0)
     if (delta_dtype == INFERO_F32 && out_dtype == INFERO_F32) LAUNCH(float, float);
     else if (delta_dtype == INFERO_BF16 && out_dtype == INFERO_BF16) LAUNCH(bf16, bf16);
@@ -113,15 +218,26 @@ int infero_add_rmsnorm(float* x, const void* delta, int delta_dtype, const void*
     return infero_check_launch("add_rmsnorm");
 }
 
-int infero_swiglu(const void* gate_up, void* out, int dtype, int n_tokens, int ff, cudaStream_t stream) {
+// gate_up: splits arrays of [n_tokens, 2 * ff] (dtype), split_stride elements apart.  out has
+// gate_up's type, or bf16 when out_bf16 is set (32-bit partial products in, bf16 out).
+int infero_swiglu(const void* gate_up, int splits, long long split_stride, void* out, int dtype, int out_bf16,
+                  int n_tokens, int ff, cudaStream_t stream) {
     const size_t total = (size_t)n_tokens * ff;
     if (total == 0) return 0;
+    INFERO_REQUIRE(splits >= 1, "swiglu: %d splits", splits);
     const int threads = 256;
-    const unsigned blocks = (unsigned)((total + threads - 1) / threads);
-    if (dtype == INFERO_F32)
-        swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, ff, total);
-    else
-        swiglu_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, ff, total);
+    auto al = [](const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; };
+    const bool vec = ff % 4 == 0 && al(gate_up, 16) && al(out, 16) && split_stride % 4 == 0;
+    const size_t work = vec ? total / 4 : total;
+    const unsigned blocks = (unsigned)((work + threads - 1) / threads);
+    bf16* ob = out_bf16 ? (bf16*)out : nullptr;
+    if (dtype == INFERO_F32) {
+        if (vec) swiglu_kernel<float, 4><<<blocks, threads, 0, stream>>>((const float*)gate_up, splits, split_stride, (float*)out, ob, ff, total);
+        else swiglu_kernel<float, 1><<<blocks, threads, 0, stream>>>((const float*)gate_up, splits, split_stride, (float*)out, ob, ff, total);
+    } else {
+        if (vec) swiglu_kernel<bf16, 4><<<blocks, threads, 0, stream>>>((const bf16*)gate_up, splits, split_stride, (bf16*)out, nullptr, ff, total);
+        else swiglu_kernel<bf16, 1><<<blocks, threads, 0, stream>>>((const bf16*)gate_up, splits, split_stride, (bf16*)out, nullptr, ff, total);
+    }
     return infero_check_launch("swiglu");
 }
 

@@ -53,6 +53,56 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int row_stride, const int
     }
 }
 
+// The same, reading q, k and v as the sum of 32-bit partial products (+ bias) that the
+// few-token matrix kernel leaves behind: value(t, c) = sum_s partial[s][t][c] + bias[c], s
+// ascending.  Rotated q goes to q_out [T, n_heads * head_dim]; k and v go to their pages.
+template <typename T>
+__global__ void rope_cache_partials_kernel(const float* __restrict__ partial, int splits, long long split_stride,
+                                           int row_width, const void* __restrict__ bias, int bias_dtype,
+                                           T* __restrict__ q_out, int q_stride, const int* __restrict__ positions,
+                                           const int* __restrict__ tok_entry, const int* __restrict__ block_table,
+                                           int max_blocks, const float* __restrict__ inv_freq, int rotary_dim,
+                                           T* __restrict__ k_cache, T* __restrict__ v_cache, int page_size,
+                                           int n_heads, int n_kv, int head_dim, int write_cache) {
+    const int t = blockIdx.x;
+    const int h = blockIdx.y;
+    const int pos = positions[t];
+    const int half = rotary_dim >> 1;
+    const bool is_q = h < n_heads;
+    const bool is_k = !is_q && h < n_heads + n_kv;
+    const size_t col0 = (size_t)h * head_dim;
+    const float* src = partial + (size_t)t * row_width + col0;
+    auto value = [&](int i) {
+        float v = 0.f;
+        for (int s = 0; s < splits; ++s) v += src[(size_t)s * split_stride + i];
+        if (bias) v += load_any(bias, bias_dtype, col0 + i);
+        return v;
+    };
+    T* dst;
+    if (is_q) {
+        dst = q_out + (size_t)t * q_stride + col0;
+    } else {
+        if (!write_cache) return;
+        const int kvh = is_k ? h - n_heads : h - n_heads - n_kv;
+        const int page = block_table[(size_t)tok_entry[t] * max_blocks + pos / page_size];
+        if (page < 0) return;
+        T* base = is_k ? k_cache : v_cache;
+        dst = base + (((size_t)page * n_kv + kvh) * page_size + (pos % page_size)) * head_dim;
+    }
+    if (is_q || is_k) {
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            float sn, cs;
+            sincosf((float)pos * inv_freq[i], &sn, &cs);
+            const float a = value(i), b = value(i + half);
+            dst[i] = from_f32<T>(a * cs - b * sn);
+            dst[i + half] = from_f32<T>(a * sn + b * cs);
+        }
+        for (int i = rotary_dim + threadIdx.x; i < head_dim; i += blockDim.x) dst[i] = from_f32<T>(value(i));
+    } else {
+        for (int i = threadIdx.x; i < head_dim; i += blockDim.x) dst[i] = from_f32<T>(value(i));
+    }
+}
+
 }  // namespace
 
 extern "C" {
@@ -76,6 +126,34 @@ int infero_rope_cache(void* qkv, int dtype, int row_stride, const int* positions
             block_table, max_blocks, inv_freq, rotary_dim, (bf16*)k_cache, (bf16*)v_cache, page_size,
             n_heads, n_kv, head_dim, write_cache);
     return infero_check_launch("rope_cache");
+}
+
+
+// partial: splits arrays of [n_tokens, (n_heads + 2 n_kv) * head_dim] float, split_stride
+// elements apart; bias nullable.  q_out and the caches have type dtype.
+int infero_rope_cache_partials(const float* partial, int splits, long long split_stride, const void* bias,
+                               int bias_dtype, void* q_out, int q_stride, int dtype, const int* positions,
+                               const int* tok_entry, const int* block_table, int max_blocks,
+                               const float* inv_freq, int rotary_dim, void* k_cache, void* v_cache, int page_size,
+                               int n_tokens, int n_heads, int n_kv, int head_dim, int write_cache,
+                               cudaStream_t stream) {
+    if (n_tokens == 0) return 0;
+    INFERO_REQUIRE(rotary_dim >= 0 && rotary_dim % 2 == 0 && rotary_dim <= head_dim,
+                   "rope_cache: rotary_dim %d must be even and <= head_dim %d", rotary_dim, head_dim);
+    INFERO_REQUIRE(n_heads + 2 * n_kv <= 65535, "rope_cache: too many heads (%d)", n_heads + 2 * n_kv);
+    INFERO_REQUIRE(splits >= 1, "rope_cache: %d splits", splits);
+    dim3 grid(n_tokens, n_heads + 2 * n_kv);
+    const int threads = head_dim >= 128 ? 64 : 32;
+    const int width = (n_heads + 2 * n_kv) * head_dim;
+    if (dtype == INFERO_F32)
+        rope_cache_partials_kernel<float><<<grid, threads, 0, stream>>>(partial, splits, split_stride, width, bias,
+            bias_dtype, (float*)q_out, q_stride, positions, tok_entry, block_table, max_blocks, inv_freq, rotary_dim,
+            (float*)k_cache, (float*)v_cache, page_size, n_heads, n_kv, head_dim, write_cache);
+    else
+        rope_cache_partials_kernel<bf16><<<grid, threads, 0, stream>>>(partial, splits, split_stride, width, bias,
+            bias_dtype, (bf16*)q_out, q_stride, positions, tok_entry, block_table, max_blocks, inv_freq, rotary_dim,
+            (bf16*)k_cache, (bf16*)v_cache, page_size, n_heads, n_kv, head_dim, write_cache);
+    return infero_check_launch("rope_cache_partials");
 }
 
 }  // extern "C"

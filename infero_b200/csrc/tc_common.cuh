@@ -165,3 +165,8 @@ __host__ __device__ constexpr uint32_t idesc_bf16_f32(int m, int n) {
 }
 
 }  // namespace tc
+
+// Host side (tc_host.cu): a cached TMA descriptor for a [rows, cols] bf16 matrix with row
+// stride ld elements and boxes of box_rows x 64 elements, 128-byte swizzle.
+int infero_tensor_map_bf16(const void* ptr, int rows, int cols, int ld, int box_rows, CUtensorMap* out);
+int infero_tc_err_flag(int** out);

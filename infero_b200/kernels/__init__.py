@@ -90,10 +90,41 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out_x: torch.Tensor, sc
                                      c_int(T), c_int(d), c_int(table.shape[0]), c_float(scale), _stream()))
 
 
-def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+class Partials:
+    """A matrix product left as 32-bit partial sums: the value is sum_s data[s] (+ bias), s in
+    ascending order.  The few-token tensor-core kernel writes these; the kernel that consumes
+    the product (norm, activation, rotary + cache append) adds them up in its own pass."""
+
+    def __init__(self, data: torch.Tensor, bias: Optional[torch.Tensor] = None):
+        assert data.dim() == 3 and data.dtype == torch.float32 and data.is_contiguous()
+        self.data = data
+        self.bias = bias
+
+    @property
+    def shape(self):
+        return self.data.shape[1:]
+
+    @property
+    def splits(self) -> int:
+        return self.data.shape[0]
+
+    @property
+    def split_stride(self) -> int:
+        return self.data.shape[1] * self.data.shape[2]
+
+    def materialize(self, dtype: torch.dtype) -> torch.Tensor:
+        """The value as one tensor (for parts that have no fused kernel of their own)."""
+        from .tc_gemm import reduce_partials
+        out = torch.empty(tuple(self.shape), dtype=dtype, device=self.data.device)
+        reduce_partials(self.data, self.bias, out)
+        return out
+
+
+def add_rmsnorm(x: torch.Tensor, delta, weight: torch.Tensor, eps: float,
                 out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
-    """x += delta (if given; 32-bit), out = rmsnorm(x) * weight.  With ``rows`` only those
-    rows are normalised (out has len(rows) rows) and x is left as it is."""
+    """x += delta (if given; 32-bit), out = rmsnorm(x) * weight.  ``delta`` is a tensor or
+    ``Partials``.  With ``rows`` only those rows are normalised (out has len(rows) rows) and x
+    is left as it is."""
     d = x.shape[1]
     assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous()
     assert weight.numel() == d and out.shape[1] == d
@@ -102,9 +133,15 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
         assert n == x.shape[0]
     else:
         assert rows.numel() == n
-    if delta is not None:
+    splits, stride, dbias, data = 1, 0, None, delta
+    if isinstance(delta, Partials):
+        data, splits, stride, dbias = delta.data, delta.splits, delta.split_stride, delta.bias
+        assert tuple(delta.shape) == tuple(x.shape)
+    elif delta is not None:
         assert delta.shape == x.shape and delta.is_contiguous()
-    _check(lib().infero_add_rmsnorm(_ptr(x), _ptr(delta), c_int(_dt(delta) if delta is not None else F32),
+    _check(lib().infero_add_rmsnorm(_ptr(x), _ptr(data), c_int(_dt(data) if data is not None else F32),
+                                    c_int(splits), ctypes.c_longlong(stride), _ptr(dbias),
+                                    c_int(_dt(dbias) if dbias is not None else F32),
                                     _ptr(weight), c_int(_dt(weight)), c_float(eps), _ptr(out), c_int(_dt(out)),
                                     _ptr(None if rows is None else _i32(rows, "rows")), c_int(n), c_int(d),
                                     _stream()))
@@ -116,12 +153,19 @@ def residual_add(x: torch.Tensor, delta: torch.Tensor) -> None:
                                      c_int(x.shape[1]), _stream()))
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, j] = silu(gate_up[t, j]) * gate_up[t, ff + j]."""
+def swiglu(gate_up, out: torch.Tensor) -> None:
+    """out[t, j] = silu(g[t, j]) * g[t, ff + j] for g = gate_up (a tensor of out's type, or
+    ``Partials`` with a bf16 out)."""
     T, ff = out.shape
-    assert gate_up.shape == (T, 2 * ff) and gate_up.dtype == out.dtype
-    assert gate_up.is_contiguous() and out.is_contiguous()
-    _check(lib().infero_swiglu(_ptr(gate_up), _ptr(out), c_int(_dt(out)), c_int(T), c_int(ff), _stream()))
+    assert out.is_contiguous()
+    if isinstance(gate_up, Partials):
+        assert tuple(gate_up.shape) == (T, 2 * ff) and gate_up.bias is None and out.dtype == torch.bfloat16
+        _check(lib().infero_swiglu(_ptr(gate_up.data), c_int(gate_up.splits), ctypes.c_longlong(gate_up.split_stride),
+                                   _ptr(out), c_int(F32), c_int(1), c_int(T), c_int(ff), _stream()))
+        return
+    assert gate_up.shape == (T, 2 * ff) and gate_up.dtype == out.dtype and gate_up.is_contiguous()
+    _check(lib().infero_swiglu(_ptr(gate_up), c_int(1), ctypes.c_longlong(0), _ptr(out), c_int(_dt(out)), c_int(0),
+                               c_int(T), c_int(ff), _stream()))
 
 
 # ---- matrix products ------------------------------------------------------------------------
@@ -165,6 +209,24 @@ def rope_cache(qkv: torch.Tensor, positions: torch.Tensor, tok_entry: torch.Tens
                                    c_int(block_table.shape[1]), _ptr(inv_freq), c_int(rotary), _ptr(k_cache),
                                    _ptr(v_cache), c_int(page_size), c_int(T), c_int(n_heads), c_int(n_kv),
                                    c_int(head_dim), c_int(1 if write_cache else 0), _stream()))
+
+
+def rope_cache_partials(qkv: Partials, q_out: torch.Tensor, positions: torch.Tensor, tok_entry: torch.Tensor,
+                        block_table: torch.Tensor, inv_freq: torch.Tensor, k_cache: torch.Tensor,
+                        v_cache: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, page_size: int,
+                        write_cache: bool = True) -> None:
+    """The same from partial sums (+ bias): rotated q goes to q_out [T, H * D], k and v to their pages."""
+    T = q_out.shape[0]
+    assert tuple(qkv.shape) == (T, (n_heads + 2 * n_kv) * head_dim) and q_out.stride(1) == 1
+    assert q_out.shape[1] == n_heads * head_dim and k_cache.dtype == q_out.dtype == v_cache.dtype
+    assert k_cache.is_contiguous() and v_cache.is_contiguous() and inv_freq.dtype == torch.float32
+    _check(lib().infero_rope_cache_partials(
+        _ptr(qkv.data), c_int(qkv.splits), ctypes.c_longlong(qkv.split_stride), _ptr(qkv.bias),
+        c_int(_dt(qkv.bias) if qkv.bias is not None else F32), _ptr(q_out), c_int(q_out.stride(0)),
+        c_int(_dt(q_out)), _ptr(_i32(positions, "positions")), _ptr(_i32(tok_entry, "tok_entry")),
+        _ptr(_i32(block_table, "block_table")), c_int(block_table.shape[1]), _ptr(inv_freq),
+        c_int(2 * inv_freq.numel()), _ptr(k_cache), _ptr(v_cache), c_int(page_size), c_int(T), c_int(n_heads),
+        c_int(n_kv), c_int(head_dim), c_int(1 if write_cache else 0), _stream()))
 
 
 def attention_generic(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,

@@ -19,6 +19,7 @@ from . import KernelError, _check, _dt, _i32, _ptr, _stream, attention_generic, 
 PREFILL_ROWS = 64          # query rows per CTA of the prefill kernel
 DECODE_MIN_CHUNK = 64      # keys per split, at least
 TARGET_CTAS = 4 * 148      # decode CTAs wanted in flight
+MAX_SPLITS = 256           # the merge kernel keeps one weight per split in shared memory
 
 
 def mma_supported(head_dim: int, page_size: int) -> bool:
@@ -34,6 +35,9 @@ def plan_decode(n_tok: int, n_kv: int, group: int, max_visible: int) -> Tuple[in
     chunk = -(-max_visible // want)
     chunk = max(DECODE_MIN_CHUNK, -(-chunk // 16) * 16)
     splits = -(-max_visible // chunk)
+    if splits > MAX_SPLITS:
+        chunk = -(-(-(-max_visible // MAX_SPLITS)) // 16) * 16
+        splits = -(-max_visible // chunk)
     return chunk, splits
 
 
@@ -42,6 +46,15 @@ def decode(q, out, k_cache, v_cache, table, tok_entry, positions, tok_first: int
            n_splits: int) -> None:
     need = int(lib_scratch(n_tok, n_heads, head_dim, n_splits))
     scratch = torch.empty(need // 4, dtype=torch.float32, device=q.device)
+    if lib().infero_attn_decode_tma_supported(c_int(head_dim), c_int(page_size)) and k_cache.is_contiguous() \
+            and v_cache.is_contiguous():
+        _check(lib().infero_attn_decode_tma(
+            _ptr(q), c_int(q.stride(0)), _ptr(out), c_int(out.stride(0)), _ptr(k_cache), _ptr(v_cache),
+            c_int(k_cache.shape[0]), _ptr(_i32(table, "block_table")), c_int(table.shape[1]),
+            _ptr(_i32(tok_entry, "tok_entry")), _ptr(_i32(positions, "positions")), c_int(tok_first), c_int(n_tok),
+            c_int(n_heads), c_int(n_kv), c_int(head_dim), c_int(page_size), c_int(window or 0), c_float(scale),
+            c_int(chunk), c_int(n_splits), _ptr(scratch), _stream()))
+        return
     _check(lib().infero_attn_decode(_ptr(q), c_int(q.stride(0)), _ptr(out), c_int(out.stride(0)), _ptr(k_cache),
                                     _ptr(v_cache), _ptr(_i32(table, "block_table")), c_int(table.shape[1]),
                                     _ptr(_i32(tok_entry, "tok_entry")), _ptr(_i32(positions, "positions")),

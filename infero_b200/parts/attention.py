@@ -73,13 +73,19 @@ class GqaAttention(Mixer):
         s = self.spec
         T = h.shape[0]
         H, Hkv, D = s.num_heads, s.num_kv_heads, s.head_dim
-        qkv = self.qkv.forward(h)                              # [T, (H + 2 Hkv) D]
+        qkv = self.qkv.forward(h, defer=True)                  # [T, (H + 2 Hkv) D]
         kv = ctx.kv_cache(slot.cache)                          # keys, values, group
         table = ctx.block_table(kv.group)
         inv = self.rope.inv_freq(h.device) if self.rope is not None else ctx.zero_inv_freq(h.device)
-        K.rope_cache(qkv, ctx.positions, ctx.tok_entry, table, inv, kv.k, kv.v, H, Hkv, D,
-                     kv.page_size, write_cache=slot.write_cache)
+        if isinstance(qkv, K.Partials):
+            q = torch.empty((T, H * D), dtype=h.dtype, device=h.device)
+            K.rope_cache_partials(qkv, q, ctx.positions, ctx.tok_entry, table, inv, kv.k, kv.v, H, Hkv, D,
+                                  kv.page_size, write_cache=slot.write_cache)
+        else:
+            q = qkv
+            K.rope_cache(qkv, ctx.positions, ctx.tok_entry, table, inv, kv.k, kv.v, H, Hkv, D,
+                         kv.page_size, write_cache=slot.write_cache)
         attn = torch.empty((T, H * D), dtype=h.dtype, device=h.device)
         from ..kernels import attention as A
-        A.paged_attention(ctx, qkv, attn, kv, table, H, Hkv, D, s.window, s.scale)
-        return self.out.forward(attn)
+        A.paged_attention(ctx, q, attn, kv, table, H, Hkv, D, s.window, s.scale)
+        return self.out.forward(attn, defer=True)

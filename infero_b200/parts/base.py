@@ -7,7 +7,9 @@ No part knows which model it is in.  A part defined outside this package plugs i
 
     Norm.forward(ctx, x, delta, rows=None) -> h      x float32 residual stream [T, d];
                                                      delta (or None) is added to x first
-    Mixer.forward(ctx, h, slot) -> delta             h [T, d] in ctx.act_dtype
+    Mixer.forward(ctx, h, slot) -> delta             h [T, d] in ctx.act_dtype; delta is a tensor or
+                                                     kernels.Partials (a product left as split-K sums;
+                                                     .materialize(dtype) gives the tensor)
     FeedForward.forward(ctx, h) -> delta
     Block.forward(ctx, x, delta, slot) -> delta      x updated in place; the returned delta
                                                      is added by whoever normalises next

@@ -26,8 +26,15 @@ class Linear:
         self.out_features, self.in_features = weight.shape
 
     def forward(self, a: torch.Tensor, out: Optional[torch.Tensor] = None,
-                out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+                out_dtype: Optional[torch.dtype] = None, defer: bool = False):
+        """``defer``: the caller's next kernel can add up partial sums itself, so for few rows on
+        the tensor-core path return ``Partials`` (32-bit split-K products + bias) instead of a
+        finished tensor."""
         M = a.shape[0]
+        if defer and out is None and 0 < M <= 256 and a.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16:
+            from ..kernels import tc_gemm
+            if tc_gemm.supported(a, self.weight):
+                return K.Partials(tc_gemm.partials(a, self.weight), self.bias)
         if out is None:
             out = torch.empty((M, self.out_features), dtype=out_dtype or a.dtype, device=a.device)
         if M == 0:

@@ -40,7 +40,7 @@ class SwiGluMlp(FeedForward):
 
     def forward(self, ctx, h):
         T = h.shape[0]
-        gu = self.gate_up.forward(h)
-        act = torch.empty((T, self.spec.intermediate), dtype=gu.dtype, device=h.device)
+        gu = self.gate_up.forward(h, defer=True)
+        act = torch.empty((T, self.spec.intermediate), dtype=h.dtype, device=h.device)
         K.swiglu(gu, act)
-        return self.down.forward(act)
+        return self.down.forward(act, defer=True)

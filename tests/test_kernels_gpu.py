@@ -289,6 +289,95 @@ def test_attention_over_pages(H, Hkv, D, dt, window):
     assert worst <= (3e-6 if dt == torch.float32 else 1.5e-2), f"{worst:.3e}"
 
 
+@pytest.mark.parametrize("H,Hkv,D", [(28, 4, 128), (14, 2, 64), (20, 1, 128), (3, 3, 64)])
+@pytest.mark.parametrize("window", [None, 100])
+@pytest.mark.parametrize("P", [16, 64])
+def test_decode_attention_fed_by_tma(H, Hkv, D, window, P):
+    """Single-token requests of very different lengths (one key, a page edge, hundreds of keys)
+    on scattered pages; one far key per request is made to dominate head 0."""
+    from infero_b200.kernels import attention as A
+    assert A.lib().infero_attn_decode_tma_supported(D, P)
+    lengths = [1, 16, 17, 64, 333, 700, 129]
+    dt = torch.bfloat16
+    n = len(lengths)
+    pages = sum(-(-L // P) for L in lengths) + 5
+    rng = np.random.default_rng(1)
+    perm = rng.permutation(pages)
+    table = torch.full((n, max(-(-L // P) for L in lengths) + 2), -1, dtype=torch.int32)
+    kc = _rand((pages, Hkv, P, D), dt, 50)               # unused rows hold finite junk, as reused pages do
+    vc = _rand((pages, Hkv, P, D), dt, 51)
+    Ks, Vs = [], []
+    nxt = 0
+    for e, L in enumerate(lengths):
+        k, v = _rand((L, Hkv, D), dt, 60 + e), _rand((L, Hkv, D), dt, 80 + e)
+        Ks.append(k); Vs.append(v)
+        for b in range(-(-L // P)):
+            table[e, b] = int(perm[nxt]); nxt += 1
+            m = min(P, L - b * P)
+            kc[table[e, b], :, :m] = k[b * P:b * P + m].transpose(0, 1)
+            vc[table[e, b], :, :m] = v[b * P:b * P + m].transpose(0, 1)
+    scale = 1.0 / math.sqrt(D)
+    q = _rand((n, H * D), dt, 7)
+    q3 = q.view(n, H, D)
+    for e, L in enumerate(lengths):
+        j = max(0, L - 90) if window else L // 3          # inside the window when there is one
+        kk = Ks[e][j, 0].float()
+        q3[e, 0] = (kk * (6.0 / scale / float(kk @ kk))).to(dt)
+    positions = torch.tensor([L - 1 for L in lengths], dtype=torch.int32, device=DEV)
+    entry = torch.arange(n, dtype=torch.int32, device=DEV)
+    for bound in (None, 2048):                            # the plan of a captured step covers more keys than there are
+        out = torch.zeros((n, H * D), dtype=dt, device=DEV)
+        A.attention_any(q, out, kc, vc, table.to(DEV), entry, positions, H, Hkv, D, P, window, scale,
+                        q_lens=[1] * n, pos0=[L - 1 for L in lengths], kv_bound=bound)
+        worst = 0.0
+        for e, L in enumerate(lengths):
+            ref = _attention_ref(q3[e].double().cpu(), Ks[e].double().cpu(), Vs[e].double().cpu(), scale, window)
+            worst = max(worst, float((out[e].double().cpu().view(H, D) - ref).abs().max() / ref.abs().max()))
+        assert worst <= 1.5e-2, f"bound {bound}: {worst:.3e}"
+    from infero_b200.kernels import tc_gemm
+    assert tc_gemm.error_flag() == 0
+
+
+def test_consumers_add_up_partial_products():
+    """The fused consumers of split-K partial sums against the plain sum."""
+    from infero_b200 import kernels as Kn
+    S, T, d, ff = 5, 6, 200, 300
+    part = _rand((S, T, d), torch.float32, 1)
+    bias = _rand((d,), torch.bfloat16, 2)
+    w = _rand((d,), torch.bfloat16, 3) + 1
+    x = _rand((T, d), torch.float32, 4)
+    v = x.double() + part.double().sum(0) + bias.double()
+    ref = v * torch.rsqrt((v * v).mean(-1, keepdim=True) + 1e-5) * w.double()
+    out = torch.empty((T, d), dtype=torch.bfloat16, device=DEV)
+    Kn.add_rmsnorm(x, Kn.Partials(part, bias), w, 1e-5, out)
+    assert float((x.double() - v).abs().max()) <= 1e-5
+    assert float((out.double() - ref).abs().max() / ref.abs().max()) <= 5e-3
+    gu = _rand((S, T, 2 * ff), torch.float32, 5)
+    act = torch.empty((T, ff), dtype=torch.bfloat16, device=DEV)
+    Kn.swiglu(Kn.Partials(gu), act)
+    g, u = gu.double().sum(0)[:, :ff], gu.double().sum(0)[:, ff:]
+    ref = g / (1 + torch.exp(-g)) * u
+    assert float((act.double() - ref).abs().max() / ref.abs().max()) <= 5e-3
+    # rotary + cache append from partial sums equals the two-step way
+    H, Hkv, D, P, Tn = 6, 2, 48, 16, 5
+    width = (H + 2 * Hkv) * D
+    part = _rand((3, Tn, width), torch.float32, 6)
+    bias = _rand((width,), torch.bfloat16, 7)
+    positions = torch.tensor([3, 4, 40, 0, 17], dtype=torch.int32, device=DEV)
+    entry = torch.tensor([0, 0, 1, 2, 1], dtype=torch.int32, device=DEV)
+    table = torch.tensor([[2, -1, -1], [5, 1, 7], [3, -1, -1]], dtype=torch.int32, device=DEV)
+    inv = torch.from_numpy((10000.0 ** (-2.0 * np.arange(D // 2) / D)).astype(np.float32)).to(DEV)
+    kc1 = torch.zeros((8, Hkv, P, D), dtype=torch.float32, device=DEV); vc1 = torch.zeros_like(kc1)
+    kc2 = torch.zeros_like(kc1); vc2 = torch.zeros_like(kc1)
+    q1 = torch.empty((Tn, H * D), dtype=torch.float32, device=DEV)
+    Kn.rope_cache_partials(Kn.Partials(part, bias), q1, positions, entry, table, inv, kc1, vc1, H, Hkv, D, P)
+    qkv = (part.sum(0) + bias.float()).contiguous()
+    Kn.rope_cache(qkv, positions, entry, table, inv, kc2, vc2, H, Hkv, D, P)
+    assert float((q1 - qkv[:, :H * D]).abs().max()) <= 2e-5
+    assert float((kc1 - kc2).abs().max()) <= 2e-5 and float((vc1 - vc2).abs().max()) <= 2e-5
+    assert int((kc1 != 0).any(-1).sum()) == Tn * Hkv
+
+
 # ---- sampling ------------------------------------------------------------------------------------
 def test_argmax_lowest_index_wins_ties():
     from infero_b200 import kernels as Kn

@@ -24,6 +24,9 @@ def _rand(shape, dtype, seed, scale=1.0):
 
 
 def _rel(got, ref):
+    from infero_b200.kernels import Partials
+    if isinstance(got, Partials):                       # a product left as split-K partial sums
+        got = got.materialize(torch.float32)
     return float((got.double().cpu() - ref).abs().max() / ref.abs().max())
 
 
@@ -120,6 +123,8 @@ def test_attention_mixer_alone(dt, window):
     ctx, _ = runner._build_context(ents, rcs)
     h = torch.cat([h_all["a"], h_all["b"][21:]]).contiguous()
     out = mixer.forward(ctx, h, spec.schedule[0])
+    from infero_b200.kernels import Partials
+    full = out.materialize(torch.float32) if isinstance(out, Partials) else out
     p = "model.layers.0.self_attn."
     worst = 0.0
     row = 0
@@ -134,7 +139,7 @@ def test_attention_mixer_alone(dt, window):
         k = P.rope_neox(k.view(T, m.num_kv_heads, m.head_dim), pos, m.position.theta, m.position.rotary_dim)
         a = P.attention(q, k, v.view(T, m.num_kv_heads, m.head_dim), m.scale, window)
         ref = a.reshape(T, -1) @ w[p + "o_proj.weight"].T
-        worst = max(worst, _rel(out[row:row + new], ref[old:]))
+        worst = max(worst, _rel(full[row:row + new], ref[old:]))
         row += new
     assert worst <= TOL[dt], f"{worst:.3e}"
 
