@@ -234,9 +234,9 @@ def time_e2e(model, cfg_json, batch, steps, warmup, clocks, page_size):
     for _ in range(batch):
         eng.add_request(random_prompt(rng, vocab, start_len), pure_argmax,
                         max_new_tokens=CONTEXT, ignore_eos=True)
-    got = 0
-    while got < batch:                       # prompts, in portions, until every request has its first token
-        got += sum(1 for ev in eng.step() if ev.token is not None)
+    started = set()
+    while len(started) < batch:              # prompts, in portions, until every request has its first token
+        started.update(ev.rid for ev in eng.step() if ev.token is not None)
     for _ in range(warmup):
         eng.step()
     torch.cuda.synchronize()

@@ -57,6 +57,16 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + TD_WARPS * STAGES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        tc::prefetch_tensormap(&map_k);
+        tc::prefetch_tensormap(&map_v);
+        for (int i = 0; i < TD_WARPS * STAGES; ++i) tc::mbar_init(&bars[i], 1);
+        *abort_flag = 0;
+        tc::fence_barrier_init();
+        tc::fence_proxy_async();
+    }
+    pdl_wait();                                        // q and this step's keys come from the kernel before
     const int split = blockIdx.x;
     const int group = n_heads / n_kv;
     const int gtiles = (group + 15) / 16;
@@ -80,14 +90,6 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             pml[(size_t)r * n_splits * 2 + 1] = 0.f;
         }
         return;
-    }
-    if (threadIdx.x == 0) {
-        tc::prefetch_tensormap(&map_k);
-        tc::prefetch_tensormap(&map_v);
-        for (int i = 0; i < TD_WARPS * STAGES; ++i) tc::mbar_init(&bars[i], 1);
-        *abort_flag = 0;
-        tc::fence_barrier_init();
-        tc::fence_proxy_async();
     }
     __syncthreads();
 
@@ -200,6 +202,8 @@ attn_combine_kernel(const float* __restrict__ partial_o, const float* __restrict
                     bf16* __restrict__ out, int out_stride, int tok_first, int n_tok, int n_heads,
                     int n_splits, int head_dim) {
     __shared__ float wsm[4][COMBINE_MAX_SPLITS];
+    pdl_launch_dependents();
+    pdl_wait();
     const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int warp = blockIdx.x * 4 + wib;
     if (warp >= n_tok * n_heads) return;
@@ -249,9 +253,9 @@ int launch_tma(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, int 
     }
     const int group = n_heads / n_kv;
     dim3 grid(n_splits, n_kv * ((group + 15) / 16), n_tok);
-    kern<<<grid, TD_THREADS, Plan::TOTAL, stream>>>(mk, mv, (const bf16*)q, q_stride, block_table, max_blocks, tok_entry,
-                                                    positions, tok_first, n_heads, n_kv, page_size, window, scale_log2,
-                                                    chunk, n_splits, po, pml, err);
+    launch_pdl(kern, grid, dim3(TD_THREADS), Plan::TOTAL, stream, mk, mv, (const bf16*)q, q_stride, block_table,
+               max_blocks, tok_entry, positions, tok_first, n_heads, n_kv, page_size, window, scale_log2, chunk,
+               n_splits, po, pml, err);
     return infero_check_launch("attn_decode_tma");
 }
 
@@ -298,8 +302,8 @@ int infero_attn_decode_tma(const void* q, int q_stride, void* out, int out_strid
                             n_heads, n_kv, page_size, window, sl2, chunk, n_splits, po, pml, err, stream);
     if (rc) return rc;
     const int warps = n_tok * n_heads;
-    attn_combine_kernel<<<(warps + 3) / 4, 128, 0, stream>>>(po, pml, (bf16*)out, out_stride, tok_first, n_tok,
-                                                             n_heads, n_splits, head_dim);
+    launch_pdl(attn_combine_kernel, dim3((warps + 3) / 4), dim3(128), 0, stream, (const float*)po, (const float*)pml,
+               (bf16*)out, out_stride, tok_first, n_tok, n_heads, n_splits, head_dim);
     return infero_check_launch("attn_combine");
 }
 

@@ -37,6 +37,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
                     const int* __restrict__ entry_q_len, const int* __restrict__ entry_pos0, int n_entries,
                     int first_entry, int n_heads, int n_kv, int page_size, int window, float scale_log2) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
+    pdl_launch_dependents();
+    pdl_wait();
     bf16* tiles = reinterpret_cast<bf16*>(smem_raw);          // [2 stages][K | V][64 rows][D]
     constexpr int TILE = tile_elems<D>(PF_KEYS);
 
@@ -135,6 +137,8 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
                    int n_heads, int n_kv, int page_size, int window, float scale_log2, int chunk,
                    int n_splits, float* __restrict__ partial_o, float* __restrict__ partial_ml) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr int TILE = tile_elems<D>(KEYS16);                       // elements of one 16-key slice
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
     const int split = blockIdx.x;
@@ -244,6 +248,8 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
 __global__ void attn_combine_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
                                     bf16* __restrict__ out, int out_stride, int tok_first, int n_tok, int n_heads,
                                     int n_splits, int head_dim) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= n_tok * n_heads) return;
     const int ti = warp / n_heads, h = warp % n_heads;
@@ -281,10 +287,9 @@ int launch_prefill(const void* q, int q_stride, void* out, int out_stride, const
         configured = true;
     }
     dim3 grid(n_tiles, n_heads);
-    kern<<<grid, PF_THREADS, smem, stream>>>((const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_cache,
-                                             (const bf16*)v_cache, block_table, max_blocks, entry_q_start, entry_q_len,
-                                             entry_pos0, n_entries, first_entry, n_heads, n_kv, page_size, window,
-                                             scale_log2);
+    launch_pdl(kern, grid, dim3(PF_THREADS), smem, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride,
+               (const bf16*)k_cache, (const bf16*)v_cache, block_table, max_blocks, entry_q_start, entry_q_len,
+               entry_pos0, n_entries, first_entry, n_heads, n_kv, page_size, window, scale_log2);
     return infero_check_launch("attn_prefill");
 }
 

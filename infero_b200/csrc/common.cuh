@@ -47,6 +47,34 @@ __device__ __forceinline__ float block_sum(float v, float* smem32) {
     return r;
 }
 
+// ---- programmatic dependent launch --------------------------------------------------------
+// A kernel launched through launch_pdl may start while the kernel before it in the stream is
+// still running.  Such a kernel calls pdl_launch_dependents() first (its successor may then be
+// scheduled as soon as every block of this grid has started) and pdl_wait() before it reads
+// anything an earlier kernel wrote or writes anything at all; what lies before pdl_wait()
+// (barrier set-up, prefetch of weights) overlaps the tail of the predecessor.  Launched the
+// ordinary way, both calls do nothing.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+int infero_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = infero_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ---- error reporting -------------------------------------------------------------------
 // Launchers return 0 on success.  On failure they return non-zero and leave a message
 // that infero_last_error() hands to the caller.

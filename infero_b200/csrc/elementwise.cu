@@ -14,6 +14,8 @@ namespace {
 template <typename TE>
 __global__ void embed_gather_kernel(const TE* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ x, int d, int vocab, float scale) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     int id = ids[t];
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);   // ids are validated on the host
@@ -61,6 +63,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
                                    const void* __restrict__ w, int wdtype, float eps,
                                    TO* __restrict__ out, const int* __restrict__ rows, int d) {
     __shared__ float red[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
     float* xr = x + (size_t)src * d;
@@ -73,6 +77,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
             float v[4];
             load4(xr + i, v);
             if (dr) {
+#pragma unroll 4
                 for (int s = 0; s < splits; ++s) {
                     float t[4];
                     load4(dr + (size_t)s * split_stride + i, t);
@@ -122,6 +127,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
 template <typename T, int VEC>
 __global__ void swiglu_kernel(const T* __restrict__ gu, int splits, long long split_stride, T* __restrict__ out_same,
                               bf16* __restrict__ out_bf16, int ff, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
     size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     if (i >= total) return;
     size_t t = i / ff;
@@ -130,6 +137,7 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, int splits, long long sp
     float g[VEC], u[VEC], h[VEC];
 #pragma unroll
     for (int k = 0; k < VEC; ++k) g[k] = u[k] = 0.f;
+#pragma unroll 4
     for (int s = 0; s < splits; ++s) {
         const T* rs = row + (size_t)s * split_stride;
         if (VEC == 4) {
@@ -157,6 +165,8 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, int splits, long long sp
 // x[t,:] += delta[t,:]   (used when no norm follows)
 template <typename TD>
 __global__ void residual_add_kernel(float* __restrict__ x, const TD* __restrict__ delta, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < total) x[i] += to_f32(delta[i]);
 }
@@ -171,9 +181,9 @@ int infero_embed_gather(const void* table, int table_dtype, const int* ids, floa
     INFERO_REQUIRE(d > 0 && vocab > 0, "embed_gather: bad sizes d=%d vocab=%d", d, vocab);
     const int threads = d >= 256 ? 256 : 64;
     if (table_dtype == INFERO_F32)
-        embed_gather_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)table, ids, x, d, vocab, scale);
+        launch_pdl(embed_gather_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)table, ids, x, d, vocab, scale);
     else
-        embed_gather_kernel<bf16><<<n_tokens, threads, 0, stream>>>((const bf16*)table, ids, x, d, vocab, scale);
+        launch_pdl(embed_gather_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, (const bf16*)table, ids, x, d, vocab, scale);
     return infero_check_launch("embed_gather");
 }
 
@@ -200,14 +210,14 @@ int infero_add_rmsnorm(float* x, const void* delta, int delta_dtype, int delta_s
             auto k = add_rmsnorm_kernel<TD, TO, 4>;                                             \
             if (smem > 48 * 1024)                                                               \
                 cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-            k<<<n_rows, threads, smem, stream>>>(x, (const TD*)delta, delta_splits, split_stride, dbias,  \
-                                                 dbias_dtype, w, w_dtype, eps, (TO*)out, rows, d);       \
+            launch_pdl(k, dim3(n_rows), dim3(threads), smem, stream, x, (const TD*)delta, delta_splits,   \
+                       split_stride, dbias, dbias_dtype, w, w_dtype, eps, (TO*)out, rows, d);            \
         } else {                                                                                \
             auto k = add_rmsnorm_kernel<TD, TO, 1>;                                             \
             if (smem > 48 * 1024)                                                               \
                 cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-            k<<<n_rows, threads, smem, stream>>>(x, (const TD*)delta, delta_splits, split_stride, dbias,  \
-                                                 dbias_dtype, w, w_dtype, eps, (TO*)out, rows, d);       \
+            launch_pdl(k, dim3(n_rows), dim3(threads), smem, stream, x, (const TD*)delta, delta_splits,   \
+                       split_stride, dbias, dbias_dtype, w, w_dtype, eps, (TO*)out, rows, d);            \
         }                                                                                       \
     } while (0)
     if (delta_dtype == INFERO_F32 && out_dtype == INFERO_F32) LAUNCH(float, float);
@@ -232,11 +242,11 @@ int infero_swiglu(const void* gate_up, int splits, long long split_stride, void*
     const unsigned blocks = (unsigned)((work + threads - 1) / threads);
     bf16* ob = out_bf16 ? (bf16*)out : nullptr;
     if (dtype == INFERO_F32) {
-        if (vec) swiglu_kernel<float, 4><<<blocks, threads, 0, stream>>>((const float*)gate_up, splits, split_stride, (float*)out, ob, ff, total);
-        else swiglu_kernel<float, 1><<<blocks, threads, 0, stream>>>((const float*)gate_up, splits, split_stride, (float*)out, ob, ff, total);
+        if (vec) launch_pdl(swiglu_kernel<float, 4>, dim3(blocks), dim3(threads), 0, stream, (const float*)gate_up, splits, split_stride, (float*)out, ob, ff, total);
+        else launch_pdl(swiglu_kernel<float, 1>, dim3(blocks), dim3(threads), 0, stream, (const float*)gate_up, splits, split_stride, (float*)out, ob, ff, total);
     } else {
-        if (vec) swiglu_kernel<bf16, 4><<<blocks, threads, 0, stream>>>((const bf16*)gate_up, splits, split_stride, (bf16*)out, nullptr, ff, total);
-        else swiglu_kernel<bf16, 1><<<blocks, threads, 0, stream>>>((const bf16*)gate_up, splits, split_stride, (bf16*)out, nullptr, ff, total);
+        if (vec) launch_pdl(swiglu_kernel<bf16, 4>, dim3(blocks), dim3(threads), 0, stream, (const bf16*)gate_up, splits, split_stride, (bf16*)out, nullptr, ff, total);
+        else launch_pdl(swiglu_kernel<bf16, 1>, dim3(blocks), dim3(threads), 0, stream, (const bf16*)gate_up, splits, split_stride, (bf16*)out, nullptr, ff, total);
     }
     return infero_check_launch("swiglu");
 }
@@ -246,9 +256,9 @@ int infero_residual_add(float* x, const void* delta, int delta_dtype, int n_toke
     if (total == 0) return 0;
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (delta_dtype == INFERO_F32)
-        residual_add_kernel<float><<<blocks, 256, 0, stream>>>(x, (const float*)delta, total);
+        launch_pdl(residual_add_kernel<float>, dim3(blocks), dim3(256), 0, stream, x, (const float*)delta, total);
     else
-        residual_add_kernel<bf16><<<blocks, 256, 0, stream>>>(x, (const bf16*)delta, total);
+        launch_pdl(residual_add_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, x, (const bf16*)delta, total);
     return infero_check_launch("residual_add");
 }
 

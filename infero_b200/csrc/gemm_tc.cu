@@ -98,6 +98,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* never_flag = abort_flag + 1;           // stays 0: for waits that must not be cut short
 
+    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int a0 = blockIdx.x * TILE_A, b0 = blockIdx.y * BN;
     const int total_kt = (K + TILE_K - 1) / TILE_K;
@@ -136,7 +137,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint64_t pol_b = policy_evict_last();
             int issued = 0;
             bool ok = true;
-            for (int i = 0; i < n_kt; ++i) {
+            // The weights do not depend on the kernel before this one: their first tiles are on
+            // their way before that kernel has finished (programmatic dependent launch); the
+            // activations follow once it has.  The ring is empty, so these stages need no wait.
+            const int pre = n_kt < STAGES ? n_kt : STAGES;
+            for (int i = 0; i < pre; ++i) {
+                uint8_t* sa = smem + i * Plan::STAGE_BYTES;
+                mbar_expect_tx(&full_bar[i], Plan::STAGE_BYTES);
+                const int kx = (kt_begin + i) * TILE_K;
+                if (a_evict_first) tma_load_2d_hint(sa, &map_a, kx, a0, &full_bar[i], pol_a);
+                else tma_load_2d(sa + A_STAGE_BYTES, &map_b, kx, b0, &full_bar[i]);
+            }
+            pdl_wait();
+            for (int i = 0; i < pre; ++i) {
+                uint8_t* sa = smem + i * Plan::STAGE_BYTES;
+                const int kx = (kt_begin + i) * TILE_K;
+                if (a_evict_first) tma_load_2d_hint(sa + A_STAGE_BYTES, &map_b, kx, b0, &full_bar[i], pol_b);
+                else tma_load_2d(sa, &map_a, kx, a0, &full_bar[i]);
+                issued = i + 1;
+            }
+            for (int i = pre; i < n_kt; ++i) {
                 const int s = i % STAGES;
                 const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
                 if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) { ok = false; break; }
@@ -255,6 +275,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 template <typename OutT>
 __global__ void reduce_partials_kernel(const float* __restrict__ partial, int splits, const void* __restrict__ bias,
                                        int bias_dtype, OutT* __restrict__ out, int M, int N, long long ldc) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t total = (size_t)M * N;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const int t = (int)(i / N), n = (int)(i - (size_t)t * N);
@@ -288,8 +310,8 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, const void* 
         configured = true;
     }
     dim3 grid((RA + TILE_A - 1) / TILE_A, (RB + BN - 1) / BN, splits);
-    kern<<<grid, GEMM_THREADS, Plan::TOTAL, stream>>>(ma, mb, (OutT*)out, bias, bias_dtype, RA, RB, K,
-                                                     ktiles_per_split, ldc, a_evict_first, err);
+    launch_pdl(kern, grid, dim3(GEMM_THREADS), Plan::TOTAL, stream, ma, mb, (OutT*)out, bias, bias_dtype, RA, RB, K,
+               ktiles_per_split, ldc, a_evict_first, err);
     return infero_check_launch("gemm_tc");
 }
 
@@ -358,9 +380,9 @@ int infero_reduce_partials(const float* partial, int splits, const void* bias, i
     const size_t total = (size_t)M * N;
     const unsigned blocks = (unsigned)((total + 255) / 256 > 4096 ? 4096 : (total + 255) / 256);
     if (out_dtype == INFERO_F32)
-        reduce_partials_kernel<float><<<blocks, 256, 0, stream>>>(partial, splits, bias, bias_dtype, (float*)out, M, N, ldc);
+        launch_pdl(reduce_partials_kernel<float>, dim3(blocks), dim3(256), 0, stream, partial, splits, bias, bias_dtype, (float*)out, M, N, ldc);
     else
-        reduce_partials_kernel<bf16><<<blocks, 256, 0, stream>>>(partial, splits, bias, bias_dtype, (bf16*)out, M, N, ldc);
+        launch_pdl(reduce_partials_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, partial, splits, bias, bias_dtype, (bf16*)out, M, N, ldc);
     return infero_check_launch("reduce_partials");
 }
 

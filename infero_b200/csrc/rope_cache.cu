@@ -21,6 +21,8 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int row_stride, const int
                                   int max_blocks, const float* __restrict__ inv_freq, int rotary_dim,
                                   T* __restrict__ k_cache, T* __restrict__ v_cache, int page_size,
                                   int n_heads, int n_kv, int head_dim, int write_cache) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int h = blockIdx.y;                 // [0,n_heads): q   [n_heads, +n_kv): k   then v
     const int pos = positions[t];
@@ -64,6 +66,8 @@ __global__ void rope_cache_partials_kernel(const float* __restrict__ partial, in
                                            int max_blocks, const float* __restrict__ inv_freq, int rotary_dim,
                                            T* __restrict__ k_cache, T* __restrict__ v_cache, int page_size,
                                            int n_heads, int n_kv, int head_dim, int write_cache) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int h = blockIdx.y;
     const int pos = positions[t];
@@ -74,6 +78,7 @@ __global__ void rope_cache_partials_kernel(const float* __restrict__ partial, in
     const float* src = partial + (size_t)t * row_width + col0;
     auto value = [&](int i) {
         float v = 0.f;
+#pragma unroll 4
         for (int s = 0; s < splits; ++s) v += src[(size_t)s * split_stride + i];
         if (bias) v += load_any(bias, bias_dtype, col0 + i);
         return v;
@@ -118,11 +123,11 @@ int infero_rope_cache(void* qkv, int dtype, int row_stride, const int* positions
     dim3 grid(n_tokens, n_heads + 2 * n_kv);
     const int threads = head_dim >= 128 ? 64 : 32;
     if (dtype == INFERO_F32)
-        rope_cache_kernel<float><<<grid, threads, 0, stream>>>((float*)qkv, row_stride, positions, tok_entry,
+        launch_pdl(rope_cache_kernel<float>, grid, dim3(threads), 0, stream, (float*)qkv, row_stride, positions, tok_entry,
             block_table, max_blocks, inv_freq, rotary_dim, (float*)k_cache, (float*)v_cache, page_size,
             n_heads, n_kv, head_dim, write_cache);
     else
-        rope_cache_kernel<bf16><<<grid, threads, 0, stream>>>((bf16*)qkv, row_stride, positions, tok_entry,
+        launch_pdl(rope_cache_kernel<bf16>, grid, dim3(threads), 0, stream, (bf16*)qkv, row_stride, positions, tok_entry,
             block_table, max_blocks, inv_freq, rotary_dim, (bf16*)k_cache, (bf16*)v_cache, page_size,
             n_heads, n_kv, head_dim, write_cache);
     return infero_check_launch("rope_cache");
@@ -146,11 +151,11 @@ int infero_rope_cache_partials(const float* partial, int splits, long long split
     const int threads = head_dim >= 128 ? 64 : 32;
     const int width = (n_heads + 2 * n_kv) * head_dim;
     if (dtype == INFERO_F32)
-        rope_cache_partials_kernel<float><<<grid, threads, 0, stream>>>(partial, splits, split_stride, width, bias,
+        launch_pdl(rope_cache_partials_kernel<float>, grid, dim3(threads), 0, stream, partial, splits, split_stride, width, bias,
             bias_dtype, (float*)q_out, q_stride, positions, tok_entry, block_table, max_blocks, inv_freq, rotary_dim,
             (float*)k_cache, (float*)v_cache, page_size, n_heads, n_kv, head_dim, write_cache);
     else
-        rope_cache_partials_kernel<bf16><<<grid, threads, 0, stream>>>(partial, splits, split_stride, width, bias,
+        launch_pdl(rope_cache_partials_kernel<bf16>, grid, dim3(threads), 0, stream, partial, splits, split_stride, width, bias,
             bias_dtype, (bf16*)q_out, q_stride, positions, tok_entry, block_table, max_blocks, inv_freq, rotary_dim,
             (bf16*)k_cache, (bf16*)v_cache, page_size, n_heads, n_kv, head_dim, write_cache);
     return infero_check_launch("rope_cache_partials");

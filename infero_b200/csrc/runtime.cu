@@ -2,11 +2,24 @@
 #include "common.cuh"
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 
 #include <atomic>
 
 static thread_local char g_error[1024] = {0};
 static std::atomic<long long> g_launches{0};
+static std::atomic<int> g_pdl{-1};
+
+// Programmatic dependent launch is on unless INFERO_PDL=0 (or infero_set_pdl(0)).
+int infero_pdl_enabled() {
+    int v = g_pdl.load(std::memory_order_relaxed);
+    if (v < 0) {
+        const char* e = getenv("INFERO_PDL");
+        v = (e && e[0] == '0') ? 0 : 1;
+        g_pdl.store(v, std::memory_order_relaxed);
+    }
+    return v;
+}
 
 void infero_set_error(const char* fmt, ...) {
     va_list ap;
@@ -35,6 +48,8 @@ int infero_abi_version() { return 1; }
 
 // Kernels launched by this library since it was loaded (one per successful or failed launch
 // check; a launch recorded into a CUDA graph counts once, at capture).
+void infero_set_pdl(int on) { g_pdl.store(on ? 1 : 0, std::memory_order_relaxed); }
+
 long long infero_launch_count() { return g_launches.load(std::memory_order_relaxed); }
 
 int infero_device_info(int device, int* sm_count, int* cc_major, int* cc_minor, int* smem_optin) {

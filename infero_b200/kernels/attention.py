@@ -18,7 +18,7 @@ from . import KernelError, _check, _dt, _i32, _ptr, _stream, attention_generic, 
 
 PREFILL_ROWS = 64          # query rows per CTA of the prefill kernel
 DECODE_MIN_CHUNK = 64      # keys per split, at least
-TARGET_CTAS = 4 * 148      # decode CTAs wanted in flight
+TARGET_CTAS = 2 * 148      # decode CTAs wanted in flight: two resident per SM
 MAX_SPLITS = 256           # the merge kernel keeps one weight per split in shared memory
 
 
