@@ -123,7 +123,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
     }
 }
 
-// out[t, j] = silu(g) * u with g = sum_s gu[s][t, j], u = sum_s gu[s][t, ff + j] (s ascending).
+// out[t, j] = silu(g) * u with g = sum_s gu[s][t, 2j], u = sum_s gu[s][t, 2j + 1] (s ascending):
+// gate and up alternate along a row, as the stacked weight's rows do.  VEC = 4 outputs per thread.
 template <typename T, int VEC>
 __global__ void swiglu_kernel(const T* __restrict__ gu, int splits, long long split_stride, T* __restrict__ out_same,
                               bf16* __restrict__ out_bf16, int ff, size_t total) {
@@ -133,26 +134,26 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, int splits, long long sp
     if (i >= total) return;
     size_t t = i / ff;
     int j = (int)(i - t * ff);
-    const T* row = gu + t * 2 * (size_t)ff;
-    float g[VEC], u[VEC], h[VEC];
+    const T* row = gu + t * 2 * (size_t)ff + 2 * (size_t)j;
+    float p[2 * VEC], h[VEC];
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) g[k] = u[k] = 0.f;
+    for (int k = 0; k < 2 * VEC; ++k) p[k] = 0.f;
 #pragma unroll 4
     for (int s = 0; s < splits; ++s) {
         const T* rs = row + (size_t)s * split_stride;
         if (VEC == 4) {
             float a[4], b[4];
-            load4(rs + j, a);
-            load4(rs + ff + j, b);
+            load4(rs, a);
+            load4(rs + 4, b);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) { g[k] += a[k]; u[k] += b[k]; }
+            for (int k = 0; k < 4; ++k) { p[k] += a[k]; p[4 + k] += b[k]; }
         } else {
-            g[0] += to_f32(rs[j]);
-            u[0] += to_f32(rs[ff + j]);
+            p[0] += to_f32(rs[0]);
+            p[1] += to_f32(rs[1]);
         }
     }
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) h[k] = g[k] / (1.0f + expf(-g[k])) * u[k];
+    for (int k = 0; k < VEC; ++k) h[k] = p[2 * k] / (1.0f + expf(-p[2 * k])) * p[2 * k + 1];
     if (VEC == 4) {
         if (out_bf16) store4(out_bf16 + i, h);
         else store4(out_same + i, h);
@@ -228,7 +229,7 @@ int infero_add_rmsnorm(float* x, const void* delta, int delta_dtype, int delta_s
     return infero_check_launch("add_rmsnorm");
 }
 
-// gate_up: splits arrays of [n_tokens, 2 * ff] (dtype), split_stride elements apart.  out has
+// gate_up: splits arrays of [n_tokens, 2 * ff] (dtype, gate and up alternating), split_stride elements apart.  out has
 // gate_up's type, or bf16 when out_bf16 is set (32-bit partial products in, bf16 out).
 int infero_swiglu(const void* gate_up, int splits, long long split_stride, void* out, int dtype, int out_bf16,
                   int n_tokens, int ff, cudaStream_t stream) {

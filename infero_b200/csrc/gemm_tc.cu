@@ -40,7 +40,11 @@ constexpr int UMMA_K = 16;
 constexpr int GEMM_THREADS = 192;
 constexpr int A_STAGE_BYTES = TILE_A * TILE_K * 2;
 
-enum : int { EPI_ROW = 0, EPI_COL = 1, EPI_PARTIAL = 2 };
+// The SWIGLU epilogues take a weight matrix whose rows alternate gate_j, up_j and write
+// silu(gate_j) * up_j to column j of a bf16 result half as wide.
+enum : int { EPI_ROW = 0, EPI_COL = 1, EPI_PARTIAL = 2, EPI_ROW_SWIGLU = 3, EPI_COL_SWIGLU = 4 };
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
 
 template <int BN, int STAGES>
 struct SmemPlan {
@@ -225,9 +229,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 __syncwarp();
                 float v[16];
                 tmem_ld16(lane_addr + (uint32_t)c0, v);
-                if (ra >= RA) continue;
                 const int rb = b0 + c0;
-                if (EPI == EPI_ROW) {
+                if (EPI == EPI_COL_SWIGLU) {
+                    // lanes 2j, 2j+1 hold gate_j and up_j of the same tokens: out[rb + i, ra / 2]
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float other = __shfl_xor_sync(0xffffffffu, v[i], 1);
+                        if (!(lane & 1) && ra + 1 < RA && rb + i < RB)
+                            out[(size_t)(rb + i) * ldc + (ra >> 1)] = from_f32<OutT>(silu_mul(v[i], other));
+                    }
+                    continue;
+                }
+                if (ra >= RA) continue;
+                if (EPI == EPI_ROW_SWIGLU) {
+                    // columns 2j, 2j+1 of this token's row are gate_j and up_j: out[ra, rb / 2 ..]
+                    OutT* dst = out + (size_t)ra * ldc + (rb >> 1);
+                    float h[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) h[i] = silu_mul(v[2 * i], v[2 * i + 1]);
+                    if (rb + 16 <= RB && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0 && sizeof(OutT) == 2) {
+                        uint32_t pk[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            __nv_bfloat162 t2 = __floats2bfloat162_rn(h[2 * i], h[2 * i + 1]);
+                            pk[i] = *reinterpret_cast<uint32_t*>(&t2);
+                        }
+                        *reinterpret_cast<uint4*>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            if (rb + 2 * i + 1 < RB) dst[i] = from_f32<OutT>(h[i]);
+                    }
+                } else if (EPI == EPI_ROW) {
                     // out[ra, rb .. rb+15] (+ bias[rb ..])
                     OutT* dst = out + (size_t)ra * ldc + rb;
                     const bool full = rb + 16 <= RB;
@@ -438,6 +471,43 @@ int infero_gemm_tc(const void* x, const void* w, const void* bias, int bias_dtyp
     if (out_dtype == INFERO_F32)
         return launch<256, 4, EPI_ROW, float>(mx, mw, out, bias, bias_dtype, M, N, K, total_kt, 1, ldc, 0, err, stream);
     return launch<256, 4, EPI_ROW, bf16>(mx, mw, out, bias, bias_dtype, M, N, K, total_kt, 1, ldc, 0, err, stream);
+}
+
+// out[M, N/2] (bf16, row stride ldc) = silu(g) * u with [g_0 u_0 g_1 u_1 ...] = x[M, K] * w[N, K]^T:
+// w's rows alternate gate and up.  With few rows this needs the one-split plan (the activation
+// is not linear, so partial sums cannot be combined afterwards): returns 2 when the plan has
+// more than one split, and nothing is launched.
+int infero_gemm_tc_swiglu(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int ldc,
+                          int sm_count, cudaStream_t stream) {
+    if (M == 0 || N == 0) return 0;
+    INFERO_REQUIRE(infero_gemm_tc_supported(x, w, M, N, K, ldx), "gemm_tc_swiglu: shape M=%d N=%d K=%d ldx=%d not supported", M, N, K, ldx);
+    INFERO_REQUIRE(N % 2 == 0 && ldc >= N / 2, "gemm_tc_swiglu: N=%d must be even and ldc=%d at least N/2", N, ldc);
+    int* err;
+    if (err_flag_ptr(&err)) return 1;
+    if (M <= 256) {
+        int splits, per;
+        long long need;
+        infero_gemm_tc_plan(M, N, K, sm_count, &splits, &per, &need);
+        if (splits > 1) return 2;
+        const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+        CUtensorMap mw, mx;
+        if (get_map(w, N, K, K, TILE_A, &mw)) return 1;
+        if (get_map(x, M, K, ldx, bn, &mx)) return 1;
+#define GO(BN_, ST_) return launch<BN_, ST_, EPI_COL_SWIGLU, bf16>(mw, mx, out, nullptr, 0, N, M, K, per, 1, ldc, 1, err, stream)
+        switch (bn) {
+            case 16: GO(16, 6);
+            case 32: GO(32, 5);
+            case 64: GO(64, 4);
+            case 128: GO(128, 3);
+            default: GO(256, 4);
+        }
+#undef GO
+    }
+    const int total_kt = (K + TILE_K - 1) / TILE_K;
+    CUtensorMap mx, mw;
+    if (get_map(x, M, K, ldx, TILE_A, &mx)) return 1;
+    if (get_map(w, N, K, K, 256, &mw)) return 1;
+    return launch<256, 4, EPI_ROW_SWIGLU, bf16>(mx, mw, out, nullptr, 0, M, N, K, total_kt, 1, ldc, 0, err, stream);
 }
 
 // Reads (and clears) the flag a tensor-core kernel raises when one of its waits ran out.

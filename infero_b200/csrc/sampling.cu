@@ -52,37 +52,61 @@ __global__ void apply_penalty_kernel(float* __restrict__ logits, int vocab, cons
     }
 }
 
-__global__ void __launch_bounds__(SAMPLE_THREADS)
-argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out) {
-    __shared__ float bv[32];
-    __shared__ int bi[32];
-    const float* z = logits + (size_t)blockIdx.x * vocab;
+// Greedy pick in two passes: every block scans one chunk of one row for its best (value, index),
+// then one warp per row merges the chunks.  "Best" is the larger value, and among equal values
+// the lower index, at every stage, so the result is the row's first maximum.
+constexpr int ARGMAX_CHUNK = 4096, ARGMAX_THREADS = 256;
+
+__device__ __forceinline__ void argmax_merge(float& best, int& idx, float ov, int oi) {
+    if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+}
+
+__global__ void __launch_bounds__(ARGMAX_THREADS)
+argmax_partial_kernel(const float* __restrict__ logits, int vocab, int n_chunks, float* __restrict__ pv,
+                      int* __restrict__ pi) {
+    __shared__ float bv[ARGMAX_THREADS / 32];
+    __shared__ int bi[ARGMAX_THREADS / 32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.y, chunk = blockIdx.x;
+    const float* z = logits + (size_t)row * vocab;
+    const int lo = chunk * ARGMAX_CHUNK, hi = min(vocab, lo + ARGMAX_CHUNK);
     float best = -CUDART_INF_F;
     int idx = 0x7fffffff;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    for (int i = lo + threadIdx.x; i < hi; i += ARGMAX_THREADS) {
         const float v = z[i];
         if (v > best) { best = v; idx = i; }       // ascending i per thread: lowest index wins ties
     }
-    // reduce (value desc, index asc)
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-        if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
-    }
+    for (int o = 16; o > 0; o >>= 1)
+        argmax_merge(best, idx, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, idx, o));
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (lane == 0) { bv[warp] = best; bi[warp] = idx; }
     __syncthreads();
     if (warp == 0) {
-        best = bv[lane]; idx = bi[lane];
+        best = lane < ARGMAX_THREADS / 32 ? bv[lane] : -CUDART_INF_F;
+        idx = lane < ARGMAX_THREADS / 32 ? bi[lane] : 0x7fffffff;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-            if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
-        }
-        if (lane == 0) out[blockIdx.x] = (idx == 0x7fffffff) ? 0 : idx;   // all -inf/NaN: token 0, as the scan from (0,-inf)
+        for (int o = 16; o > 0; o >>= 1)
+            argmax_merge(best, idx, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, idx, o));
+        if (lane == 0) { pv[(size_t)row * n_chunks + chunk] = best; pi[(size_t)row * n_chunks + chunk] = idx; }
     }
+}
+
+__global__ void __launch_bounds__(128)
+argmax_final_kernel(const float* __restrict__ pv, const int* __restrict__ pi, int n_rows, int n_chunks,
+                    int* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= n_rows) return;
+    float best = -CUDART_INF_F;
+    int idx = 0x7fffffff;
+    for (int c = lane; c < n_chunks; c += 32) argmax_merge(best, idx, pv[(size_t)row * n_chunks + c], pi[(size_t)row * n_chunks + c]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        argmax_merge(best, idx, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, idx, o));
+    if (lane == 0) out[row] = (idx == 0x7fffffff) ? 0 : idx;   // all -inf / NaN: token 0
 }
 
 // Exclusive prefix sum of one int per thread over the block; returns the total too.
@@ -249,11 +273,23 @@ int infero_apply_penalty(float* logits, int n_rows, int vocab, const int* pen_to
     return infero_check_launch("apply_penalty");
 }
 
-int infero_argmax(const float* logits, int n_rows, int vocab, int* out, cudaStream_t stream) {
+// Bytes of scratch infero_argmax needs for n_rows rows of vocab logits.
+long long infero_argmax_scratch(int n_rows, int vocab) {
+    const int n_chunks = (vocab + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK;
+    return (long long)n_rows * n_chunks * 8;
+}
+
+int infero_argmax(const float* logits, int n_rows, int vocab, int* out, void* scratch, cudaStream_t stream) {
     if (n_rows == 0) return 0;
-    INFERO_REQUIRE(vocab > 0, "argmax: empty vocabulary");
-    argmax_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, vocab, out);
-    return infero_check_launch("argmax");
+    INFERO_REQUIRE(vocab > 0 && n_rows <= 65535, "argmax: bad sizes rows=%d vocab=%d", n_rows, vocab);
+    const int n_chunks = (vocab + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK;
+    float* pv = (float*)scratch;
+    int* pi = (int*)(pv + (size_t)n_rows * n_chunks);
+    launch_pdl(argmax_partial_kernel, dim3(n_chunks, n_rows), dim3(ARGMAX_THREADS), 0, stream, logits, vocab, n_chunks, pv, pi);
+    if (infero_check_launch("argmax_partial")) return 1;
+    launch_pdl(argmax_final_kernel, dim3((n_rows + 3) / 4), dim3(128), 0, stream, (const float*)pv, (const int*)pi,
+               n_rows, n_chunks, out);
+    return infero_check_launch("argmax_final");
 }
 
 int infero_sample(const float* logits, int n_rows, int vocab, const float* temperature, const int* top_k,

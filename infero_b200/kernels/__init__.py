@@ -154,8 +154,8 @@ def residual_add(x: torch.Tensor, delta: torch.Tensor) -> None:
 
 
 def swiglu(gate_up, out: torch.Tensor) -> None:
-    """out[t, j] = silu(g[t, j]) * g[t, ff + j] for g = gate_up (a tensor of out's type, or
-    ``Partials`` with a bf16 out)."""
+    """out[t, j] = silu(g[t, 2j]) * g[t, 2j + 1] for g = gate_up (a tensor of out's type, or
+    ``Partials`` with a bf16 out): gate and up alternate along a row."""
     T, ff = out.shape
     assert out.is_contiguous()
     if isinstance(gate_up, Partials):
@@ -258,7 +258,10 @@ def apply_penalty(logits: torch.Tensor, pen_tokens: torch.Tensor, pen_counts: to
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     R, V = logits.shape
     assert logits.dtype == torch.float32 and logits.is_contiguous() and out.numel() >= R
-    _check(lib().infero_argmax(_ptr(logits), c_int(R), c_int(V), _ptr(_i32(out, "out")), _stream()))
+    f = lib().infero_argmax_scratch
+    f.restype = ctypes.c_longlong
+    scratch = torch.empty(int(f(c_int(R), c_int(V))) // 4, dtype=torch.float32, device=logits.device)
+    _check(lib().infero_argmax(_ptr(logits), c_int(R), c_int(V), _ptr(_i32(out, "out")), _ptr(scratch), _stream()))
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,

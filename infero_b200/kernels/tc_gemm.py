@@ -57,6 +57,20 @@ def gemm(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: to
                                 c_int(tile_n), _stream()))
 
 
+def gemm_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+    """out[M, N/2] = silu(g) * u where (g_j, u_j) are columns (2j, 2j+1) of a @ w^T.  Returns False
+    (nothing launched) when few rows would need more than one split of K."""
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.shape == (M, N // 2) and out.stride(1) == 1 and out.dtype == torch.bfloat16
+    rc = lib().infero_gemm_tc_swiglu(_ptr(a), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)),
+                                     c_int(out.stride(0)), c_int(sm_count(a.device)), _stream())
+    if rc == 2:
+        return False
+    _check(rc)
+    return True
+
+
 def partials(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """float32 [splits, M, N] whose sum over the first axis is a @ w^T (M <= 256)."""
     M, K = a.shape

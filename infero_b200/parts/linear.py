@@ -52,3 +52,14 @@ class Linear:
                 return out
         K.gemm_tiled(a, w, self.bias, out)
         return out
+
+    def forward_swiglu(self, a: torch.Tensor, out: torch.Tensor) -> bool:
+        """For a weight whose rows alternate gate_j, up_j: out[:, j] = silu(a @ gate_j) * (a @ up_j)
+        inside the product kernel's epilogue.  False when that kernel cannot take it (then nothing
+        was launched and the caller does product and activation separately)."""
+        if a.dtype != torch.bfloat16 or self.weight.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+            return False
+        from ..kernels import tc_gemm
+        if a.shape[0] == 0 or not tc_gemm.supported(a, self.weight):
+            return False
+        return tc_gemm.gemm_swiglu(a, self.weight, out)

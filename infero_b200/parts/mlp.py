@@ -14,7 +14,10 @@ from .linear import Linear
 class SwiGluMlp(FeedForward):
     """delta = down(silu(gate(h)) * up(h)) (crates/model/src/lib.rs:7391-7451, :7506-7531;
     crates/kernels/src/cu/ops.cu:111-133).  gate and up are stacked into one [2*ff, d]
-    matrix at bind time so one product feeds the SwiGLU kernel."""
+    matrix at bind time, rows alternating gate_j, up_j, so that one product yields each pair
+    side by side: the tensor-core kernel applies the activation in its epilogue, and where it
+    cannot (32-bit path, a product cut into several splits) the SwiGLU kernel takes the same
+    alternating layout."""
 
     def __init__(self, spec: FeedForwardSpec, prefix: str):
         self.spec = spec
@@ -35,12 +38,13 @@ class SwiGluMlp(FeedForward):
         g, u = tensors[self._n("gate_proj.weight")], tensors[self._n("up_proj.weight")]
         if g.dtype != u.dtype:
             g, u = g.float(), u.float()
-        self.gate_up = Linear(torch.cat([g, u], dim=0), None, self._n("gate_up"))
+        self.gate_up = Linear(torch.stack([g, u], dim=1).reshape(2 * g.shape[0], g.shape[1]), None,
+                              self._n("gate_up"))
         self.down = Linear(tensors[self._n("down_proj.weight")], None, self._n("down_proj"))
 
     def forward(self, ctx, h):
         T = h.shape[0]
-        gu = self.gate_up.forward(h, defer=True)
         act = torch.empty((T, self.spec.intermediate), dtype=h.dtype, device=h.device)
-        K.swiglu(gu, act)
+        if not self.gate_up.forward_swiglu(h, act):
+            K.swiglu(self.gate_up.forward(h, defer=True), act)
         return self.down.forward(act, defer=True)
