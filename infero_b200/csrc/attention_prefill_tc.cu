@@ -1,0 +1,415 @@
+// Prompt-portion attention over the paged cache on the 5th-generation tensor cores.
+//
+// One CTA = 128 consecutive query tokens of one request and one head.  It walks the visible
+// keys in tiles of 128:
+//   S = Q K^T     tcgen05.mma, both operands in shared memory (TMA, 128-byte swizzle), S in TMEM
+//   P = 2^(S*c - m), running maximum m and sum l per row; one thread owns one query row (it
+//                 reads its row of S from TMEM with tcgen05.ld), writes P back over S as bf16
+//                 and, when its maximum moved, rescales its row of O in TMEM
+//   O += P V      tcgen05.mma with P from TMEM and V from shared memory (N-contiguous operand)
+// Warp roles: 0..3 softmax and epilogue (128 rows), 4 loads (one thread issues TMA for Q once,
+// then key and value tiles page by page from the block table, each into its own two-stage
+// ring), 5 owns TMEM and issues the MMAs.  S is double-buffered so that Q K^T of the next tile
+// runs while the softmax of this one does.  Scores, maxima, sums and O are 32-bit; P is rounded
+// to bf16 for the second product, as the keys and values are.
+//
+// Same formula as attention_generic.cu: key j is visible from the query at position p iff
+// lo <= j <= p with lo = max(0, p - window + 1).  The reference's prefill attention is
+// attn_prefill_mma_ws4 (crates/kernels/src/lib.rs:3717) on mma.sync; its formula is
+// crates/kernels/src/cu/ops.cu:709-811.
+//
+// Head sizes 64 and 128; page sizes that are multiples of 16.  Every wait is bounded; a wait
+// that runs out raises the error flag and the CTA leaves in order (TMEM freed).
+#include "tc_common.cuh"
+#include <math_constants.h>
+
+namespace {
+
+using namespace tc;
+
+constexpr int QROWS = 128, KTILE = 128, PFT_THREADS = 192, SLICE = 16;
+
+template <int D>
+struct PfPlan {
+    static constexpr int DB = D / 64;                        // 64-element blocks along the head
+    static constexpr int BLOCK_BYTES = 128 * 128;            // 128 rows of one block
+    static constexpr int TILE_BYTES = DB * BLOCK_BYTES;      // Q, or one K tile, or one V tile
+    static constexpr int Q_OFF = 0;
+    static constexpr int K_OFF = TILE_BYTES;                 // two stages
+    static constexpr int V_OFF = 3 * TILE_BYTES;             // two stages
+    static constexpr int BAR_OFFSET = 5 * TILE_BYTES;
+    static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;
+    static constexpr uint32_t TMEM_COLS = 512;
+    static constexpr uint32_t S_COL = 0, O_COL = 256;        // S buffers at 0 and 128
+};
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <int D>
+__global__ void __launch_bounds__(PFT_THREADS)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, int out_stride,
+                       const int* __restrict__ block_table, int max_blocks, const int* __restrict__ entry_q_start,
+                       const int* __restrict__ entry_q_len, const int* __restrict__ entry_pos0, int n_entries,
+                       int first_entry, int n_tiles, int n_heads, int n_kv, int page_size, int window,
+                       float scale_log2, int* __restrict__ err_flag) {
+    using Plan = PfPlan<D>;
+    constexpr int DB = Plan::DB;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Plan::BAR_OFFSET);
+    uint64_t* q_full = bars;                 // 1
+    uint64_t* k_full = bars + 1;             // 2
+    uint64_t* v_full = bars + 3;             // 2
+    uint64_t* k_empty = bars + 5;            // 2
+    uint64_t* v_empty = bars + 7;            // 2
+    uint64_t* s_full = bars + 9;             // 2
+    uint64_t* p_full = bars + 11;            // 2 (128 arrivals)
+    uint64_t* o_done = bars + 13;            // 1
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* never_flag = abort_flag + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        prefetch_tensormap(&map_q);
+        prefetch_tensormap(&map_k);
+        prefetch_tensormap(&map_v);
+        mbar_init(q_full, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&k_full[i], 1);
+            mbar_init(&v_full[i], 1);
+            mbar_init(&k_empty[i], 1);
+            mbar_init(&v_empty[i], 1);
+            mbar_init(&s_full[i], 1);
+            mbar_init(&p_full[i], 128);
+        }
+        mbar_init(o_done, 1);
+        *abort_flag = 0;
+        *never_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    if (warp == 5) {
+        tmem_alloc(tmem_slot, Plan::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();                                        // q, the tables and this step's keys come from earlier kernels
+
+    // ---- which request and which block of 128 query rows? (longest first) ------------------------
+    const int h = blockIdx.x;
+    int e = -1, tile_in_e = 0;
+    {
+        int left = n_tiles - 1 - (int)blockIdx.y;
+        for (int i = first_entry; i < n_entries; ++i) {
+            const int nt = (entry_q_len[i] + QROWS - 1) / QROWS;
+            if (left < nt) { e = i; tile_in_e = left; break; }
+            left -= nt;
+        }
+    }
+    int n_kt = 0, kt_begin = 0, q_len = 0, pos0 = 0, tok0 = 0, row_first = 0, rows_here = 0;
+    if (e >= 0) {
+        q_len = entry_q_len[e]; pos0 = entry_pos0[e]; tok0 = entry_q_start[e];
+        row_first = tile_in_e * QROWS;
+        rows_here = min(QROWS, q_len - row_first);
+        const int first_pos = pos0 + row_first, last_pos = first_pos + rows_here - 1;
+        const int key_lo = window > 0 ? max(0, first_pos - window + 1) : 0;
+        kt_begin = key_lo / KTILE;
+        n_kt = last_pos / KTILE - kt_begin + 1;
+    }
+    const int kvh = h / (n_heads / n_kv);
+    const int* table = block_table + (size_t)(e < 0 ? 0 : e) * max_blocks;
+    const int first_pos = pos0 + row_first;
+
+    if (warp == 4) {
+        // ---- loader ---------------------------------------------------------------------------------
+        if (n_kt > 0 && elect_one()) {
+            mbar_expect_tx(q_full, Plan::TILE_BYTES);
+#pragma unroll
+            for (int b = 0; b < DB; ++b)
+                tma_load_2d(smem + Plan::Q_OFF + b * Plan::BLOCK_BYTES, &map_q, h * D + b * 64, tok0 + row_first, q_full);
+            bool ok = true;
+            int k_issued = 0, v_issued = 0;
+            auto load_tile = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, int j) {
+                mbar_expect_tx(bar, Plan::TILE_BYTES);
+                const int kb = (kt_begin + j) * KTILE;
+#pragma unroll 1
+                for (int sl = 0; sl < KTILE / SLICE; ++sl) {
+                    const int key0 = kb + sl * SLICE;
+                    const int blk = key0 / page_size;
+                    const int page = blk < max_blocks ? table[blk] : -1;
+                    // a page that is not held (beyond the request's end) is never visible; any finite rows do
+                    const int row = (page < 0 ? 0 : (page * n_kv + kvh) * page_size) + key0 % page_size;
+#pragma unroll
+                    for (int b = 0; b < DB; ++b)
+                        tma_load_2d(dst + b * Plan::BLOCK_BYTES + sl * (SLICE * 128), map, b * 64, row, bar);
+                }
+            };
+            for (int i = 0; i <= n_kt && ok; ++i) {
+                if (i < n_kt) {
+                    const int s = i & 1;
+                    if (!mbar_wait(&k_empty[s], ((uint32_t)(i >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+                    load_tile(&map_k, smem + Plan::K_OFF + s * Plan::TILE_BYTES, &k_full[s], i);
+                    k_issued = i + 1;
+                }
+                if (i > 0) {
+                    const int j = i - 1, s = j & 1;
+                    if (!mbar_wait(&v_empty[s], ((uint32_t)(j >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+                    load_tile(&map_v, smem + Plan::V_OFF + s * Plan::TILE_BYTES, &v_full[s], j);
+                    v_issued = j + 1;
+                }
+            }
+            if (!ok) {
+                *abort_flag = 1;
+                atomicExch(err_flag, 5);
+            }
+            if (*abort_flag) {
+                // let copies that are still in flight land before the block goes away
+                mbar_wait(q_full, 0, never_flag);
+                for (int i = max(0, k_issued - 2); i < k_issued; ++i) mbar_wait(&k_full[i & 1], (uint32_t)(i >> 1) & 1u, never_flag);
+                for (int i = max(0, v_issued - 2); i < v_issued; ++i) mbar_wait(&v_full[i & 1], (uint32_t)(i >> 1) & 1u, never_flag);
+            }
+        }
+    } else if (warp == 5) {
+        // ---- MMA issue ------------------------------------------------------------------------------
+        if (n_kt > 0 && elect_one()) {
+            constexpr uint32_t idesc_qk = idesc_bf16_f32(QROWS, KTILE);
+            constexpr uint32_t idesc_pv = idesc_bf16_f32_b_mn(QROWS, D);
+            const uint32_t q_addr = smem_u32(smem + Plan::Q_OFF);
+            bool ok = true;
+            auto issue_qk = [&](int j) {
+                const uint32_t k_addr = smem_u32(smem + Plan::K_OFF + (j & 1) * Plan::TILE_BYTES);
+                const uint32_t s_tmem = tmem_base + Plan::S_COL + (uint32_t)(j & 1) * KTILE;
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint32_t off = (uint32_t)(ks >> 2) * Plan::BLOCK_BYTES + (uint32_t)(ks & 3) * 32u;
+                    umma_bf16(s_tmem, smem_desc_k_sw128(q_addr + off), smem_desc_k_sw128(k_addr + off), idesc_qk,
+                              ks > 0 ? 1u : 0u);
+                }
+                umma_commit(&k_empty[j & 1]);
+                umma_commit(&s_full[j & 1]);
+            };
+            if (!mbar_wait(q_full, 0, abort_flag) || !mbar_wait(&k_full[0], 0, abort_flag)) ok = false;
+            if (ok) {
+                tc_fence_after_sync();
+                issue_qk(0);
+            }
+            for (int j = 0; j < n_kt && ok; ++j) {
+                if (j + 1 < n_kt) {
+                    if (!mbar_wait(&k_full[(j + 1) & 1], (uint32_t)((j + 1) >> 1) & 1u, abort_flag)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    issue_qk(j + 1);
+                }
+                if (!mbar_wait(&p_full[j & 1], (uint32_t)(j >> 1) & 1u, abort_flag) ||
+                    !mbar_wait(&v_full[j & 1], (uint32_t)(j >> 1) & 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t v_addr = smem_u32(smem + Plan::V_OFF + (j & 1) * Plan::TILE_BYTES);
+                const uint32_t p_tmem = tmem_base + Plan::S_COL + (uint32_t)(j & 1) * KTILE;
+#pragma unroll
+                for (int ks = 0; ks < KTILE / 16; ++ks) {
+                    // 16 keys: 8 columns of P (two bf16 each), 16 rows of V (2048 bytes)
+                    const uint64_t vd = smem_desc_mn_sw128(v_addr + (uint32_t)ks * 2048u, Plan::BLOCK_BYTES, 1024u);
+                    umma_bf16_ts(tmem_base + Plan::O_COL, p_tmem + (uint32_t)ks * 8u, vd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                }
+                umma_commit(&v_empty[j & 1]);
+                umma_commit(o_done);
+            }
+            if (!ok) {
+                *abort_flag = 1;
+                atomicExch(err_flag, 6);
+            }
+        }
+    } else if (n_kt > 0) {
+        // ---- softmax, correction of O, epilogue: one query row per thread --------------------------
+        const int r = warp * 32 + lane;
+        const bool valid = r < rows_here;
+        const int pos_r = first_pos + r;
+        const int hi_r = valid ? pos_r : -1;
+        const int lo_r = window > 0 ? max(0, pos_r - window + 1) : 0;
+        const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
+        float m = -CUDART_INF_F, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_kt; ++j) {
+            const int b = j & 1;
+            if (!__all_sync(0xffffffffu, mbar_wait(&s_full[b], (uint32_t)(j >> 1) & 1u, abort_flag))) { ok = false; break; }   // warp-uniform
+            tc_fence_after_sync();
+            const uint32_t s_addr = tmem_base + lane_sel + Plan::S_COL + (uint32_t)b * KTILE;
+            const int kb = (kt_begin + j) * KTILE;
+            // every key of the tile visible from every row of the block?  (rows past the portion's
+            // end then compute on, unmasked; nothing of theirs is stored)
+            const bool open_tile = (kb + KTILE - 1 <= first_pos) &&
+                                   (window <= 0 || kb >= first_pos + rows_here - 1 - window + 1);
+            float mx = -CUDART_INF_F;
+#pragma unroll 1
+            for (int c = 0; c < KTILE / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32_nowait(s_addr + (uint32_t)c * 32u, v);
+                tmem_wait_ld();
+                if (open_tile) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int key = kb + c * 32 + i;
+                        if (key >= lo_r && key <= hi_r) mx = fmaxf(mx, __uint_as_float(v[i]));
+                    }
+                }
+            }
+            const float m_new = fmaxf(m, mx * scale_log2);
+            const float sub = m_new == -CUDART_INF_F ? 0.f : m_new;     // a row with no key yet: avoid inf - inf
+            const float corr = exp2f(m - sub);
+            float sum = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < KTILE / 32; ++c) {
+                uint32_t v[32], pk[16];
+                tmem_ld32_nowait(s_addr + (uint32_t)c * 32u, v);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float p0 = exp2f(fmaf(__uint_as_float(v[i]), scale_log2, -sub));
+                    float p1 = exp2f(fmaf(__uint_as_float(v[i + 1]), scale_log2, -sub));
+                    if (!open_tile) {
+                        const int key = kb + c * 32 + i;
+                        if (!(key >= lo_r && key <= hi_r)) p0 = 0.f;
+                        if (!(key + 1 >= lo_r && key + 1 <= hi_r)) p1 = 0.f;
+                    }
+                    sum += p0 + p1;
+                    pk[i >> 1] = pack2(p0, p1);
+                }
+                // P over S: the words written (16c .. 16c+15) lie below the columns still to be read
+                tmem_st16(s_addr + (uint32_t)c * 16u, pk);
+            }
+            l = l * corr + sum;
+            m = m_new;
+            if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
+                // the row's maximum moved: O so far is scaled down; the product before must be done
+                if (!__all_sync(0xffffffffu, mbar_wait(o_done, (uint32_t)(j - 1) & 1u, abort_flag))) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t o_addr = tmem_base + lane_sel + Plan::O_COL;
+#pragma unroll 1
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld32_nowait(o_addr + (uint32_t)c * 32u, v);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
+                    tmem_st32(o_addr + (uint32_t)c * 32u, v);
+                }
+            }
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(&p_full[b]);
+        }
+        if (ok && !__all_sync(0xffffffffu, mbar_wait(o_done, (uint32_t)(n_kt - 1) & 1u, abort_flag))) ok = false;
+        tc_fence_after_sync();
+        if (ok) {
+            // every lane takes part in the TMEM loads (they are warp-wide); only lanes that own a
+            // row of the portion store
+            const float inv = 1.0f / l;
+            const uint32_t o_addr = tmem_base + lane_sel + Plan::O_COL;
+            bf16* orow = out + (size_t)(tok0 + row_first + (valid ? r : 0)) * out_stride + (size_t)h * D;
+#pragma unroll 1
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32_nowait(o_addr + (uint32_t)c * 32u, v);
+                tmem_wait_ld();
+                if (valid) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 w;
+                        w.x = pack2(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
+                        w.y = pack2(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
+                        w.z = pack2(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
+                        w.w = pack2(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
+                        *reinterpret_cast<uint4*>(orow + c * 32 + i) = w;
+                    }
+                }
+                __syncwarp();
+            }
+        } else if (lane == 0) {
+            *abort_flag = 1;
+            atomicExch(err_flag, 7);
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, Plan::TMEM_COLS);
+    }
+}
+
+template <int D>
+int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, int out_stride,
+           const int* block_table, int max_blocks, const int* entry_q_start, const int* entry_q_len,
+           const int* entry_pos0, int n_entries, int first_entry, int n_tiles, int n_heads, int n_kv, int page_size,
+           int window, float scale_log2, int* err, cudaStream_t stream) {
+    using Plan = PfPlan<D>;
+    auto kern = attn_prefill_tc_kernel<D>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::TOTAL);
+        if (e != cudaSuccess) {
+            infero_set_error("attn_prefill_tc: cannot get %d bytes of shared memory: %s", Plan::TOTAL, cudaGetErrorString(e));
+            return 1;
+        }
+        configured = true;
+    }
+    launch_pdl(kern, dim3(n_heads, n_tiles), dim3(PFT_THREADS), Plan::TOTAL, stream, mq, mk, mv, (bf16*)out, out_stride,
+               block_table, max_blocks, entry_q_start, entry_q_len, entry_pos0, n_entries, first_entry, n_tiles, n_heads,
+               n_kv, page_size, window, scale_log2, err);
+    return infero_check_launch("attn_prefill_tc");
+}
+
+}  // namespace
+
+extern "C" {
+
+int infero_attn_prefill_tc_supported(int head_dim, int page_size, int q_stride, int out_stride) {
+    return (head_dim == 64 || head_dim == 128) && page_size % 16 == 0 && q_stride % 8 == 0 && out_stride % 8 == 0;
+}
+
+// The same contract as infero_attn_prefill (attention_mma.cu) with 128 query rows per block:
+// n_tiles = sum over the requests first_entry .. n_entries - 1 of ceil(q_len / 128).  q is
+// [n_tokens, >= n_heads * head_dim] bf16 with row stride q_stride; the caches are
+// [num_pages, n_kv, page_size, head_dim] bf16, contiguous; all 16-byte aligned.
+int infero_attn_prefill_tc(const void* q, int q_stride, int n_tokens, void* out, int out_stride, const void* k_cache,
+                           const void* v_cache, int num_pages, const int* block_table, int max_blocks,
+                           const int* entry_q_start, const int* entry_q_len, const int* entry_pos0, int n_entries,
+                           int first_entry, int n_tiles, int n_heads, int n_kv, int head_dim, int page_size,
+                           int window, float scale, cudaStream_t stream) {
+    if (n_tiles == 0) return 0;
+    INFERO_REQUIRE(infero_attn_prefill_tc_supported(head_dim, page_size, q_stride, out_stride),
+                   "attn_prefill_tc: head_dim %d / page_size %d / strides %d, %d not supported", head_dim, page_size,
+                   q_stride, out_stride);
+    INFERO_REQUIRE(n_kv > 0 && n_heads % n_kv == 0 && n_tiles <= 65535, "attn_prefill_tc: bad sizes heads %d / %d, %d tiles",
+                   n_heads, n_kv, n_tiles);
+    INFERO_REQUIRE((long long)num_pages * n_kv * page_size < (1ll << 31), "attn_prefill_tc: cache of %d pages too large", num_pages);
+    INFERO_REQUIRE((reinterpret_cast<uintptr_t>(q) & 15u) == 0 && (reinterpret_cast<uintptr_t>(out) & 15u) == 0,
+                   "attn_prefill_tc: q and out must be 16-byte aligned");
+    CUtensorMap mq, mk, mv;
+    const int rows = num_pages * n_kv * page_size;
+    if (infero_tensor_map_bf16(q, n_tokens, n_heads * head_dim, q_stride, QROWS, &mq)) return 1;
+    if (infero_tensor_map_bf16(k_cache, rows, head_dim, head_dim, SLICE, &mk)) return 1;
+    if (infero_tensor_map_bf16(v_cache, rows, head_dim, head_dim, SLICE, &mv)) return 1;
+    int* err;
+    if (infero_tc_err_flag(&err)) return 1;
+    const float sl2 = scale * 1.4426950408889634f;
+    if (head_dim == 128)
+        return launch<128>(mq, mk, mv, out, out_stride, block_table, max_blocks, entry_q_start, entry_q_len, entry_pos0,
+                           n_entries, first_entry, n_tiles, n_heads, n_kv, page_size, window, sl2, err, stream);
+    return launch<64>(mq, mk, mv, out, out_stride, block_table, max_blocks, entry_q_start, entry_q_len, entry_pos0,
+                      n_entries, first_entry, n_tiles, n_heads, n_kv, page_size, window, sl2, err, stream);
+}
+
+}  // extern "C"

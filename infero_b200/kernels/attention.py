@@ -80,6 +80,24 @@ def prefill(q, out, k_cache, v_cache, table, entry_q_start, entry_q_len, entry_p
                                      c_int(window or 0), c_float(scale), _stream()))
 
 
+def prefill_tc_supported(q, out, head_dim: int, page_size: int) -> bool:
+    return bool(lib().infero_attn_prefill_tc_supported(c_int(head_dim), c_int(page_size), c_int(q.stride(0)),
+                                                       c_int(out.stride(0)))) \
+        and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0
+
+
+def prefill_tc(q, out, k_cache, v_cache, table, entry_q_start, entry_q_len, entry_pos0, n_entries: int,
+               first_entry: int, n_tiles: int, n_heads: int, n_kv: int, head_dim: int, page_size: int,
+               window: Optional[int], scale: float) -> None:
+    """The tcgen05 kernel: 128 query rows per block (n_tiles counts blocks of 128)."""
+    _check(lib().infero_attn_prefill_tc(
+        _ptr(q), c_int(q.stride(0)), c_int(q.shape[0]), _ptr(out), c_int(out.stride(0)), _ptr(k_cache), _ptr(v_cache),
+        c_int(k_cache.shape[0]), _ptr(_i32(table, "block_table")), c_int(table.shape[1]),
+        _ptr(_i32(entry_q_start, "entry_q_start")), _ptr(_i32(entry_q_len, "entry_q_len")),
+        _ptr(_i32(entry_pos0, "entry_pos0")), c_int(n_entries), c_int(first_entry), c_int(n_tiles), c_int(n_heads),
+        c_int(n_kv), c_int(head_dim), c_int(page_size), c_int(window or 0), c_float(scale), _stream()))
+
+
 def attention_any(q, out, k_cache, v_cache, table, tok_entry, positions, n_heads: int, n_kv: int, head_dim: int,
                   page_size: int, window: Optional[int], scale: float, q_lens: Sequence[int], pos0: Sequence[int],
                   entry_q_start=None, entry_q_len=None, entry_pos0=None, kv_bound: Optional[int] = None) -> None:
@@ -112,6 +130,11 @@ def attention_any(q, out, k_cache, v_cache, table, tok_entry, positions, n_heads
             entry_q_start = torch.tensor(starts, dtype=torch.int32, device=dev)
             entry_q_len = torch.tensor([int(n) for n in q_lens], dtype=torch.int32, device=dev)
             entry_pos0 = torch.tensor([int(p) for p in pos0], dtype=torch.int32, device=dev)
+        if prefill_tc_supported(q, out, head_dim, page_size) and k_cache.is_contiguous() and v_cache.is_contiguous():
+            n_tiles = sum(-(-int(n) // 128) for n in q_lens[n_dec:])
+            prefill_tc(q, out, k_cache, v_cache, table, entry_q_start, entry_q_len, entry_pos0, E, n_dec, n_tiles,
+                       n_heads, n_kv, head_dim, page_size, window, scale)
+            return
         n_tiles = sum(-(-int(n) // PREFILL_ROWS) for n in q_lens[n_dec:])
         prefill(q, out, k_cache, v_cache, table, entry_q_start, entry_q_len, entry_pos0, E, n_dec, n_tiles,
                 n_heads, n_kv, head_dim, page_size, window, scale)

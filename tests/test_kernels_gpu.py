@@ -306,6 +306,66 @@ def test_attention_over_pages(H, Hkv, D, dt, window):
     assert worst <= (3e-6 if dt == torch.float32 else 1.5e-2), f"{worst:.3e}"
 
 
+@pytest.mark.parametrize("H,Hkv,D", [(7, 1, 128), (4, 2, 64)])
+@pytest.mark.parametrize("window", [None, 200])
+@pytest.mark.parametrize("P", [16, 64])
+def test_prefill_attention_on_tensor_memory(H, Hkv, D, window, P):
+    """Prompt portions that span several blocks of 128 rows and several tiles of 128 keys: a
+    request from its start, one that continues 300 cached tokens, and a two-token portion."""
+    from infero_b200.kernels import attention as A
+    dt = torch.bfloat16
+    lens = [(0, 300), (300, 260), (77, 2), (129, 1)]
+    pages = sum(-(-(o + n) // P) for o, n in lens) + 4
+    rng = np.random.default_rng(3)
+    perm = rng.permutation(pages)
+    table = torch.full((len(lens), max(-(-(o + n) // P) for o, n in lens) + 1), -1, dtype=torch.int32)
+    kc = _rand((pages, Hkv, P, D), dt, 50)
+    vc = _rand((pages, Hkv, P, D), dt, 51)
+    Ks, Vs = [], []
+    nxt = 0
+    for e, (o, n) in enumerate(lens):
+        L = o + n
+        k, v = _rand((L, Hkv, D), dt, 60 + e), _rand((L, Hkv, D), dt, 80 + e)
+        Ks.append(k); Vs.append(v)
+        for b in range(-(-L // P)):
+            table[e, b] = int(perm[nxt]); nxt += 1
+            m = min(P, L - b * P)
+            kc[table[e, b], :, :m] = k[b * P:b * P + m].transpose(0, 1)
+            vc[table[e, b], :, :m] = v[b * P:b * P + m].transpose(0, 1)
+    T = sum(n for _, n in lens)
+    scale = 1.0 / math.sqrt(D)
+    width = (H + 2 * Hkv) * D                              # q sits in front of a wider row, as in the model
+    qkv = _rand((T, width), dt, 7)
+    q = qkv[:, :H * D]
+    # one far key per request dominates head 0 for its last rows
+    t0 = 0
+    for e, (o, n) in enumerate(lens):
+        j = max(0, o + n - 150) if window else (o + n) // 4
+        kk = Ks[e][j, 0].float()
+        qkv[t0 + n - 1, :D] = (kk * (6.0 / scale / float(kk @ kk))).to(dt)
+        t0 += n
+    positions = torch.tensor([o + i for o, n in lens for i in range(n)], dtype=torch.int32, device=DEV)
+    entry = torch.tensor([e for e, (_, n) in enumerate(lens) for _ in range(n)], dtype=torch.int32, device=DEV)
+    out = torch.zeros((T, H * D), dtype=dt, device=DEV)
+    assert A.prefill_tc_supported(q, out, D, P)
+    # the first request goes first (no leading single-token request), so everything takes the prefill path
+    A.attention_any(q, out, kc, vc, table.to(DEV), entry, positions, H, Hkv, D, P, window, scale,
+                    q_lens=[n for _, n in lens], pos0=[o for o, _ in lens])
+    worst = 0.0
+    t = 0
+    for e, (o, n) in enumerate(lens):
+        for i in range(n):
+            L = o + i + 1
+            ref = _attention_ref(qkv[t, :H * D].double().cpu().view(H, D), Ks[e][:L].double().cpu(),
+                                 Vs[e][:L].double().cpu(), scale, window)
+            got = out[t].double().cpu().view(H, D)
+            worst = max(worst, float((got - ref).abs().max() / ref.abs().max()))
+            t += 1
+    assert worst <= 1.5e-2, f"{worst:.3e}"
+    from infero_b200.kernels import tc_gemm
+    assert tc_gemm.error_flag() == 0
+
+
 @pytest.mark.parametrize("H,Hkv,D", [(28, 4, 128), (14, 2, 64), (20, 1, 128), (3, 3, 64)])
 @pytest.mark.parametrize("window", [None, 100])
 @pytest.mark.parametrize("P", [16, 64])
