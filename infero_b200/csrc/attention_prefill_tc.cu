@@ -1,11 +1,12 @@
 // Prompt-portion attention over the paged cache on the 5th-generation tensor cores.
 //
 // One CTA = 128 consecutive query tokens of one request and one head.  It walks the visible
-// keys in tiles of 128:
+// keys in tiles of 64 (two CTAs share an SM: 96 KB of shared memory and 256 TMEM columns each,
+// so one's softmax runs under the other's MMAs):
 //   S = Q K^T     tcgen05.mma, both operands in shared memory (TMA, 128-byte swizzle), S in TMEM
 //   P = 2^(S*c - m), running maximum m and sum l per row; one thread owns one query row (it
-//                 reads its row of S from TMEM with tcgen05.ld), writes P back over S as bf16
-//                 and, when its maximum moved, rescales its row of O in TMEM
+//                 reads its row of S from TMEM with tcgen05.ld into registers, once), writes P
+//                 back over S as bf16 and, when its maximum moved, rescales its row of O in TMEM
 //   O += P V      tcgen05.mma with P from TMEM and V from shared memory (N-contiguous operand)
 // Warp roles: 0..3 softmax and epilogue (128 rows), 4 loads (one thread issues TMA for Q once,
 // then key and value tiles page by page from the block table, each into its own two-stage
@@ -27,22 +28,31 @@ namespace {
 
 using namespace tc;
 
-constexpr int QROWS = 128, KTILE = 128, PFT_THREADS = 192, SLICE = 16;
+constexpr int QROWS = 128, KTILE = 64, PFT_THREADS = 192, SLICE = 16;
 
 template <int D>
 struct PfPlan {
     static constexpr int DB = D / 64;                        // 64-element blocks along the head
-    static constexpr int BLOCK_BYTES = 128 * 128;            // 128 rows of one block
-    static constexpr int TILE_BYTES = DB * BLOCK_BYTES;      // Q, or one K tile, or one V tile
+    static constexpr int QBLOCK_BYTES = QROWS * 128;         // the query rows of one block
+    static constexpr int KBLOCK_BYTES = KTILE * 128;         // the key (or value) rows of one block
+    static constexpr int Q_BYTES = DB * QBLOCK_BYTES;
+    static constexpr int KV_BYTES = DB * KBLOCK_BYTES;       // one K tile, or one V tile
     static constexpr int Q_OFF = 0;
-    static constexpr int K_OFF = TILE_BYTES;                 // two stages
-    static constexpr int V_OFF = 3 * TILE_BYTES;             // two stages
-    static constexpr int BAR_OFFSET = 5 * TILE_BYTES;
+    static constexpr int K_OFF = Q_BYTES;                    // two stages
+    static constexpr int V_OFF = Q_BYTES + 2 * KV_BYTES;     // two stages
+    static constexpr int BAR_OFFSET = Q_BYTES + 4 * KV_BYTES;
     static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;
-    static constexpr uint32_t TMEM_COLS = 512;
-    static constexpr uint32_t S_COL = 0, O_COL = 256;        // S buffers at 0 and 128
+    // two S buffers of KTILE columns, then O: 256 columns, so that two CTAs share an SM's 512
+    static constexpr uint32_t S_COL = 0, O_COL = 2 * KTILE;
+    static constexpr uint32_t TMEM_COLS = 256;
+    static_assert(2 * KTILE + D <= 256, "S, S and O must fit 256 TMEM columns");
 };
 
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&h);
@@ -133,14 +143,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (warp == 4) {
         // ---- loader ---------------------------------------------------------------------------------
         if (n_kt > 0 && elect_one()) {
-            mbar_expect_tx(q_full, Plan::TILE_BYTES);
+            mbar_expect_tx(q_full, Plan::Q_BYTES);
 #pragma unroll
             for (int b = 0; b < DB; ++b)
-                tma_load_2d(smem + Plan::Q_OFF + b * Plan::BLOCK_BYTES, &map_q, h * D + b * 64, tok0 + row_first, q_full);
+                tma_load_2d(smem + Plan::Q_OFF + b * Plan::QBLOCK_BYTES, &map_q, h * D + b * 64, tok0 + row_first, q_full);
             bool ok = true;
             int k_issued = 0, v_issued = 0;
             auto load_tile = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, int j) {
-                mbar_expect_tx(bar, Plan::TILE_BYTES);
+                mbar_expect_tx(bar, Plan::KV_BYTES);
                 const int kb = (kt_begin + j) * KTILE;
 #pragma unroll 1
                 for (int sl = 0; sl < KTILE / SLICE; ++sl) {
@@ -151,20 +161,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     const int row = (page < 0 ? 0 : (page * n_kv + kvh) * page_size) + key0 % page_size;
 #pragma unroll
                     for (int b = 0; b < DB; ++b)
-                        tma_load_2d(dst + b * Plan::BLOCK_BYTES + sl * (SLICE * 128), map, b * 64, row, bar);
+                        tma_load_2d(dst + b * Plan::KBLOCK_BYTES + sl * (SLICE * 128), map, b * 64, row, bar);
                 }
             };
             for (int i = 0; i <= n_kt && ok; ++i) {
                 if (i < n_kt) {
                     const int s = i & 1;
                     if (!mbar_wait(&k_empty[s], ((uint32_t)(i >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
-                    load_tile(&map_k, smem + Plan::K_OFF + s * Plan::TILE_BYTES, &k_full[s], i);
+                    load_tile(&map_k, smem + Plan::K_OFF + s * Plan::KV_BYTES, &k_full[s], i);
                     k_issued = i + 1;
                 }
                 if (i > 0) {
                     const int j = i - 1, s = j & 1;
                     if (!mbar_wait(&v_empty[s], ((uint32_t)(j >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
-                    load_tile(&map_v, smem + Plan::V_OFF + s * Plan::TILE_BYTES, &v_full[s], j);
+                    load_tile(&map_v, smem + Plan::V_OFF + s * Plan::KV_BYTES, &v_full[s], j);
                     v_issued = j + 1;
                 }
             }
@@ -187,12 +197,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const uint32_t q_addr = smem_u32(smem + Plan::Q_OFF);
             bool ok = true;
             auto issue_qk = [&](int j) {
-                const uint32_t k_addr = smem_u32(smem + Plan::K_OFF + (j & 1) * Plan::TILE_BYTES);
+                const uint32_t k_addr = smem_u32(smem + Plan::K_OFF + (j & 1) * Plan::KV_BYTES);
                 const uint32_t s_tmem = tmem_base + Plan::S_COL + (uint32_t)(j & 1) * KTILE;
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
-                    const uint32_t off = (uint32_t)(ks >> 2) * Plan::BLOCK_BYTES + (uint32_t)(ks & 3) * 32u;
-                    umma_bf16(s_tmem, smem_desc_k_sw128(q_addr + off), smem_desc_k_sw128(k_addr + off), idesc_qk,
+                    const uint32_t in_block = (uint32_t)(ks & 3) * 32u;
+                    umma_bf16(s_tmem, smem_desc_k_sw128(q_addr + (uint32_t)(ks >> 2) * Plan::QBLOCK_BYTES + in_block),
+                              smem_desc_k_sw128(k_addr + (uint32_t)(ks >> 2) * Plan::KBLOCK_BYTES + in_block), idesc_qk,
                               ks > 0 ? 1u : 0u);
                 }
                 umma_commit(&k_empty[j & 1]);
@@ -212,12 +223,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 if (!mbar_wait(&p_full[j & 1], (uint32_t)(j >> 1) & 1u, abort_flag) ||
                     !mbar_wait(&v_full[j & 1], (uint32_t)(j >> 1) & 1u, abort_flag)) { ok = false; break; }
                 tc_fence_after_sync();
-                const uint32_t v_addr = smem_u32(smem + Plan::V_OFF + (j & 1) * Plan::TILE_BYTES);
+                const uint32_t v_addr = smem_u32(smem + Plan::V_OFF + (j & 1) * Plan::KV_BYTES);
                 const uint32_t p_tmem = tmem_base + Plan::S_COL + (uint32_t)(j & 1) * KTILE;
 #pragma unroll
                 for (int ks = 0; ks < KTILE / 16; ++ks) {
                     // 16 keys: 8 columns of P (two bf16 each), 16 rows of V (2048 bytes)
-                    const uint64_t vd = smem_desc_mn_sw128(v_addr + (uint32_t)ks * 2048u, Plan::BLOCK_BYTES, 1024u);
+                    const uint64_t vd = smem_desc_mn_sw128(v_addr + (uint32_t)ks * 2048u, Plan::KBLOCK_BYTES, 1024u);
                     umma_bf16_ts(tmem_base + Plan::O_COL, p_tmem + (uint32_t)ks * 8u, vd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
                 }
                 umma_commit(&v_empty[j & 1]);
@@ -248,47 +259,38 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             // end then compute on, unmasked; nothing of theirs is stored)
             const bool open_tile = (kb + KTILE - 1 <= first_pos) &&
                                    (window <= 0 || kb >= first_pos + rows_here - 1 - window + 1);
+            // the row's KTILE scores, once: all loads in flight, then one wait
+            uint32_t sv[KTILE];
+#pragma unroll
+            for (int c = 0; c < KTILE / 32; ++c) tmem_ld32_nowait(s_addr + (uint32_t)c * 32u, sv + c * 32);
+            tmem_wait_ld();
             float mx = -CUDART_INF_F;
-#pragma unroll 1
-            for (int c = 0; c < KTILE / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld32_nowait(s_addr + (uint32_t)c * 32u, v);
-                tmem_wait_ld();
-                if (open_tile) {
+            if (open_tile) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
-                } else {
+                for (int i = 0; i < KTILE; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
+            } else {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int key = kb + c * 32 + i;
-                        if (key >= lo_r && key <= hi_r) mx = fmaxf(mx, __uint_as_float(v[i]));
-                    }
+                for (int i = 0; i < KTILE; ++i) {
+                    const int key = kb + i;
+                    if (!(key >= lo_r && key <= hi_r)) sv[i] = 0xff800000u;      // -inf: contributes 2^-inf = 0
+                    mx = fmaxf(mx, __uint_as_float(sv[i]));
                 }
             }
             const float m_new = fmaxf(m, mx * scale_log2);
             const float sub = m_new == -CUDART_INF_F ? 0.f : m_new;     // a row with no key yet: avoid inf - inf
-            const float corr = exp2f(m - sub);
+            const float corr = ex2(m - sub);
             float sum = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < KTILE / 32; ++c) {
-                uint32_t v[32], pk[16];
-                tmem_ld32_nowait(s_addr + (uint32_t)c * 32u, v);
-                tmem_wait_ld();
+            uint32_t pk[KTILE / 2];
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float p0 = exp2f(fmaf(__uint_as_float(v[i]), scale_log2, -sub));
-                    float p1 = exp2f(fmaf(__uint_as_float(v[i + 1]), scale_log2, -sub));
-                    if (!open_tile) {
-                        const int key = kb + c * 32 + i;
-                        if (!(key >= lo_r && key <= hi_r)) p0 = 0.f;
-                        if (!(key + 1 >= lo_r && key + 1 <= hi_r)) p1 = 0.f;
-                    }
-                    sum += p0 + p1;
-                    pk[i >> 1] = pack2(p0, p1);
-                }
-                // P over S: the words written (16c .. 16c+15) lie below the columns still to be read
-                tmem_st16(s_addr + (uint32_t)c * 16u, pk);
+            for (int i = 0; i < KTILE; i += 2) {
+                const float p0 = ex2(fmaf(__uint_as_float(sv[i]), scale_log2, -sub));
+                const float p1 = ex2(fmaf(__uint_as_float(sv[i + 1]), scale_log2, -sub));
+                sum += p0 + p1;
+                pk[i >> 1] = pack2(p0, p1);
             }
+            // P over S (every score is in registers by now)
+#pragma unroll
+            for (int c = 0; c < KTILE / 32; ++c) tmem_st16(s_addr + (uint32_t)c * 16u, pk + c * 16);
             l = l * corr + sum;
             m = m_new;
             if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
@@ -310,6 +312,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             tc_fence_before_sync();
             mbar_arrive(&p_full[b]);
         }
+        // The last product.  A parity wait can only tell the running phase from the one before it,
+        // and the loop above skips its wait on o_done whenever no row's maximum moved, so the
+        // barrier may still be two phases back (product n_kt-2 waiting for its values): wait for
+        // that one first, then for the last.
+        if (ok && n_kt >= 2 && !__all_sync(0xffffffffu, mbar_wait(o_done, (uint32_t)(n_kt - 2) & 1u, abort_flag))) ok = false;
         if (ok && !__all_sync(0xffffffffu, mbar_wait(o_done, (uint32_t)(n_kt - 1) & 1u, abort_flag))) ok = false;
         tc_fence_after_sync();
         if (ok) {

@@ -352,6 +352,7 @@ def test_prefill_attention_on_tensor_memory(H, Hkv, D, window, P):
     A.attention_any(q, out, kc, vc, table.to(DEV), entry, positions, H, Hkv, D, P, window, scale,
                     q_lens=[n for _, n in lens], pos0=[o for o, _ in lens])
     worst = 0.0
+    bad = []
     t = 0
     for e, (o, n) in enumerate(lens):
         for i in range(n):
@@ -359,9 +360,12 @@ def test_prefill_attention_on_tensor_memory(H, Hkv, D, window, P):
             ref = _attention_ref(qkv[t, :H * D].double().cpu().view(H, D), Ks[e][:L].double().cpu(),
                                  Vs[e][:L].double().cpu(), scale, window)
             got = out[t].double().cpu().view(H, D)
-            worst = max(worst, float((got - ref).abs().max() / ref.abs().max()))
+            err = float((got - ref).abs().max() / ref.abs().max())
+            if err > 1.5e-2:
+                bad.append((e, i, [round(float(x), 3) for x in ((got - ref).abs().amax(dim=1) / ref.abs().max())]))
+            worst = max(worst, err)
             t += 1
-    assert worst <= 1.5e-2, f"{worst:.3e}"
+    assert worst <= 1.5e-2, f"{worst:.3e} at (request, row, per-head error): {bad[:6]} ... {len(bad)} rows"
     from infero_b200.kernels import tc_gemm
     assert tc_gemm.error_flag() == 0
 
