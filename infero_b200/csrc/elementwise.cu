@@ -72,7 +72,10 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
     TO* orow = out + (size_t)r * d;
     extern __shared__ float vbuf[];      // d floats: the summed row, read twice
     float ss = 0.f;
+    // first loop: loads only (global stores wait for the second loop, so that the loads of all
+    // of a thread's vectors can be in flight together)
     if (VEC == 4) {
+#pragma unroll 4
         for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
             float v[4];
             load4(xr + i, v);
@@ -88,7 +91,6 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
                     load4_any(dbias, dbias_dtype, i, t);
                     v[0] += t[0]; v[1] += t[1]; v[2] += t[2]; v[3] += t[3];
                 }
-                if (!rows) store4(xr + i, v);
             }
             store4(vbuf + i, v);
             ss = fmaf(v[0], v[0], ss); ss = fmaf(v[1], v[1], ss); ss = fmaf(v[2], v[2], ss); ss = fmaf(v[3], v[3], ss);
@@ -99,7 +101,6 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
             if (dr) {
                 for (int s = 0; s < splits; ++s) v += to_f32(dr[(size_t)s * split_stride + i]);
                 if (dbias) v += load_any(dbias, dbias_dtype, i);
-                if (!rows) xr[i] = v;
             }
             vbuf[i] = v;
             ss = fmaf(v, v, ss);
@@ -107,18 +108,22 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
     }
     ss = block_sum(ss, red);
     const float sc = 1.0f / sqrtf(ss / (float)d + eps);
+    const bool write_x = dr && !rows;
     if (VEC == 4) {
+#pragma unroll 4
         for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
             float v[4], ww[4];
             load4(vbuf + i, v);
+            if (write_x) store4(xr + i, v);
             load4_any(w, wdtype, i, ww);
             v[0] = v[0] * sc * ww[0]; v[1] = v[1] * sc * ww[1]; v[2] = v[2] * sc * ww[2]; v[3] = v[3] * sc * ww[3];
             store4(orow + i, v);
         }
     } else {
         for (int i = threadIdx.x; i < d; i += blockDim.x) {
-            float v = vbuf[i] * sc;
-            orow[i] = from_f32<TO>(v * load_any(w, wdtype, i));
+            const float v0 = vbuf[i];
+            if (write_x) xr[i] = v0;
+            orow[i] = from_f32<TO>(v0 * sc * load_any(w, wdtype, i));
         }
     }
 }
@@ -202,6 +207,10 @@ int infero_add_rmsnorm(float* x, const void* delta, int delta_dtype, int delta_s
     auto al = [](const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; };
     const bool vec = d % 4 == 0 && al(x, 16) && al(out, 16) && al(w, 16) && (!delta || al(delta, 16)) &&
                      (!dbias || al(dbias, 16)) && split_stride % 4 == 0;
+    // one vector per thread where the width allows it: with few rows (decode) the kernel is one
+    // round trip to memory, and all of a row's loads are in flight together.  The block size
+    // depends on the width only, so a row's arithmetic (and its rounding) does not depend on
+    // how many rows the step has.
     int threads = vec ? (d / 4 + 31) / 32 * 32 : 256;
     if (threads > 1024) threads = 1024;
     if (threads < 32) threads = 32;

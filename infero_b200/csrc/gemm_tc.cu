@@ -304,6 +304,230 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 }
 
+// ---- many tokens: persistent, two accumulators --------------------------------------------------
+// One CTA per SM walks over 128 x 256 tiles of the result (tile t = blockIdx.x, + gridDim.x, ...).
+// Tile numbers run over the token blocks of one block of 256 features first, so that at any
+// moment the CTAs together work on a few feature blocks and all token blocks, which L2 holds.  The shared-memory ring runs on across tiles; tensor memory
+// holds two accumulators of 256 columns, so the four epilogue warps drain tile i while the MMAs
+// of tile i + 1 run.  A = activations [RA, K], B = weights [RB, K].
+constexpr int PERS_BN = 256, PERS_STAGES = 4;
+
+template <int EPI, typename OutT>
+__global__ void __launch_bounds__(GEMM_THREADS)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                          OutT* __restrict__ out, const void* __restrict__ bias, int bias_dtype,
+                          int RA, int RB, int K, long long ldc, int* __restrict__ err_flag) {
+    constexpr int BN = PERS_BN, STAGES = PERS_STAGES;
+    using Plan = SmemPlan<BN, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Plan::BAR_OFFSET);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* acc_full = empty_bar + STAGES;             // 2
+    uint64_t* acc_empty = acc_full + 2;                  // 2 (four arrivals: one per epilogue warp)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* never_flag = abort_flag + 1;
+
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_a = (RA + TILE_A - 1) / TILE_A, tiles_b = (RB + BN - 1) / BN;
+    const int n_tiles = tiles_a * tiles_b;
+    const int n_kt = (K + TILE_K - 1) / TILE_K;
+    const int my_tiles = (int)blockIdx.x < n_tiles ? (n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+
+    if (threadIdx.x == 0) {
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&acc_full[a], 1);
+            mbar_init(&acc_empty[a], 4);
+        }
+        *abort_flag = 0;
+        *never_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 2 * BN);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---- loader: the ring index runs over (tile, k-tile) pairs ---------------------------------
+        if (elect_one()) {
+            const long long total = (long long)my_tiles * n_kt;
+            long long issued = 0;
+            bool ok = true;
+            // (tile, k-tile) of the next load, kept as running counters
+            int tile = (int)blockIdx.x, kt = 0;
+            int a0 = (tile % tiles_a) * TILE_A, b0 = (tile / tiles_a) * BN;
+            auto advance = [&]() {
+                if (++kt == n_kt) {
+                    kt = 0;
+                    tile += (int)gridDim.x;
+                    a0 = (tile % tiles_a) * TILE_A;
+                    b0 = (tile / tiles_a) * BN;
+                }
+            };
+            // weights of the first stages before the kernel in front has finished, activations after
+            const int pre = (int)(total < STAGES ? total : STAGES);
+            int pa0[STAGES], pkx[STAGES];
+            for (int it = 0; it < pre; ++it) {
+                mbar_expect_tx(&full_bar[it], Plan::STAGE_BYTES);
+                tma_load_2d(smem + it * Plan::STAGE_BYTES + A_STAGE_BYTES, &map_b, kt * TILE_K, b0, &full_bar[it]);
+                pa0[it] = a0;
+                pkx[it] = kt * TILE_K;
+                advance();
+            }
+            pdl_wait();
+            for (int it = 0; it < pre; ++it) {
+                tma_load_2d(smem + it * Plan::STAGE_BYTES, &map_a, pkx[it], pa0[it], &full_bar[it]);
+                issued = it + 1;
+            }
+            int s = pre % STAGES;
+            uint32_t ph = (uint32_t)(pre / STAGES) & 1u;
+            for (long long it = pre; it < total; ++it) {
+                if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+                uint8_t* sa = smem + s * Plan::STAGE_BYTES;
+                mbar_expect_tx(&full_bar[s], Plan::STAGE_BYTES);
+                tma_load_2d(sa, &map_a, kt * TILE_K, a0, &full_bar[s]);
+                tma_load_2d(sa + A_STAGE_BYTES, &map_b, kt * TILE_K, b0, &full_bar[s]);
+                issued = it + 1;
+                advance();
+                if (++s == STAGES) { s = 0; ph ^= 1u; }
+            }
+            if (!ok) {
+                *abort_flag = 1;
+                atomicExch(err_flag, 1);
+            }
+            if (*abort_flag) {
+                for (long long it = issued > STAGES ? issued - STAGES : 0; it < issued; ++it)
+                    mbar_wait(&full_bar[it % STAGES], (uint32_t)(it / STAGES) & 1u, never_flag);
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issue ---------------------------------------------------------------------------
+        if (elect_one()) {
+            constexpr uint32_t idesc = idesc_bf16_f32(TILE_A, BN);
+            bool ok = true;
+            int s = 0;
+            uint32_t ph = 0;
+            for (int i = 0; i < my_tiles && ok; ++i) {
+                const int a = i & 1;
+                // the epilogue has drained this accumulator's previous tile
+                if (!mbar_wait(&acc_empty[a], ((uint32_t)(i >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t acc = tmem_base + (uint32_t)a * BN;
+                for (int kt = 0; kt < n_kt; ++kt) {
+                    if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t sa = smem_u32(smem + s * Plan::STAGE_BYTES);
+                    const uint64_t da = smem_desc_k_sw128(sa);
+                    const uint64_t db = smem_desc_k_sw128(sa + A_STAGE_BYTES);
+#pragma unroll
+                    for (int k = 0; k < TILE_K / UMMA_K; ++k)
+                        umma_bf16(acc, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kt > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(&empty_bar[s]);
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                }
+                if (ok) umma_commit(&acc_full[a]);
+            }
+            if (!ok) {
+                *abort_flag = 1;
+                atomicExch(err_flag, 2);
+            }
+        }
+    } else {
+        // ---- epilogue: tile i while the MMAs of tile i + 1 run ------------------------------------
+        const int q = warp & 3;
+        bool ok = true;
+        for (int i = 0; i < my_tiles; ++i) {
+            const int a = i & 1;
+            const int t = (int)blockIdx.x + i * (int)gridDim.x;
+            const int a0 = (t % tiles_a) * TILE_A, b0 = (t / tiles_a) * BN;
+            const int ra = a0 + q * 32 + lane;
+            if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[a], (uint32_t)(i >> 1) & 1u, abort_flag))) { ok = false; break; }
+            tc_fence_after_sync();
+            const uint32_t lane_addr = tmem_base + (uint32_t)a * BN + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                if (b0 + c0 >= RB) break;                    // uniform over the block
+                uint32_t u[32];
+                tmem_ld32_nowait(lane_addr + (uint32_t)c0, u);
+                tmem_wait_ld();
+                if (ra < RA) {
+#pragma unroll
+                    for (int hseg = 0; hseg < 2; ++hseg) {
+                        const int rb = b0 + c0 + hseg * 16;
+                        if (rb >= RB) break;
+                        float v[16];
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) v[e] = __uint_as_float(u[hseg * 16 + e]);
+                        if (EPI == EPI_ROW_SWIGLU) {
+                            OutT* dst = out + (size_t)ra * ldc + (rb >> 1);
+                            float h[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) h[e] = silu_mul(v[2 * e], v[2 * e + 1]);
+                            if (rb + 16 <= RB && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0 && sizeof(OutT) == 2) {
+                                uint32_t pk[4];
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    __nv_bfloat162 t2 = __floats2bfloat162_rn(h[2 * e], h[2 * e + 1]);
+                                    pk[e] = *reinterpret_cast<uint32_t*>(&t2);
+                                }
+                                *reinterpret_cast<uint4*>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < 8; ++e)
+                                    if (rb + 2 * e + 1 < RB) dst[e] = from_f32<OutT>(h[e]);
+                            }
+                        } else {
+                            OutT* dst = out + (size_t)ra * ldc + rb;
+                            if (bias) {
+#pragma unroll
+                                for (int e = 0; e < 16; ++e)
+                                    if (rb + e < RB) v[e] += load_any(bias, bias_dtype, rb + e);
+                            }
+                            if (rb + 16 <= RB) {
+                                store16<OutT>(dst, v, (reinterpret_cast<uintptr_t>(dst) & 15u) == 0);
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < 16; ++e)
+                                    if (rb + e < RB) dst[e] = from_f32<OutT>(v[e]);
+                            }
+                        }
+                    }
+                }
+                __syncwarp();
+            }
+            // this warp has read its quarter of the accumulator: hand it back
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[a]);
+        }
+        if (!ok && lane == 0) {
+            *abort_flag = 1;
+            atomicExch(err_flag, 3);
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, 2 * BN);
+    }
+}
+
 // out[t, n] = sum_s partial[s, t, n] (+ bias[n]); the sum runs over s in ascending order.
 template <typename OutT>
 __global__ void reduce_partials_kernel(const float* __restrict__ partial, int splits, const void* __restrict__ bias,
@@ -346,6 +570,27 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, const void* 
     launch_pdl(kern, grid, dim3(GEMM_THREADS), Plan::TOTAL, stream, ma, mb, (OutT*)out, bias, bias_dtype, RA, RB, K,
                ktiles_per_split, ldc, a_evict_first, err);
     return infero_check_launch("gemm_tc");
+}
+
+template <int EPI, typename OutT>
+int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void* out, const void* bias, int bias_dtype,
+                      int RA, int RB, int K, long long ldc, int sm_count, int* err, cudaStream_t stream) {
+    using Plan = SmemPlan<PERS_BN, PERS_STAGES>;
+    auto kern = gemm_tc_persistent_kernel<EPI, OutT>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::TOTAL);
+        if (e != cudaSuccess) {
+            infero_set_error("gemm_tc: cannot get %d bytes of shared memory: %s", Plan::TOTAL, cudaGetErrorString(e));
+            return 1;
+        }
+        configured = true;
+    }
+    const int n_tiles = ((RA + TILE_A - 1) / TILE_A) * ((RB + PERS_BN - 1) / PERS_BN);
+    const int ctas = n_tiles < sm_count ? n_tiles : (sm_count > 0 ? sm_count : 148);
+    launch_pdl(kern, dim3(ctas), dim3(GEMM_THREADS), Plan::TOTAL, stream, ma, mb, (OutT*)out, bias, bias_dtype, RA, RB,
+               K, ldc, err);
+    return infero_check_launch("gemm_tc_persistent");
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -468,9 +713,14 @@ int infero_gemm_tc(const void* x, const void* w, const void* bias, int bias_dtyp
             return launch<128, 3, EPI_ROW, float>(mx, mw, out, bias, bias_dtype, M, N, K, total_kt, 1, ldc, 0, err, stream);
         return launch<128, 3, EPI_ROW, bf16>(mx, mw, out, bias, bias_dtype, M, N, K, total_kt, 1, ldc, 0, err, stream);
     }
+    if (tile_n == 256) {                                   // the one-tile-per-CTA kernel, kept for comparison
+        if (out_dtype == INFERO_F32)
+            return launch<256, 4, EPI_ROW, float>(mx, mw, out, bias, bias_dtype, M, N, K, total_kt, 1, ldc, 0, err, stream);
+        return launch<256, 4, EPI_ROW, bf16>(mx, mw, out, bias, bias_dtype, M, N, K, total_kt, 1, ldc, 0, err, stream);
+    }
     if (out_dtype == INFERO_F32)
-        return launch<256, 4, EPI_ROW, float>(mx, mw, out, bias, bias_dtype, M, N, K, total_kt, 1, ldc, 0, err, stream);
-    return launch<256, 4, EPI_ROW, bf16>(mx, mw, out, bias, bias_dtype, M, N, K, total_kt, 1, ldc, 0, err, stream);
+        return launch_persistent<EPI_ROW, float>(mx, mw, out, bias, bias_dtype, M, N, K, ldc, sm_count, err, stream);
+    return launch_persistent<EPI_ROW, bf16>(mx, mw, out, bias, bias_dtype, M, N, K, ldc, sm_count, err, stream);
 }
 
 // out[M, N/2] (bf16, row stride ldc) = silu(g) * u with [g_0 u_0 g_1 u_1 ...] = x[M, K] * w[N, K]^T:
@@ -507,7 +757,8 @@ int infero_gemm_tc_swiglu(const void* x, const void* w, void* out, int M, int N,
     CUtensorMap mx, mw;
     if (get_map(x, M, K, ldx, TILE_A, &mx)) return 1;
     if (get_map(w, N, K, K, 256, &mw)) return 1;
-    return launch<256, 4, EPI_ROW_SWIGLU, bf16>(mx, mw, out, nullptr, 0, M, N, K, total_kt, 1, ldc, 0, err, stream);
+    (void)total_kt;
+    return launch_persistent<EPI_ROW_SWIGLU, bf16>(mx, mw, out, nullptr, 0, M, N, K, ldc, sm_count, err, stream);
 }
 
 // Reads (and clears) the flag a tensor-core kernel raises when one of its waits ran out.

@@ -55,6 +55,79 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int row_stride, const int
     }
 }
 
+// bf16, many tokens: one block per token.  The sines and cosines of the token's position are
+// worked out once (they are the same for every head) and kept in shared memory; then every
+// thread moves 8 + 8 elements at a time: rotate q in place, rotate k into its page, copy v.
+// Needs rotary_dim % 16 == 0, head_dim % 8 == 0 and 16-byte aligned rows.
+__global__ void __launch_bounds__(256)
+rope_cache_vec_kernel(bf16* __restrict__ qkv, int row_stride, const int* __restrict__ positions,
+                      const int* __restrict__ tok_entry, const int* __restrict__ block_table, int max_blocks,
+                      const float* __restrict__ inv_freq, int rotary_dim, bf16* __restrict__ k_cache,
+                      bf16* __restrict__ v_cache, int page_size, int n_heads, int n_kv, int head_dim,
+                      int write_cache) {
+    extern __shared__ float2 sc[];                 // [rotary_dim / 2] (sin, cos)
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const int half = rotary_dim >> 1;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float sn, cs;
+        sincosf((float)pos * inv_freq[i], &sn, &cs);
+        sc[i] = make_float2(sn, cs);
+    }
+    __syncthreads();
+    bf16* row = qkv + (size_t)t * row_stride;
+    const int page = write_cache ? block_table[(size_t)tok_entry[t] * max_blocks + pos / page_size] : -1;
+    const size_t in_page = (size_t)(pos % page_size) * head_dim;
+    const int hc = half >> 3;                      // chunks of 8 pairs per head
+    const int rot_items = (n_heads + n_kv) * hc;
+    for (int it = threadIdx.x; it < rot_items; it += blockDim.x) {
+        const int h = it / hc, c = it - h * hc;
+        const bf16* src = row + (size_t)h * head_dim + c * 8;
+        bf16* dst;
+        if (h < n_heads) {
+            dst = row + (size_t)h * head_dim + c * 8;
+        } else {
+            if (page < 0) continue;
+            dst = k_cache + ((size_t)page * n_kv + (h - n_heads)) * page_size * head_dim + in_page + c * 8;
+        }
+        uint4 ua = *reinterpret_cast<const uint4*>(src), ub = *reinterpret_cast<const uint4*>(src + half);
+        const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&ua);
+        const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&ub);
+        uint4 oa, ob;
+        __nv_bfloat162* qa = reinterpret_cast<__nv_bfloat162*>(&oa);
+        __nv_bfloat162* qb = reinterpret_cast<__nv_bfloat162*>(&ob);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 s0 = sc[c * 8 + 2 * k], s1 = sc[c * 8 + 2 * k + 1];
+            const float a0 = __low2float(pa[k]), a1 = __high2float(pa[k]);
+            const float b0 = __low2float(pb[k]), b1 = __high2float(pb[k]);
+            qa[k] = __floats2bfloat162_rn(a0 * s0.y - b0 * s0.x, a1 * s1.y - b1 * s1.x);
+            qb[k] = __floats2bfloat162_rn(a0 * s0.x + b0 * s0.y, a1 * s1.x + b1 * s1.y);
+        }
+        *reinterpret_cast<uint4*>(dst) = oa;
+        *reinterpret_cast<uint4*>(dst + half) = ob;
+    }
+    if (page < 0) return;
+    // what is not rotated: the tail of every k head beyond rotary_dim, and v
+    const int tail = (head_dim - rotary_dim) >> 3, dc = head_dim >> 3;
+    const int copy_items = n_kv * (tail + dc);
+    for (int it = threadIdx.x; it < copy_items; it += blockDim.x) {
+        const int kvh = it / (tail + dc), c = it - kvh * (tail + dc);
+        const bf16* src;
+        bf16* dst;
+        if (c < tail) {
+            src = row + (size_t)(n_heads + kvh) * head_dim + rotary_dim + c * 8;
+            dst = k_cache + ((size_t)page * n_kv + kvh) * page_size * head_dim + in_page + rotary_dim + c * 8;
+        } else {
+            src = row + (size_t)(n_heads + n_kv + kvh) * head_dim + (c - tail) * 8;
+            dst = v_cache + ((size_t)page * n_kv + kvh) * page_size * head_dim + in_page + (c - tail) * 8;
+        }
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+    }
+}
+
 // The same, reading q, k and v as the sum of 32-bit partial products (+ bias) that the
 // few-token matrix kernel leaves behind: value(t, c) = sum_s partial[s][t][c] + bias[c], s
 // ascending.  Rotated q goes to q_out [T, n_heads * head_dim]; k and v go to their pages.
@@ -120,6 +193,14 @@ int infero_rope_cache(void* qkv, int dtype, int row_stride, const int* positions
     INFERO_REQUIRE(rotary_dim >= 0 && rotary_dim % 2 == 0 && rotary_dim <= head_dim,
                    "rope_cache: rotary_dim %d must be even and <= head_dim %d", rotary_dim, head_dim);
     INFERO_REQUIRE(n_heads + 2 * n_kv <= 65535, "rope_cache: too many heads (%d)", n_heads + 2 * n_kv);
+    auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    if (dtype == INFERO_BF16 && n_tokens >= 16 && rotary_dim % 16 == 0 && rotary_dim > 0 && head_dim % 8 == 0 &&
+        row_stride % 8 == 0 && al16(qkv) && al16(k_cache) && al16(v_cache)) {
+        launch_pdl(rope_cache_vec_kernel, dim3(n_tokens), dim3(256), (size_t)(rotary_dim / 2) * sizeof(float2), stream,
+                   (bf16*)qkv, row_stride, positions, tok_entry, block_table, max_blocks, inv_freq, rotary_dim,
+                   (bf16*)k_cache, (bf16*)v_cache, page_size, n_heads, n_kv, head_dim, write_cache);
+        return infero_check_launch("rope_cache_vec");
+    }
     dim3 grid(n_tokens, n_heads + 2 * n_kv);
     const int threads = head_dim >= 128 ? 64 : 32;
     if (dtype == INFERO_F32)
