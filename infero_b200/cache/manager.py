@@ -57,6 +57,11 @@ class CacheManager:
         self.allocators = [PageAllocator(num_pages, g) for g in range(len(self.groups))]
         self._free_slots: List[int] = list(range(max_requests - 1, -1, -1))
         self.requests: Dict[Hashable, RequestCache] = {}
+        # device-bound copy of every block table, one row per request slot, kept up to date as
+        # pages come and go, so that a step gathers its rows instead of rebuilding them
+        self._table_width = max_blocks if max_blocks is not None else 0
+        self._table_np = [np.full((max_requests, max(1, self._table_width)), -1, dtype=np.int32)
+                          for _ in self.groups]
         self.pages_reclaimed = 0          # window pages returned before their request ended
         self.pages_reused = 0             # allocations served by a page that was held before
         self._ever_held = [bytearray(num_pages) for _ in self.groups]
@@ -70,6 +75,8 @@ class CacheManager:
         rc = RequestCache(rid=rid, slot=self._free_slots.pop(),
                           tables=[[] for _ in self.groups], first_live=[0 for _ in self.groups])
         self.requests[rid] = rc
+        for t in self._table_np:
+            t[rc.slot, :] = -1
         return rc
 
     def close(self, rid: Hashable) -> None:
@@ -119,7 +126,10 @@ class CacheManager:
                 if self._ever_held[g][p]:
                     self.pages_reused += 1
                 self._ever_held[g][p] = 1
+            first = len(rc.tables[g])
             rc.tables[g].extend(pages)
+            if pages:
+                self._mirror(g, rc.slot, first, pages)
         rc.reserved += n_new
 
     def commit(self, rc: RequestCache, n_new: int) -> None:
@@ -142,6 +152,8 @@ class CacheManager:
                 if table[k] >= 0:
                     freed.append(table[k])
                     table[k] = -1
+                    if k < self._table_np[g].shape[1]:
+                        self._table_np[g][rc.slot, k] = -1
                 k += 1
             rc.first_live[g] = k
             if freed:
@@ -157,16 +169,33 @@ class CacheManager:
             extra = [p for p in table[keep:] if p >= 0]
             del table[keep:]
             self.allocators[g].free(extra)
+            self._table_np[g][rc.slot, keep:] = -1
         rc.reserved = 0
 
     # ---- tables for the device -----------------------------------------------------------
+    def _mirror(self, group: int, slot: int, first: int, pages) -> None:
+        t = self._table_np[group]
+        end = first + len(pages)
+        if end > t.shape[1]:                       # no fixed width was given: grow
+            wider = np.full((t.shape[0], max(end, 2 * t.shape[1])), -1, dtype=np.int32)
+            wider[:, :t.shape[1]] = t
+            self._table_np[group] = t = wider
+        t[slot, first:end] = pages
+
     def block_table_array(self, group: int, rcs: Sequence[RequestCache], width: int) -> np.ndarray:
-        out = np.full((max(1, len(rcs)), width), -1, dtype=np.int32)
-        for i, rc in enumerate(rcs):
-            t = rc.tables[group]
-            if len(t) > width:
-                raise ValueError(f"request {rc.rid!r} holds {len(t)} pages, table width is {width}")
-            out[i, :len(t)] = t
+        """[len(rcs), width] int32: logical page -> page id (-1 where none is held)."""
+        t = self._table_np[group]
+        if not rcs:
+            return np.full((1, width), -1, dtype=np.int32)
+        slots = np.fromiter((rc.slot for rc in rcs), dtype=np.intp, count=len(rcs))
+        if width <= t.shape[1]:
+            out = t[slots, :width]
+        else:
+            out = np.full((len(rcs), width), -1, dtype=np.int32)
+            out[:, :t.shape[1]] = t[slots]
+        for rc in rcs:
+            if len(rc.tables[group]) > width:
+                raise ValueError(f"request {rc.rid!r} holds {len(rc.tables[group])} pages, table width is {width}")
         return out
 
     # ---- invariants (used by tests and debug runs) -----------------------------------------
@@ -187,6 +216,12 @@ class CacheManager:
                 raise AssertionError(f"group {g}: {len(held)} held + {alloc.num_free} free != {alloc.num_pages}")
             if len(set(alloc._free)) != len(alloc._free):
                 raise AssertionError(f"group {g}: a page is on the free list twice")
+        for g in range(len(self.groups)):
+            for rc in self.requests.values():
+                row = self._table_np[g][rc.slot]
+                t = rc.tables[g]
+                if list(row[:len(t)]) != list(t) or (row[len(t):] != -1).any():
+                    raise AssertionError(f"group {g}: the table copy of request {rc.rid!r} is out of date")
         slots = [rc.slot for rc in self.requests.values()]
         if len(set(slots)) != len(slots) or set(slots) & set(self._free_slots):
             raise AssertionError("a state slot is held twice")
