@@ -66,7 +66,9 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         tc::fence_barrier_init();
         tc::fence_proxy_async();
     }
-    pdl_wait();                                        // q and this step's keys come from the kernel before
+    // positions and block tables are set before the step's first kernel, and every cached key
+    // but the token's own was written by earlier steps: all of that may be read before the
+    // kernel in front (which writes q and the token's own key and value) has finished
     const int split = blockIdx.x;
     const int group = n_heads / n_kv;
     const int gtiles = (group + 15) / 16;
@@ -85,6 +87,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     float* pml = partial_ml + (((size_t)ti * n_heads + h0) * n_splits + split) * 2;
     if (k_begin >= k_end) {
         // nothing in this split: leave (m, l) = (-inf, 0) so the merge skips it
+        pdl_wait();
         for (int r = threadIdx.x; r < valid; r += TD_THREADS) {
             pml[(size_t)r * n_splits * 2] = -CUDART_INF_F;
             pml[(size_t)r * n_splits * 2 + 1] = 0.f;
@@ -95,14 +98,6 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 
     uint8_t* my = smem + (size_t)warp * Plan::WARP_BYTES;
     uint64_t* my_bar = bars + warp * STAGES;
-
-    uint32_t qf[D / 16][4];
-    load_q<D>(qf, q + (size_t)t * q_stride + (size_t)h0 * D, (size_t)D, valid, lane);
-    float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
-    float o[D / 8][4];
-#pragma unroll
-    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-
     const int n_slices = (k_end - k_begin + KEYS16 - 1) / KEYS16;
     const int my_slices = n_slices > warp ? (n_slices - warp + TD_WARPS - 1) / TD_WARPS : 0;
     const uint64_t policy = tc::policy_evict_first();                 // the cache is read once per step
@@ -122,8 +117,23 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             }
         }
     };
+    // a slice that ends before the token's own position holds nothing of this step
+    auto old_keys_only = [&](int i) { return k_begin + (warp + i * TD_WARPS) * KEYS16 + KEYS16 <= pos; };
 #pragma unroll
-    for (int i = 0; i < STAGES - 1; ++i) issue(i);
+    for (int i = 0; i < STAGES - 1; ++i)
+        if (old_keys_only(i)) issue(i);
+    pdl_wait();                                        // q and this step's key and value
+#pragma unroll
+    for (int i = 0; i < STAGES - 1; ++i)
+        if (!old_keys_only(i)) issue(i);
+
+    uint32_t qf[D / 16][4];
+    load_q<D>(qf, q + (size_t)t * q_stride + (size_t)h0 * D, (size_t)D, valid, lane);
+    float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
     bool ok = true;
     int waited = 0;
     for (int i = 0; i < my_slices; ++i) {

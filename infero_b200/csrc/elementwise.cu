@@ -128,6 +128,56 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
     }
 }
 
+// Many rows, one vector per thread: a block walks over rows blockIdx.x, + gridDim.x, ... and
+// has the next row's loads in flight while it reduces and writes the current one.  Thread t
+// owns elements 4t .. 4t+3 of every row and the block size is the same as in the kernel above,
+// so each row is computed by exactly the same operations in the same order.
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_rows_kernel(float* __restrict__ x, const TD* __restrict__ delta,
+                                        const void* __restrict__ dbias, int dbias_dtype,
+                                        const void* __restrict__ w, int wdtype, float eps,
+                                        TO* __restrict__ out, int n_rows, int d) {
+    __shared__ float red[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int i = threadIdx.x * 4;
+    const bool mine = i < d;
+    float ww[4] = {0.f, 0.f, 0.f, 0.f}, bb[4] = {0.f, 0.f, 0.f, 0.f};
+    if (mine) {
+        load4_any(w, wdtype, i, ww);
+        if (dbias) load4_any(dbias, dbias_dtype, i, bb);
+    }
+    float xv[4] = {0.f, 0.f, 0.f, 0.f}, dv[4] = {0.f, 0.f, 0.f, 0.f};
+    int r = blockIdx.x;
+    if (r < n_rows && mine) {
+        load4(x + (size_t)r * d + i, xv);
+        if (delta) load4(delta + (size_t)r * d + i, dv);
+    }
+    for (; r < n_rows; r += gridDim.x) {
+        float v[4] = {xv[0], xv[1], xv[2], xv[3]};
+        if (delta) {
+            v[0] += dv[0]; v[1] += dv[1]; v[2] += dv[2]; v[3] += dv[3];
+            if (dbias) { v[0] += bb[0]; v[1] += bb[1]; v[2] += bb[2]; v[3] += bb[3]; }
+        }
+        const int rn = r + gridDim.x;
+        if (rn < n_rows && mine) {                   // the next row, before this one is reduced
+            load4(x + (size_t)rn * d + i, xv);
+            if (delta) load4(delta + (size_t)rn * d + i, dv);
+        }
+        float ss = 0.f;
+        if (mine) {
+            ss = fmaf(v[0], v[0], ss); ss = fmaf(v[1], v[1], ss); ss = fmaf(v[2], v[2], ss); ss = fmaf(v[3], v[3], ss);
+        }
+        ss = block_sum(ss, red);
+        const float sc = 1.0f / sqrtf(ss / (float)d + eps);
+        if (mine) {
+            if (delta) store4(x + (size_t)r * d + i, v);
+            v[0] = v[0] * sc * ww[0]; v[1] = v[1] * sc * ww[1]; v[2] = v[2] * sc * ww[2]; v[3] = v[3] * sc * ww[3];
+            store4(out + (size_t)r * d + i, v);
+        }
+    }
+}
+
 // out[t, j] = silu(g) * u with g = sum_s gu[s][t, 2j], u = sum_s gu[s][t, 2j + 1] (s ascending):
 // gate and up alternate along a row, as the stacked weight's rows do.  VEC = 4 outputs per thread.
 template <typename T, int VEC>
@@ -214,6 +264,26 @@ int infero_add_rmsnorm(float* x, const void* delta, int delta_dtype, int delta_s
     int threads = vec ? (d / 4 + 31) / 32 * 32 : 256;
     if (threads > 1024) threads = 1024;
     if (threads < 32) threads = 32;
+    if (vec && !rows && delta_splits == 1 && n_rows >= 256 && d <= 4 * threads) {
+        // many rows (prompt portions): the pipelined kernel, same arithmetic per row
+        int dev = 0, sms = 148;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        int per_sm = 2048 / threads;
+        if (per_sm > 8) per_sm = 8;
+        if (per_sm < 1) per_sm = 1;
+        int blocks = sms * per_sm;
+        if (blocks > n_rows) blocks = n_rows;
+#define LAUNCH_ROWS(TD, TO)                                                                      \
+        launch_pdl(add_rmsnorm_rows_kernel<TD, TO>, dim3(blocks), dim3(threads), 0, stream, x, (const TD*)delta, dbias, \
+                   dbias_dtype, w, w_dtype, eps, (TO*)out, n_rows, d)
+        if (delta_dtype == INFERO_F32 && out_dtype == INFERO_F32) LAUNCH_ROWS(float, float);
+        else if (delta_dtype == INFERO_BF16 && out_dtype == INFERO_BF16) LAUNCH_ROWS(bf16, bf16);
+        else if (delta_dtype == INFERO_F32 && out_dtype == INFERO_BF16) LAUNCH_ROWS(float, bf16);
+        else LAUNCH_ROWS(bf16, float);
+#undef LAUNCH_ROWS
+        return infero_check_launch("add_rmsnorm_rows");
+    }
 #define LAUNCH(TD, TO)                                                                          \
     do {                                                                                        \
         if (vec) {                                                                              \

@@ -29,6 +29,7 @@
 #include <mutex>
 #include <unordered_map>
 #include <cstring>
+#include <cstdlib>
 
 namespace {
 
@@ -310,15 +311,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // moment the CTAs together work on a few feature blocks and all token blocks, which L2 holds.  The shared-memory ring runs on across tiles; tensor memory
 // holds two accumulators of 256 columns, so the four epilogue warps drain tile i while the MMAs
 // of tile i + 1 run.  A = activations [RA, K], B = weights [RB, K].
-constexpr int PERS_BN = 256, PERS_STAGES = 4;
+// The tile width bn (a multiple of 16 up to 256) is chosen per problem so that the tiles fill
+// whole rounds of the CTAs (3584 features in tiles of 256 are 224 tiles with 16 token blocks:
+// two rounds on 148 SMs, the second half empty; in tiles of 208 they are 288 and nearly fill two).
+constexpr int PERS_MAX_BN = 256, PERS_STAGES = 4;
 
 template <int EPI, typename OutT>
 __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                           OutT* __restrict__ out, const void* __restrict__ bias, int bias_dtype,
-                          int RA, int RB, int K, long long ldc, int* __restrict__ err_flag) {
-    constexpr int BN = PERS_BN, STAGES = PERS_STAGES;
-    using Plan = SmemPlan<BN, STAGES>;
+                          int RA, int RB, int K, long long ldc, int BN, int* __restrict__ err_flag) {
+    constexpr int STAGES = PERS_STAGES;
+    using Plan = SmemPlan<PERS_MAX_BN, STAGES>;             // where the barriers sit; stages are packed by BN
+    const int stage_bytes = A_STAGE_BYTES + BN * TILE_K * 2;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
@@ -354,7 +359,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         fence_proxy_async();
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, 2 * BN);
+        tmem_alloc(tmem_slot, 2 * PERS_MAX_BN);
         tmem_relinquish();
     }
     tc_fence_before_sync();
@@ -383,23 +388,23 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             const int pre = (int)(total < STAGES ? total : STAGES);
             int pa0[STAGES], pkx[STAGES];
             for (int it = 0; it < pre; ++it) {
-                mbar_expect_tx(&full_bar[it], Plan::STAGE_BYTES);
-                tma_load_2d(smem + it * Plan::STAGE_BYTES + A_STAGE_BYTES, &map_b, kt * TILE_K, b0, &full_bar[it]);
+                mbar_expect_tx(&full_bar[it], stage_bytes);
+                tma_load_2d(smem + it * stage_bytes + A_STAGE_BYTES, &map_b, kt * TILE_K, b0, &full_bar[it]);
                 pa0[it] = a0;
                 pkx[it] = kt * TILE_K;
                 advance();
             }
             pdl_wait();
             for (int it = 0; it < pre; ++it) {
-                tma_load_2d(smem + it * Plan::STAGE_BYTES, &map_a, pkx[it], pa0[it], &full_bar[it]);
+                tma_load_2d(smem + it * stage_bytes, &map_a, pkx[it], pa0[it], &full_bar[it]);
                 issued = it + 1;
             }
             int s = pre % STAGES;
             uint32_t ph = (uint32_t)(pre / STAGES) & 1u;
             for (long long it = pre; it < total; ++it) {
                 if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) { ok = false; break; }
-                uint8_t* sa = smem + s * Plan::STAGE_BYTES;
-                mbar_expect_tx(&full_bar[s], Plan::STAGE_BYTES);
+                uint8_t* sa = smem + s * stage_bytes;
+                mbar_expect_tx(&full_bar[s], stage_bytes);
                 tma_load_2d(sa, &map_a, kt * TILE_K, a0, &full_bar[s]);
                 tma_load_2d(sa + A_STAGE_BYTES, &map_b, kt * TILE_K, b0, &full_bar[s]);
                 issued = it + 1;
@@ -418,7 +423,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     } else if (warp == 1) {
         // ---- MMA issue ---------------------------------------------------------------------------
         if (elect_one()) {
-            constexpr uint32_t idesc = idesc_bf16_f32(TILE_A, BN);
+            const uint32_t idesc = idesc_bf16_f32(TILE_A, BN);
             bool ok = true;
             int s = 0;
             uint32_t ph = 0;
@@ -427,11 +432,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                 // the epilogue has drained this accumulator's previous tile
                 if (!mbar_wait(&acc_empty[a], ((uint32_t)(i >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
                 tc_fence_after_sync();
-                const uint32_t acc = tmem_base + (uint32_t)a * BN;
+                const uint32_t acc = tmem_base + (uint32_t)a * PERS_MAX_BN;
                 for (int kt = 0; kt < n_kt; ++kt) {
                     if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
-                    const uint32_t sa = smem_u32(smem + s * Plan::STAGE_BYTES);
+                    const uint32_t sa = smem_u32(smem + s * stage_bytes);
                     const uint64_t da = smem_desc_k_sw128(sa);
                     const uint64_t db = smem_desc_k_sw128(sa + A_STAGE_BYTES);
 #pragma unroll
@@ -458,10 +463,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             const int ra = a0 + q * 32 + lane;
             if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[a], (uint32_t)(i >> 1) & 1u, abort_flag))) { ok = false; break; }
             tc_fence_after_sync();
-            const uint32_t lane_addr = tmem_base + (uint32_t)a * BN + ((uint32_t)(q * 32) << 16);
+            const uint32_t lane_addr = tmem_base + (uint32_t)a * PERS_MAX_BN + ((uint32_t)(q * 32) << 16);
+            const int col_end = min(RB, b0 + BN);                // what this tile owns
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
-                if (b0 + c0 >= RB) break;                    // uniform over the block
+                if (b0 + c0 >= col_end) break;               // uniform over the block
                 uint32_t u[32];
                 tmem_ld32_nowait(lane_addr + (uint32_t)c0, u);
                 tmem_wait_ld();
@@ -469,7 +475,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 #pragma unroll
                     for (int hseg = 0; hseg < 2; ++hseg) {
                         const int rb = b0 + c0 + hseg * 16;
-                        if (rb >= RB) break;
+                        if (rb >= col_end) break;
                         float v[16];
 #pragma unroll
                         for (int e = 0; e < 16; ++e) v[e] = __uint_as_float(u[hseg * 16 + e]);
@@ -524,7 +530,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     __syncthreads();
     if (warp == 1) {
         tc_fence_after_sync();
-        tmem_dealloc(tmem_base, 2 * BN);
+        tmem_dealloc(tmem_base, 2 * PERS_MAX_BN);
     }
 }
 
@@ -572,10 +578,32 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, const void* 
     return infero_check_launch("gemm_tc");
 }
 
+// Tile width for the persistent kernel: the multiple of 16 (64..256) with the shortest schedule.
+// A tile's time does not shrink in proportion to its width (the token operand is read from
+// shared memory for every MMA whatever the width): measured at K = 18944 a tile of width bn
+// costs about bn + 200 columns' worth.
+int pick_tile_n(int M, int N, int ctas, int multiple) {
+    if (const char* e = getenv("INFERO_GEMM_TILE_N")) {       // tuning knob: force a width
+        const int v = atoi(e);
+        if (v >= 16 && v <= PERS_MAX_BN && v % multiple == 0) return v;
+    }
+    const int tiles_a = (M + TILE_A - 1) / TILE_A;
+    long long best_cost = -1;
+    int best = PERS_MAX_BN;
+    for (int bn = PERS_MAX_BN; bn >= 64; bn -= 16) {
+        if (bn % multiple) continue;
+        const long long tiles = (long long)tiles_a * ((N + bn - 1) / bn);
+        const long long rounds = (tiles + ctas - 1) / ctas;
+        const long long cost = rounds * (bn + 200);
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
+    }
+    return best;
+}
+
 template <int EPI, typename OutT>
-int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void* out, const void* bias, int bias_dtype,
-                      int RA, int RB, int K, long long ldc, int sm_count, int* err, cudaStream_t stream) {
-    using Plan = SmemPlan<PERS_BN, PERS_STAGES>;
+int launch_persistent(const void* x, const void* w, void* out, const void* bias, int bias_dtype,
+                      int RA, int RB, int K, int ldx, long long ldc, int sm_count, int* err, cudaStream_t stream) {
+    using Plan = SmemPlan<PERS_MAX_BN, PERS_STAGES>;
     auto kern = gemm_tc_persistent_kernel<EPI, OutT>;
     static bool configured = false;
     if (!configured) {
@@ -586,10 +614,15 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void* out, c
         }
         configured = true;
     }
-    const int n_tiles = ((RA + TILE_A - 1) / TILE_A) * ((RB + PERS_BN - 1) / PERS_BN);
-    const int ctas = n_tiles < sm_count ? n_tiles : (sm_count > 0 ? sm_count : 148);
+    const int sms = sm_count > 0 ? sm_count : 148;
+    const int bn = pick_tile_n(RA, RB, sms, EPI == EPI_ROW_SWIGLU ? 32 : 16);
+    CUtensorMap ma, mb;
+    if (get_map(x, RA, K, ldx, TILE_A, &ma)) return 1;
+    if (get_map(w, RB, K, K, bn, &mb)) return 1;
+    const int n_tiles = ((RA + TILE_A - 1) / TILE_A) * ((RB + bn - 1) / bn);
+    const int ctas = n_tiles < sms ? n_tiles : sms;
     launch_pdl(kern, dim3(ctas), dim3(GEMM_THREADS), Plan::TOTAL, stream, ma, mb, (OutT*)out, bias, bias_dtype, RA, RB,
-               K, ldc, err);
+               K, ldc, bn, err);
     return infero_check_launch("gemm_tc_persistent");
 }
 
@@ -719,8 +752,8 @@ int infero_gemm_tc(const void* x, const void* w, const void* bias, int bias_dtyp
         return launch<256, 4, EPI_ROW, bf16>(mx, mw, out, bias, bias_dtype, M, N, K, total_kt, 1, ldc, 0, err, stream);
     }
     if (out_dtype == INFERO_F32)
-        return launch_persistent<EPI_ROW, float>(mx, mw, out, bias, bias_dtype, M, N, K, ldc, sm_count, err, stream);
-    return launch_persistent<EPI_ROW, bf16>(mx, mw, out, bias, bias_dtype, M, N, K, ldc, sm_count, err, stream);
+        return launch_persistent<EPI_ROW, float>(x, w, out, bias, bias_dtype, M, N, K, ldx, ldc, sm_count, err, stream);
+    return launch_persistent<EPI_ROW, bf16>(x, w, out, bias, bias_dtype, M, N, K, ldx, ldc, sm_count, err, stream);
 }
 
 // out[M, N/2] (bf16, row stride ldc) = silu(g) * u with [g_0 u_0 g_1 u_1 ...] = x[M, K] * w[N, K]^T:
@@ -757,8 +790,7 @@ int infero_gemm_tc_swiglu(const void* x, const void* w, void* out, int M, int N,
     CUtensorMap mx, mw;
     if (get_map(x, M, K, ldx, TILE_A, &mx)) return 1;
     if (get_map(w, N, K, K, 256, &mw)) return 1;
-    (void)total_kt;
-    return launch_persistent<EPI_ROW_SWIGLU, bf16>(mx, mw, out, nullptr, 0, M, N, K, ldc, sm_count, err, stream);
+    return launch_persistent<EPI_ROW_SWIGLU, bf16>(x, w, out, nullptr, 0, M, N, K, ldx, ldc, sm_count, err, stream);
 }
 
 // Reads (and clears) the flag a tensor-core kernel raises when one of its waits ran out.

@@ -181,6 +181,101 @@ __global__ void rope_cache_partials_kernel(const float* __restrict__ partial, in
     }
 }
 
+// The same for bf16 outputs with vector loads: one block per token, sines and cosines shared by
+// all heads, every thread sums 4 + 4 columns over the splits, rotates and stores.
+// Needs rotary_dim % 8 == 0, head_dim % 4 == 0 and 16-byte aligned rows of the partial sums.
+__global__ void __launch_bounds__(256)
+rope_cache_partials_vec_kernel(const float* __restrict__ partial, int splits, long long split_stride, int row_width,
+                               const void* __restrict__ bias, int bias_dtype, bf16* __restrict__ q_out, int q_stride,
+                               const int* __restrict__ positions, const int* __restrict__ tok_entry,
+                               const int* __restrict__ block_table, int max_blocks,
+                               const float* __restrict__ inv_freq, int rotary_dim, bf16* __restrict__ k_cache,
+                               bf16* __restrict__ v_cache, int page_size, int n_heads, int n_kv, int head_dim,
+                               int write_cache) {
+    extern __shared__ float2 sc[];
+    pdl_launch_dependents();
+    // positions and block tables are set before the step's first kernel: the sines can be worked
+    // out while the product in front is still running
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const int half = rotary_dim >> 1;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float sn, cs;
+        sincosf((float)pos * inv_freq[i], &sn, &cs);
+        sc[i] = make_float2(sn, cs);
+    }
+    const int page = write_cache ? block_table[(size_t)tok_entry[t] * max_blocks + pos / page_size] : -1;
+    __syncthreads();
+    pdl_wait();
+    const float* src_row = partial + (size_t)t * row_width;
+    const size_t in_page = (size_t)(pos % page_size) * head_dim;
+    auto sum4 = [&](size_t col, float* v) {
+        v[0] = v[1] = v[2] = v[3] = 0.f;
+#pragma unroll 4
+        for (int s = 0; s < splits; ++s) {
+            const float4 f = *reinterpret_cast<const float4*>(src_row + (size_t)s * split_stride + col);
+            v[0] += f.x; v[1] += f.y; v[2] += f.z; v[3] += f.w;
+        }
+        if (bias) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) v[k] += load_any(bias, bias_dtype, col + k);
+        }
+    };
+    auto store4bf = [](bf16* p, const float* v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 u;
+        u.x = *reinterpret_cast<uint32_t*>(&a);
+        u.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = u;
+    };
+    const int hc = half >> 2;                      // chunks of 4 pairs per head
+    const int rot_items = (n_heads + n_kv) * hc;
+    for (int it = threadIdx.x; it < rot_items; it += blockDim.x) {
+        const int h = it / hc, c = it - h * hc;
+        bf16* dst;
+        if (h < n_heads) {
+            dst = q_out + (size_t)t * q_stride + (size_t)h * head_dim + c * 4;
+        } else {
+            if (page < 0) continue;
+            dst = k_cache + ((size_t)page * n_kv + (h - n_heads)) * page_size * head_dim + in_page + c * 4;
+        }
+        float a[4], b[4], ra[4], rb[4];
+        sum4((size_t)h * head_dim + c * 4, a);
+        sum4((size_t)h * head_dim + half + c * 4, b);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 s1 = sc[c * 4 + k];
+            ra[k] = a[k] * s1.y - b[k] * s1.x;
+            rb[k] = a[k] * s1.x + b[k] * s1.y;
+        }
+        store4bf(dst, ra);
+        store4bf(dst + half, rb);
+    }
+    // not rotated: the tail of q and k heads beyond rotary_dim, and v
+    const int tail = (head_dim - rotary_dim) >> 2, dc = head_dim >> 2;
+    const int tail_items = (n_heads + n_kv) * tail;
+    for (int it = threadIdx.x; it < tail_items; it += blockDim.x) {
+        const int h = it / tail, c = it - h * tail;
+        bf16* dst;
+        if (h < n_heads) {
+            dst = q_out + (size_t)t * q_stride + (size_t)h * head_dim + rotary_dim + c * 4;
+        } else {
+            if (page < 0) continue;
+            dst = k_cache + ((size_t)page * n_kv + (h - n_heads)) * page_size * head_dim + in_page + rotary_dim + c * 4;
+        }
+        float v[4];
+        sum4((size_t)h * head_dim + rotary_dim + c * 4, v);
+        store4bf(dst, v);
+    }
+    if (page < 0) return;
+    for (int it = threadIdx.x; it < n_kv * dc; it += blockDim.x) {
+        const int kvh = it / dc, c = it - kvh * dc;
+        float v[4];
+        sum4((size_t)(n_heads + n_kv + kvh) * head_dim + c * 4, v);
+        store4bf(v_cache + ((size_t)page * n_kv + kvh) * page_size * head_dim + in_page + c * 4, v);
+    }
+}
+
 }  // namespace
 
 extern "C" {
@@ -228,9 +323,18 @@ int infero_rope_cache_partials(const float* partial, int splits, long long split
                    "rope_cache: rotary_dim %d must be even and <= head_dim %d", rotary_dim, head_dim);
     INFERO_REQUIRE(n_heads + 2 * n_kv <= 65535, "rope_cache: too many heads (%d)", n_heads + 2 * n_kv);
     INFERO_REQUIRE(splits >= 1, "rope_cache: %d splits", splits);
+    const int width = (n_heads + 2 * n_kv) * head_dim;
+    auto al = [](const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; };
+    if (dtype == INFERO_BF16 && rotary_dim % 8 == 0 && head_dim % 4 == 0 && q_stride % 4 == 0 && width % 4 == 0 &&
+        split_stride % 4 == 0 && al(partial, 16) && al(q_out, 8) && al(k_cache, 8) && al(v_cache, 8)) {
+        launch_pdl(rope_cache_partials_vec_kernel, dim3(n_tokens), dim3(256), (size_t)(rotary_dim / 2) * sizeof(float2),
+                   stream, partial, splits, split_stride, width, bias, bias_dtype, (bf16*)q_out, q_stride, positions,
+                   tok_entry, block_table, max_blocks, inv_freq, rotary_dim, (bf16*)k_cache, (bf16*)v_cache, page_size,
+                   n_heads, n_kv, head_dim, write_cache);
+        return infero_check_launch("rope_cache_partials_vec");
+    }
     dim3 grid(n_tokens, n_heads + 2 * n_kv);
     const int threads = head_dim >= 128 ? 64 : 32;
-    const int width = (n_heads + 2 * n_kv) * head_dim;
     if (dtype == INFERO_F32)
         launch_pdl(rope_cache_partials_kernel<float>, grid, dim3(threads), 0, stream, partial, splits, split_stride, width, bias,
             bias_dtype, (float*)q_out, q_stride, positions, tok_entry, block_table, max_blocks, inv_freq, rotary_dim,

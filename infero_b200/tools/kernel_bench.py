@@ -6,9 +6,9 @@
 KERNEL: gemm_qkv | gemm_o | gemm_gate_up | gemm_down | gemm_head | attn_prefill | attn_decode
         | norm | rope | swiglu
 
-Every repetition works on its own copy of the inputs (enough copies to exceed the L2 cache), is
-timed with CUDA events after warm-up, and the median is reported with the achieved GB/s or
-TFLOP/s.  The reference times whole passes the same way (crates/model/examples/
+The kernel runs on several copies of its inputs (enough to exceed the L2 cache), back to back; a
+round over all copies is timed with CUDA events after warm-up, and the median time per launch is
+reported with the achieved GB/s or TFLOP/s.  The reference times whole passes the same way (crates/model/examples/
 prefill_profile.rs:38-55) and per kernel with events (crates/cuda/src/profile.rs:28-130).
 This is also the small case to put under ``ncu``: one kernel, a few launches.
 """
@@ -133,18 +133,21 @@ def main(argv=None) -> int:
     for i in range(args.warmup):
         runs[i % len(runs)]()
     torch.cuda.synchronize()
+    # one timed repetition = every input copy once, back to back (the launches queue up, so the
+    # host's launch cost is hidden behind kernels that take longer than it)
     times = []
     for i in range(args.reps):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        runs[i % len(runs)]()
+        for run in runs:
+            run()
         e1.record()
         torch.cuda.synchronize()
-        times.append(e0.elapsed_time(e1) * 1e3)
+        times.append(e0.elapsed_time(e1) * 1e3 / len(runs))
     times.sort()
     us = times[len(times) // 2]
     err = tc_gemm.error_flag()
-    line = f"{name}: {us:.1f} us median of {args.reps} (min {times[0]:.1f}), {len(runs)} input copies"
+    line = f"{name}: {us:.1f} us per launch, median of {args.reps} rounds over {len(runs)} input copies (min {times[0]:.1f})"
     if bytes_:
         line += f", {bytes_ / us / 1e3:.0f} GB/s"
     if flops:

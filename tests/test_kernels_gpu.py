@@ -33,6 +33,7 @@ GEMM_TC_SHAPES = [
     (1, 128, 64), (1, 3584, 3584), (8, 4608, 3584), (8, 3584, 18944), (3, 1000, 96), (16, 777, 224),
     (17, 512, 64), (33, 300, 176), (64, 1152, 896), (65, 2048, 1024), (130, 640, 520), (256, 384, 200),
     (257, 512, 128), (300, 777, 224), (512, 1000, 96), (1024, 4608, 3584), (2048, 1280, 4864), (384, 96, 256),
+    (2048, 3584, 320), (1500, 3000, 136), (20000, 200, 72),     # tile widths other than 256; many rounds per CTA
 ]
 
 
@@ -84,7 +85,8 @@ def test_gemm_tensor_core_partials_sum_in_fixed_order():
     assert tc_gemm.error_flag() == 0
 
 
-@pytest.mark.parametrize("M,N,K", [(8, 37888, 3584), (64, 1024, 512), (300, 400, 264), (2048, 1280, 512), (5, 354, 64)])
+@pytest.mark.parametrize("M,N,K", [(8, 37888, 3584), (64, 1024, 512), (300, 400, 264), (2048, 1280, 512), (5, 354, 64),
+                                   (2048, 7168, 192), (700, 3000, 72)])
 def test_gemm_tensor_core_with_swiglu_epilogue(M, N, K):
     from infero_b200.kernels import tc_gemm
     a = _rand((M, K), torch.bfloat16, 1)
@@ -177,6 +179,27 @@ def test_add_rmsnorm(d, eps, act):
     Kn.add_rmsnorm(x1, delta, w, eps, out2, rows)
     assert torch.equal(x1, x0)
     assert torch.equal(out2, out[rows.long()])
+
+
+@pytest.mark.parametrize("act", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("d", [96, 3584])
+def test_add_rmsnorm_many_rows_equal_few_rows_bit_for_bit(act, d):
+    """300 rows at once (the pipelined kernel) against the same rows 100 at a time."""
+    from infero_b200 import kernels as Kn
+    T = 300
+    x = _rand((T, d), torch.float32, 1)
+    delta = _rand((T, d), act, 2)
+    w = _rand((d,), act, 3) + 1
+    xa, xb = x.clone(), x.clone()
+    oa = torch.empty((T, d), dtype=act, device=DEV)
+    ob = torch.empty_like(oa)
+    Kn.add_rmsnorm(xa, delta, w, 1e-6, oa)
+    for t0 in range(0, T, 100):
+        Kn.add_rmsnorm(xb[t0:t0 + 100], delta[t0:t0 + 100], w, 1e-6, ob[t0:t0 + 100])
+    assert torch.equal(xa, xb) and torch.equal(oa, ob)
+    v = x.double() + delta.double()
+    ref = v * torch.rsqrt((v * v).mean(-1, keepdim=True) + 1e-6) * w.double()
+    assert float((oa.double() - ref).abs().max() / ref.abs().max()) <= (1e-6 if act == torch.float32 else 5e-3)
 
 
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
