@@ -230,16 +230,20 @@ attn_combine_kernel(const float* __restrict__ partial_o, const float* __restrict
     }
     __syncwarp();
     float L = 0.f;
-    for (int s = 0; s < n_splits; ++s) L += ml[s * 2 + 1] * wgt[s];    // ascending, same in every lane
+    for (int s = 0; s < n_splits; ++s) L += ml[s * 2 + 1] * wgt[s];    // ascending, same in every lane (l is written for every split)
     const float inv = 1.0f / L;
     bf16* orow = out + (size_t)(tok_first + ti) * out_stride + (size_t)h * head_dim;
     for (int d = lane * 2; d < head_dim; d += 64) {
         float a0 = 0.f, a1 = 0.f;
 #pragma unroll 8
         for (int s = 0; s < n_splits; ++s) {
-            const float2 v = *reinterpret_cast<const float2*>(po + (size_t)s * head_dim + d);
-            a0 = fmaf(v.x, wgt[s], a0);
-            a1 = fmaf(v.y, wgt[s], a1);
+            // a split without keys has weight 0 and wrote no partial output: what lies there is
+            // whatever the memory held (possibly NaN), so it is left out, not multiplied by 0
+            const float ws = wgt[s];
+            float2 v = *reinterpret_cast<const float2*>(po + (size_t)s * head_dim + d);
+            if (ws == 0.f) v = make_float2(0.f, 0.f);
+            a0 = fmaf(v.x, ws, a0);
+            a1 = fmaf(v.y, ws, a1);
         }
         *reinterpret_cast<uint32_t*>(orow + d) = pack_bf16(a0 * inv, a1 * inv);
     }

@@ -453,6 +453,14 @@ def test_decode_attention_fed_by_tma(H, Hkv, D, window, P):
     positions = torch.tensor([L - 1 for L in lengths], dtype=torch.int32, device=DEV)
     entry = torch.arange(n, dtype=torch.int32, device=DEV)
     for bound in (None, 2048):                            # the plan of a captured step covers more keys than there are
+        # the scratch for the splits' partial results comes from the allocator uninitialised: make
+        # sure the block it gets is full of NaN, as reused memory may be
+        vis = bound or max(lengths)
+        if window:
+            vis = min(vis, window + 15)
+        chunk, splits = A.plan_decode(n, Hkv, H // Hkv, vis)
+        poison = torch.full((int(A.lib_scratch(n, H, D, splits)) // 4,), float("nan"), dtype=torch.float32, device=DEV)
+        del poison
         out = torch.zeros((n, H * D), dtype=dt, device=DEV)
         A.attention_any(q, out, kc, vc, table.to(DEV), entry, positions, H, Hkv, D, P, window, scale,
                         q_lens=[1] * n, pos0=[L - 1 for L in lengths], kv_bound=bound)
