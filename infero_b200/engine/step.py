@@ -151,7 +151,8 @@ class ModelRunner:
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Run the batch; returns float32 logits [rows wanted, vocab] on the device, in the
-        order of the entries and of each entry's ``want`` (None if nothing is wanted).
+        order of the entries and of each entry's ``want`` (None if nothing is wanted).  A captured
+        decode step returns its graph's own output tensor: use or copy it before the next step.
         Raises OutOfPages (nothing reserved, nothing run) when the cache cannot hold it."""
         rcs = self._validate(entries)
         done: List[RequestCache] = []

@@ -46,11 +46,14 @@ def test_serving_sizes_bfloat16_against_32_bit(name):
         rows = []
         for i in toks:
             r.open(i)
-        rows.append(r.step([StepEntry(0, toks[0][:600], [0, 599]), StepEntry(1, toks[1][:290], [289])]))
-        rows.append(r.step([StepEntry(2, toks[2][:32], [31]), StepEntry(0, toks[0][600:690], [89])]))
+        # (a captured step returns its graph's own output tensor, which the next replay overwrites:
+        # every result is copied out at once)
+        rows.append(r.step([StepEntry(0, toks[0][:600], [0, 599]), StepEntry(1, toks[1][:290], [289])]).float().cpu())
+        rows.append(r.step([StepEntry(2, toks[2][:32], [31]), StepEntry(0, toks[0][600:690], [89])]).float().cpu())
         for k in range(10):                 # first eager, then captured and replayed
-            rows.append(r.step([StepEntry(0, [toks[0][690 + k]], [0]), StepEntry(1, [toks[1][290 + k]], [0])]))
-        out[dtype] = torch.cat([x.float().cpu() for x in rows])
+            rows.append(r.step([StepEntry(0, [toks[0][690 + k]], [0]),
+                                StepEntry(1, [toks[1][290 + k]], [0])]).float().cpu())
+        out[dtype] = torch.cat(rows)
         if dtype == "bfloat16":
             assert r.graph_replays >= 8
         del r, model
