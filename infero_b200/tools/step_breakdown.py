@@ -1,0 +1,123 @@
+"""What each class of kernel costs inside a captured decode step.
+
+    python -m infero_b200.tools.step_breakdown [--batch 8] [--context 3900] [--layers 28] [--steps 30]
+
+Kernels of a captured step overlap (programmatic dependent launch), so a profiler's serialised
+per-launch times do not add up to the step.  This tool measures the step as it runs, with CUDA
+events, once whole and once with each class of kernel left out, and reports the differences.
+The results of the shortened steps are garbage (and are thrown away); only their time is used.
+Sizes are Qwen2.5-7B's unless overridden; weights are random.
+"""
+from __future__ import annotations
+
+import argparse
+import random
+import sys
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="step_breakdown")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=3900)
+    ap.add_argument("--layers", type=int, default=28)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--hidden", type=int, default=3584)
+    ap.add_argument("--heads", type=int, default=28)
+    ap.add_argument("--kv-heads", type=int, default=4)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--intermediate", type=int, default=18944)
+    ap.add_argument("--vocab", type=int, default=152064)
+    args = ap.parse_args(argv)
+
+    import torch
+    from infero_b200 import kernels as K
+    from infero_b200.config import EngineConfig
+    from infero_b200.engine import ModelRunner, StepEntry
+    from infero_b200.kernels import attention as A
+    from infero_b200.kernels import tc_gemm
+    from infero_b200.loading import random_model
+
+    cfg = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "num_hidden_layers": args.layers,
+           "hidden_size": args.hidden, "num_attention_heads": args.heads, "num_key_value_heads": args.kv_heads,
+           "head_dim": args.head_dim, "intermediate_size": args.intermediate, "vocab_size": args.vocab,
+           "rope_theta": 1e6, "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "hidden_act": "silu",
+           "max_position_embeddings": 32768}
+    model, _ = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0", generate_on_device=True)
+    real = {"norm": K.add_rmsnorm, "rope": K.rope_cache_partials, "attn": A.paged_attention,
+            "partials": tc_gemm.partials, "swiglu": tc_gemm.gemm_swiglu}
+    da, dkv = args.heads * args.head_dim, args.kv_heads * args.head_dim
+    shapes = {"gemm_qkv": {(da + 2 * dkv, args.hidden)}, "gemm_o": {(args.hidden, da)},
+              "gemm_down": {(args.hidden, args.intermediate)}}
+    shapes["all_gemm"] = shapes["gemm_qkv"] | shapes["gemm_o"] | shapes["gemm_down"]
+
+    def restore():
+        K.add_rmsnorm, K.rope_cache_partials, A.paged_attention = real["norm"], real["rope"], real["attn"]
+        tc_gemm.partials, tc_gemm.gemm_swiglu = real["partials"], real["swiglu"]
+
+    def without(tag):
+        if tag == "norm":
+            K.add_rmsnorm = lambda *a, **k: None
+        elif tag == "rope":
+            K.rope_cache_partials = lambda *a, **k: None
+        elif tag == "attn":
+            A.paged_attention = lambda *a, **k: None
+        if tag in shapes:
+            skip = shapes[tag]
+
+            def fake(a, w):
+                if (w.shape[0], w.shape[1]) in skip:
+                    s, _, _ = tc_gemm.plan(a.shape[0], w.shape[0], w.shape[1], a.device)
+                    return torch.empty((s, a.shape[0], w.shape[0]), dtype=torch.float32, device=a.device)
+                return real["partials"](a, w)
+            tc_gemm.partials = fake
+        if tag in ("gemm_gate_up", "all_gemm"):
+            tc_gemm.gemm_swiglu = lambda a, w, out: True
+
+    B = args.batch
+    blocks = -(-(args.context + args.steps + 16) // 16)
+
+    def measure(tag):
+        restore()
+        runner = ModelRunner(model, EngineConfig(dtype="bfloat16", page_size=16, num_pages=B * blocks, max_seqs=B,
+                                                 ctx=blocks * 16, max_batch_tokens=2048, max_logit_rows=max(B, 8),
+                                                 cuda_graphs=True))
+        rng = random.Random(1)
+        for r in range(B):
+            runner.open(r)
+            done = 0
+            while done < args.context:
+                n = min(2048, args.context - done)
+                runner.step([StepEntry(r, [rng.randrange(args.vocab) for _ in range(n)], [])])
+                done += n
+        without(tag)
+        picked = torch.empty(B, dtype=torch.int32, device="cuda:0")
+
+        def one():
+            K.argmax(runner.step([StepEntry(r, [5], [0]) for r in range(B)]), picked)
+        for _ in range(4):
+            one()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            one()
+        e1.record()
+        torch.cuda.synchronize()
+        restore()
+        for r in range(B):
+            runner.close(r)
+        del runner
+        torch.cuda.empty_cache()
+        return e0.elapsed_time(e1) / args.steps
+
+    base = measure("none")
+    print(f"batch {B}, context {args.context}, {args.layers} layers: whole step {base:.3f} ms")
+    for tag in ("norm", "rope", "attn", "gemm_qkv", "gemm_o", "gemm_gate_up", "gemm_down", "all_gemm"):
+        ms = measure(tag)
+        print(f"  without {tag:13s} {ms:.3f} ms: costs {1000 * (base - ms) / args.layers:6.1f} us per layer "
+              f"({100 * (base - ms) / base:4.1f} % of the step)")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
