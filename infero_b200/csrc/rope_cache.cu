@@ -228,51 +228,56 @@ rope_cache_partials_vec_kernel(const float* __restrict__ partial, int splits, lo
         u.y = *reinterpret_cast<uint32_t*>(&b);
         *reinterpret_cast<uint2*>(p) = u;
     };
+    // work items: rotated chunks of q and k heads, unrotated tails, chunks of v; the blocks of a
+    // token (gridDim.y of them) share the items so that every thread has about one
     const int hc = half >> 2;                      // chunks of 4 pairs per head
     const int rot_items = (n_heads + n_kv) * hc;
-    for (int it = threadIdx.x; it < rot_items; it += blockDim.x) {
-        const int h = it / hc, c = it - h * hc;
-        bf16* dst;
-        if (h < n_heads) {
-            dst = q_out + (size_t)t * q_stride + (size_t)h * head_dim + c * 4;
-        } else {
-            if (page < 0) continue;
-            dst = k_cache + ((size_t)page * n_kv + (h - n_heads)) * page_size * head_dim + in_page + c * 4;
-        }
-        float a[4], b[4], ra[4], rb[4];
-        sum4((size_t)h * head_dim + c * 4, a);
-        sum4((size_t)h * head_dim + half + c * 4, b);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const float2 s1 = sc[c * 4 + k];
-            ra[k] = a[k] * s1.y - b[k] * s1.x;
-            rb[k] = a[k] * s1.x + b[k] * s1.y;
-        }
-        store4bf(dst, ra);
-        store4bf(dst + half, rb);
-    }
-    // not rotated: the tail of q and k heads beyond rotary_dim, and v
     const int tail = (head_dim - rotary_dim) >> 2, dc = head_dim >> 2;
     const int tail_items = (n_heads + n_kv) * tail;
-    for (int it = threadIdx.x; it < tail_items; it += blockDim.x) {
-        const int h = it / tail, c = it - h * tail;
-        bf16* dst;
-        if (h < n_heads) {
-            dst = q_out + (size_t)t * q_stride + (size_t)h * head_dim + rotary_dim + c * 4;
+    const int v_items = n_kv * dc;
+    const int total = rot_items + tail_items + v_items;
+    for (int it0 = blockIdx.y * blockDim.x + threadIdx.x; it0 < total; it0 += gridDim.y * blockDim.x) {
+        if (it0 < rot_items) {
+            const int h = it0 / hc, c = it0 - h * hc;
+            bf16* dst;
+            if (h < n_heads) {
+                dst = q_out + (size_t)t * q_stride + (size_t)h * head_dim + c * 4;
+            } else {
+                if (page < 0) continue;
+                dst = k_cache + ((size_t)page * n_kv + (h - n_heads)) * page_size * head_dim + in_page + c * 4;
+            }
+            float a[4], b[4], ra[4], rb[4];
+            sum4((size_t)h * head_dim + c * 4, a);
+            sum4((size_t)h * head_dim + half + c * 4, b);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 s1 = sc[c * 4 + k];
+                ra[k] = a[k] * s1.y - b[k] * s1.x;
+                rb[k] = a[k] * s1.x + b[k] * s1.y;
+            }
+            store4bf(dst, ra);
+            store4bf(dst + half, rb);
+        } else if (it0 < rot_items + tail_items) {
+            const int it = it0 - rot_items;
+            const int h = it / tail, c = it - h * tail;
+            bf16* dst;
+            if (h < n_heads) {
+                dst = q_out + (size_t)t * q_stride + (size_t)h * head_dim + rotary_dim + c * 4;
+            } else {
+                if (page < 0) continue;
+                dst = k_cache + ((size_t)page * n_kv + (h - n_heads)) * page_size * head_dim + in_page + rotary_dim + c * 4;
+            }
+            float v[4];
+            sum4((size_t)h * head_dim + rotary_dim + c * 4, v);
+            store4bf(dst, v);
         } else {
             if (page < 0) continue;
-            dst = k_cache + ((size_t)page * n_kv + (h - n_heads)) * page_size * head_dim + in_page + rotary_dim + c * 4;
+            const int it = it0 - rot_items - tail_items;
+            const int kvh = it / dc, c = it - kvh * dc;
+            float v[4];
+            sum4((size_t)(n_heads + n_kv + kvh) * head_dim + c * 4, v);
+            store4bf(v_cache + ((size_t)page * n_kv + kvh) * page_size * head_dim + in_page + c * 4, v);
         }
-        float v[4];
-        sum4((size_t)h * head_dim + rotary_dim + c * 4, v);
-        store4bf(dst, v);
-    }
-    if (page < 0) return;
-    for (int it = threadIdx.x; it < n_kv * dc; it += blockDim.x) {
-        const int kvh = it / dc, c = it - kvh * dc;
-        float v[4];
-        sum4((size_t)(n_heads + n_kv + kvh) * head_dim + c * 4, v);
-        store4bf(v_cache + ((size_t)page * n_kv + kvh) * page_size * head_dim + in_page + c * 4, v);
     }
 }
 
@@ -327,7 +332,11 @@ int infero_rope_cache_partials(const float* partial, int splits, long long split
     auto al = [](const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; };
     if (dtype == INFERO_BF16 && rotary_dim % 8 == 0 && head_dim % 4 == 0 && q_stride % 4 == 0 && width % 4 == 0 &&
         split_stride % 4 == 0 && al(partial, 16) && al(q_out, 8) && al(k_cache, 8) && al(v_cache, 8)) {
-        launch_pdl(rope_cache_partials_vec_kernel, dim3(n_tokens), dim3(256), (size_t)(rotary_dim / 2) * sizeof(float2),
+        const int items = (n_heads + n_kv) * (head_dim / 4) + n_kv * (head_dim / 4) - (n_heads + n_kv) * (rotary_dim / 8);
+        int by = (items + 255) / 256;
+        if (by > 16) by = 16;
+        if (by < 1) by = 1;
+        launch_pdl(rope_cache_partials_vec_kernel, dim3(n_tokens, by), dim3(256), (size_t)(rotary_dim / 2) * sizeof(float2),
                    stream, partial, splits, split_stride, width, bias, bias_dtype, (bf16*)q_out, q_stride, positions,
                    tok_entry, block_table, max_blocks, inv_freq, rotary_dim, (bf16*)k_cache, (bf16*)v_cache, page_size,
                    n_heads, n_kv, head_dim, write_cache);
