@@ -38,6 +38,61 @@ struct TdPlan {
     static constexpr int TOTAL = DATA_BYTES + TD_WARPS * STAGES * 8 + 16 + 1024;
 };
 
+// The CTA that finishes last among the splits of one (token, kv head, group tile) merges them:
+// out[t, h, :] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), M = max_s m_s.  Every CTA of the
+// launch calls this after its partial result is written; `counter` counts the arrivals and is
+// set back to zero by the last one, so the same (zeroed once) array serves every launch.
+// Splits without keys wrote (m, l) = (-inf, 0) and no output: they are left out, not multiplied
+// by zero (what lies in the scratch there may be NaN).
+template <int D>
+__device__ __forceinline__ void merge_if_last(int* counter, float* wbuf, const float* po_base, const float* pml_base,
+                                              int n_splits, int valid, bf16* out_rows) {
+    __shared__ int s_last;
+    __threadfence();                                   // this thread's partial results, before the count
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int old = atomicAdd(counter, 1);
+        s_last = old == n_splits - 1;
+        if (s_last) *counter = 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* linv = wbuf + 16 * n_splits;
+    for (int r = warp; r < valid; r += TD_WARPS) {
+        const float* ml = pml_base + (size_t)r * n_splits * 2;
+        float M = -CUDART_INF_F;
+        for (int s = lane; s < n_splits; s += 32) M = fmaxf(M, __ldcg(ml + s * 2));
+        M = warp_max(M);
+        float L = 0.f;
+        for (int s = lane; s < n_splits; s += 32) {
+            const float ms = __ldcg(ml + s * 2);
+            const float w = ms == -CUDART_INF_F ? 0.f : exp2f(ms - M);
+            wbuf[r * n_splits + s] = w;
+            L += __ldcg(ml + s * 2 + 1) * w;
+        }
+        L = warp_sum(L);
+        if (lane == 0) linv[r] = 1.0f / L;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < valid * (D / 2); idx += TD_THREADS) {
+        const int r = idx / (D / 2), d = (idx - r * (D / 2)) * 2;
+        const float* pob = po_base + (size_t)r * n_splits * D + d;
+        float a0 = 0.f, a1 = 0.f;
+#pragma unroll 4
+        for (int s = 0; s < n_splits; ++s) {
+            const float ws = wbuf[r * n_splits + s];
+            float2 v = __ldcg(reinterpret_cast<const float2*>(pob + (size_t)s * D));
+            if (ws == 0.f) v = make_float2(0.f, 0.f);
+            a0 = fmaf(v.x, ws, a0);
+            a1 = fmaf(v.y, ws, a1);
+        }
+        const float inv = linv[r];
+        *reinterpret_cast<uint32_t*>(out_rows + (size_t)r * D + d) = pack_bf16(a0 * inv, a1 * inv);
+    }
+}
+
 // partial_o [n_tok, n_heads, n_splits, D] float (unnormalised), partial_ml [n_tok, n_heads, n_splits, 2].
 template <int D>
 __global__ void __launch_bounds__(TD_THREADS)
@@ -46,6 +101,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                        int max_blocks, const int* __restrict__ tok_entry, const int* __restrict__ positions,
                        int tok_first, int n_heads, int n_kv, int page_size, int window, float scale_log2,
                        int chunk, int n_splits, float* __restrict__ partial_o, float* __restrict__ partial_ml,
+                       bf16* __restrict__ out, int out_stride, int* __restrict__ counters,
                        int* __restrict__ err_flag) {
     using Plan = TdPlan<D>;
     using Layout = Swizzled128<D, 16>;
@@ -92,6 +148,10 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             pml[(size_t)r * n_splits * 2] = -CUDART_INF_F;
             pml[(size_t)r * n_splits * 2 + 1] = 0.f;
         }
+        if (counters)
+            merge_if_last<D>(counters + (size_t)ti * gridDim.y + blockIdx.y, reinterpret_cast<float*>(smem),
+                             po - (size_t)split * D, pml - (size_t)split * 2, n_splits, valid,
+                             out + (size_t)t * out_stride + (size_t)h0 * D);
         return;
     }
     __syncthreads();
@@ -201,6 +261,10 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             pml[(size_t)r * n_splits * 2 + 1] = ll;
         }
     }
+    if (counters)                                      // (its first barrier also ends the reads of red_o above)
+        merge_if_last<D>(counters + (size_t)ti * gridDim.y + blockIdx.y, reinterpret_cast<float*>(smem),
+                         po - (size_t)split * D, pml - (size_t)split * 2, n_splits, valid,
+                         out + (size_t)t * out_stride + (size_t)h0 * D);
 }
 
 // out[t, h, :] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), M = max_s m_s; splits in
@@ -253,7 +317,7 @@ template <int D>
 int launch_tma(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, int q_stride, const int* block_table,
                int max_blocks, const int* tok_entry, const int* positions, int tok_first, int n_tok, int n_heads,
                int n_kv, int page_size, int window, float scale_log2, int chunk, int n_splits, float* po, float* pml,
-               int* err, cudaStream_t stream) {
+               void* out, int out_stride, int* counters, int* err, cudaStream_t stream) {
     using Plan = TdPlan<D>;
     auto kern = attn_decode_tma_kernel<D>;
     static bool configured = false;
@@ -269,7 +333,7 @@ int launch_tma(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, int 
     dim3 grid(n_splits, n_kv * ((group + 15) / 16), n_tok);
     launch_pdl(kern, grid, dim3(TD_THREADS), Plan::TOTAL, stream, mk, mv, (const bf16*)q, q_stride, block_table,
                max_blocks, tok_entry, positions, tok_first, n_heads, n_kv, page_size, window, scale_log2, chunk,
-               n_splits, po, pml, err);
+               n_splits, po, pml, (bf16*)out, out_stride, counters, err);
     return infero_check_launch("attn_decode_tma");
 }
 
@@ -283,12 +347,14 @@ int infero_attn_decode_tma_supported(int head_dim, int page_size) {
 
 // The same contract as infero_attn_decode (attention_mma.cu), plus num_pages: the caches are
 // [num_pages, n_kv, page_size, head_dim] bf16, contiguous and 16-byte aligned.  n_splits is
-// at most 256.  scratch: infero_attn_decode_scratch bytes.
+// at most 256.  scratch: infero_attn_decode_scratch bytes.  counters: n_counters ints, zero before the
+// first call (each launch leaves them zero again), at least n_tok * n_kv * ceil(group / 16); with
+// them the last CTA of every group of splits merges the group; without (null) a second kernel does.
 int infero_attn_decode_tma(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
                            const void* v_cache, int num_pages, const int* block_table, int max_blocks,
                            const int* tok_entry, const int* positions, int tok_first, int n_tok, int n_heads,
                            int n_kv, int head_dim, int page_size, int window, float scale, int chunk, int n_splits,
-                           void* scratch, cudaStream_t stream) {
+                           void* scratch, int* counters, int n_counters, cudaStream_t stream) {
     if (n_tok == 0) return 0;
     INFERO_REQUIRE(infero_attn_decode_tma_supported(head_dim, page_size),
                    "attn_decode_tma: head_dim %d / page_size %d not supported", head_dim, page_size);
@@ -304,17 +370,23 @@ int infero_attn_decode_tma(const void* q, int q_stride, void* out, int out_strid
     if (infero_tensor_map_bf16(v_cache, rows, head_dim, head_dim, 16, &mv)) return 1;
     int* err;
     if (infero_tc_err_flag(&err)) return 1;
+    if (counters) {
+        const int groups = n_tok * n_kv * ((n_heads / n_kv + 15) / 16);
+        INFERO_REQUIRE(groups <= n_counters, "attn_decode_tma: %d arrival counters needed, %d given", groups, n_counters);
+    }
     const float sl2 = scale * 1.4426950408889634f;
     float* po = (float*)scratch;
     float* pml = po + (size_t)n_tok * n_heads * n_splits * head_dim;
     int rc;
     if (head_dim == 128)
         rc = launch_tma<128>(mk, mv, q, q_stride, block_table, max_blocks, tok_entry, positions, tok_first, n_tok,
-                             n_heads, n_kv, page_size, window, sl2, chunk, n_splits, po, pml, err, stream);
+                             n_heads, n_kv, page_size, window, sl2, chunk, n_splits, po, pml, out, out_stride, counters,
+                             err, stream);
     else
         rc = launch_tma<64>(mk, mv, q, q_stride, block_table, max_blocks, tok_entry, positions, tok_first, n_tok,
-                            n_heads, n_kv, page_size, window, sl2, chunk, n_splits, po, pml, err, stream);
-    if (rc) return rc;
+                            n_heads, n_kv, page_size, window, sl2, chunk, n_splits, po, pml, out, out_stride, counters,
+                            err, stream);
+    if (rc || counters) return rc;                     // merged by the last CTA of every group
     const int warps = n_tok * n_heads;
     launch_pdl(attn_combine_kernel, dim3((warps + 3) / 4), dim3(128), 0, stream, (const float*)po, (const float*)pml,
                (bf16*)out, out_stride, tok_first, n_tok, n_heads, n_splits, head_dim);

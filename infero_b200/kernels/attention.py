@@ -41,6 +41,18 @@ def plan_decode(n_tok: int, n_kv: int, group: int, max_visible: int) -> Tuple[in
     return chunk, splits
 
 
+_COUNTERS = {}
+N_COUNTERS = 1 << 16
+
+
+def _arrival_counters(device) -> torch.Tensor:
+    """Zeroed ints the decode kernel counts finished splits in (every launch leaves them zero)."""
+    key = str(device)
+    if key not in _COUNTERS:
+        _COUNTERS[key] = torch.zeros(N_COUNTERS, dtype=torch.int32, device=device)
+    return _COUNTERS[key]
+
+
 def decode(q, out, k_cache, v_cache, table, tok_entry, positions, tok_first: int, n_tok: int, n_heads: int,
            n_kv: int, head_dim: int, page_size: int, window: Optional[int], scale: float, chunk: int,
            n_splits: int) -> None:
@@ -53,7 +65,8 @@ def decode(q, out, k_cache, v_cache, table, tok_entry, positions, tok_first: int
             c_int(k_cache.shape[0]), _ptr(_i32(table, "block_table")), c_int(table.shape[1]),
             _ptr(_i32(tok_entry, "tok_entry")), _ptr(_i32(positions, "positions")), c_int(tok_first), c_int(n_tok),
             c_int(n_heads), c_int(n_kv), c_int(head_dim), c_int(page_size), c_int(window or 0), c_float(scale),
-            c_int(chunk), c_int(n_splits), _ptr(scratch), _stream()))
+            c_int(chunk), c_int(n_splits), _ptr(scratch), _ptr(_arrival_counters(q.device)), c_int(N_COUNTERS),
+            _stream()))
         return
     _check(lib().infero_attn_decode(_ptr(q), c_int(q.stride(0)), _ptr(out), c_int(out.stride(0)), _ptr(k_cache),
                                     _ptr(v_cache), _ptr(_i32(table, "block_table")), c_int(table.shape[1]),
