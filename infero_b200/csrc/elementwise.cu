@@ -13,11 +13,15 @@ namespace {
 
 template <typename TE>
 __global__ void embed_gather_kernel(const TE* __restrict__ table, const int* __restrict__ ids,
-                                    float* __restrict__ x, int d, int vocab, float scale) {
+                                    const int* __restrict__ device_tokens, float* __restrict__ x, int d, int vocab,
+                                    float scale) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
     int id = ids[t];
+    // a negative id -(s + 1) stands for "the token the sampler left in device_tokens[s]": the step
+    // was launched before the host had seen that token
+    if (id < 0 && device_tokens) id = device_tokens[-id - 1];
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);   // ids are validated on the host
     const TE* row = table + (size_t)id * d;
     float* o = x + (size_t)t * d;
@@ -231,15 +235,15 @@ __global__ void residual_add_kernel(float* __restrict__ x, const TD* __restrict_
 
 extern "C" {
 
-int infero_embed_gather(const void* table, int table_dtype, const int* ids, float* x,
+int infero_embed_gather(const void* table, int table_dtype, const int* ids, const int* device_tokens, float* x,
                         int n_tokens, int d, int vocab, float scale, cudaStream_t stream) {
     if (n_tokens == 0) return 0;
     INFERO_REQUIRE(d > 0 && vocab > 0, "embed_gather: bad sizes d=%d vocab=%d", d, vocab);
     const int threads = d >= 256 ? 256 : 64;
     if (table_dtype == INFERO_F32)
-        launch_pdl(embed_gather_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)table, ids, x, d, vocab, scale);
+        launch_pdl(embed_gather_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)table, ids, device_tokens, x, d, vocab, scale);
     else
-        launch_pdl(embed_gather_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, (const bf16*)table, ids, x, d, vocab, scale);
+        launch_pdl(embed_gather_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, (const bf16*)table, ids, device_tokens, x, d, vocab, scale);
     return infero_check_launch("embed_gather");
 }
 

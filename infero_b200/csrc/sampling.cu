@@ -109,6 +109,20 @@ argmax_final_kernel(const float* __restrict__ pv, const int* __restrict__ pi, in
     if (lane == 0) out[row] = (idx == 0x7fffffff) ? 0 : idx;   // all -inf / NaN: token 0
 }
 
+// final[r] = use_sample[r] ? sampled[r] : greedy[r];  device_tokens[slot[r]] = final[r]: the
+// sampler's picks, left on the device for a step that is launched before the host reads them.
+__global__ void keep_tokens_kernel(const int* __restrict__ greedy, const int* __restrict__ sampled,
+                                   const int* __restrict__ use_sample, const int* __restrict__ slot,
+                                   int* __restrict__ final_tok, int* __restrict__ device_tokens, int n_rows) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= n_rows) return;
+    const int tok = (sampled && use_sample[r]) ? sampled[r] : greedy[r];
+    final_tok[r] = tok;
+    if (slot[r] >= 0) device_tokens[slot[r]] = tok;
+}
+
 // Exclusive prefix sum of one int per thread over the block; returns the total too.
 __device__ __forceinline__ int block_exclusive_scan(int v, int* total, int* warp_sums) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -298,6 +312,15 @@ int infero_sample(const float* logits, int n_rows, int vocab, const float* tempe
     INFERO_REQUIRE(vocab > 0, "sample: empty vocabulary");
     sample_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, vocab, temperature, top_k, top_p, draw, out);
     return infero_check_launch("sample");
+}
+
+// rows_info: [n_rows] slot per row, then [n_rows] use_sample flags.  final_tok [n_rows].
+int infero_keep_tokens(const int* greedy, const int* sampled, const int* rows_info, int* final_tok,
+                       int* device_tokens, int n_rows, cudaStream_t stream) {
+    if (n_rows == 0) return 0;
+    launch_pdl(keep_tokens_kernel, dim3((n_rows + 127) / 128), dim3(128), 0, stream, greedy, sampled,
+               rows_info + n_rows, rows_info, final_tok, device_tokens, n_rows);
+    return infero_check_launch("keep_tokens");
 }
 
 int infero_sample_max_k() { return SAMPLE_MAX_K; }

@@ -13,7 +13,7 @@ from typing import Any, Dict, Hashable, List, Optional, Sequence
 import torch
 
 from ..config.engine_config import EngineConfig
-from ..sampling import SamplingParams, sample_rows
+from ..sampling import ReadyTokens, SamplingParams, sample_rows_async
 from .scheduler import Event, PlanItem, Request, Scheduler
 from .step import ModelRunner, StepEntry
 
@@ -42,7 +42,7 @@ class Engine:
                  kv_slots: Optional[int] = None, gpu_memory_fraction: Optional[float] = None,
                  max_batch_tokens: int = 2048, page_size: int = 16, device: str = "cuda:0",
                  cuda_graphs: bool = True, max_prefill_chunk: Optional[int] = None,
-                 generate_on_device: bool = False, model=None):
+                 generate_on_device: bool = False, model=None, run_ahead: bool = True):
         from .. import kernels
         from ..loading import load_model, random_model
         if not torch.cuda.is_available():
@@ -68,7 +68,7 @@ class Engine:
                                 seed=seed, cuda_graphs=cuda_graphs, device=device)
         self.runner = ModelRunner(self.model, self.cfg)
         self.scheduler = Scheduler(self.runner.manager, self._execute, max_seqs, max_batch_tokens, ctx,
-                                   max_prefill_chunk=max_prefill_chunk)
+                                   max_prefill_chunk=max_prefill_chunk, launch=self._launch, run_ahead=run_ahead)
         self._ids = itertools.count()
         self.eos_token_ids = tuple(self.model.spec.eos_token_ids)
 
@@ -128,11 +128,18 @@ class Engine:
     def forward(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         return self.runner.step(entries)
 
-    def _execute(self, items: List[PlanItem]) -> List[int]:
+    def _launch(self, items: List[PlanItem]):
+        """Run a planned batch and sample; returns at once with the tokens still on their way
+        (``.result()`` waits).  The picks also stay on the device, per request slot, for a step
+        launched before they are read."""
         entries = [StepEntry(it.run.req.rid, it.tokens, [len(it.tokens) - 1] if it.samples else [])
                    for it in items]
         logits = self.runner.step(entries)
         rows = [it for it in items if it.samples]
         if not rows:
-            return []
-        return sample_rows(logits, [it.run.sampler for it in rows], [it.run.generated for it in rows])
+            return ReadyTokens([])
+        return sample_rows_async(logits, [it.run.sampler for it in rows], [it.run.generated for it in rows],
+                                 [it.run.rc.slot for it in rows], self.runner.device_tokens)
+
+    def _execute(self, items: List[PlanItem]) -> List[int]:
+        return self._launch(items).result()

@@ -18,6 +18,16 @@ youngest running request is preempted by recompute: its pages are freed and it r
 to the front of the queue with prompt + generated tokens as its new prompt (its sampler
 state and output so far are kept); (4) a request that cannot proceed even alone (it
 holds the whole pool) finishes with reason "length".
+
+Running ahead.  With a ``launch`` function (steps that return before their tokens have reached the
+host) the scheduler keeps one step in flight: while step k runs it launches step k+1 for the
+same requests, feeding each the token step k is about to pick, which the sampler leaves on the
+device.  It does so only when nothing can change the batch behind its back: every running
+request is decoding, none reaches its length limit at step k, none samples with a repetition
+penalty (that needs the token on the host), nobody waits for admission, and pages for one more
+token each are free.  A request that ends at step k on an end-of-sequence token has then run
+one token too far; that token is dropped.  (The reference's scheduler reads every step's tokens
+before it plans the next, crates/server/src/scheduler.rs:1268-1429.)
 """
 from __future__ import annotations
 
@@ -27,7 +37,7 @@ from typing import Callable, Deque, Dict, Hashable, List, Optional, Sequence, Tu
 
 from ..cache import CacheManager, OutOfPages, RequestCache
 from ..sampling import RowSampler, SamplingParams
-from .step import StepEntry
+from .step import FROM_DEVICE, StepEntry
 
 
 @dataclass
@@ -51,6 +61,7 @@ class Running:
     pending: Optional[int] = None          # sampled, not yet fed
     admitted_at: int = 0
     preemptions: int = 0
+    finished: bool = False
 
 
 @dataclass
@@ -70,14 +81,34 @@ class PlanItem:
     is_decode: bool
 
 
+class _Done:
+    """Tokens that are already here (a synchronous ``execute``)."""
+
+    def __init__(self, tokens):
+        self._tokens = list(tokens)
+
+    def result(self):
+        return self._tokens
+
+
+@dataclass
+class _InFlight:
+    items: List[PlanItem]
+    pending: object                        # .result() -> one token per sampling item
+
+
 class Scheduler:
     """``execute(items) -> tokens`` runs a planned batch and returns one sampled token per
     item with ``samples`` set, in order.  The engine supplies it; tests supply a fake."""
 
     def __init__(self, manager: CacheManager, execute: Callable[[List[PlanItem]], List[int]],
-                 max_seqs: int, max_batch_tokens: int, ctx: int, max_prefill_chunk: Optional[int] = None):
+                 max_seqs: int, max_batch_tokens: int, ctx: int, max_prefill_chunk: Optional[int] = None,
+                 launch: Optional[Callable[[List[PlanItem]], object]] = None, run_ahead: bool = True):
         self.manager = manager
         self.execute = execute
+        self.launch = launch                   # like execute, but returns an object with .result()
+        self.run_ahead = run_ahead and launch is not None
+        self._inflight: Optional[_InFlight] = None
         self.max_seqs = max_seqs
         self.max_batch_tokens = max_batch_tokens
         self.ctx = ctx
@@ -86,7 +117,7 @@ class Scheduler:
         self.running: List[Running] = []
         self.clock = 0
         self.stats = {"steps": 0, "preemptions": 0, "decode_tokens": 0, "prefill_tokens": 0,
-                      "rejected": 0, "finished": 0}
+                      "rejected": 0, "finished": 0, "steps_ahead": 0, "tokens_dropped": 0}
         self._events: List[Event] = []
 
     # ---- queue ------------------------------------------------------------------------------
@@ -103,7 +134,7 @@ class Scheduler:
         self.waiting.append(req)
 
     def is_idle(self) -> bool:
-        return not self.waiting and not self.running and not self._events
+        return not self.waiting and not self.running and not self._events and self._inflight is None
 
     # ---- admission ----------------------------------------------------------------------------
     def _pages_for(self, n_tokens: int) -> int:
@@ -202,26 +233,46 @@ class Scheduler:
         return True
 
     # ---- one step -----------------------------------------------------------------------------
-    def step(self) -> List[Event]:
-        events, self._events = self._events, []
-        self._admit()
-        events += self._events
-        self._events = []
-        if not self.running:
-            return events
-        items = self._plan()
-        while not items:
-            if not self._preempt_youngest():
-                # a single request that cannot move: the cache is full for it
-                run = self.running[0]
-                events.append(self._finish(run, "length", "cache exhausted"))
-                return events
-            items = self._plan()
-        sampled = self.execute(items)
+    def _start(self, items: List[PlanItem]) -> _InFlight:
+        pending = self.launch(items) if self.launch is not None else _Done(self.execute(items))
         self.stats["steps"] += 1
+        return _InFlight(items, pending)
+
+    def _can_run_ahead(self, cur: _InFlight) -> bool:
+        """May the step after ``cur`` be launched before ``cur``'s tokens are known?"""
+        if not self.run_ahead or self.waiting or len(cur.items) != len(self.running):
+            return False
+        for it in cur.items:
+            run, req = it.run, it.run.req
+            if not it.samples or run.finished:
+                return False                                   # a prompt is still being fed
+            if req.params.repetition_penalty != 1.0:
+                return False                                   # the penalty needs the token on the host
+            if len(run.generated) + 2 > req.max_new_tokens or len(req.prompt) + len(run.generated) + 2 > self.ctx:
+                return False                                   # it ends at ``cur`` or at the step after
+        n_groups = len(self.manager.groups)
+        used = [0] * n_groups
+        for it in cur.items:
+            need = self.manager.pages_needed(it.run.rc, 1)
+            for g in range(n_groups):
+                used[g] += need[g]
+        return all(used[g] <= self.manager.free_pages(g) for g in range(n_groups)) \
+            and len(cur.items) <= self.max_batch_tokens
+
+    def _complete(self, cur: _InFlight) -> List[Event]:
+        """Wait for the step's tokens and advance its requests."""
+        sampled = cur.pending.result()
+        events: List[Event] = []
         k = 0
-        for it in items:
+        for it in cur.items:
             run = it.run
+            tok = None
+            if it.samples:
+                tok = int(sampled[k])
+                k += 1
+            if run.finished:                       # ended a step earlier: this one ran a token too far
+                self.stats["tokens_dropped"] += 1
+                continue
             if it.is_decode:
                 run.pending = None
                 run.tokens.append(it.tokens[0])
@@ -231,11 +282,48 @@ class Scheduler:
                 run.fed += len(it.tokens)
                 self.stats["prefill_tokens"] += len(it.tokens)
             if it.samples:
-                tok = int(sampled[k])
-                k += 1
                 ev = self._advance(run, tok)
                 if ev is not None:
                     events.append(ev)
+        return events
+
+    def step(self) -> List[Event]:
+        events, self._events = self._events, []
+        if self._inflight is None:
+            self._admit()
+            events += self._events
+            self._events = []
+            if not self.running:
+                return events
+            items = self._plan()
+            while not items:
+                if not self._preempt_youngest():
+                    # a single request that cannot move: the cache is full for it
+                    run = self.running[0]
+                    events.append(self._finish(run, "length", "cache exhausted"))
+                    return events
+                items = self._plan()
+            self._inflight = self._start(items)
+        cur = self._inflight
+        ahead = None
+        if self._can_run_ahead(cur):
+            # every request decodes on: feed each the token ``cur`` is picking, from the device
+            ahead = self._start([PlanItem(it.run, [FROM_DEVICE], samples=True, is_decode=True) for it in cur.items])
+            self.stats["steps_ahead"] += 1
+        events += self._complete(cur)
+        if ahead is not None:
+            for it in ahead.items:                 # now the host knows what was fed
+                if not it.run.finished:
+                    it.tokens = [it.run.pending]
+        self._inflight = ahead
+        return events
+
+    def drain(self) -> List[Event]:
+        """Complete what is in flight (before aborting, or at the end)."""
+        events: List[Event] = []
+        while self._inflight is not None:
+            cur, self._inflight = self._inflight, None
+            events += self._complete(cur)
         return events
 
     def _advance(self, run: Running, tok: int) -> Optional[Event]:
@@ -255,6 +343,7 @@ class Scheduler:
         return Event(req.rid, tok)
 
     def _finish(self, run: Running, reason: str, message: Optional[str] = None) -> Event:
+        run.finished = True
         if run in self.running:
             self.running.remove(run)
         if run.req.rid in self.manager.requests:
@@ -265,6 +354,10 @@ class Scheduler:
     def abort_all(self, message: str) -> List[Event]:
         """A failed step fails every running and waiting request (crates/server/src/scheduler.rs:2314-2322)."""
         events = []
+        try:
+            self.drain()
+        except Exception:                           # noqa: BLE001  (the step that failed)
+            self._inflight = None
         for run in list(self.running):
             events.append(self._finish(run, "error", message))
         while self.waiting:

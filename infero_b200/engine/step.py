@@ -21,6 +21,11 @@ from ..config.engine_config import EngineConfig
 from ..models.decoder import DecoderModel
 
 
+# As a token of a single-token entry: "the token the sampler picked for this request in the
+# step before, which is still on the device" (``ModelRunner.device_tokens[slot]``).
+FROM_DEVICE = -1
+
+
 class StepError(ValueError):
     """A batch the step function refuses (nothing was run, nothing was reserved)."""
 
@@ -59,6 +64,7 @@ class StepContext:
         self.max_q_len = 0
         self.max_kv_len = 0
         self.kv_bound: Optional[int] = None     # plan decode attention for this many keys (captured steps)
+        self.device_tokens: torch.Tensor = runner.device_tokens
         self._empty_f32 = None
 
     def kv_cache(self, slot: int):
@@ -92,6 +98,8 @@ class ModelRunner:
                                     cfg.max_seqs, self.act_dtype, self.device)
         self.manager = CacheManager(self.storage.bookkeeping_groups(), self.num_pages, cfg.page_size,
                                     cfg.max_seqs, max_blocks=self.max_blocks)
+        # the sampler's last pick per request slot, for steps launched before the host has read it
+        self.device_tokens = torch.zeros(max(1, cfg.max_seqs), dtype=torch.int32, device=self.device)
         self.steps_run = 0
         self.tokens_run = 0
         # captured decode steps: (entries, key bound) -> _DecodeGraph; a shape is run eagerly the
@@ -138,7 +146,7 @@ class ModelRunner:
                 if not (0 <= int(w) < n):
                     raise StepError(f"request {e.rid!r}: wanted place {w} outside its {n} tokens")
             for tkn in e.tokens:
-                if not (0 <= int(tkn) < vocab):
+                if not (0 <= int(tkn) < vocab) and not (n == 1 and int(tkn) == FROM_DEVICE):
                     raise StepError(f"request {e.rid!r}: token id {tkn} outside the vocabulary of {vocab}")
             total += n
             rows += len(e.want)
@@ -202,11 +210,13 @@ class ModelRunner:
         slots = np.fromiter((rc.slot for rc in rcs), dtype=np.int32, count=E)
         if T == E:
             token_ids = np.fromiter((e.tokens[0] for e in entries), dtype=np.int32, count=E)
+            token_ids = np.where(token_ids < 0, -(slots + 1), token_ids)      # FROM_DEVICE -> -(slot + 1)
             tok_entry = np.arange(E, dtype=np.int32)
             positions = pos0
         else:
             token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
             tok_entry = np.repeat(np.arange(E, dtype=np.int32), lens)
+            token_ids = np.where(token_ids < 0, -(slots[tok_entry] + 1), token_ids)
             positions = np.arange(T, dtype=np.int32) - np.repeat(q_start, lens) + np.repeat(pos0, lens)
         want_rows = [q_start[i] + np.asarray(e.want, dtype=np.int32) for i, e in enumerate(entries) if len(e.want)]
         rows = np.concatenate(want_rows).astype(np.int32) if want_rows else np.zeros(0, dtype=np.int32)

@@ -81,13 +81,16 @@ def _i32(t: torch.Tensor, name: str) -> torch.Tensor:
 
 
 # ---- embedding, norms, elementwise ---------------------------------------------------------
-def embed_gather(table: torch.Tensor, ids: torch.Tensor, out_x: torch.Tensor, scale: float = 1.0) -> None:
-    """out_x[t,:] = table[ids[t],:] * scale, out_x float32 [T, d]."""
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out_x: torch.Tensor, scale: float = 1.0,
+                 device_tokens: Optional[torch.Tensor] = None) -> None:
+    """out_x[t,:] = table[ids[t],:] * scale, out_x float32 [T, d].  An id -(s + 1) is replaced
+    by device_tokens[s] (the token a sampler left on the device) when that array is given."""
     T, d = out_x.shape
     assert out_x.dtype == torch.float32 and out_x.is_contiguous() and table.is_contiguous()
     assert table.shape[1] == d and ids.numel() == T
-    _check(lib().infero_embed_gather(_ptr(table), c_int(_dt(table)), _ptr(_i32(ids, "ids")), _ptr(out_x),
-                                     c_int(T), c_int(d), c_int(table.shape[0]), c_float(scale), _stream()))
+    _check(lib().infero_embed_gather(_ptr(table), c_int(_dt(table)), _ptr(_i32(ids, "ids")),
+                                     _ptr(None if device_tokens is None else _i32(device_tokens, "device_tokens")),
+                                     _ptr(out_x), c_int(T), c_int(d), c_int(table.shape[0]), c_float(scale), _stream()))
 
 
 class Partials:
@@ -271,6 +274,16 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
     assert temperature.dtype == torch.float32 and top_p.dtype == torch.float32 and draw.dtype == torch.float64
     _check(lib().infero_sample(_ptr(logits), c_int(R), c_int(V), _ptr(temperature), _ptr(_i32(top_k, "top_k")),
                                _ptr(top_p), _ptr(draw), _ptr(_i32(out, "out")), _stream()))
+
+
+def keep_tokens(greedy: torch.Tensor, sampled: Optional[torch.Tensor], rows_info: torch.Tensor,
+                final_tok: torch.Tensor, device_tokens: torch.Tensor) -> None:
+    """final_tok[r] = sampled[r] if rows_info[R + r] else greedy[r]; device_tokens[rows_info[r]] = final_tok[r]."""
+    R = final_tok.numel()
+    assert rows_info.numel() == 2 * R
+    _check(lib().infero_keep_tokens(_ptr(_i32(greedy, "greedy")), _ptr(None if sampled is None else _i32(sampled, "sampled")),
+                                    _ptr(_i32(rows_info, "rows_info")), _ptr(_i32(final_tok, "final_tok")),
+                                    _ptr(_i32(device_tokens, "device_tokens")), c_int(R), _stream()))
 
 
 def sample_max_k() -> int:

@@ -109,7 +109,7 @@ class DecoderModel:
         s = self.spec
         T = token_ids.numel()
         x = torch.empty((T, s.hidden), dtype=torch.float32, device=token_ids.device)
-        K.embed_gather(self.embed, token_ids, x, s.embed_scale)
+        K.embed_gather(self.embed, token_ids, x, s.embed_scale, getattr(ctx, "device_tokens", None))
         delta = None
         for entry in s.schedule:
             delta = self.blocks[entry.block].forward(ctx, x, delta, entry)

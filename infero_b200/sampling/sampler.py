@@ -39,10 +39,31 @@ class RowSampler:
         return sorted(Counter(recent).items())
 
 
-def sample_rows(logits: torch.Tensor, samplers: Sequence[RowSampler],
-                histories: Sequence[Sequence[int]]) -> List[int]:
-    """Pick one token per row of ``logits`` [R, vocab] (float32, device; modified in place
-    when a repetition penalty applies).  Returns host ints (one device-to-host copy)."""
+class PendingTokens:
+    """Tokens picked on the device, on their way to the host."""
+
+    def __init__(self, host: torch.Tensor, ready: "torch.cuda.Event", n: int):
+        self._host, self._ready, self._n = host, ready, n
+
+    def result(self) -> List[int]:
+        self._ready.synchronize()
+        return [int(t) for t in self._host[:self._n].numpy()]
+
+
+class ReadyTokens:
+    def __init__(self, tokens: List[int]):
+        self._tokens = list(tokens)
+
+    def result(self) -> List[int]:
+        return self._tokens
+
+
+def sample_rows_async(logits: torch.Tensor, samplers: Sequence[RowSampler], histories: Sequence[Sequence[int]],
+                      slots: Optional[Sequence[int]] = None,
+                      device_tokens: Optional[torch.Tensor] = None) -> PendingTokens:
+    """As ``sample_rows``, without waiting: the picks go to pinned host memory by an asynchronous
+    copy, and (when ``slots`` and ``device_tokens`` are given) stay on the device in
+    ``device_tokens[slot]`` so that the next step can be launched before the host has them."""
     R, V = logits.shape
     assert len(samplers) == R and len(histories) == R
     dev = logits.device
@@ -58,15 +79,36 @@ def sample_rows(logits: torch.Tensor, samplers: Sequence[RowSampler],
         K.apply_penalty(logits, torch.from_numpy(toks).to(dev), torch.from_numpy(cnts).to(dev),
                         torch.from_numpy(pen).to(dev))
     greedy = [s.params.is_greedy() for s in samplers]
-    out = torch.empty(2 * R, dtype=torch.int32, device=dev)
+    out = torch.empty(3 * R, dtype=torch.int32, device=dev)      # argmax | sampled | final
     K.argmax(logits, out[:R])
+    sampled = None
     if not all(greedy):
         temp = np.array([max(s.params.temperature, 0.0) for s in samplers], dtype=np.float32)
         topk = np.array([s.params.top_k for s in samplers], dtype=np.int32)
         topp = np.array([s.params.top_p for s in samplers], dtype=np.float32)
         # a draw is taken for every row, greedy or not, as the reference does (sampling.rs:113-121)
         draw = np.array([s.next_draw() for s in samplers], dtype=np.float64)
+        sampled = out[R:2 * R]
         K.sample(logits, torch.from_numpy(temp).to(dev), torch.from_numpy(topk).to(dev),
-                 torch.from_numpy(topp).to(dev), torch.from_numpy(draw).to(dev), out[R:])
-    host = out.cpu().numpy()
-    return [int(host[r] if greedy[r] else host[R + r]) for r in range(R)]
+                 torch.from_numpy(topp).to(dev), torch.from_numpy(draw).to(dev), sampled)
+    info = np.empty(2 * R, dtype=np.int32)
+    info[:R] = -1 if slots is None or device_tokens is None else np.asarray(slots, dtype=np.int32)
+    info[R:] = [0 if g else 1 for g in greedy]
+    info_pinned = torch.empty(2 * R, dtype=torch.int32, pin_memory=True)
+    info_pinned.numpy()[:] = info
+    keep = device_tokens if device_tokens is not None else out[2 * R:]      # slot -1: nothing is kept
+    K.keep_tokens(out[:R], sampled, info_pinned.to(dev, non_blocking=True), out[2 * R:], keep)
+    host = torch.empty(R, dtype=torch.int32, pin_memory=True)
+    host.copy_(out[2 * R:], non_blocking=True)
+    ready = torch.cuda.Event()
+    ready.record()
+    pending = PendingTokens(host, ready, R)
+    pending._keep = (out, info_pinned)          # alive until the copies have run
+    return pending
+
+
+def sample_rows(logits: torch.Tensor, samplers: Sequence[RowSampler],
+                histories: Sequence[Sequence[int]]) -> List[int]:
+    """Pick one token per row of ``logits`` [R, vocab] (float32, device; modified in place
+    when a repetition penalty applies).  Returns host ints (one device-to-host copy)."""
+    return sample_rows_async(logits, samplers, histories).result()

@@ -189,3 +189,34 @@ def test_greedy_generation_through_the_entry_point(name, dtype):
                     break
     assert eng.runner.graph_replays > 0
     assert not eng.runner.manager.requests
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_running_ahead_changes_no_token(dtype):
+    """One step in flight (tokens fed from the device, end-of-sequence seen a step late) against
+    waiting for every step's tokens: same tokens, same reasons, nothing left in the cache."""
+    from infero_b200.engine import Engine
+    from infero_b200.sampling import SamplingParams
+    mdir = model_dir("B", seed=77, qk_gain=1.5)
+    reqs = make_requests("B", [9, 30, 3, 21, 14, 40], seed=41)
+    results = []
+    for ahead in (False, True):
+        eng = Engine(mdir, dtype=dtype, ctx=160, max_seqs=3, kv_slots=320, max_batch_tokens=32, run_ahead=ahead)
+        # greedy rows and seeded temperature rows; a handful of token ids end a request
+        eos = tuple(range(0, 1000, 9))
+        for i, toks in enumerate(reqs.values()):
+            p = SamplingParams(temperature=0.0 if i % 2 == 0 else 0.9, top_k=8, top_p=0.95, repetition_penalty=1.0, seed=5 + i)
+            eng.add_request(toks, p, max_new_tokens=24, eos_token_ids=eos, rid=i)
+        out, why = {}, {}
+        while not eng.is_idle():
+            for ev in eng.step():
+                if ev.token is not None:
+                    out.setdefault(ev.rid, []).append(ev.token)
+                if ev.finished:
+                    why[ev.rid] = ev.reason
+        results.append((out, why))
+        assert not eng.runner.manager.requests
+        if ahead:
+            assert eng.scheduler.stats["steps_ahead"] > 0
+    assert results[0] == results[1]
+    assert "stop" in results[0][1].values() or "length" in results[0][1].values()

@@ -219,3 +219,101 @@ def test_random_load_with_a_window_group_drains_and_matches(seed):
         assert reasons[k] == "length"
         assert out[k] == expected_output(p, len(out[k]))
     assert all(a.num_free == a.num_pages for a in m.allocators)
+
+
+# ---- running ahead: one step in flight ---------------------------------------------------------------
+class FakeLauncher(FakeExecutor):
+    """The same fake model behind the asynchronous interface: a step is 'launched' (pages taken,
+    the picked tokens left 'on the device') and its tokens are only handed over by .result()."""
+
+    class _Pending:
+        def __init__(self, tokens, log):
+            self._tokens, self._log = tokens, log
+
+        def result(self):
+            self._log.append("read")
+            return self._tokens
+
+    def __init__(self, manager, vocab=100):
+        super().__init__(manager, vocab)
+        self.device = {}               # rid -> last picked token, as the sampler leaves it on the device
+        self.log = []
+
+    def launch(self, items):
+        from infero_b200.engine.step import FROM_DEVICE
+        resolved = []                  # what the device would do: take the request's last pick
+        for it in items:
+            toks = [self.device[it.run.req.rid]] if it.tokens == [FROM_DEVICE] else list(it.tokens)
+            resolved.append(toks)
+        self.log.append("launch")
+        self.batches.append([(it.run.req.rid, len(t), it.is_decode, it.samples) for it, t in zip(items, resolved)])
+        out = []
+        for it, toks in zip(items, resolved):
+            self.manager.reserve(it.run.rc, len(toks))
+        for it, toks in zip(items, resolved):
+            self.manager.commit(it.run.rc, len(toks))
+            hist = self.seen.setdefault(it.run.req.rid, [])
+            if it.run.rc.length - len(toks) == 0:
+                hist.clear()
+            hist.extend(toks)
+            if it.samples:
+                tok = (sum(hist) + len(hist)) % self.vocab
+                self.device[it.run.req.rid] = tok
+                out.append(tok)
+        return self._Pending(out, self.log)
+
+
+def make_ahead(run_ahead=True, **kw):
+    m = CacheManager([GroupSpec(None)], num_pages=kw.get("num_pages", 64), page_size=16, max_requests=kw.get("max_seqs", 4))
+    ex = FakeLauncher(m)
+    s = Scheduler(m, ex, max_seqs=kw.get("max_seqs", 4), max_batch_tokens=kw.get("budget", 64), ctx=kw.get("ctx", 512),
+                  launch=ex.launch, run_ahead=run_ahead)
+    return s, ex, m
+
+
+def pure(rid, prompt, n=8, **kw):
+    return Request(rid, list(prompt), SamplingParams(temperature=0.0, repetition_penalty=1.0), max_new_tokens=n, **kw)
+
+
+def test_running_ahead_launches_the_next_step_before_reading_this_one():
+    s, ex, m = make_ahead()
+    s.enqueue(pure("a", range(1, 20), n=12))
+    out, reasons = run_all(s)
+    assert out["a"] == expected_output(range(1, 20), 12) and reasons["a"][0] == "length"
+    assert s.stats["steps_ahead"] >= 8
+    # in steady state a launch comes between two reads
+    assert "launch launch read launch read" in " ".join(ex.log)
+    assert all(a.num_free == a.num_pages for a in m.allocators)
+
+
+def test_running_ahead_gives_the_same_tokens_as_waiting_for_every_step():
+    rng = random.Random(3)
+    reqs = [(f"r{i}", [rng.randrange(1, 100) for _ in range(rng.randrange(1, 60))], rng.randrange(1, 25))
+            for i in range(14)]
+    results = []
+    for ahead in (False, True):
+        s, ex, m = make_ahead(run_ahead=ahead, num_pages=40, budget=48)
+        # tokens 7 and 42 end a request (the fake model hits them now and then)
+        for rid, prompt, n in reqs:
+            s.enqueue(pure(rid, prompt, n=n, eos_token_ids=(7, 42, 13, 77)))
+        out, reasons = run_all(s)
+        results.append((out, reasons))
+        assert all(a.num_free == a.num_pages for a in m.allocators)
+        if ahead:
+            assert s.stats["steps_ahead"] > 0 and s.stats["tokens_dropped"] > 0
+    assert results[0] == results[1]
+    for rid, prompt, n in reqs:
+        assert results[1][0].get(rid, []) == expected_output(prompt, n, eos=(7, 42, 13, 77))
+
+
+def test_no_running_ahead_with_a_repetition_penalty_or_a_waiting_request():
+    s, ex, m = make_ahead()
+    s.enqueue(Request("a", list(range(1, 9)), SamplingParams.greedy(), max_new_tokens=6))     # penalty 1.05
+    run_all(s)
+    assert s.stats["steps_ahead"] == 0
+    s, ex, m = make_ahead(max_seqs=1)
+    s.enqueue(pure("a", range(1, 9), n=6))
+    s.enqueue(pure("b", range(1, 5), n=3))       # waits for a's slot: a is never run ahead of
+    out, _ = run_all(s)
+    assert out["a"] == expected_output(range(1, 9), 6) and out["b"] == expected_output(range(1, 5), 3)
+    assert "launch launch" not in " ".join(ex.log[:10])
