@@ -80,13 +80,21 @@ __device__ __forceinline__ void merge_if_last(int* counter, float* wbuf, const f
         const int r = idx / (D / 2), d = (idx - r * (D / 2)) * 2;
         const float* pob = po_base + (size_t)r * n_splits * D + d;
         float a0 = 0.f, a1 = 0.f;
-#pragma unroll 4
-        for (int s = 0; s < n_splits; ++s) {
-            const float ws = wbuf[r * n_splits + s];
-            float2 v = __ldcg(reinterpret_cast<const float2*>(pob + (size_t)s * D));
-            if (ws == 0.f) v = make_float2(0.f, 0.f);
-            a0 = fmaf(v.x, ws, a0);
-            a1 = fmaf(v.y, ws, a1);
+        // sixteen splits' loads in flight at a time (they come from L2; the sum stays in order)
+        for (int s0 = 0; s0 < n_splits; s0 += 16) {
+            float2 v[16];
+#pragma unroll
+            for (int k = 0; k < 16; ++k)
+                v[k] = s0 + k < n_splits ? __ldcg(reinterpret_cast<const float2*>(pob + (size_t)(s0 + k) * D))
+                                         : make_float2(0.f, 0.f);
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+                const float ws = s0 + k < n_splits ? wbuf[r * n_splits + s0 + k] : 0.f;
+                if (ws != 0.f) {
+                    a0 = fmaf(v[k].x, ws, a0);
+                    a1 = fmaf(v[k].y, ws, a1);
+                }
+            }
         }
         const float inv = linv[r];
         *reinterpret_cast<uint32_t*>(out_rows + (size_t)r * D + d) = pack_bf16(a0 * inv, a1 * inv);

@@ -315,10 +315,21 @@ class _DecodeGraph:
         self.ctx = ctx
         torch.cuda.current_stream(runner.device).synchronize()
         from .. import kernels as K
+        import gc
         before = K.launch_count()
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
-            self.logits = runner.model.forward(ctx, ctx.token_ids, rows)
+        # No garbage collection while the stream is capturing: an old CUDA graph that is freed in
+        # the middle of a capture (runners sit in reference cycles, so they go when the collector
+        # gets to them) invalidates the capture.  Collect first, then hold the collector off.
+        gc.collect()
+        was_enabled = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(self.graph):
+                self.logits = runner.model.forward(ctx, ctx.token_ids, rows)
+        finally:
+            if was_enabled:
+                gc.enable()
         self.n_kernels = K.launch_count() - before
 
     def load(self, entries, rcs, parts=None) -> None:

@@ -17,7 +17,9 @@ import torch
 from . import KernelError, _check, _dt, _i32, _ptr, _stream, attention_generic, lib
 
 PREFILL_ROWS = 64          # query rows per CTA of the prefill kernel
-DECODE_MIN_CHUNK = 64      # keys per split, at least
+import os as _os
+
+DECODE_MIN_CHUNK = int(_os.environ.get("INFERO_DECODE_MIN_CHUNK", "256"))   # keys per split, at least (a tuning knob)
 TARGET_CTAS = 2 * 148      # decode CTAs wanted in flight: two resident per SM
 MAX_SPLITS = 256           # the merge kernel keeps one weight per split in shared memory
 

@@ -27,6 +27,7 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--intermediate", type=int, default=18944)
     ap.add_argument("--vocab", type=int, default=152064)
+    ap.add_argument("--only", default=None, help="leave out just this class (norm, rope, attn, gemm_qkv, ...)")
     args = ap.parse_args(argv)
 
     import torch
@@ -112,7 +113,8 @@ def main(argv=None) -> int:
 
     base = measure("none")
     print(f"batch {B}, context {args.context}, {args.layers} layers: whole step {base:.3f} ms")
-    for tag in ("norm", "rope", "attn", "gemm_qkv", "gemm_o", "gemm_gate_up", "gemm_down", "all_gemm"):
+    tags = ("norm", "rope", "attn", "gemm_qkv", "gemm_o", "gemm_gate_up", "gemm_down", "all_gemm")
+    for tag in (tags if args.only is None else (args.only,)):
         ms = measure(tag)
         print(f"  without {tag:13s} {ms:.3f} ms: costs {1000 * (base - ms) / args.layers:6.1f} us per layer "
               f"({100 * (base - ms) / base:4.1f} % of the step)")
