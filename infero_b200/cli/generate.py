@@ -35,6 +35,8 @@ def main(argv=None) -> int:
     ap.add_argument("--top-k", type=int, default=None)
     ap.add_argument("--top-p", type=float, default=None)
     ap.add_argument("--ignore-eos", action="store_true")
+    ap.add_argument("--no-warmup", action="store_true",
+                    help="time the very first run (kernel loading and graph capture included)")
     args = ap.parse_args(argv)
     if args.kv_quant not in ("f16", "bf16", "none"):
         print(f"generate: --kv-quant {args.kv_quant}: quantised caches are not built (f16 only)", file=sys.stderr)
@@ -72,6 +74,10 @@ def main(argv=None) -> int:
     print(f"kv cache : {eng.cfg.dtype}, {eng.runner.storage.bytes() / (1 << 20):.1f} MiB for "
           f"{eng.runner.num_pages * eng.cfg.page_size} positions")
 
+    if not args.no_warmup:
+        # a throw-away request of the same length: loads the kernels and captures the decode step,
+        # so that the timed run below measures the engine and not its first call
+        eng.generate([tokens], params, max_new_tokens=min(4, args.max_new), ignore_eos=True)
     eng.add_request(tokens, params, max_new_tokens=args.max_new, ignore_eos=args.ignore_eos)
     torch.cuda.synchronize()
     t0 = time.perf_counter()
