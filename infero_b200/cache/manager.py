@@ -13,16 +13,18 @@ Beside the pages each live request owns one slot index into fixed-size state arr
 (the reference keeps GatedDeltaNet state that way, crates/model/src/gdn_state.rs:64-116,
 reset when a sequence starts at length 0, crates/model/src/cache.rs:612-617).
 
-This module is host-only bookkeeping; the device arrays live in ``storage``.
+The bookkeeping itself is C++ (``csrc/host_cache.cpp``, part of the engine's shared library,
+no CUDA in it); this module is its Python face.  The device arrays live in ``storage``.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+import ctypes
+from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
 import numpy as np
 
-from .pages import OutOfPages, PageAllocator
+from .pages import OutOfPages
 
 
 class OutOfSlots(RuntimeError):
@@ -35,55 +37,124 @@ class GroupSpec:
     window: Optional[int] = None
 
 
-@dataclass
+def _lib():
+    from ..kernels import lib
+    L = lib()
+    if not getattr(L, "_cache_api_ready", False):
+        L.infero_cache_new.restype = ctypes.c_void_p
+        L.infero_cache_mirror.restype = ctypes.POINTER(ctypes.c_int)
+        L.infero_cache_counter.restype = ctypes.c_longlong
+        L.infero_cache_error.restype = ctypes.c_char_p
+        L.infero_step_layout.restype = ctypes.c_longlong
+        L._cache_api_ready = True
+    return L
+
+
 class RequestCache:
-    rid: Hashable
-    slot: int
-    length: int = 0                       # tokens whose keys are in the cache
-    reserved: int = 0                     # tokens reserved by the running step, not yet committed
-    tables: List[List[int]] = field(default_factory=list)   # per group: logical page -> page id / -1
-    first_live: List[int] = field(default_factory=list)     # per group: first logical page still held
-    fresh: bool = True                    # state slot still has to be zeroed
+    """One live request as the cache sees it (a view of the C++ record of its slot)."""
+    __slots__ = ("rid", "slot", "_m")
+
+    def __init__(self, rid: Hashable, slot: int, manager: "CacheManager"):
+        self.rid, self.slot, self._m = rid, slot, manager
+
+    @property
+    def length(self) -> int:                     # tokens whose keys are in the cache
+        return self._m._L.infero_cache_length(self._m._h, self.slot)
+
+    @property
+    def reserved(self) -> int:                   # tokens reserved by the running step, not yet committed
+        return self._m._L.infero_cache_reserved(self._m._h, self.slot)
+
+    @property
+    def fresh(self) -> bool:                     # nothing committed yet: state slots still have to be zeroed
+        return bool(self._m._L.infero_cache_fresh(self._m._h, self.slot))
+
+    @property
+    def tables(self) -> List[List[int]]:         # per group: logical page -> page id, -1 once given back
+        m = self._m
+        return [[int(p) for p in m._mirror(g)[self.slot, :m._L.infero_cache_table_len(m._h, g, self.slot)]]
+                for g in range(len(m.groups))]
+
+    def table_len(self, group: int) -> int:
+        return self._m._L.infero_cache_table_len(self._m._h, group, self.slot)
+
+    @property
+    def first_live(self) -> List[int]:
+        m = self._m
+        return [m._L.infero_cache_first_live(m._h, g, self.slot) for g in range(len(m.groups))]
+
+
+class _AllocatorView:
+    """Read-only view of one group's page pool."""
+
+    def __init__(self, manager: "CacheManager", group: int):
+        self._m, self.group = manager, group
+        self.num_pages = manager.num_pages
+
+    @property
+    def num_free(self) -> int:
+        return self._m._L.infero_cache_num_free(self._m._h, self.group)
+
+    def held_pages(self) -> List[int]:
+        buf = (ctypes.c_int * self.num_pages)()
+        n = self._m._L.infero_cache_held(self._m._h, self.group, buf, self.num_pages)
+        return [int(buf[i]) for i in range(n)]
 
 
 class CacheManager:
     def __init__(self, groups: Sequence[GroupSpec], num_pages: int, page_size: int, max_requests: int,
                  max_blocks: Optional[int] = None):
+        if num_pages <= 0:
+            raise ValueError("a page pool needs at least one page")
         self.groups = list(groups)
         self.page_size = page_size
         self.num_pages = num_pages
         self.max_requests = max_requests
         self.max_blocks = max_blocks
-        self.allocators = [PageAllocator(num_pages, g) for g in range(len(self.groups))]
-        self._free_slots: List[int] = list(range(max_requests - 1, -1, -1))
+        self._L = _lib()
+        windows = (ctypes.c_int * max(1, len(self.groups)))(*[int(g.window or 0) for g in self.groups])
+        self._h = ctypes.c_void_p(self._L.infero_cache_new(len(self.groups), windows, num_pages, page_size,
+                                                           max_requests, int(max_blocks or 0)))
+        if not self._h:
+            raise ValueError("bad cache geometry")
+        self.allocators = [_AllocatorView(self, g) for g in range(len(self.groups))]
         self.requests: Dict[Hashable, RequestCache] = {}
-        # device-bound copy of every block table, one row per request slot, kept up to date as
-        # pages come and go, so that a step gathers its rows instead of rebuilding them
-        self._table_width = max_blocks if max_blocks is not None else 0
-        self._table_np = [np.full((max_requests, max(1, self._table_width)), -1, dtype=np.int32)
-                          for _ in self.groups]
-        self.pages_reclaimed = 0          # window pages returned before their request ended
-        self.pages_reused = 0             # allocations served by a page that was held before
-        self._ever_held = [bytearray(num_pages) for _ in self.groups]
+        self._need = (ctypes.c_int * max(1, len(self.groups)))()
+        self._info = (ctypes.c_int * 3)()
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._L.infero_cache_delete(h)
+
+    def _mirror(self, group: int) -> np.ndarray:
+        """[max_requests, width] int32 view of the C++ side's copy of every block table."""
+        width = self._L.infero_cache_width(self._h)
+        ptr = self._L.infero_cache_mirror(self._h, group)
+        return np.ctypeslib.as_array(ptr, shape=(self.max_requests, width))
+
+    @property
+    def pages_reclaimed(self) -> int:             # window pages returned before their request ended
+        return int(self._L.infero_cache_counter(self._h, 0))
+
+    @property
+    def pages_reused(self) -> int:                # allocations served by a page that was held before
+        return int(self._L.infero_cache_counter(self._h, 1))
 
     # ---- requests ------------------------------------------------------------------------
     def open(self, rid: Hashable) -> RequestCache:
         if rid in self.requests:
             raise KeyError(f"request {rid!r} is already open")
-        if not self._free_slots:
+        slot = self._L.infero_cache_open(self._h)
+        if slot < 0:
             raise OutOfSlots(f"all {self.max_requests} request slots are in use")
-        rc = RequestCache(rid=rid, slot=self._free_slots.pop(),
-                          tables=[[] for _ in self.groups], first_live=[0 for _ in self.groups])
+        rc = RequestCache(rid, slot, self)
         self.requests[rid] = rc
-        for t in self._table_np:
-            t[rc.slot, :] = -1
         return rc
 
     def close(self, rid: Hashable) -> None:
         rc = self.requests.pop(rid)
-        for g, table in enumerate(rc.tables):
-            self.allocators[g].free([p for p in table if p >= 0])
-        self._free_slots.append(rc.slot)
+        self._L.infero_cache_close(self._h, rc.slot)
 
     def get(self, rid: Hashable) -> RequestCache:
         return self.requests[rid]
@@ -91,139 +162,73 @@ class CacheManager:
     # ---- pages ---------------------------------------------------------------------------
     def pages_needed(self, rc: RequestCache, n_new: int) -> List[int]:
         """New pages per group to hold n_new more tokens after what is held or reserved."""
-        end = rc.length + rc.reserved + n_new
-        want = -(-end // self.page_size)
-        return [max(0, want - len(t)) for t in rc.tables]
+        self._L.infero_cache_pages_needed(self._h, rc.slot, int(n_new), self._need)
+        return [int(self._need[g]) for g in range(len(self.groups))]
 
     def can_reserve(self, items: Sequence[Tuple[RequestCache, int]]) -> bool:
         need = [0] * len(self.groups)
         for rc, n in items:
             for g, k in enumerate(self.pages_needed(rc, n)):
                 need[g] += k
-        return all(need[g] <= self.allocators[g].num_free for g in range(len(self.groups)))
+        return all(need[g] <= self.free_pages(g) for g in range(len(self.groups)))
 
     def free_pages(self, group: int = 0) -> int:
-        return self.allocators[group].num_free
+        return self._L.infero_cache_num_free(self._h, group)
 
     def min_free_pages(self) -> int:
-        return min((a.num_free for a in self.allocators), default=self.num_pages)
+        return min((self.free_pages(g) for g in range(len(self.groups))), default=self.num_pages)
 
     def reserve(self, rc: RequestCache, n_new: int) -> None:
         """Take the pages n_new more tokens need, in every group, or none at all."""
         if n_new <= 0:
             raise ValueError("reserve needs at least one token")
-        need = self.pages_needed(rc, n_new)
-        if self.max_blocks is not None:
-            want = -(-(rc.length + rc.reserved + n_new) // self.page_size)
-            if want > self.max_blocks:
-                raise OutOfPages(-1, want, self.max_blocks)
-        for g, k in enumerate(need):
-            if k > self.allocators[g].num_free:
-                raise OutOfPages(g, k, self.allocators[g].num_free)
-        for g, k in enumerate(need):
-            pages = self.allocators[g].alloc(k)
-            for p in pages:
-                if self._ever_held[g][p]:
-                    self.pages_reused += 1
-                self._ever_held[g][p] = 1
-            first = len(rc.tables[g])
-            rc.tables[g].extend(pages)
-            if pages:
-                self._mirror(g, rc.slot, first, pages)
-        rc.reserved += n_new
+        rcode = self._L.infero_cache_reserve(self._h, rc.slot, int(n_new), self._info)
+        if rcode:
+            raise OutOfPages(int(self._info[0]), int(self._info[1]), int(self._info[2]))
 
     def commit(self, rc: RequestCache, n_new: int) -> None:
         """The step wrote n_new tokens: advance, and give back what a window has passed."""
-        if n_new > rc.reserved:
+        if self._L.infero_cache_commit(self._h, rc.slot, int(n_new)):
             raise ValueError("commit of more tokens than were reserved")
-        rc.reserved -= n_new
-        rc.length += n_new
-        rc.fresh = False
-        P = self.page_size
-        for g, spec in enumerate(self.groups):
-            if spec.window is None:
-                continue
-            # logical page k covers [kP, kP+P-1]; dead iff kP + P - 1 <= length - window
-            dead_upto = (rc.length - spec.window + 1) // P if rc.length - spec.window + 1 > 0 else 0
-            table = rc.tables[g]
-            k = rc.first_live[g]
-            freed = []
-            while k < dead_upto and k < len(table):
-                if table[k] >= 0:
-                    freed.append(table[k])
-                    table[k] = -1
-                    if k < self._table_np[g].shape[1]:
-                        self._table_np[g][rc.slot, k] = -1
-                k += 1
-            rc.first_live[g] = k
-            if freed:
-                self.allocators[g].free(freed)
-                self.pages_reclaimed += len(freed)
 
     def abort_reservation(self, rc: RequestCache) -> None:
         """Drop pages reserved for a step that did not run."""
-        if rc.reserved == 0:
-            return
-        keep = -(-rc.length // self.page_size)
-        for g, table in enumerate(rc.tables):
-            extra = [p for p in table[keep:] if p >= 0]
-            del table[keep:]
-            self.allocators[g].free(extra)
-            self._table_np[g][rc.slot, keep:] = -1
-        rc.reserved = 0
+        self._L.infero_cache_abort(self._h, rc.slot)
 
     # ---- tables for the device -----------------------------------------------------------
-    def _mirror(self, group: int, slot: int, first: int, pages) -> None:
-        t = self._table_np[group]
-        end = first + len(pages)
-        if end > t.shape[1]:                       # no fixed width was given: grow
-            wider = np.full((t.shape[0], max(end, 2 * t.shape[1])), -1, dtype=np.int32)
-            wider[:, :t.shape[1]] = t
-            self._table_np[group] = t = wider
-        t[slot, first:end] = pages
-
     def block_table_array(self, group: int, rcs: Sequence[RequestCache], width: int) -> np.ndarray:
         """[len(rcs), width] int32: logical page -> page id (-1 where none is held)."""
-        t = self._table_np[group]
+        t = self._mirror(group)
         if not rcs:
             return np.full((1, width), -1, dtype=np.int32)
+        for rc in rcs:
+            if rc.table_len(group) > width:
+                raise ValueError(f"request {rc.rid!r} holds {rc.table_len(group)} pages, table width is {width}")
         slots = np.fromiter((rc.slot for rc in rcs), dtype=np.intp, count=len(rcs))
         if width <= t.shape[1]:
-            out = t[slots, :width]
-        else:
-            out = np.full((len(rcs), width), -1, dtype=np.int32)
-            out[:, :t.shape[1]] = t[slots]
-        for rc in rcs:
-            if len(rc.tables[group]) > width:
-                raise ValueError(f"request {rc.rid!r} holds {len(rc.tables[group])} pages, table width is {width}")
+            return t[slots, :width].copy()
+        out = np.full((len(rcs), width), -1, dtype=np.int32)
+        out[:, :t.shape[1]] = t[slots]
         return out
+
+    def step_layout(self, slots: np.ndarray, n_tokens: np.ndarray, tokens: np.ndarray, want_counts: np.ndarray,
+                    wants: np.ndarray, table_width: int, out: np.ndarray) -> List[int]:
+        """Write a step's int32 arrays into ``out`` (see csrc/host_cache.cpp: token ids, positions,
+        token -> entry, per entry first row / row count / cached length / slot, wanted rows, one
+        block table per group) and return the section sizes.  All arguments are int32 arrays."""
+        sizes = (ctypes.c_longlong * (8 + len(self.groups)))()
+        as_p = lambda a: a.ctypes.data_as(ctypes.POINTER(ctypes.c_int))     # noqa: E731
+        total = self._L.infero_step_layout(self._h, int(slots.size), as_p(slots), as_p(n_tokens), as_p(tokens),
+                                           as_p(want_counts), as_p(wants), int(table_width), as_p(out),
+                                           ctypes.c_longlong(out.size), sizes)
+        if total < 0:
+            raise ValueError("step layout does not fit its buffer, or a request holds more pages than the table is wide")
+        return [int(v) for v in sizes]
 
     # ---- invariants (used by tests and debug runs) -----------------------------------------
     def check(self) -> None:
-        for g, alloc in enumerate(self.allocators):
-            held = set()
-            for rc in self.requests.values():
-                for p in rc.tables[g]:
-                    if p < 0:
-                        continue
-                    if p in held:
-                        raise AssertionError(f"group {g}: page {p} is held twice")
-                    held.add(p)
-            if held != set(alloc.held_pages()):
-                raise AssertionError(f"group {g}: pages lost or leaked "
-                                     f"(tables {sorted(held)} vs allocator {alloc.held_pages()})")
-            if len(held) + alloc.num_free != alloc.num_pages:
-                raise AssertionError(f"group {g}: {len(held)} held + {alloc.num_free} free != {alloc.num_pages}")
-            if len(set(alloc._free)) != len(alloc._free):
-                raise AssertionError(f"group {g}: a page is on the free list twice")
-        for g in range(len(self.groups)):
-            for rc in self.requests.values():
-                row = self._table_np[g][rc.slot]
-                t = rc.tables[g]
-                if list(row[:len(t)]) != list(t) or (row[len(t):] != -1).any():
-                    raise AssertionError(f"group {g}: the table copy of request {rc.rid!r} is out of date")
+        if self._L.infero_cache_check(self._h):
+            raise AssertionError(self._L.infero_cache_error(self._h).decode())
         slots = [rc.slot for rc in self.requests.values()]
-        if len(set(slots)) != len(slots) or set(slots) & set(self._free_slots):
+        if len(set(slots)) != len(slots):
             raise AssertionError("a state slot is held twice")
-        if len(slots) + len(self._free_slots) != self.max_requests:
-            raise AssertionError("a state slot was lost")

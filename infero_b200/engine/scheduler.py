@@ -142,7 +142,7 @@ class Scheduler:
 
     def _outstanding_pages(self) -> int:
         """Pages the running requests still have to take to hold their prompt plus one token."""
-        return sum(max(0, self._pages_for(len(r.tokens) + 1) - max((len(t) for t in r.rc.tables), default=0))
+        return sum(max(0, self._pages_for(len(r.tokens) + 1) - max((r.rc.table_len(g) for g in range(len(self.manager.groups))), default=0))
                    for r in self.running)
 
     def _admit(self) -> None:

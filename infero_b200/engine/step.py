@@ -197,33 +197,36 @@ class ModelRunner:
         return logits
 
     # ---- device inputs of a step ---------------------------------------------------------------
-    def _host_arrays(self, entries: Sequence[StepEntry], rcs: Sequence[RequestCache]):
-        """The int32 arrays a step needs, in the order they lie in the device buffer:
-        token ids, positions, token -> entry, then per entry first row, row count, cached
-        length and state slot, the rows whose logits are wanted, and one block table per group."""
+    def _layout_args(self, entries: Sequence[StepEntry], rcs: Sequence[RequestCache]):
+        """What the C++ layout builder takes: per entry slot, token count and wanted count, the
+        flat token ids and wanted places, and the number of ints the step's arrays need."""
         E = len(entries)
+        slots = np.fromiter((rc.slot for rc in rcs), dtype=np.int32, count=E)
         lens = np.fromiter((len(e.tokens) for e in entries), dtype=np.int32, count=E)
         T = int(lens.sum())
-        q_start = np.zeros(E, dtype=np.int32)
-        np.cumsum(lens[:-1], out=q_start[1:])
-        pos0 = np.fromiter((rc.length for rc in rcs), dtype=np.int32, count=E)
-        slots = np.fromiter((rc.slot for rc in rcs), dtype=np.int32, count=E)
         if T == E:
-            token_ids = np.fromiter((e.tokens[0] for e in entries), dtype=np.int32, count=E)
-            token_ids = np.where(token_ids < 0, -(slots + 1), token_ids)      # FROM_DEVICE -> -(slot + 1)
-            tok_entry = np.arange(E, dtype=np.int32)
-            positions = pos0
+            tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int32, count=E)
         else:
-            token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
-            tok_entry = np.repeat(np.arange(E, dtype=np.int32), lens)
-            token_ids = np.where(token_ids < 0, -(slots[tok_entry] + 1), token_ids)
-            positions = np.arange(T, dtype=np.int32) - np.repeat(q_start, lens) + np.repeat(pos0, lens)
-        want_rows = [q_start[i] + np.asarray(e.want, dtype=np.int32) for i, e in enumerate(entries) if len(e.want)]
-        rows = np.concatenate(want_rows).astype(np.int32) if want_rows else np.zeros(0, dtype=np.int32)
-        n_groups = len(self.manager.groups)
-        tables = [self.manager.block_table_array(g, rcs, self.max_blocks) for g in range(n_groups)]
-        parts = [token_ids, positions, tok_entry, q_start, lens, pos0, slots, rows] + [t.reshape(-1) for t in tables]
-        return parts, (q_start, lens, pos0, slots)
+            tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+        want_counts = np.fromiter((len(e.want) for e in entries), dtype=np.int32, count=E)
+        R = int(want_counts.sum())
+        if R == E and T == E:
+            wants = np.zeros(E, dtype=np.int32)
+        elif R:
+            wants = np.concatenate([np.asarray(e.want, dtype=np.int32) for e in entries if len(e.want)])
+        else:
+            wants = np.zeros(1, dtype=np.int32)
+        total = 3 * T + 4 * E + R + len(self.manager.groups) * max(1, E) * self.max_blocks
+        return (slots, lens, tokens, want_counts, wants), total, T
+
+    def _fill(self, args, out: np.ndarray):
+        """Lay the step's arrays out in ``out`` (pinned host memory); returns the section sizes and
+        host copies of the per-entry arrays."""
+        sizes = self.manager.step_layout(*args, self.max_blocks, out)
+        T, E = sizes[0], sizes[3]
+        o = 3 * T
+        host = tuple(out[o + k * E:o + (k + 1) * E].copy() for k in range(4))    # first row, rows, cached length, slot
+        return sizes, host
 
     def _context_from(self, dev: torch.Tensor, sizes: Sequence[int], host, E: int, T: int):
         views = []
@@ -244,14 +247,13 @@ class ModelRunner:
         return ctx, (d_rows if sizes[7] else None)
 
     def _build_context(self, entries: Sequence[StepEntry], rcs: Sequence[RequestCache]):
-        parts, host = self._host_arrays(entries, rcs)
-        sizes = [p.size for p in parts]
+        args, total, T = self._layout_args(entries, rcs)
         # one pinned staging buffer, one host-to-device copy
-        staging = torch.empty(int(sum(sizes)), dtype=torch.int32, pin_memory=(self.device.type == "cuda"))
-        np.concatenate(parts, out=staging.numpy())
+        staging = torch.empty(total, dtype=torch.int32, pin_memory=(self.device.type == "cuda"))
+        sizes, host = self._fill(args, staging.numpy())
         dev = staging.to(self.device, non_blocking=True)
         self.last_h2d_bytes = staging.numel() * 4
-        ctx, rows = self._context_from(dev, sizes, host, len(entries), int(host[1].sum()))
+        ctx, rows = self._context_from(dev, sizes, host, len(entries), T)
         ctx._staging = staging          # keep the pinned buffer alive until the copy has run
         return ctx, rows
 
@@ -301,14 +303,12 @@ class _DecodeGraph:
     def __init__(self, runner: ModelRunner, key, entries, rcs):
         self.runner = runner
         E, bound = key
-        parts, host = runner._host_arrays(entries, rcs)
-        self.sizes = [p.size for p in parts]
-        n = int(sum(self.sizes))
+        args, n, _ = runner._layout_args(entries, rcs)
         self.dev = torch.zeros(n, dtype=torch.int32, device=runner.device)
         self.staging = [torch.empty(n, dtype=torch.int32, pin_memory=True) for _ in range(2)]
         self.copied = [None, None]
         self.turn = 0
-        self.load(entries, rcs, parts)
+        self.sizes, host = self.load(entries, rcs, args)
         ctx, rows = runner._context_from(self.dev, self.sizes, host, E, E)
         ctx.kv_bound = bound
         ctx.max_kv_len = bound
@@ -332,16 +332,17 @@ class _DecodeGraph:
                 gc.enable()
         self.n_kernels = K.launch_count() - before
 
-    def load(self, entries, rcs, parts=None) -> None:
-        if parts is None:
-            parts, _ = self.runner._host_arrays(entries, rcs)
+    def load(self, entries, rcs, args=None):
+        if args is None:
+            args, _, _ = self.runner._layout_args(entries, rcs)
         i = self.turn
         self.turn ^= 1
         if self.copied[i] is not None:
             self.copied[i].synchronize()
-        np.concatenate(parts, out=self.staging[i].numpy())
+        filled = self.runner._fill(args, self.staging[i].numpy())
         self.dev.copy_(self.staging[i], non_blocking=True)
         self.runner.last_h2d_bytes = self.dev.numel() * 4
         ev = torch.cuda.Event()
         ev.record()
         self.copied[i] = ev
+        return filled

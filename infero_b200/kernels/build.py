@@ -42,7 +42,8 @@ def find_nvcc() -> str:
 
 
 def sources() -> List[str]:
-    return sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
+    """CUDA files, and plain C++ files of the host side (nvcc hands those to the host compiler)."""
+    return sorted(f for f in os.listdir(CSRC) if f.endswith((".cu", ".cpp")))
 
 
 def _headers() -> List[str]:
