@@ -76,7 +76,17 @@ class GqaAttention(Mixer):
         qkv = self.qkv.forward(h, defer=True)                  # [T, (H + 2 Hkv) D]
         kv = ctx.kv_cache(slot.cache)                          # keys, values, group
         table = ctx.block_table(kv.group)
-        inv = self.rope.inv_freq(h.device) if self.rope is not None else ctx.zero_inv_freq(h.device)
+        rotary = self.rope is None or hasattr(self.rope, "inv_freq")
+        if rotary:
+            inv = self.rope.inv_freq(h.device) if self.rope is not None else ctx.zero_inv_freq(h.device)
+        else:
+            # a position encoding that is no rotary table: it rewrites q and k itself, and the
+            # cache append runs with zero angles
+            inv = ctx.zero_inv_freq(h.device)
+            if isinstance(qkv, K.Partials):
+                qkv = qkv.materialize(h.dtype)
+            self.rope.apply(ctx, qkv[:, :H * D].unflatten(1, (H, D)),
+                            qkv[:, H * D:(H + Hkv) * D].unflatten(1, (Hkv, D)))
         if isinstance(qkv, K.Partials):
             q = torch.empty((T, H * D), dtype=h.dtype, device=h.device)
             K.rope_cache_partials(qkv, q, ctx.positions, ctx.tok_entry, table, inv, kv.k, kv.v, H, Hkv, D,

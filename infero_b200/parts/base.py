@@ -11,6 +11,8 @@ No part knows which model it is in.  A part defined outside this package plugs i
                                                      kernels.Partials (a product left as split-K sums;
                                                      .materialize(dtype) gives the tensor)
     FeedForward.forward(ctx, h) -> delta
+    PositionEncoding                                 a rotary table or an in-place rewrite of q and k
+                                                     (see the class)
     Block.forward(ctx, x, delta, slot) -> delta      x updated in place; the returned delta
                                                      is added by whoever normalises next
 
@@ -80,4 +82,10 @@ class FeedForward(Part):
 
 
 class PositionEncoding(Part):
-    pass
+    """Built from a ``PositionSpec``.  One of two forms, which the mixer tells apart by the method:
+
+    ``inv_freq(device) -> float32 [rotary_dim / 2]``: a rotary table; the mixer's fused kernel turns
+    pairs (i, i + rotary_dim/2) of every head of q and k by position * inv_freq[i].
+
+    ``apply(ctx, q, k)``: anything else; q ``[T, heads, head]`` and k ``[T, kv heads, head]`` are views
+    to be rewritten in place, with ``ctx.positions`` (int32 ``[T]``) the tokens' positions."""

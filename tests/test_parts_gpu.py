@@ -66,6 +66,56 @@ def test_swiglu_part(dt):
     assert _rel(out, ref) <= TOL[dt]
 
 
+def test_rope_part_table():
+    """The part owns the table of inverse frequencies: 64-bit on the host, rounded once."""
+    from infero_b200.config.spec import PositionSpec
+    from infero_b200.parts import RopeNeox
+    theta, rotary = 12345.0, 24
+    inv = RopeNeox(PositionSpec("rope_neox", theta, rotary)).inv_freq(DEV)
+    ref = torch.tensor([theta ** (-2.0 * i / rotary) for i in range(rotary // 2)], dtype=torch.float64)
+    assert inv.dtype == torch.float32 and inv.device.type == "cuda" and inv.shape == (rotary // 2,)
+    assert torch.equal(inv.cpu(), ref.float())
+    with pytest.raises(ValueError):
+        RopeNeox(PositionSpec("rope_neox", theta, 7))
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_block_alone(dt):
+    """One pre-norm block, called directly on a residual stream with a pending delta, against the
+    plain layer: the block adds the pending delta, leaves x after the mixer's add, and returns the
+    feed-forward's delta for the next norm to add."""
+    from infero_b200.engine import StepEntry
+    spec = _spec(layers=1, H=4, Hkv=4, D=16, d=88, ff=136, theta=777.0, eps=1e-4)
+    model, runner, w = _build(spec, dt)
+    block = model.blocks[0]
+    T = 37
+    cfg = {"num_attention_heads": 4, "num_key_value_heads": 4, "head_dim": 16, "hidden_size": 88,
+           "rms_norm_eps": 1e-4, "rope_theta": 777.0}
+    x0 = _rand((T, 88), torch.float32, 21)
+    pending = _rand((T, 88), dt, 22, 0.3)
+    start = x0.double().cpu() + pending.double().cpu()
+    ref = P.decoder_layer(start, w, cfg, 0, torch.arange(T))
+    # a step's context for one whole request of T tokens (the token ids play no part here)
+    runner.open("r")
+    captured = {}
+    real_forward = block.forward
+
+    def spy(ctx, x, delta, slot):
+        x.copy_(x0)
+        captured["delta"] = real_forward(ctx, x, pending, slot)
+        captured["x"] = x.clone()
+        return captured["delta"]
+
+    block.forward = spy
+    runner.step([StepEntry("r", [1] * T, [T - 1])])
+    block.forward = real_forward
+    from infero_b200.kernels import Partials
+    delta = captured["delta"]
+    delta = delta.materialize(torch.float32) if isinstance(delta, Partials) else delta.float()
+    got = captured["x"].double().cpu() + delta.double().cpu()
+    assert _rel(got, ref) <= TOL[dt]
+
+
 # ---- a model assembled from a hand-written spec: mixer, block, schedule ----------------------------
 def _spec(window=None, layers=1, schedule=None, H=6, Hkv=2, D=48, d=80, ff=144, V=300, theta=5000.0, eps=2e-5,
           tie=False):

@@ -1,0 +1,182 @@
+"""Parts from outside the package, defined here with plain torch: a feed-forward that routes every
+token to one of several small experts, and a position encoding that is no rotary table of the
+package's kind.  They are registered, named by a configuration layer by layer beside the
+package's own parts, built, loaded from a model folder written in random-weights mode and stepped
+in portions and mixed batches, without a change to the package's files.  They are toys: no
+model of anyone's."""
+import math
+import tempfile
+
+import pytest
+import torch
+
+import plain_qwen2 as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _adjacent_pairs(x, positions, base):
+    """Turn the pairs (2i, 2i+1) of the last axis by position * base^(-i / (D/2)); x [T, heads, D]."""
+    D = x.shape[-1]
+    inv = base ** (-torch.arange(D // 2, dtype=torch.float64, device=x.device) / (D // 2))
+    ang = positions.to(torch.float64)[:, None] * inv[None, :]
+    c, s = ang.cos()[:, None, :].to(x.dtype), ang.sin()[:, None, :].to(x.dtype)
+    a, b = x[..., 0::2], x[..., 1::2]
+    out = torch.empty_like(x)
+    out[..., 0::2] = a * c - b * s
+    out[..., 1::2] = a * s + b * c
+    return out
+
+
+def _register():
+    from infero_b200 import register_architecture, register_part
+    from infero_b200.config.spec import (BlockSpec, FeedForwardSpec, MixerSpec, ModelSpec, NormSpec, PositionSpec,
+                                          ScheduleEntry)
+    from infero_b200.parts.base import FeedForward, PositionEncoding, TensorDecl
+
+    class AdjacentPairs(PositionEncoding):
+        """The second form of a position encoding: it rewrites q and k in place."""
+
+        def __init__(self, spec):
+            self.base = float(spec.theta)
+
+        def apply(self, ctx, q, k):
+            pos = ctx.positions[:q.shape[0]]
+            q.copy_(_adjacent_pairs(q.float(), pos, self.base).to(q.dtype))
+            k.copy_(_adjacent_pairs(k.float(), pos, self.base).to(k.dtype))
+
+    class TopOneExperts(FeedForward):
+        """p = softmax(h Wr^T) in 32-bit; e = argmax p; delta = p_e * relu(h W1_e^T) W2_e^T."""
+
+        def __init__(self, spec, prefix):
+            self.d, self.inner, self.prefix = spec.hidden, spec.intermediate, prefix
+            self.n = int(dict(spec.extra)["experts"])
+
+        def declare(self):
+            p = self.prefix
+            return [TensorDecl(f"{p}.moe.router.weight", (self.n, self.d)),
+                    TensorDecl(f"{p}.moe.w1", (self.n, self.inner, self.d)),
+                    TensorDecl(f"{p}.moe.w2", (self.n, self.d, self.inner))]
+
+        def bind(self, tensors):
+            p = self.prefix
+            self.router, self.w1, self.w2 = (tensors[f"{p}.moe.{n}"] for n in ("router.weight", "w1", "w2"))
+
+        def forward(self, ctx, h):
+            prob = torch.softmax(h.float() @ self.router.float().T, dim=-1)
+            top, which = prob.max(dim=-1)
+            w1, w2 = self.w1.float()[which], self.w2.float()[which]          # [T, inner, d], [T, d, inner]
+            mid = torch.relu(torch.einsum("tid,td->ti", w1, h.float()))
+            return (top[:, None] * torch.einsum("tdi,ti->td", w2, mid)).to(h.dtype)
+
+    def to_spec(c):
+        d, D = c["width"], c["head"]
+        norm = NormSpec("rmsnorm", d, c["eps"])
+        blocks = []
+        for i, (pos_kind, ffn_kind) in enumerate(c["layers"]):
+            position = PositionSpec(pos_kind, c["theta"], D)
+            mixer = MixerSpec("gqa_attention", d, c["heads"], c["kv_heads"], D, qkv_bias=True,
+                              scale=1 / math.sqrt(D), position=position)
+            if ffn_kind == "top_one":
+                ffn = FeedForwardSpec("top_one", d, c["expert_inner"], extra=(("experts", c["experts"]),))
+            else:
+                ffn = FeedForwardSpec("swiglu", d, c["inner"])
+            blocks.append(BlockSpec("prenorm", f"model.layers.{i}", mixer, ffn, norm, norm))
+        return ModelSpec("ToyRoutedForCausalLM", c["vocab"], d, tuple(blocks),
+                         tuple(ScheduleEntry(i, i) for i in range(len(blocks))), norm, False)
+
+    register_part("position", "adjacent_pairs", AdjacentPairs)
+    register_part("feed_forward", "top_one", TopOneExperts)
+    register_architecture("ToyRoutedForCausalLM", lambda raw: dict(raw), to_spec)
+
+
+TOY = {"architectures": ["ToyRoutedForCausalLM"], "width": 72, "inner": 104, "expert_inner": 40, "experts": 3,
+       "vocab": 173, "eps": 3e-5, "heads": 3, "kv_heads": 1, "head": 32, "theta": 3000.0,
+       "layers": [["rope_neox", "top_one"], ["adjacent_pairs", "swiglu"], ["adjacent_pairs", "top_one"]]}
+TOY_DENSE = dict(TOY, layers=[["adjacent_pairs", "swiglu"], ["rope_neox", "swiglu"]])
+
+
+def _plain(c, w, toks):
+    """The same model on whole sequences in 64-bit, no cache."""
+    T = len(toks)
+    H, Hkv, D = c["heads"], c["kv_heads"], c["head"]
+    x = w["model.embed_tokens.weight"][torch.tensor(toks)]
+    pos = torch.arange(T)
+    for i, (pos_kind, ffn_kind) in enumerate(c["layers"]):
+        p = f"model.layers.{i}."
+        h = P.rms_norm(x, w[p + "input_layernorm.weight"], c["eps"])
+        q, k, v = ((h @ w[p + f"self_attn.{n}_proj.weight"].T + w[p + f"self_attn.{n}_proj.bias"]) for n in "qkv")
+        q, k, v = q.view(T, H, D), k.view(T, Hkv, D), v.view(T, Hkv, D)
+        if pos_kind == "rope_neox":
+            q, k = P.rope_neox(q, pos, c["theta"], D), P.rope_neox(k, pos, c["theta"], D)
+        else:
+            q, k = _adjacent_pairs(q, pos, c["theta"]), _adjacent_pairs(k, pos, c["theta"])
+        a = P.attention(q, k, v, 1 / math.sqrt(D), None)
+        x = x + a.reshape(T, H * D) @ w[p + "self_attn.o_proj.weight"].T
+        h = P.rms_norm(x, w[p + "post_attention_layernorm.weight"], c["eps"])
+        if ffn_kind == "top_one":
+            prob = torch.softmax(h @ w[p + "moe.router.weight"].T, dim=-1)
+            rows = []
+            for t in range(T):
+                e = int(prob[t].argmax())
+                rows.append(prob[t, e] * (w[p + "moe.w2"][e] @ torch.relu(w[p + "moe.w1"][e] @ h[t])))
+            x = x + torch.stack(rows)
+        else:
+            x = x + P.swiglu_mlp(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
+                                 w[p + "mlp.down_proj.weight"])
+    return P.rms_norm(x, w["model.norm.weight"], c["eps"]) @ w["lm_head.weight"].T
+
+
+def _rel(got, ref):
+    return float((got.double().cpu() - ref).abs().max() / ref.abs().max())
+
+
+def _replay(cfg, dtype, tol):
+    from infero_b200.config import EngineConfig
+    from infero_b200.engine import ModelRunner, StepEntry
+    from infero_b200.loading import load_model, write_random_model_dir
+    _register()
+    with tempfile.TemporaryDirectory(prefix="infero_b200_toy_") as tmp:
+        write_random_model_dir(tmp, cfg, seed=11, dtype=dtype, std=0.12, norm_std=0.1)
+        model, _ = load_model(tmp, dtype, DEV)
+        _, w = P.read_model(tmp, torch.float64)
+    runner = ModelRunner(model, EngineConfig(dtype=dtype, page_size=16, num_pages=9, max_seqs=2, ctx=128,
+                                             max_batch_tokens=256, max_logit_rows=256, cuda_graphs=False))
+    g = torch.Generator().manual_seed(2)
+    reqs = {r: [int(t) for t in torch.randint(0, cfg["vocab"], (n,), generator=g)]
+            for r, n in (("a", 61), ("b", 19), ("c", 40))}
+    plain = {r: _plain(cfg, w, t) for r, t in reqs.items()}
+    got = {r: [] for r in reqs}
+
+    def run(parts):
+        out = runner.step([StepEntry(r, reqs[r][a:b], list(range(b - a))) for r, a, b in parts])
+        row = 0
+        for r, a, b in parts:
+            got[r].append(out[row:row + b - a].float().cpu())
+            row += b - a
+
+    runner.open("a"); runner.open("b")
+    run([("a", 0, 33), ("b", 0, 2)])
+    run([("b", 2, 3), ("a", 33, 50)])
+    run([("a", 50, 51), ("b", 3, 19)])
+    runner.close("b")
+    runner.open("c")                                      # on b's pages
+    run([("c", 0, 38), ("a", 51, 52)])
+    for t in range(52, 61):
+        run([("a", t, t + 1)] + ([("c", 38 + t - 52, 39 + t - 52)] if t < 54 else []))
+    for r in reqs:
+        err = _rel(torch.cat(got[r]), plain[r])
+        assert err <= tol, f"request {r}: {err:.3e}"
+    runner.manager.check()
+
+
+def test_a_routed_feed_forward_and_another_position_encoding_plug_in():
+    """Layers with different feed-forwards and position encodings in one model, 32-bit."""
+    _replay(TOY, "float32", 2e-5)
+
+
+def test_another_position_encoding_in_bfloat16():
+    """The in-place form of a position encoding on the bf16 path (q and k are then materialised
+    from the split-K sums before the cache append)."""
+    _replay(TOY_DENSE, "bfloat16", 3e-2)
