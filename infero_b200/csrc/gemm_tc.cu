@@ -25,6 +25,7 @@
 // Sizes: any M and N; K a multiple of 8 (rows must start on 16-byte boundaries for TMA);
 // edges are zero-filled by TMA on the way in and masked on the way out.
 #include "tc_common.cuh"
+#include <atomic>
 #include <cudaTypedefs.h>
 #include <mutex>
 #include <unordered_map>
@@ -305,6 +306,66 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 }
 
+// One epilogue warp's share of a finished accumulator: its 32 rows (TMEM lanes at lane_addr, result
+// row ra for this thread) by BN columns starting at feature b0, written as the epilogue EPI says.
+template <int EPI, typename OutT>
+__device__ __forceinline__ void drain_accumulator(uint32_t lane_addr, int ra, int b0, int BN, int RA, int RB,
+                                                  OutT* __restrict__ out, const void* __restrict__ bias,
+                                                  int bias_dtype, long long ldc) {
+    const int col_end = min(RB, b0 + BN);                // what this tile owns
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (b0 + c0 >= col_end) break;               // uniform over the block
+        uint32_t u[32];
+        tmem_ld32_nowait(lane_addr + (uint32_t)c0, u);
+        tmem_wait_ld();
+        if (ra < RA) {
+#pragma unroll
+            for (int hseg = 0; hseg < 2; ++hseg) {
+                const int rb = b0 + c0 + hseg * 16;
+                if (rb >= col_end) break;
+                float v[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) v[e] = __uint_as_float(u[hseg * 16 + e]);
+                if (EPI == EPI_ROW_SWIGLU) {
+                    OutT* dst = out + (size_t)ra * ldc + (rb >> 1);
+                    float h[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) h[e] = silu_mul(v[2 * e], v[2 * e + 1]);
+                    if (rb + 16 <= RB && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0 && sizeof(OutT) == 2) {
+                        uint32_t pk[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            __nv_bfloat162 t2 = __floats2bfloat162_rn(h[2 * e], h[2 * e + 1]);
+                            pk[e] = *reinterpret_cast<uint32_t*>(&t2);
+                        }
+                        *reinterpret_cast<uint4*>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e)
+                            if (rb + 2 * e + 1 < RB) dst[e] = from_f32<OutT>(h[e]);
+                    }
+                } else {
+                    OutT* dst = out + (size_t)ra * ldc + rb;
+                    if (bias) {
+#pragma unroll
+                        for (int e = 0; e < 16; ++e)
+                            if (rb + e < RB) v[e] += load_any(bias, bias_dtype, rb + e);
+                    }
+                    if (rb + 16 <= RB) {
+                        store16<OutT>(dst, v, (reinterpret_cast<uintptr_t>(dst) & 15u) == 0);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 16; ++e)
+                            if (rb + e < RB) dst[e] = from_f32<OutT>(v[e]);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    }
+}
+
 // ---- many tokens: persistent, two accumulators --------------------------------------------------
 // One CTA per SM walks over 128 x 256 tiles of the result (tile t = blockIdx.x, + gridDim.x, ...).
 // Tile numbers run over the token blocks of one block of 256 features first, so that at any
@@ -464,58 +525,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[a], (uint32_t)(i >> 1) & 1u, abort_flag))) { ok = false; break; }
             tc_fence_after_sync();
             const uint32_t lane_addr = tmem_base + (uint32_t)a * PERS_MAX_BN + ((uint32_t)(q * 32) << 16);
-            const int col_end = min(RB, b0 + BN);                // what this tile owns
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                if (b0 + c0 >= col_end) break;               // uniform over the block
-                uint32_t u[32];
-                tmem_ld32_nowait(lane_addr + (uint32_t)c0, u);
-                tmem_wait_ld();
-                if (ra < RA) {
-#pragma unroll
-                    for (int hseg = 0; hseg < 2; ++hseg) {
-                        const int rb = b0 + c0 + hseg * 16;
-                        if (rb >= col_end) break;
-                        float v[16];
-#pragma unroll
-                        for (int e = 0; e < 16; ++e) v[e] = __uint_as_float(u[hseg * 16 + e]);
-                        if (EPI == EPI_ROW_SWIGLU) {
-                            OutT* dst = out + (size_t)ra * ldc + (rb >> 1);
-                            float h[8];
-#pragma unroll
-                            for (int e = 0; e < 8; ++e) h[e] = silu_mul(v[2 * e], v[2 * e + 1]);
-                            if (rb + 16 <= RB && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0 && sizeof(OutT) == 2) {
-                                uint32_t pk[4];
-#pragma unroll
-                                for (int e = 0; e < 4; ++e) {
-                                    __nv_bfloat162 t2 = __floats2bfloat162_rn(h[2 * e], h[2 * e + 1]);
-                                    pk[e] = *reinterpret_cast<uint32_t*>(&t2);
-                                }
-                                *reinterpret_cast<uint4*>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                            } else {
-#pragma unroll
-                                for (int e = 0; e < 8; ++e)
-                                    if (rb + 2 * e + 1 < RB) dst[e] = from_f32<OutT>(h[e]);
-                            }
-                        } else {
-                            OutT* dst = out + (size_t)ra * ldc + rb;
-                            if (bias) {
-#pragma unroll
-                                for (int e = 0; e < 16; ++e)
-                                    if (rb + e < RB) v[e] += load_any(bias, bias_dtype, rb + e);
-                            }
-                            if (rb + 16 <= RB) {
-                                store16<OutT>(dst, v, (reinterpret_cast<uintptr_t>(dst) & 15u) == 0);
-                            } else {
-#pragma unroll
-                                for (int e = 0; e < 16; ++e)
-                                    if (rb + e < RB) dst[e] = from_f32<OutT>(v[e]);
-                            }
-                        }
-                    }
-                }
-                __syncwarp();
-            }
+            drain_accumulator<EPI, OutT>(lane_addr, ra, b0, BN, RA, RB, out, bias, bias_dtype, ldc);
             // this warp has read its quarter of the accumulator: hand it back
             tc_fence_before_sync();
             __syncwarp();
@@ -531,6 +541,192 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     if (warp == 1) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, 2 * PERS_MAX_BN);
+    }
+}
+
+// ---- many tokens: a pair of CTAs per tile (cta_group::2) ---------------------------------------------
+// A cluster of two CTAs works on tiles of 256 token rows x BN features.  Each CTA loads its own 128
+// rows of the activations and its own half of the tile's weight rows, so every byte enters the
+// pair's shared memory once and an SM's shared memory takes 128 + BN/2 rows per step of K instead
+// of 128 + BN; the CTA of rank 0 issues the MMAs for both, each CTA's tensor memory holds the
+// accumulator rows of its own tokens, and each CTA's four epilogue warps write those rows.  All
+// loads of a stage report to rank 0's barrier; the commits that free a stage or publish an
+// accumulator reach both CTAs; the epilogue warps of both hand an accumulator back on rank 0's
+// barrier.  The pairs walk the tiles as the single CTAs above do.
+constexpr int PAIR_STAGES = 6, PAIR_ROWS = 2 * TILE_A;
+
+template <int EPI, typename OutT>
+__global__ void __launch_bounds__(GEMM_THREADS)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    OutT* __restrict__ out, const void* __restrict__ bias, int bias_dtype,
+                    int RA, int RB, int K, long long ldc, int BN, int* __restrict__ err_flag) {
+    constexpr int STAGES = PAIR_STAGES;
+    constexpr int BAR_OFFSET = STAGES * (A_STAGE_BYTES + (PERS_MAX_BN / 2) * TILE_K * 2);
+    const int half_bn = BN >> 1;
+    const int stage_bytes = A_STAGE_BYTES + half_bn * TILE_K * 2;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + BAR_OFFSET);    // used in rank 0
+    uint64_t* empty_bar = full_bar + STAGES;                                 // in both
+    uint64_t* acc_full = empty_bar + STAGES;                                 // 2, in both
+    uint64_t* acc_empty = acc_full + 2;                                      // 2, used in rank 0 (eight arrivals)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* never_flag = abort_flag + 1;
+
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int pair = (int)(blockIdx.x >> 1), n_pairs = (int)(gridDim.x >> 1);
+    const int tiles_a = (RA + PAIR_ROWS - 1) / PAIR_ROWS, tiles_b = (RB + BN - 1) / BN;
+    const int n_tiles = tiles_a * tiles_b;
+    const int n_kt = (K + TILE_K - 1) / TILE_K;
+    const int my_tiles = pair < n_tiles ? (n_tiles - 1 - pair) / n_pairs + 1 : 0;
+
+    if (threadIdx.x == 0) {
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&acc_full[a], 1);
+            mbar_init(&acc_empty[a], 8);
+        }
+        *abort_flag = 0;
+        *never_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, 2 * PERS_MAX_BN);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before_sync();
+    cluster_sync_all();                                   // both CTAs' barriers exist before either is used
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---- loader (one thread in each CTA) ---------------------------------------------------------
+        if (elect_one()) {
+            const long long total = (long long)my_tiles * n_kt;
+            long long issued = 0;
+            bool ok = true;
+            int tile = pair, kt = 0;
+            int a0 = (tile % tiles_a) * PAIR_ROWS + (int)rank * TILE_A;
+            int b0 = (tile / tiles_a) * BN + (int)rank * half_bn;
+            auto advance = [&]() {
+                if (++kt == n_kt) {
+                    kt = 0;
+                    tile += n_pairs;
+                    a0 = (tile % tiles_a) * PAIR_ROWS + (int)rank * TILE_A;
+                    b0 = (tile / tiles_a) * BN + (int)rank * half_bn;
+                }
+            };
+            uint32_t lead_full[STAGES];
+            for (int s = 0; s < STAGES; ++s) lead_full[s] = cluster_addr_of(&full_bar[s], 0);
+            // weights of the first stages before the kernel in front has finished, activations after
+            const int pre = (int)(total < STAGES ? total : STAGES);
+            int pa0[STAGES], pkx[STAGES];
+            for (int it = 0; it < pre; ++it) {
+                if (rank == 0) mbar_expect_tx(&full_bar[it], 2 * stage_bytes);
+                tma_load_2d_pair(smem + it * stage_bytes + A_STAGE_BYTES, &map_b, kt * TILE_K, b0, lead_full[it]);
+                pa0[it] = a0;
+                pkx[it] = kt * TILE_K;
+                advance();
+            }
+            pdl_wait();
+            for (int it = 0; it < pre; ++it) {
+                tma_load_2d_pair(smem + it * stage_bytes, &map_a, pkx[it], pa0[it], lead_full[it]);
+                issued = it + 1;
+            }
+            int s = pre % STAGES;
+            uint32_t ph = (uint32_t)(pre / STAGES) & 1u;
+            for (long long it = pre; it < total; ++it) {
+                if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+                uint8_t* sa = smem + s * stage_bytes;
+                if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * stage_bytes);
+                tma_load_2d_pair(sa, &map_a, kt * TILE_K, a0, lead_full[s]);
+                tma_load_2d_pair(sa + A_STAGE_BYTES, &map_b, kt * TILE_K, b0, lead_full[s]);
+                issued = it + 1;
+                advance();
+                if (++s == STAGES) { s = 0; ph ^= 1u; }
+            }
+            if (!ok) {
+                *abort_flag = 1;
+                atomicExch(err_flag, 1);
+            }
+            if (*abort_flag && rank == 0) {
+                // what is still in flight into rank 0's own stages reports to these barriers
+                for (long long it = issued > STAGES ? issued - STAGES : 0; it < issued; ++it)
+                    mbar_wait(&full_bar[it % STAGES], (uint32_t)(it / STAGES) & 1u, never_flag);
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issue: rank 0 for the pair -----------------------------------------------------------
+        if (rank == 0 && elect_one()) {
+            const uint32_t idesc = idesc_bf16_f32(PAIR_ROWS, BN);
+            bool ok = true;
+            int s = 0;
+            uint32_t ph = 0;
+            for (int i = 0; i < my_tiles && ok; ++i) {
+                const int a = i & 1;
+                if (!mbar_wait(&acc_empty[a], ((uint32_t)(i >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t acc = tmem_base + (uint32_t)a * PERS_MAX_BN;
+                for (int kt = 0; kt < n_kt; ++kt) {
+                    if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t sa = smem_u32(smem + s * stage_bytes);
+                    const uint64_t da = smem_desc_k_sw128(sa);
+                    const uint64_t db = smem_desc_k_sw128(sa + A_STAGE_BYTES);
+#pragma unroll
+                    for (int k = 0; k < TILE_K / UMMA_K; ++k)
+                        umma_bf16_pair(acc, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kt > 0 || k > 0) ? 1u : 0u);
+                    umma_commit_pair(&empty_bar[s]);
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                }
+                if (ok) umma_commit_pair(&acc_full[a]);
+            }
+            if (!ok) {
+                *abort_flag = 1;
+                atomicExch(err_flag, 2);
+            }
+        }
+    } else {
+        // ---- epilogue: each CTA its own 128 rows ------------------------------------------------------
+        const int q = warp & 3;
+        bool ok = true;
+        uint32_t lead_empty[2];
+        for (int a = 0; a < 2; ++a) lead_empty[a] = cluster_addr_of(&acc_empty[a], 0);
+        for (int i = 0; i < my_tiles; ++i) {
+            const int a = i & 1;
+            const int t = pair + i * n_pairs;
+            const int a0 = (t % tiles_a) * PAIR_ROWS + (int)rank * TILE_A, b0 = (t / tiles_a) * BN;
+            const int ra = a0 + q * 32 + lane;
+            if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[a], (uint32_t)(i >> 1) & 1u, abort_flag))) { ok = false; break; }
+            tc_fence_after_sync();
+            const uint32_t lane_addr = tmem_base + (uint32_t)a * PERS_MAX_BN + ((uint32_t)(q * 32) << 16);
+            drain_accumulator<EPI, OutT>(lane_addr, ra, b0, BN, RA, RB, out, bias, bias_dtype, ldc);
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(lead_empty[a]);
+        }
+        if (!ok && lane == 0) {
+            *abort_flag = 1;
+            atomicExch(err_flag, 3);
+        }
+    }
+    // neither CTA may leave while the other can still read its shared memory or signal its barriers
+    __syncwarp();
+    tc_fence_before_sync();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, 2 * PERS_MAX_BN);
     }
 }
 
@@ -626,11 +822,102 @@ int launch_persistent(const void* x, const void* w, void* out, const void* bias,
     return infero_check_launch("gemm_tc_persistent");
 }
 
+// Tile width for pairs of CTAs (256 token rows per tile).
+int pick_pair_tile_n(int M, int N, int pairs, int multiple) {
+    if (const char* e = getenv("INFERO_GEMM_TILE_N")) {
+        const int v = atoi(e);
+        if (v >= 32 && v <= PERS_MAX_BN && v % multiple == 0) return v;
+    }
+    const int tiles_a = (M + PAIR_ROWS - 1) / PAIR_ROWS;
+    long long best_cost = -1;
+    int best = PERS_MAX_BN;
+    for (int bn = PERS_MAX_BN; bn >= 64; bn -= 32) {
+        if (bn % multiple) continue;
+        const long long tiles = (long long)tiles_a * ((N + bn - 1) / bn);
+        const long long rounds = (tiles + pairs - 1) / pairs;
+        const long long cost = rounds * (bn + 100);
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
+    }
+    return best;
+}
+
+// 0: pairs not tried yet; > 0: clusters of two that fit on the device at once; < 0: unusable
+template <int EPI, typename OutT>
+int launch_pair(const void* x, const void* w, void* out, const void* bias, int bias_dtype,
+                int RA, int RB, int K, int ldx, long long ldc, int* err, cudaStream_t stream) {
+    constexpr int SMEM = PAIR_STAGES * (A_STAGE_BYTES + (PERS_MAX_BN / 2) * TILE_K * 2) + 256 + 1024;
+    auto kern = gemm_tc_pair_kernel<EPI, OutT>;
+    static int max_pairs = 0;
+    if (max_pairs == 0) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e == cudaSuccess) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(2);
+            cfg.blockDim = dim3(GEMM_THREADS);
+            cfg.dynamicSmemBytes = SMEM;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 2;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            int n = 0;
+            e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+            max_pairs = (e == cudaSuccess && n > 0) ? n : -1;
+        } else {
+            max_pairs = -1;
+        }
+        if (max_pairs < 0) cudaGetLastError();
+    }
+    if (max_pairs < 0) return -1;
+    const int bn = pick_pair_tile_n(RA, RB, max_pairs, 32);
+    CUtensorMap ma, mb;
+    if (get_map(x, RA, K, ldx, TILE_A, &ma)) return 1;
+    if (get_map(w, RB, K, K, bn / 2, &mb)) return 1;
+    const int n_tiles = ((RA + PAIR_ROWS - 1) / PAIR_ROWS) * ((RB + bn - 1) / bn);
+    const int pairs = n_tiles < max_pairs ? n_tiles : max_pairs;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = infero_pdl_enabled() ? 2 : 1;
+    cudaLaunchKernelEx(&cfg, kern, ma, mb, (OutT*)out, bias, bias_dtype, RA, RB, K, ldc, bn, err);
+    return infero_check_launch("gemm_tc_pair");
+}
+
+// Pairs of CTAs are used unless INFERO_GEMM_PAIR=0 (or infero_gemm_set_pairs(0)), for token counts
+// that fill tiles of 256 rows nearly as well as tiles of 128.
+std::atomic<int> g_pairs{-1};
+bool pairs_wanted(int M) {
+    int v = g_pairs.load(std::memory_order_relaxed);
+    if (v < 0) {
+        const char* e = getenv("INFERO_GEMM_PAIR");
+        v = (e && e[0] == '0') ? 0 : 1;
+        g_pairs.store(v, std::memory_order_relaxed);
+    }
+    if (!v) return false;
+    const long long pad256 = (long long)((M + PAIR_ROWS - 1) / PAIR_ROWS) * PAIR_ROWS;
+    const long long pad128 = (long long)((M + TILE_A - 1) / TILE_A) * TILE_A;
+    return pad256 * 100 <= pad128 * 107;
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace
 
 extern "C" {
+
+void infero_gemm_set_pairs(int on) { g_pairs.store(on ? 1 : 0, std::memory_order_relaxed); }
 
 // Can the tensor-core kernel take this product?  (bf16 operands are the caller's business.)
 int infero_gemm_tc_supported(const void* x, const void* w, int M, int N, int K, int ldx) {
@@ -751,6 +1038,12 @@ int infero_gemm_tc(const void* x, const void* w, const void* bias, int bias_dtyp
             return launch<256, 4, EPI_ROW, float>(mx, mw, out, bias, bias_dtype, M, N, K, total_kt, 1, ldc, 0, err, stream);
         return launch<256, 4, EPI_ROW, bf16>(mx, mw, out, bias, bias_dtype, M, N, K, total_kt, 1, ldc, 0, err, stream);
     }
+    if (pairs_wanted(M)) {
+        const int r = out_dtype == INFERO_F32
+                          ? launch_pair<EPI_ROW, float>(x, w, out, bias, bias_dtype, M, N, K, ldx, ldc, err, stream)
+                          : launch_pair<EPI_ROW, bf16>(x, w, out, bias, bias_dtype, M, N, K, ldx, ldc, err, stream);
+        if (r >= 0) return r;
+    }
     if (out_dtype == INFERO_F32)
         return launch_persistent<EPI_ROW, float>(x, w, out, bias, bias_dtype, M, N, K, ldx, ldc, sm_count, err, stream);
     return launch_persistent<EPI_ROW, bf16>(x, w, out, bias, bias_dtype, M, N, K, ldx, ldc, sm_count, err, stream);
@@ -790,6 +1083,10 @@ int infero_gemm_tc_swiglu(const void* x, const void* w, void* out, int M, int N,
     CUtensorMap mx, mw;
     if (get_map(x, M, K, ldx, TILE_A, &mx)) return 1;
     if (get_map(w, N, K, K, 256, &mw)) return 1;
+    if (pairs_wanted(M)) {
+        const int r = launch_pair<EPI_ROW_SWIGLU, bf16>(x, w, out, nullptr, 0, M, N, K, ldx, ldc, err, stream);
+        if (r >= 0) return r;
+    }
     return launch_persistent<EPI_ROW_SWIGLU, bf16>(x, w, out, nullptr, 0, M, N, K, ldx, ldc, sm_count, err, stream);
 }
 

@@ -189,6 +189,65 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
         : "memory");
 }
 
+// ---- a pair of CTAs on one tile (cluster of two, cta_group::2) ------------------------------------
+// The two CTAs of a cluster share one MMA: each holds half of the rows of A and half of the rows of
+// B in its own shared memory and half of the accumulator's rows in its own tensor memory; the CTA
+// of rank 0 issues the instruction for both.  TMA loads of either CTA report to a barrier of rank
+// 0 (no multicast is used anywhere); tcgen05.commit tells both CTAs' barriers.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// The address, in the cluster's shared window, of the same shared-memory location in the CTA of the given rank.
+__device__ __forceinline__ uint32_t cluster_addr_of(const void* local_smem, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(local_smem)), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int x, int y,
+                                                 uint32_t cluster_bar_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(cluster_bar_addr)
+        : "memory");
+}
+// Executed by the same warp of both CTAs with the same destination offset.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)),
+                 "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// Arrive on the barrier at this shared-memory offset in both CTAs once the pair's MMAs issued so far have finished.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(smem_u32(bar)), "h"((uint16_t)3)
+        : "memory");
+}
+// D (256 x N over the two CTAs' tensor memories) (+)= A * B^T; descriptors name rank 0's shared memory,
+// the same offsets are read in rank 1.
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+
 // ---- descriptors -----------------------------------------------------------------------------
 // Shared-memory operand, K-major, 128-byte swizzle: rows of 128 bytes (64 bf16), groups of
 // eight rows 1024 bytes apart, tile base aligned to 1024 bytes.  Stepping 16 elements along

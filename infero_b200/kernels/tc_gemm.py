@@ -57,6 +57,12 @@ def gemm(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: to
                                 c_int(tile_n), _stream()))
 
 
+def set_pairs(on: bool) -> None:
+    """Many-token products on pairs of CTAs (cta_group::2) or on single CTAs; on unless
+    ``INFERO_GEMM_PAIR=0``."""
+    lib().infero_gemm_set_pairs(c_int(1 if on else 0))
+
+
 def gemm_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
     """out[M, N/2] = silu(g) * u where (g_j, u_j) are columns (2j, 2j+1) of a @ w^T.  Returns False
     (nothing launched) when few rows would need more than one split of K."""

@@ -33,14 +33,25 @@ GEMM_TC_SHAPES = [
     (1, 128, 64), (1, 3584, 3584), (8, 4608, 3584), (8, 3584, 18944), (3, 1000, 96), (16, 777, 224),
     (17, 512, 64), (33, 300, 176), (64, 1152, 896), (65, 2048, 1024), (130, 640, 520), (256, 384, 200),
     (257, 512, 128), (300, 777, 224), (512, 1000, 96), (1024, 4608, 3584), (2048, 1280, 4864), (384, 96, 256),
-    (2048, 3584, 320), (1500, 3000, 136), (20000, 200, 72),     # tile widths other than 256; many rounds per CTA
+    (2048, 3584, 320), (1500, 3000, 136), (20000, 200, 72), (511, 130, 64), (769, 3584, 136), (1000, 48, 512),     # tile widths other than 256; many rounds per CTA
 ]
+
+
+@pytest.fixture(params=["pairs", "single"])
+def cta_pairs(request):
+    """Many-token products both ways: on pairs of CTAs sharing an MMA, and on single CTAs."""
+    from infero_b200.kernels import tc_gemm
+    tc_gemm.set_pairs(request.param == "pairs")
+    yield request.param
+    tc_gemm.set_pairs(True)
 
 
 @pytest.mark.parametrize("M,N,K", GEMM_TC_SHAPES)
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-def test_gemm_tensor_core(M, N, K, out_dtype):
+def test_gemm_tensor_core(M, N, K, out_dtype, cta_pairs):
     from infero_b200.kernels import tc_gemm
+    if cta_pairs == "single" and M <= 256:
+        pytest.skip("few rows take another kernel either way")
     a = _rand((M, K), torch.bfloat16, 1)
     w = _rand((N, K), torch.bfloat16, 2, 0.05)
     bias = _rand((N,), torch.bfloat16, 3)
@@ -87,8 +98,10 @@ def test_gemm_tensor_core_partials_sum_in_fixed_order():
 
 @pytest.mark.parametrize("M,N,K", [(8, 37888, 3584), (64, 1024, 512), (300, 400, 264), (2048, 1280, 512), (5, 354, 64),
                                    (2048, 7168, 192), (700, 3000, 72)])
-def test_gemm_tensor_core_with_swiglu_epilogue(M, N, K):
+def test_gemm_tensor_core_with_swiglu_epilogue(M, N, K, cta_pairs):
     from infero_b200.kernels import tc_gemm
+    if cta_pairs == "single" and M <= 256:
+        pytest.skip("few rows take another kernel either way")
     a = _rand((M, K), torch.bfloat16, 1)
     w = _rand((N, K), torch.bfloat16, 2, 0.1)
     out = torch.full((M, N // 2), 7.0, dtype=torch.bfloat16, device=DEV)
