@@ -1,18 +1,22 @@
 // Prompt-portion attention over the paged cache on the 5th-generation tensor cores.
 //
-// One CTA = 128 consecutive query tokens of one request and one head.  It walks the visible
-// keys in tiles of 64 (two CTAs share an SM: 96 KB of shared memory and 256 TMEM columns each,
-// so one's softmax runs under the other's MMAs):
+// One CTA = 128 consecutive query tokens of one request and TWO heads that share a kv head (the
+// last head of an odd group works alone).  Both heads see the same keys, so every key and value
+// tile is fetched from L2 once for 256 query rows: with one head per CTA the kernel was bound by
+// L2 bandwidth (128 flops per byte fetched; measured 665 TFLOP/s with the softmax taken out).
+// The CTA walks the visible keys in tiles of 64; per head:
 //   S = Q K^T     tcgen05.mma, both operands in shared memory (TMA, 128-byte swizzle), S in TMEM
-//   P = 2^(S*c - m), running maximum m and sum l per row; one thread owns one query row (it
+//   P = 2^(S*c - m), reference point m and sum l per row; one thread owns one query row (it
 //                 reads its row of S from TMEM with tcgen05.ld into registers, once), writes P
-//                 back over S as bf16 and, when its maximum moved, rescales its row of O in TMEM
+//                 back over S as bf16 and, when its reference point moved, rescales its row of O
 //   O += P V      tcgen05.mma with P from TMEM and V from shared memory (N-contiguous operand)
-// Warp roles: 0..3 softmax and epilogue (128 rows), 4 loads (one thread issues TMA for Q once,
-// then key and value tiles page by page from the block table, each into its own two-stage
-// ring), 5 owns TMEM and issues the MMAs.  S is double-buffered so that Q K^T of the next tile
-// runs while the softmax of this one does.  Scores, maxima, sums and O are 32-bit; P is rounded
-// to bf16 for the second product, as the keys and values are.
+// Warp roles: 0..3 softmax and epilogue of the first head (128 rows), 4..7 of the second, 8 loads
+// the two Q blocks once and then the key tiles, 9 the value tiles (each into its own ring, page by
+// page from the block table, four lanes side by side), 10 owns TMEM and issues the MMAs of both heads.  Each
+// head has two S buffers and one O (256 TMEM columns), so Q K^T of the next tile runs while the
+// softmax of this one does, and one head's softmax runs under the other's products.  Scores,
+// maxima, sums and O are 32-bit; P is rounded to bf16 for the second product, as the keys and
+// values are.
 //
 // Same formula as attention_generic.cu: key j is visible from the query at position p iff
 // lo <= j <= p with lo = max(0, p - window + 1).  The reference's prefill attention is
@@ -28,24 +32,29 @@ namespace {
 
 using namespace tc;
 
-constexpr int QROWS = 128, KTILE = 64, PFT_THREADS = 192, SLICE = 16;
+constexpr int QROWS = 128, KTILE = 64, SLICE = 16;
+constexpr int PFT_K_WARP = 8, PFT_V_WARP = 9, PFT_MMA_WARP = 10, PFT_THREADS = 352;      // warps 0..7: softmax
+constexpr float RESCALE_STEP = 8.0f;
 
 template <int D>
 struct PfPlan {
     static constexpr int DB = D / 64;                        // 64-element blocks along the head
+    static constexpr int STAGES = D == 128 ? 4 : 8;          // key tiles (and value tiles) in flight
     static constexpr int QBLOCK_BYTES = QROWS * 128;         // the query rows of one block
     static constexpr int KBLOCK_BYTES = KTILE * 128;         // the key (or value) rows of one block
-    static constexpr int Q_BYTES = DB * QBLOCK_BYTES;
+    static constexpr int Q_BYTES = DB * QBLOCK_BYTES;        // one head's queries
     static constexpr int KV_BYTES = DB * KBLOCK_BYTES;       // one K tile, or one V tile
-    static constexpr int Q_OFF = 0;
-    static constexpr int K_OFF = Q_BYTES;                    // two stages
-    static constexpr int V_OFF = Q_BYTES + 2 * KV_BYTES;     // two stages
-    static constexpr int BAR_OFFSET = Q_BYTES + 4 * KV_BYTES;
-    static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;
-    // two S buffers of KTILE columns, then O: 256 columns, so that two CTAs share an SM's 512
-    static constexpr uint32_t S_COL = 0, O_COL = 2 * KTILE;
-    static constexpr uint32_t TMEM_COLS = 256;
+    static constexpr int Q_OFF = 0;                          // two heads
+    static constexpr int K_OFF = 2 * Q_BYTES;
+    static constexpr int V_OFF = K_OFF + STAGES * KV_BYTES;
+    static constexpr int BAR_OFFSET = V_OFF + STAGES * KV_BYTES;
+    static constexpr int N_BARS = 1 + 4 * STAGES + 2 * 5;
+    static constexpr int TOTAL = BAR_OFFSET + 8 * N_BARS + 64 + 1024;
+    // per head: two S buffers of KTILE columns, then O; 256 columns per head, the SM's 512 for the CTA
+    static constexpr uint32_t HEAD_COLS = 256, S_COL = 0, O_COL = 2 * KTILE;
+    static constexpr uint32_t TMEM_COLS = 512;
     static_assert(2 * KTILE + D <= 256, "S, S and O must fit 256 TMEM columns");
+    static_assert(TOTAL > 116 * 1024, "one CTA per SM: it takes all of the SM's tensor memory");
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -67,20 +76,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        int first_entry, int n_tiles, int n_heads, int n_kv, int page_size, int window,
                        float scale_log2, int* __restrict__ err_flag) {
     using Plan = PfPlan<D>;
-    constexpr int DB = Plan::DB;
+    constexpr int DB = Plan::DB, ST = Plan::STAGES;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Plan::BAR_OFFSET);
     uint64_t* q_full = bars;                 // 1
-    uint64_t* k_full = bars + 1;             // 2
-    uint64_t* v_full = bars + 3;             // 2
-    uint64_t* k_empty = bars + 5;            // 2
-    uint64_t* v_empty = bars + 7;            // 2
-    uint64_t* s_full = bars + 9;             // 2
-    uint64_t* p_full = bars + 11;            // 2 (128 arrivals)
-    uint64_t* o_done = bars + 13;            // 1
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+    uint64_t* k_full = bars + 1;             // ST
+    uint64_t* v_full = k_full + ST;          // ST
+    uint64_t* k_empty = v_full + ST;         // ST
+    uint64_t* v_empty = k_empty + ST;        // ST
+    uint64_t* s_full = v_empty + ST;         // [head][2]
+    uint64_t* p_full = s_full + 4;           // [head][2] (128 arrivals)
+    uint64_t* o_done = p_full + 4;           // [head]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* never_flag = abort_flag + 1;
 
@@ -91,21 +100,24 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         prefetch_tensormap(&map_k);
         prefetch_tensormap(&map_v);
         mbar_init(q_full, 1);
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < ST; ++i) {
             mbar_init(&k_full[i], 1);
             mbar_init(&v_full[i], 1);
             mbar_init(&k_empty[i], 1);
             mbar_init(&v_empty[i], 1);
+        }
+        for (int i = 0; i < 4; ++i) {
             mbar_init(&s_full[i], 1);
             mbar_init(&p_full[i], 128);
         }
-        mbar_init(o_done, 1);
+        mbar_init(&o_done[0], 1);
+        mbar_init(&o_done[1], 1);
         *abort_flag = 0;
         *never_flag = 0;
         fence_barrier_init();
         fence_proxy_async();
     }
-    if (warp == 5) {
+    if (warp == PFT_MMA_WARP) {
         tmem_alloc(tmem_slot, Plan::TMEM_COLS);
         tmem_relinquish();
     }
@@ -115,11 +127,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t tmem_base = *tmem_slot;
     pdl_wait();                                        // q, the tables and this step's keys come from earlier kernels
 
-    // ---- which request and which block of 128 query rows? (longest first) ------------------------
-    const int h = blockIdx.x;
+    // ---- which kv head and pair of heads, which request and which block of 128 query rows? ------
+    const int group = n_heads / n_kv;
+    const int pairs = (group + 1) >> 1;
+    const int kvh = (int)blockIdx.x / pairs;
+    const int head0 = kvh * group + 2 * ((int)blockIdx.x % pairs);
+    const int n_q = (head0 + 1 < (kvh + 1) * group) ? 2 : 1;            // heads of this CTA
     int e = -1, tile_in_e = 0;
     {
-        int left = n_tiles - 1 - (int)blockIdx.y;
+        int left = n_tiles - 1 - (int)blockIdx.y;                           // longest first
         for (int i = first_entry; i < n_entries; ++i) {
             const int nt = (entry_q_len[i] + QROWS - 1) / QROWS;
             if (left < nt) { e = i; tile_in_e = left; break; }
@@ -136,47 +152,48 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         kt_begin = key_lo / KTILE;
         n_kt = last_pos / KTILE - kt_begin + 1;
     }
-    const int kvh = h / (n_heads / n_kv);
     const int* table = block_table + (size_t)(e < 0 ? 0 : e) * max_blocks;
     const int first_pos = pos0 + row_first;
 
-    if (warp == 4) {
-        // ---- loader ---------------------------------------------------------------------------------
-        if (n_kt > 0 && elect_one()) {
-            mbar_expect_tx(q_full, Plan::Q_BYTES);
-#pragma unroll
-            for (int b = 0; b < DB; ++b)
-                tma_load_2d(smem + Plan::Q_OFF + b * Plan::QBLOCK_BYTES, &map_q, h * D + b * 64, tok0 + row_first, q_full);
-            bool ok = true;
-            int k_issued = 0, v_issued = 0;
-            auto load_tile = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, int j) {
-                mbar_expect_tx(bar, Plan::KV_BYTES);
-                const int kb = (kt_begin + j) * KTILE;
-#pragma unroll 1
-                for (int sl = 0; sl < KTILE / SLICE; ++sl) {
-                    const int key0 = kb + sl * SLICE;
-                    const int blk = key0 / page_size;
-                    const int page = blk < max_blocks ? table[blk] : -1;
-                    // a page that is not held (beyond the request's end) is never visible; any finite rows do
-                    const int row = (page < 0 ? 0 : (page * n_kv + kvh) * page_size) + key0 % page_size;
+    if (warp == PFT_K_WARP || warp == PFT_V_WARP) {
+        // ---- loaders: one warp for the keys (and Q), one for the values ------------------------------
+        // Lane s < 4 fetches slice s (16 rows, one page or part of one) of every tile: the four look-ups
+        // in the block table and the four pairs of TMA instructions of a tile run side by side instead
+        // of one after the other in a single thread.
+        const bool is_k = warp == PFT_K_WARP;
+        if (n_kt > 0 && lane < KTILE / SLICE) {
+            const CUtensorMap* map = is_k ? &map_k : &map_v;
+            uint64_t* full = is_k ? k_full : v_full;
+            uint64_t* empty = is_k ? k_empty : v_empty;
+            uint8_t* ring = smem + (is_k ? Plan::K_OFF : Plan::V_OFF);
+            if (is_k && lane == 0) {
+                mbar_expect_tx(q_full, n_q * Plan::Q_BYTES);
+                for (int t = 0; t < n_q; ++t)
 #pragma unroll
                     for (int b = 0; b < DB; ++b)
-                        tma_load_2d(dst + b * Plan::KBLOCK_BYTES + sl * (SLICE * 128), map, b * 64, row, bar);
-                }
+                        tma_load_2d(smem + Plan::Q_OFF + t * Plan::Q_BYTES + b * Plan::QBLOCK_BYTES, &map_q,
+                                    (head0 + t) * D + b * 64, tok0 + row_first, q_full);
+            }
+            auto row_of = [&](int j) {
+                const int key0 = (kt_begin + j) * KTILE + lane * SLICE;
+                const int blk = key0 / page_size;
+                const int page = blk < max_blocks ? table[blk] : -1;
+                // a page that is not held (beyond the request's end) is never visible; any finite rows do
+                return (page < 0 ? 0 : (page * n_kv + kvh) * page_size) + key0 % page_size;
             };
-            for (int i = 0; i <= n_kt && ok; ++i) {
-                if (i < n_kt) {
-                    const int s = i & 1;
-                    if (!mbar_wait(&k_empty[s], ((uint32_t)(i >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
-                    load_tile(&map_k, smem + Plan::K_OFF + s * Plan::KV_BYTES, &k_full[s], i);
-                    k_issued = i + 1;
-                }
-                if (i > 0) {
-                    const int j = i - 1, s = j & 1;
-                    if (!mbar_wait(&v_empty[s], ((uint32_t)(j >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
-                    load_tile(&map_v, smem + Plan::V_OFF + s * Plan::KV_BYTES, &v_full[s], j);
-                    v_issued = j + 1;
-                }
+            bool ok = true;
+            int issued = 0;
+            int row = row_of(0);
+            for (int i = 0; i < n_kt; ++i) {
+                const int s = i % ST;
+                const int next_row = i + 1 < n_kt ? row_of(i + 1) : 0;      // looked up while waiting
+                if (!mbar_wait(&empty[s], ((uint32_t)(i / ST) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+                if (lane == 0) mbar_expect_tx(&full[s], Plan::KV_BYTES);
+                uint8_t* dst = ring + s * Plan::KV_BYTES + lane * (SLICE * 128);
+#pragma unroll
+                for (int b = 0; b < DB; ++b) tma_load_2d(dst + b * Plan::KBLOCK_BYTES, map, b * 64, row, &full[s]);
+                issued = i + 1;
+                row = next_row;
             }
             if (!ok) {
                 *abort_flag = 1;
@@ -184,30 +201,32 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             if (*abort_flag) {
                 // let copies that are still in flight land before the block goes away
-                mbar_wait(q_full, 0, never_flag);
-                for (int i = max(0, k_issued - 2); i < k_issued; ++i) mbar_wait(&k_full[i & 1], (uint32_t)(i >> 1) & 1u, never_flag);
-                for (int i = max(0, v_issued - 2); i < v_issued; ++i) mbar_wait(&v_full[i & 1], (uint32_t)(i >> 1) & 1u, never_flag);
+                if (is_k && lane == 0) mbar_wait(q_full, 0, never_flag);
+                for (int i = max(0, issued - ST); i < issued; ++i) mbar_wait(&full[i % ST], (uint32_t)(i / ST) & 1u, never_flag);
             }
         }
-    } else if (warp == 5) {
-        // ---- MMA issue ------------------------------------------------------------------------------
+    } else if (warp == PFT_MMA_WARP) {
+        // ---- MMA issue, both heads ------------------------------------------------------------------
         if (n_kt > 0 && elect_one()) {
             constexpr uint32_t idesc_qk = idesc_bf16_f32(QROWS, KTILE);
             constexpr uint32_t idesc_pv = idesc_bf16_f32_b_mn(QROWS, D);
-            const uint32_t q_addr = smem_u32(smem + Plan::Q_OFF);
             bool ok = true;
+            // S = Q K^T of key tile j for every head of the CTA; the key stage is free after the last
             auto issue_qk = [&](int j) {
-                const uint32_t k_addr = smem_u32(smem + Plan::K_OFF + (j & 1) * Plan::KV_BYTES);
-                const uint32_t s_tmem = tmem_base + Plan::S_COL + (uint32_t)(j & 1) * KTILE;
+                const uint32_t k_addr = smem_u32(smem + Plan::K_OFF + (j % ST) * Plan::KV_BYTES);
+                for (int t = 0; t < n_q; ++t) {
+                    const uint32_t q_addr = smem_u32(smem + Plan::Q_OFF + t * Plan::Q_BYTES);
+                    const uint32_t s_tmem = tmem_base + (uint32_t)t * Plan::HEAD_COLS + Plan::S_COL + (uint32_t)(j & 1) * KTILE;
 #pragma unroll
-                for (int ks = 0; ks < D / 16; ++ks) {
-                    const uint32_t in_block = (uint32_t)(ks & 3) * 32u;
-                    umma_bf16(s_tmem, smem_desc_k_sw128(q_addr + (uint32_t)(ks >> 2) * Plan::QBLOCK_BYTES + in_block),
-                              smem_desc_k_sw128(k_addr + (uint32_t)(ks >> 2) * Plan::KBLOCK_BYTES + in_block), idesc_qk,
-                              ks > 0 ? 1u : 0u);
+                    for (int ks = 0; ks < D / 16; ++ks) {
+                        const uint32_t in_block = (uint32_t)(ks & 3) * 32u;
+                        umma_bf16(s_tmem, smem_desc_k_sw128(q_addr + (uint32_t)(ks >> 2) * Plan::QBLOCK_BYTES + in_block),
+                                  smem_desc_k_sw128(k_addr + (uint32_t)(ks >> 2) * Plan::KBLOCK_BYTES + in_block), idesc_qk,
+                                  ks > 0 ? 1u : 0u);
+                    }
+                    umma_commit(&s_full[t * 2 + (j & 1)]);
                 }
-                umma_commit(&k_empty[j & 1]);
-                umma_commit(&s_full[j & 1]);
+                umma_commit(&k_empty[j % ST]);
             };
             if (!mbar_wait(q_full, 0, abort_flag) || !mbar_wait(&k_full[0], 0, abort_flag)) ok = false;
             if (ok) {
@@ -216,44 +235,53 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             for (int j = 0; j < n_kt && ok; ++j) {
                 if (j + 1 < n_kt) {
-                    if (!mbar_wait(&k_full[(j + 1) & 1], (uint32_t)((j + 1) >> 1) & 1u, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(&k_full[(j + 1) % ST], (uint32_t)((j + 1) / ST) & 1u, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
                     issue_qk(j + 1);
                 }
-                if (!mbar_wait(&p_full[j & 1], (uint32_t)(j >> 1) & 1u, abort_flag) ||
-                    !mbar_wait(&v_full[j & 1], (uint32_t)(j >> 1) & 1u, abort_flag)) { ok = false; break; }
-                tc_fence_after_sync();
-                const uint32_t v_addr = smem_u32(smem + Plan::V_OFF + (j & 1) * Plan::KV_BYTES);
-                const uint32_t p_tmem = tmem_base + Plan::S_COL + (uint32_t)(j & 1) * KTILE;
+                if (!mbar_wait(&v_full[j % ST], (uint32_t)(j / ST) & 1u, abort_flag)) { ok = false; break; }
+                const uint32_t v_addr = smem_u32(smem + Plan::V_OFF + (j % ST) * Plan::KV_BYTES);
+                for (int t = 0; t < n_q && ok; ++t) {
+                    if (!mbar_wait(&p_full[t * 2 + (j & 1)], (uint32_t)(j >> 1) & 1u, abort_flag)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t head_tmem = tmem_base + (uint32_t)t * Plan::HEAD_COLS;
+                    const uint32_t p_tmem = head_tmem + Plan::S_COL + (uint32_t)(j & 1) * KTILE;
 #pragma unroll
-                for (int ks = 0; ks < KTILE / 16; ++ks) {
-                    // 16 keys: 8 columns of P (two bf16 each), 16 rows of V (2048 bytes)
-                    const uint64_t vd = smem_desc_mn_sw128(v_addr + (uint32_t)ks * 2048u, Plan::KBLOCK_BYTES, 1024u);
-                    umma_bf16_ts(tmem_base + Plan::O_COL, p_tmem + (uint32_t)ks * 8u, vd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                    for (int ks = 0; ks < KTILE / 16; ++ks) {
+                        // 16 keys: 8 columns of P (two bf16 each), 16 rows of V (2048 bytes)
+                        const uint64_t vd = smem_desc_mn_sw128(v_addr + (uint32_t)ks * 2048u, Plan::KBLOCK_BYTES, 1024u);
+                        umma_bf16_ts(head_tmem + Plan::O_COL, p_tmem + (uint32_t)ks * 8u, vd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&o_done[t]);
                 }
-                umma_commit(&v_empty[j & 1]);
-                umma_commit(o_done);
+                if (ok) umma_commit(&v_empty[j % ST]);
             }
             if (!ok) {
                 *abort_flag = 1;
                 atomicExch(err_flag, 6);
             }
         }
-    } else if (n_kt > 0) {
-        // ---- softmax, correction of O, epilogue: one query row per thread --------------------------
-        const int r = warp * 32 + lane;
+    } else if (n_kt > 0 && (warp >> 2) < n_q) {
+        // ---- softmax, correction of O, epilogue: one query row of one head per thread -----------------
+        const int t = warp >> 2;                             // which head of the CTA
+        const int h = head0 + t;
+        const int r = (warp & 3) * 32 + lane;
         const bool valid = r < rows_here;
         const int pos_r = first_pos + r;
         const int hi_r = valid ? pos_r : -1;
         const int lo_r = window > 0 ? max(0, pos_r - window + 1) : 0;
-        const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
+        const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
+        const uint32_t head_tmem = tmem_base + (uint32_t)t * Plan::HEAD_COLS + lane_sel;
+        uint64_t* my_s_full = s_full + t * 2;
+        uint64_t* my_p_full = p_full + t * 2;
+        uint64_t* my_o_done = o_done + t;
         float m = -CUDART_INF_F, l = 0.f;
         bool ok = true;
         for (int j = 0; j < n_kt; ++j) {
             const int b = j & 1;
-            if (!__all_sync(0xffffffffu, mbar_wait(&s_full[b], (uint32_t)(j >> 1) & 1u, abort_flag))) { ok = false; break; }   // warp-uniform
+            if (!__all_sync(0xffffffffu, mbar_wait(&my_s_full[b], (uint32_t)(j >> 1) & 1u, abort_flag))) { ok = false; break; }   // warp-uniform
             tc_fence_after_sync();
-            const uint32_t s_addr = tmem_base + lane_sel + Plan::S_COL + (uint32_t)b * KTILE;
+            const uint32_t s_addr = head_tmem + Plan::S_COL + (uint32_t)b * KTILE;
             const int kb = (kt_begin + j) * KTILE;
             // every key of the tile visible from every row of the block?  (rows past the portion's
             // end then compute on, unmasked; nothing of theirs is stored)
@@ -264,66 +292,75 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
             for (int c = 0; c < KTILE / 32; ++c) tmem_ld32_nowait(s_addr + (uint32_t)c * 32u, sv + c * 32);
             tmem_wait_ld();
-            float mx = -CUDART_INF_F;
+            // four running maxima (and sums below): a chain of 16 dependent operations instead of 64
+            float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
             if (open_tile) {
 #pragma unroll
-                for (int i = 0; i < KTILE; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
+                for (int i = 0; i < KTILE; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
             } else {
 #pragma unroll
                 for (int i = 0; i < KTILE; ++i) {
                     const int key = kb + i;
                     if (!(key >= lo_r && key <= hi_r)) sv[i] = 0xff800000u;      // -inf: contributes 2^-inf = 0
-                    mx = fmaxf(mx, __uint_as_float(sv[i]));
+                    mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
                 }
             }
-            const float m_new = fmaxf(m, mx * scale_log2);
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            // The reference point m of the exponentials follows the row's maximum lazily: it moves only
+            // when the maximum has grown by more than RESCALE_STEP (in powers of two) since it was set,
+            // so that O is seldom rescaled; meanwhile P stays below 2^RESCALE_STEP, which bf16 holds with
+            // the same relative precision, and l and O refer to the same m, so the quotient is unchanged.
+            const float m_seen = fmaxf(m, mx * scale_log2);
+            const float m_new = (m_seen - m > RESCALE_STEP) ? m_seen : m;       // m = -inf: inf > step, moves
             const float sub = m_new == -CUDART_INF_F ? 0.f : m_new;     // a row with no key yet: avoid inf - inf
             const float corr = ex2(m - sub);
-            float sum = 0.f;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t pk[KTILE / 2];
 #pragma unroll
             for (int i = 0; i < KTILE; i += 2) {
                 const float p0 = ex2(fmaf(__uint_as_float(sv[i]), scale_log2, -sub));
                 const float p1 = ex2(fmaf(__uint_as_float(sv[i + 1]), scale_log2, -sub));
-                sum += p0 + p1;
+                sum4[(i >> 1) & 3] += p0 + p1;
                 pk[i >> 1] = pack2(p0, p1);
             }
+            const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             // P over S (every score is in registers by now)
 #pragma unroll
             for (int c = 0; c < KTILE / 32; ++c) tmem_st16(s_addr + (uint32_t)c * 16u, pk + c * 16);
             l = l * corr + sum;
             m = m_new;
-            if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
-                // the row's maximum moved: O so far is scaled down; the product before must be done
-                if (!__all_sync(0xffffffffu, mbar_wait(o_done, (uint32_t)(j - 1) & 1u, abort_flag))) { ok = false; break; }
-                tc_fence_after_sync();
-                const uint32_t o_addr = tmem_base + lane_sel + Plan::O_COL;
+            if (j > 0) {
+                // The product before this one.  It is waited for at every tile, needed or not (by now it
+                // has nearly always finished): a parity wait can only tell the running phase from the one
+                // before it, so the waiter must never fall two phases behind the barrier.
+                if (!__all_sync(0xffffffffu, mbar_wait(my_o_done, (uint32_t)(j - 1) & 1u, abort_flag))) { ok = false; break; }
+                if (__any_sync(0xffffffffu, corr != 1.0f)) {
+                    // a row's reference point moved: its O so far is scaled down
+                    tc_fence_after_sync();
+                    const uint32_t o_addr = head_tmem + Plan::O_COL;
 #pragma unroll 1
-                for (int c = 0; c < D / 32; ++c) {
-                    uint32_t v[32];
-                    tmem_ld32_nowait(o_addr + (uint32_t)c * 32u, v);
-                    tmem_wait_ld();
+                    for (int c = 0; c < D / 32; ++c) {
+                        uint32_t v[32];
+                        tmem_ld32_nowait(o_addr + (uint32_t)c * 32u, v);
+                        tmem_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
-                    tmem_st32(o_addr + (uint32_t)c * 32u, v);
+                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
+                        tmem_st32(o_addr + (uint32_t)c * 32u, v);
+                    }
                 }
             }
             tmem_wait_st();
             tc_fence_before_sync();
-            mbar_arrive(&p_full[b]);
+            mbar_arrive(&my_p_full[b]);
         }
-        // The last product.  A parity wait can only tell the running phase from the one before it,
-        // and the loop above skips its wait on o_done whenever no row's maximum moved, so the
-        // barrier may still be two phases back (product n_kt-2 waiting for its values): wait for
-        // that one first, then for the last.
-        if (ok && n_kt >= 2 && !__all_sync(0xffffffffu, mbar_wait(o_done, (uint32_t)(n_kt - 2) & 1u, abort_flag))) ok = false;
-        if (ok && !__all_sync(0xffffffffu, mbar_wait(o_done, (uint32_t)(n_kt - 1) & 1u, abort_flag))) ok = false;
+        // the last product (the one before it was waited for inside the loop)
+        if (ok && !__all_sync(0xffffffffu, mbar_wait(my_o_done, (uint32_t)(n_kt - 1) & 1u, abort_flag))) ok = false;
         tc_fence_after_sync();
         if (ok) {
             // every lane takes part in the TMEM loads (they are warp-wide); only lanes that own a
             // row of the portion store
             const float inv = 1.0f / l;
-            const uint32_t o_addr = tmem_base + lane_sel + Plan::O_COL;
+            const uint32_t o_addr = head_tmem + Plan::O_COL;
             bf16* orow = out + (size_t)(tok0 + row_first + (valid ? r : 0)) * out_stride + (size_t)h * D;
 #pragma unroll 1
             for (int c = 0; c < D / 32; ++c) {
@@ -350,7 +387,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == PFT_MMA_WARP) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, Plan::TMEM_COLS);
     }
@@ -372,7 +409,8 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
         }
         configured = true;
     }
-    launch_pdl(kern, dim3(n_heads, n_tiles), dim3(PFT_THREADS), Plan::TOTAL, stream, mq, mk, mv, (bf16*)out, out_stride,
+    const int group = n_heads / n_kv;
+    launch_pdl(kern, dim3(n_kv * ((group + 1) / 2), n_tiles), dim3(PFT_THREADS), Plan::TOTAL, stream, mq, mk, mv, (bf16*)out, out_stride,
                block_table, max_blocks, entry_q_start, entry_q_len, entry_pos0, n_entries, first_entry, n_tiles, n_heads,
                n_kv, page_size, window, scale_log2, err);
     return infero_check_launch("attn_prefill_tc");

@@ -133,6 +133,10 @@ def main(argv=None) -> int:
     for i in range(args.warmup):
         runs[i % len(runs)]()
     torch.cuda.synchronize()
+    if tc_gemm.error_flag():
+        print(f"kernel_bench: {name} raised error flag {tc_gemm.error_flag()} during warm-up (a wait inside the "
+              "kernel ran out); not timed", file=sys.stderr)
+        return 1
     # one timed repetition = every input copy once, back to back (the launches queue up, so the
     # host's launch cost is hidden behind kernels that take longer than it)
     times = []
