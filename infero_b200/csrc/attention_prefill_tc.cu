@@ -32,7 +32,7 @@ namespace {
 
 using namespace tc;
 
-constexpr int QROWS = 128, KTILE = 64, SLICE = 16;
+constexpr int QROWS = 128, KTILE = 64;
 constexpr int PFT_K_WARP = 8, PFT_V_WARP = 9, PFT_MMA_WARP = 10, PFT_THREADS = 352;      // warps 0..7: softmax
 constexpr float RESCALE_STEP = 8.0f;
 
@@ -62,6 +62,18 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// max of three in one instruction, and a multiply-add on a pair of 32-bit floats in one instruction
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ void fma2(float& x0, float& x1, float a0, float a1, float b, float c) {
+    asm("{\n .reg .b64 ra, rb, rc, rd;\n mov.b64 ra, {%2, %3};\n mov.b64 rb, {%4, %4};\n mov.b64 rc, {%5, %5};\n"
+        " fma.rn.f32x2 rd, ra, rb, rc;\n mov.b64 {%0, %1}, rd;\n}"
+        : "=f"(x0), "=f"(x1)
+        : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&h);
@@ -73,7 +85,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, int out_stride,
                        const int* __restrict__ block_table, int max_blocks, const int* __restrict__ entry_q_start,
                        const int* __restrict__ entry_q_len, const int* __restrict__ entry_pos0, int n_entries,
-                       int first_entry, int n_tiles, int n_heads, int n_kv, int page_size, int window,
+                       int first_entry, int n_tiles, int n_heads, int n_kv, int page_size, int slice, int window,
                        float scale_log2, int* __restrict__ err_flag) {
     using Plan = PfPlan<D>;
     constexpr int DB = Plan::DB, ST = Plan::STAGES;
@@ -157,11 +169,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
     if (warp == PFT_K_WARP || warp == PFT_V_WARP) {
         // ---- loaders: one warp for the keys (and Q), one for the values ------------------------------
-        // Lane s < 4 fetches slice s (16 rows, one page or part of one) of every tile: the four look-ups
-        // in the block table and the four pairs of TMA instructions of a tile run side by side instead
-        // of one after the other in a single thread.
+        // A tile is fetched in slices of `slice` rows (64, 32 or 16: what lies in one page), one TMA box per
+        // slice and 64-element block.  Lane s fetches slice s of every tile, so the look-ups in the block
+        // table and the TMA instructions of a tile run side by side instead of one after the other in
+        // a single thread.  Boxes of 16 rows (2 KB) are slow: about one per 130 cycles per SM.
         const bool is_k = warp == PFT_K_WARP;
-        if (n_kt > 0 && lane < KTILE / SLICE) {
+        if (n_kt > 0 && lane < KTILE / slice) {
             const CUtensorMap* map = is_k ? &map_k : &map_v;
             uint64_t* full = is_k ? k_full : v_full;
             uint64_t* empty = is_k ? k_empty : v_empty;
@@ -175,7 +188,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                                     (head0 + t) * D + b * 64, tok0 + row_first, q_full);
             }
             auto row_of = [&](int j) {
-                const int key0 = (kt_begin + j) * KTILE + lane * SLICE;
+                const int key0 = (kt_begin + j) * KTILE + lane * slice;
                 const int blk = key0 / page_size;
                 const int page = blk < max_blocks ? table[blk] : -1;
                 // a page that is not held (beyond the request's end) is never visible; any finite rows do
@@ -189,7 +202,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 const int next_row = i + 1 < n_kt ? row_of(i + 1) : 0;      // looked up while waiting
                 if (!mbar_wait(&empty[s], ((uint32_t)(i / ST) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
                 if (lane == 0) mbar_expect_tx(&full[s], Plan::KV_BYTES);
-                uint8_t* dst = ring + s * Plan::KV_BYTES + lane * (SLICE * 128);
+                uint8_t* dst = ring + s * Plan::KV_BYTES + lane * (slice * 128);
 #pragma unroll
                 for (int b = 0; b < DB; ++b) tma_load_2d(dst + b * Plan::KBLOCK_BYTES, map, b * 64, row, &full[s]);
                 issued = i + 1;
@@ -296,7 +309,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
             if (open_tile) {
 #pragma unroll
-                for (int i = 0; i < KTILE; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
+                for (int i = 0; i < KTILE; i += 2)
+                    mx4[(i >> 1) & 3] = fmax3(mx4[(i >> 1) & 3], __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
             } else {
 #pragma unroll
                 for (int i = 0; i < KTILE; ++i) {
@@ -318,8 +332,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             uint32_t pk[KTILE / 2];
 #pragma unroll
             for (int i = 0; i < KTILE; i += 2) {
-                const float p0 = ex2(fmaf(__uint_as_float(sv[i]), scale_log2, -sub));
-                const float p1 = ex2(fmaf(__uint_as_float(sv[i + 1]), scale_log2, -sub));
+                float x0, x1;
+                fma2(x0, x1, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]), scale_log2, -sub);
+                const float p0 = ex2(x0), p1 = ex2(x1);
                 sum4[(i >> 1) & 3] += p0 + p1;
                 pk[i >> 1] = pack2(p0, p1);
             }
@@ -397,7 +412,7 @@ template <int D>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, int out_stride,
            const int* block_table, int max_blocks, const int* entry_q_start, const int* entry_q_len,
            const int* entry_pos0, int n_entries, int first_entry, int n_tiles, int n_heads, int n_kv, int page_size,
-           int window, float scale_log2, int* err, cudaStream_t stream) {
+           int slice, int window, float scale_log2, int* err, cudaStream_t stream) {
     using Plan = PfPlan<D>;
     auto kern = attn_prefill_tc_kernel<D>;
     static bool configured = false;
@@ -412,7 +427,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
     const int group = n_heads / n_kv;
     launch_pdl(kern, dim3(n_kv * ((group + 1) / 2), n_tiles), dim3(PFT_THREADS), Plan::TOTAL, stream, mq, mk, mv, (bf16*)out, out_stride,
                block_table, max_blocks, entry_q_start, entry_q_len, entry_pos0, n_entries, first_entry, n_tiles, n_heads,
-               n_kv, page_size, window, scale_log2, err);
+               n_kv, page_size, slice, window, scale_log2, err);
     return infero_check_launch("attn_prefill_tc");
 }
 
@@ -445,16 +460,18 @@ int infero_attn_prefill_tc(const void* q, int q_stride, int n_tokens, void* out,
     CUtensorMap mq, mk, mv;
     const int rows = num_pages * n_kv * page_size;
     if (infero_tensor_map_bf16(q, n_tokens, n_heads * head_dim, q_stride, QROWS, &mq)) return 1;
-    if (infero_tensor_map_bf16(k_cache, rows, head_dim, head_dim, SLICE, &mk)) return 1;
-    if (infero_tensor_map_bf16(v_cache, rows, head_dim, head_dim, SLICE, &mv)) return 1;
+    // one TMA box = the rows of a tile that lie in one page: 64, 32 or 16 of them
+    const int slice = page_size % 64 == 0 ? 64 : page_size % 32 == 0 ? 32 : 16;
+    if (infero_tensor_map_bf16(k_cache, rows, head_dim, head_dim, slice, &mk)) return 1;
+    if (infero_tensor_map_bf16(v_cache, rows, head_dim, head_dim, slice, &mv)) return 1;
     int* err;
     if (infero_tc_err_flag(&err)) return 1;
     const float sl2 = scale * 1.4426950408889634f;
     if (head_dim == 128)
         return launch<128>(mq, mk, mv, out, out_stride, block_table, max_blocks, entry_q_start, entry_q_len, entry_pos0,
-                           n_entries, first_entry, n_tiles, n_heads, n_kv, page_size, window, sl2, err, stream);
+                           n_entries, first_entry, n_tiles, n_heads, n_kv, page_size, slice, window, sl2, err, stream);
     return launch<64>(mq, mk, mv, out, out_stride, block_table, max_blocks, entry_q_start, entry_q_len, entry_pos0,
-                      n_entries, first_entry, n_tiles, n_heads, n_kv, page_size, window, sl2, err, stream);
+                      n_entries, first_entry, n_tiles, n_heads, n_kv, page_size, slice, window, sl2, err, stream);
 }
 
 }  // extern "C"

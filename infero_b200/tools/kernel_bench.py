@@ -139,6 +139,9 @@ def main(argv=None) -> int:
         return 1
     # one timed repetition = every input copy once, back to back (the launches queue up, so the
     # host's launch cost is hidden behind kernels that take longer than it)
+    from .clocks import ClockSampler
+    clocks = ClockSampler()
+    clocks.on = True
     times = []
     for i in range(args.reps):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -156,6 +159,9 @@ def main(argv=None) -> int:
         line += f", {bytes_ / us / 1e3:.0f} GB/s"
     if flops:
         line += f", {flops / us / 1e6:.1f} TFLOP/s"
+    c = clocks.summary()
+    if c.get("sm_mhz"):
+        line += f"; SM clock {c['sm_mhz']} MHz of {c['sm_max_mhz']}" + (f" ({', '.join(c['reasons'])})" if c["reasons"] else "")
     print(line + (f"  [error flag {err}]" if err else ""))
     return 0
 
