@@ -156,6 +156,18 @@ class CacheManager:
         rc = self.requests.pop(rid)
         self._L.infero_cache_close(self._h, rc.slot)
 
+    def adopt(self, rid: Hashable, slot: int) -> RequestCache:
+        """A slot that native code (the scheduler) has opened for ``rid``."""
+        if rid in self.requests:
+            raise KeyError(f"request {rid!r} is already open")
+        rc = RequestCache(rid, slot, self)
+        self.requests[rid] = rc
+        return rc
+
+    def forget(self, rid: Hashable) -> None:
+        """The slot of ``rid`` was closed by native code."""
+        self.requests.pop(rid, None)
+
     def get(self, rid: Hashable) -> RequestCache:
         return self.requests[rid]
 

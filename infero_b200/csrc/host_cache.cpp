@@ -127,6 +127,11 @@ int infero_cache_fresh(void* h, int slot) { return static_cast<Cache*>(h)->reqs[
 int infero_cache_num_free(void* h, int group) { return (int)static_cast<Cache*>(h)->groups[group].free_stack.size(); }
 int infero_cache_table_len(void* h, int group, int slot) { return (int)static_cast<Cache*>(h)->reqs[slot].tables[group].size(); }
 int infero_cache_first_live(void* h, int group, int slot) { return static_cast<Cache*>(h)->reqs[slot].first_live[group]; }
+// n_groups, num_pages, page_size, max_requests
+void infero_cache_geometry(void* h, int* out) {
+    Cache* c = static_cast<Cache*>(h);
+    out[0] = (int)c->groups.size(); out[1] = c->num_pages; out[2] = c->page_size; out[3] = c->max_requests;
+}
 int infero_cache_width(void* h) { return static_cast<Cache*>(h)->width; }
 const int* infero_cache_mirror(void* h, int group) { return static_cast<Cache*>(h)->mirror[group].data(); }
 long long infero_cache_counter(void* h, int which) {

@@ -28,14 +28,19 @@ penalty (that needs the token on the host), nobody waits for admission, and page
 token each are free.  A request that ends at step k on an end-of-sequence token has then run
 one token too far; that token is dropped.  (The reference's scheduler reads every step's tokens
 before it plans the next, crates/server/src/scheduler.rs:1268-1429.)
+
+The decisions themselves (admission, the plan of a step, the victim of a preemption, the end of a
+request, whether to run ahead) are made in C++ (``csrc/host_sched.cpp``, in the engine's shared
+library, no CUDA in it) on counters alone; this module keeps what belongs to Python (token lists,
+samplers, events) and is that code's face.
 """
 from __future__ import annotations
 
-from collections import deque
+import ctypes
 from dataclasses import dataclass, field
-from typing import Callable, Deque, Dict, Hashable, List, Optional, Sequence, Tuple
+from typing import Callable, Dict, Hashable, List, Optional, Tuple
 
-from ..cache import CacheManager, OutOfPages, RequestCache
+from ..cache import CacheManager, RequestCache
 from ..sampling import RowSampler, SamplingParams
 from .step import FROM_DEVICE, StepEntry
 
@@ -52,14 +57,15 @@ class Request:
 
 @dataclass
 class Running:
+    """A request from the moment it is queued (``rc`` is None while it waits)."""
     req: Request
-    rc: RequestCache
+    rc: Optional[RequestCache]
     sampler: RowSampler
     tokens: List[int]                      # everything that must be in the cache: prompt (+ generated on recompute)
+    sid: int = -1                          # the native scheduler's name for it
     fed: int = 0                           # how many of ``tokens`` are in the cache
     generated: List[int] = field(default_factory=list)
     pending: Optional[int] = None          # sampled, not yet fed
-    admitted_at: int = 0
     preemptions: int = 0
     finished: bool = False
 
@@ -97,6 +103,19 @@ class _InFlight:
     pending: object                        # .result() -> one token per sampling item
 
 
+def _lib():
+    from ..kernels import lib
+    L = lib()
+    if not getattr(L, "_sched_api_ready", False):
+        L.infero_sched_new.restype = ctypes.c_void_p
+        L.infero_sched_stat.restype = ctypes.c_longlong
+        L._sched_api_ready = True
+    return L
+
+
+_NATIVE_STATS = ("preemptions", "decode_tokens", "prefill_tokens", "rejected", "finished", "tokens_dropped")
+
+
 class Scheduler:
     """``execute(items) -> tokens`` runs a planned batch and returns one sampled token per
     item with ``samples`` set, in order.  The engine supplies it; tests supply a fake."""
@@ -113,151 +132,130 @@ class Scheduler:
         self.max_batch_tokens = max_batch_tokens
         self.ctx = ctx
         self.max_prefill_chunk = max_prefill_chunk
-        self.waiting: Deque[Running | Request] = deque()
-        self.running: List[Running] = []
-        self.clock = 0
-        self.stats = {"steps": 0, "preemptions": 0, "decode_tokens": 0, "prefill_tokens": 0,
-                      "rejected": 0, "finished": 0, "steps_ahead": 0, "tokens_dropped": 0}
+        self._L = _lib()
+        self._h = ctypes.c_void_p(self._L.infero_sched_new(manager._h, int(max_seqs), int(max_batch_tokens), int(ctx),
+                                                           int(max_prefill_chunk or 0)))
+        if not self._h:
+            raise ValueError("bad scheduler limits")
+        self._runs: Dict[int, Running] = {}          # by native id: waiting, running, or ended with a step still in flight
+        self._ended: List[int] = []                  # ids to hand back once no step in flight names them
+        self._buf = (ctypes.c_int * (5 * max(max_seqs, 1) * 2 + 16))()
+        self._steps = 0
+        self._steps_ahead = 0
         self._events: List[Event] = []
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._L.infero_sched_delete(h)
+
+    # ---- views ------------------------------------------------------------------------------
+    def _ids(self, fn) -> List[int]:
+        cap = len(self._buf)
+        n = fn(self._h, self._buf, cap)
+        while n >= cap:                              # a long queue: ask again with room for all of it
+            self._buf = (ctypes.c_int * (2 * cap))()
+            cap = len(self._buf)
+            n = fn(self._h, self._buf, cap)
+        return [int(self._buf[i]) for i in range(n)]
+
+    @property
+    def running(self) -> List[Running]:
+        return [self._runs[i] for i in self._ids(self._L.infero_sched_running)]
+
+    @property
+    def waiting(self) -> List[Running]:
+        return [self._runs[i] for i in self._ids(self._L.infero_sched_waiting)]
+
+    @property
+    def stats(self) -> Dict[str, int]:
+        out = {name: int(self._L.infero_sched_stat(self._h, i)) for i, name in enumerate(_NATIVE_STATS)}
+        out["steps"] = self._steps
+        out["steps_ahead"] = self._steps_ahead
+        return out
 
     # ---- queue ------------------------------------------------------------------------------
     def enqueue(self, req: Request) -> None:
-        if not req.prompt:
+        needs_host = req.params.repetition_penalty != 1.0        # the penalty needs every token on the host
+        sid = self._L.infero_sched_enqueue(self._h, len(req.prompt), int(req.max_new_tokens), int(needs_host))
+        if sid == -1:
             self._events.append(Event(req.rid, None, True, "error", "empty prompt"))
-            self.stats["rejected"] += 1
             return
-        if len(req.prompt) + 1 > self.ctx:
+        if sid == -2:
             self._events.append(Event(req.rid, None, True, "error",
                                       f"prompt of {len(req.prompt)} tokens does not fit the context of {self.ctx}"))
-            self.stats["rejected"] += 1
             return
-        self.waiting.append(req)
+        self._runs[sid] = Running(req=req, rc=None, sampler=RowSampler(req.params), tokens=list(req.prompt), sid=sid)
 
     def is_idle(self) -> bool:
-        return not self.waiting and not self.running and not self._events and self._inflight is None
+        return (self._inflight is None and not self._events and self._L.infero_sched_num_waiting(self._h) == 0
+                and self._L.infero_sched_num_running(self._h) == 0)
+
+    def _release(self, sid: int) -> None:
+        self._runs.pop(sid, None)
+        self._L.infero_sched_release(self._h, sid)
 
     # ---- admission ----------------------------------------------------------------------------
-    def _pages_for(self, n_tokens: int) -> int:
-        return -(-n_tokens // self.manager.page_size)
-
-    def _outstanding_pages(self) -> int:
-        """Pages the running requests still have to take to hold their prompt plus one token."""
-        return sum(max(0, self._pages_for(len(r.tokens) + 1) - max((r.rc.table_len(g) for g in range(len(self.manager.groups))), default=0))
-                   for r in self.running)
-
     def _admit(self) -> None:
-        committed = 0
-        while self.waiting and len(self.running) < self.max_seqs:
-            head = self.waiting[0]
-            tokens = head.tokens if isinstance(head, Running) else head.prompt
-            need = self._pages_for(len(tokens) + 1)
-            if need > self.manager.num_pages:
+        while True:
+            cap = len(self._buf) // 3
+            n = self._L.infero_sched_admit(self._h, self._buf, cap)
+            triples = [(int(self._buf[3 * i]), int(self._buf[3 * i + 1]), int(self._buf[3 * i + 2])) for i in range(n)]
+            for sid, code, value in triples:
+                run = self._runs[sid]
+                if code == 0:
+                    run.rc = self.manager.adopt(run.req.rid, value)
+                    continue
                 # can never fit, even alone
-                self.waiting.popleft()
-                resumed = isinstance(head, Running)
-                rid = head.req.rid if resumed else head.rid
-                self._events.append(Event(rid, None, True, "length" if resumed else "error",
-                                          f"{len(tokens)} tokens need {need} pages, the pool has {self.manager.num_pages}"))
-                self.stats["rejected"] += 1
-                continue
-            if need > self.manager.min_free_pages() - self._outstanding_pages():
-                break                                   # stays at the front; tried again next step
-            self.waiting.popleft()
-            if isinstance(head, Running):
-                run = head
-                run.rc = self.manager.open(run.req.rid)
-            else:
-                run = Running(req=head, rc=self.manager.open(head.rid), sampler=RowSampler(head.params),
-                              tokens=list(head.prompt))
-            run.admitted_at = self.clock
-            self.clock += 1
-            self.running.append(run)
+                run.finished = True
+                self._events.append(Event(run.req.rid, None, True, "length" if code == 2 else "error",
+                                          f"{len(run.tokens)} tokens need {value} pages, the pool has {self.manager.num_pages}"))
+                self._release(sid)
+            if n < cap:
+                break
 
     # ---- planning -----------------------------------------------------------------------------
     def _plan(self) -> List[PlanItem]:
-        budget = self.max_batch_tokens
+        n = self._L.infero_sched_plan(self._h, self._buf, len(self._buf) // 5)
         items: List[PlanItem] = []
-        n_groups = len(self.manager.groups)
-        used = [0] * n_groups                      # pages this plan takes, per group
-        P = self.manager.page_size
-
-        def free(g: int) -> int:
-            return self.manager.free_pages(g) - used[g]
-
-        # decodes first
-        for run in self.running:
-            if run.pending is None or run.fed < len(run.tokens) or budget <= 0:
-                continue
-            need = self.manager.pages_needed(run.rc, 1)
-            if any(need[g] > free(g) for g in range(n_groups)):
-                continue
-            for g in range(n_groups):
-                used[g] += need[g]
-            items.append(PlanItem(run, [run.pending], samples=True, is_decode=True))
-            budget -= 1
-        # then prompt portions, in running order
-        for run in self.running:
-            if budget <= 0:
-                break
-            remaining = len(run.tokens) - run.fed
-            if remaining <= 0:
-                continue
-            slack = (-(run.rc.length + run.rc.reserved)) % P       # free rows in its last page
-            room = slack + max(0, min((free(g) for g in range(n_groups)), default=0)) * P
-            n = min(remaining, budget, room)
-            if self.max_prefill_chunk:
-                n = min(n, self.max_prefill_chunk)
-            if n <= 0:
-                continue
-            need = self.manager.pages_needed(run.rc, n)
-            for g in range(n_groups):
-                used[g] += need[g]
-            items.append(PlanItem(run, run.tokens[run.fed:run.fed + n], samples=(n == remaining), is_decode=False))
-            budget -= n
+        for i in range(n):
+            sid, first, count, samples, is_decode = (int(self._buf[5 * i + k]) for k in range(5))
+            run = self._runs[sid]
+            if is_decode:
+                items.append(PlanItem(run, [run.pending], samples=True, is_decode=True))
+            else:
+                items.append(PlanItem(run, run.tokens[first:first + count], samples=bool(samples), is_decode=False))
         return items
 
     def _preempt_youngest(self) -> bool:
         """Free the youngest running request and put it back at the front of the queue; what it
         generated so far becomes part of the prompt it recomputes."""
-        if len(self.running) <= 1:
+        sid = self._L.infero_sched_preempt_youngest(self._h)
+        if sid < 0:
             return False
-        victim = max(self.running, key=lambda r: r.admitted_at)
-        self.running.remove(victim)
-        self.manager.close(victim.req.rid)
+        victim = self._runs[sid]
+        self.manager.forget(victim.req.rid)
+        victim.rc = None
         victim.tokens = list(victim.req.prompt) + list(victim.generated)
         victim.pending = None          # it is the last of ``generated`` and is fed with the recompute
         victim.fed = 0
         victim.preemptions += 1
-        self.stats["preemptions"] += 1
-        self.waiting.appendleft(victim)
         return True
 
     # ---- one step -----------------------------------------------------------------------------
     def _start(self, items: List[PlanItem]) -> _InFlight:
         pending = self.launch(items) if self.launch is not None else _Done(self.execute(items))
-        self.stats["steps"] += 1
+        self._steps += 1
         return _InFlight(items, pending)
 
     def _can_run_ahead(self, cur: _InFlight) -> bool:
         """May the step after ``cur`` be launched before ``cur``'s tokens are known?"""
-        if not self.run_ahead or self.waiting or len(cur.items) != len(self.running):
+        if not self.run_ahead:
             return False
-        for it in cur.items:
-            run, req = it.run, it.run.req
-            if not it.samples or run.finished:
-                return False                                   # a prompt is still being fed
-            if req.params.repetition_penalty != 1.0:
-                return False                                   # the penalty needs the token on the host
-            if len(run.generated) + 2 > req.max_new_tokens or len(req.prompt) + len(run.generated) + 2 > self.ctx:
-                return False                                   # it ends at ``cur`` or at the step after
-        n_groups = len(self.manager.groups)
-        used = [0] * n_groups
-        for it in cur.items:
-            need = self.manager.pages_needed(it.run.rc, 1)
-            for g in range(n_groups):
-                used[g] += need[g]
-        return all(used[g] <= self.manager.free_pages(g) for g in range(n_groups)) \
-            and len(cur.items) <= self.max_batch_tokens
+        n = len(cur.items)
+        ids = (ctypes.c_int * max(1, n))(*[it.run.sid for it in cur.items])
+        samples = (ctypes.c_int * max(1, n))(*[int(it.samples) for it in cur.items])
+        return bool(self._L.infero_sched_can_run_ahead(self._h, n, ids, samples))
 
     def _complete(self, cur: _InFlight) -> List[Event]:
         """Wait for the step's tokens and advance its requests."""
@@ -265,27 +263,54 @@ class Scheduler:
         events: List[Event] = []
         k = 0
         for it in cur.items:
-            run = it.run
+            run, req = it.run, it.run.req
             tok = None
             if it.samples:
                 tok = int(sampled[k])
                 k += 1
-            if run.finished:                       # ended a step earlier: this one ran a token too far
-                self.stats["tokens_dropped"] += 1
+            is_eos = tok is not None and not req.ignore_eos and tok in req.eos_token_ids
+            code = self._L.infero_sched_complete(self._h, run.sid, len(it.tokens), int(it.is_decode), int(it.samples),
+                                                 int(is_eos))
+            if code == 5:                          # ended a step earlier: this one ran a token too far
                 continue
             if it.is_decode:
                 run.pending = None
                 run.tokens.append(it.tokens[0])
                 run.fed += 1
-                self.stats["decode_tokens"] += 1
             else:
                 run.fed += len(it.tokens)
-                self.stats["prefill_tokens"] += len(it.tokens)
-            if it.samples:
-                ev = self._advance(run, tok)
-                if ev is not None:
-                    events.append(ev)
+            if code == 0:
+                continue
+            if code == 1:
+                run.generated.append(tok)
+                run.pending = tok
+                events.append(Event(req.rid, tok))
+                continue
+            # the request ended: on an end-of-sequence token (not appended), or with this token as its last
+            self._ended_natively(run)
+            if code == 2:
+                events.append(Event(req.rid, None, True, "stop"))
+            else:
+                run.generated.append(tok)
+                events.append(Event(req.rid, tok, True, "length", "context full" if code == 4 else None))
         return events
+
+    def _ended_natively(self, run: Running) -> None:
+        run.finished = True
+        run.rc = None
+        self.manager.forget(run.req.rid)
+        self._ended.append(run.sid)
+
+    def _hand_back_ended(self) -> None:
+        """Ids of ended requests go back once no step in flight names them."""
+        named = {it.run.sid for it in self._inflight.items} if self._inflight is not None else set()
+        keep = []
+        for sid in self._ended:
+            if sid in named:
+                keep.append(sid)
+            else:
+                self._release(sid)
+        self._ended = keep
 
     def step(self) -> List[Event]:
         events, self._events = self._events, []
@@ -293,7 +318,7 @@ class Scheduler:
             self._admit()
             events += self._events
             self._events = []
-            if not self.running:
+            if self._L.infero_sched_num_running(self._h) == 0:
                 return events
             items = self._plan()
             while not items:
@@ -301,6 +326,7 @@ class Scheduler:
                     # a single request that cannot move: the cache is full for it
                     run = self.running[0]
                     events.append(self._finish(run, "length", "cache exhausted"))
+                    self._hand_back_ended()
                     return events
                 items = self._plan()
             self._inflight = self._start(items)
@@ -309,13 +335,14 @@ class Scheduler:
         if self._can_run_ahead(cur):
             # every request decodes on: feed each the token ``cur`` is picking, from the device
             ahead = self._start([PlanItem(it.run, [FROM_DEVICE], samples=True, is_decode=True) for it in cur.items])
-            self.stats["steps_ahead"] += 1
+            self._steps_ahead += 1
         events += self._complete(cur)
         if ahead is not None:
             for it in ahead.items:                 # now the host knows what was fed
                 if not it.run.finished:
                     it.tokens = [it.run.pending]
         self._inflight = ahead
+        self._hand_back_ended()
         return events
 
     def drain(self) -> List[Event]:
@@ -324,31 +351,14 @@ class Scheduler:
         while self._inflight is not None:
             cur, self._inflight = self._inflight, None
             events += self._complete(cur)
+        self._hand_back_ended()
         return events
 
-    def _advance(self, run: Running, tok: int) -> Optional[Event]:
-        req = run.req
-        if not req.ignore_eos and tok in req.eos_token_ids:
-            return self._finish(run, "stop")                 # the end token is not appended
-        run.generated.append(tok)
-        if len(run.generated) >= req.max_new_tokens:
-            ev = self._finish(run, "length")
-            ev.token = tok
-            return ev
-        if len(req.prompt) + len(run.generated) >= self.ctx:
-            ev = self._finish(run, "length", "context full")
-            ev.token = tok
-            return ev
-        run.pending = tok
-        return Event(req.rid, tok)
-
     def _finish(self, run: Running, reason: str, message: Optional[str] = None) -> Event:
-        run.finished = True
-        if run in self.running:
-            self.running.remove(run)
-        if run.req.rid in self.manager.requests:
-            self.manager.close(run.req.rid)
-        self.stats["finished"] += 1
+        """End a request from outside the normal course (cache exhausted, a failed step)."""
+        if not run.finished:
+            self._L.infero_sched_finish(self._h, run.sid)
+            self._ended_natively(run)
         return Event(run.req.rid, None, True, reason, message)
 
     def abort_all(self, message: str) -> List[Event]:
@@ -358,10 +368,15 @@ class Scheduler:
             self.drain()
         except Exception:                           # noqa: BLE001  (the step that failed)
             self._inflight = None
-        for run in list(self.running):
+        for run in self.running:
             events.append(self._finish(run, "error", message))
-        while self.waiting:
-            w = self.waiting.popleft()
-            rid = w.req.rid if isinstance(w, Running) else w.rid
-            events.append(Event(rid, None, True, "error", message))
+        while True:
+            sid = self._L.infero_sched_pop_waiting(self._h)
+            if sid < 0:
+                break
+            run = self._runs[sid]
+            run.finished = True
+            events.append(Event(run.req.rid, None, True, "error", message))
+            self._release(sid)
+        self._hand_back_ended()
         return events

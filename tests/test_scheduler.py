@@ -317,3 +317,21 @@ def test_no_running_ahead_with_a_repetition_penalty_or_a_waiting_request():
     out, _ = run_all(s)
     assert out["a"] == expected_output(range(1, 9), 6) and out["b"] == expected_output(range(1, 5), 3)
     assert "launch launch" not in " ".join(ex.log[:10])
+
+
+def test_native_records_are_handed_back():
+    """The decisions are made by the C++ core on integer records; when everything has drained
+    neither side holds a record, and ids are used again."""
+    s, ex, m = make(num_pages=12, budget=48, max_seqs=3)
+    rng = random.Random(3)
+    for round_ in range(3):
+        for i in range(7):
+            s.enqueue(req(f"r{round_}_{i}", [rng.randrange(1, 90) for _ in range(rng.randrange(1, 70))], n=rng.randrange(1, 9)))
+        out, reasons = run_all(s)
+        assert len(reasons) == 7 * (round_ + 1) or all(r[0] in ("length", "stop") for r in reasons.values())
+        assert not s._runs and not s._ended and not m.requests
+        assert s.running == [] and s.waiting == []
+        m.check()
+    assert s.stats["finished"] == 21
+    sid = s._L.infero_sched_enqueue(s._h, 5, 1, 0)
+    assert 0 <= sid < 8, "ids of finished requests are used again"
