@@ -32,7 +32,7 @@ struct TdPlan {
     static constexpr int STAGE_BYTES = 2 * HALF_BYTES;
     static constexpr int WARP_BYTES = STAGES * STAGE_BYTES;
     static constexpr int TILES_BYTES = TD_WARPS * WARP_BYTES;
-    static constexpr int RED_BYTES = TD_WARPS * 16 * (D + 2) * 4;
+    static constexpr int RED_BYTES = TD_WARPS * 16 * (D + 3) * 4;
     static constexpr int DATA_BYTES = TILES_BYTES > RED_BYTES ? TILES_BYTES : RED_BYTES;
     static constexpr int BAR_OFFSET = DATA_BYTES;
     static constexpr int TOTAL = DATA_BYTES + TD_WARPS * STAGES * 8 + 16 + 1024;
@@ -58,46 +58,62 @@ __device__ __forceinline__ void merge_if_last(int* counter, float* wbuf, const f
     __syncthreads();
     if (!s_last) return;
     __threadfence();
+    // Everything below waits on reads from L2, so each phase issues all of its loads at once.
+    // (m, l) of every row and split in one go
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    float* linv = wbuf + 16 * n_splits;
+    const int n_ml = valid * n_splits;
+    float* sm_m = wbuf;                                // [valid][n_splits]
+    float* sm_l = wbuf + 16 * n_splits;
+    float* sm_w = wbuf + 32 * n_splits;
+    float* linv = wbuf + 48 * n_splits;                // [16]
+    for (int i = threadIdx.x; i < n_ml; i += TD_THREADS) {
+        const float2 v = __ldcg(reinterpret_cast<const float2*>(pml_base) + i);     // rows are n_splits pairs apart
+        sm_m[i] = v.x;
+        sm_l[i] = v.y;
+    }
+    __syncthreads();
     for (int r = warp; r < valid; r += TD_WARPS) {
-        const float* ml = pml_base + (size_t)r * n_splits * 2;
         float M = -CUDART_INF_F;
-        for (int s = lane; s < n_splits; s += 32) M = fmaxf(M, __ldcg(ml + s * 2));
+        for (int s = lane; s < n_splits; s += 32) M = fmaxf(M, sm_m[r * n_splits + s]);
         M = warp_max(M);
         float L = 0.f;
         for (int s = lane; s < n_splits; s += 32) {
-            const float ms = __ldcg(ml + s * 2);
+            const float ms = sm_m[r * n_splits + s];
             const float w = ms == -CUDART_INF_F ? 0.f : exp2f(ms - M);
-            wbuf[r * n_splits + s] = w;
-            L += __ldcg(ml + s * 2 + 1) * w;
+            sm_w[r * n_splits + s] = w;
+            L += sm_l[r * n_splits + s] * w;
         }
         L = warp_sum(L);
         if (lane == 0) linv[r] = 1.0f / L;
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < valid * (D / 2); idx += TD_THREADS) {
-        const int r = idx / (D / 2), d = (idx - r * (D / 2)) * 2;
+    // four columns per thread, sixteen splits' loads in flight at a time; the sum stays in order
+    for (int idx = threadIdx.x; idx < valid * (D / 4); idx += TD_THREADS) {
+        const int r = idx / (D / 4), d = (idx - r * (D / 4)) * 4;
         const float* pob = po_base + (size_t)r * n_splits * D + d;
-        float a0 = 0.f, a1 = 0.f;
-        // sixteen splits' loads in flight at a time (they come from L2; the sum stays in order)
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
         for (int s0 = 0; s0 < n_splits; s0 += 16) {
-            float2 v[16];
+            float4 v[16];
 #pragma unroll
             for (int k = 0; k < 16; ++k)
-                v[k] = s0 + k < n_splits ? __ldcg(reinterpret_cast<const float2*>(pob + (size_t)(s0 + k) * D))
-                                         : make_float2(0.f, 0.f);
+                v[k] = s0 + k < n_splits ? __ldcg(reinterpret_cast<const float4*>(pob + (size_t)(s0 + k) * D))
+                                         : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
             for (int k = 0; k < 16; ++k) {
-                const float ws = s0 + k < n_splits ? wbuf[r * n_splits + s0 + k] : 0.f;
+                const float ws = s0 + k < n_splits ? sm_w[r * n_splits + s0 + k] : 0.f;
                 if (ws != 0.f) {
                     a0 = fmaf(v[k].x, ws, a0);
                     a1 = fmaf(v[k].y, ws, a1);
+                    a2 = fmaf(v[k].z, ws, a2);
+                    a3 = fmaf(v[k].w, ws, a3);
                 }
             }
         }
         const float inv = linv[r];
-        *reinterpret_cast<uint32_t*>(out_rows + (size_t)r * D + d) = pack_bf16(a0 * inv, a1 * inv);
+        uint2 w2;
+        w2.x = pack_bf16(a0 * inv, a1 * inv);
+        w2.y = pack_bf16(a2 * inv, a3 * inv);
+        *reinterpret_cast<uint2*>(out_rows + (size_t)r * D + d) = w2;
     }
 }
 
@@ -250,24 +266,35 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         red_ml[((size_t)warp * 16 + g + 8) * 2 + 1] = l1;
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < valid * D; idx += TD_THREADS) {
-        const int r = idx / D, d = idx - r * D;
+    // per row: the common maximum, each warp's factor 2^(m_w - max) and the row's (m, l), once
+    float* red_f = red_ml + TD_WARPS * 16 * 2;                        // [4 warps][16 rows]
+    if (threadIdx.x < valid) {
+        const int r = threadIdx.x;
         float mm = -CUDART_INF_F;
 #pragma unroll
         for (int w = 0; w < TD_WARPS; ++w) mm = fmaxf(mm, red_ml[((size_t)w * 16 + r) * 2]);
-        float acc = 0.f, ll = 0.f;
+        float ll = 0.f;
 #pragma unroll
         for (int w = 0; w < TD_WARPS; ++w) {
             const float mw = red_ml[((size_t)w * 16 + r) * 2];
             const float f = mw == -CUDART_INF_F ? 0.f : exp2f(mw - mm);
-            acc += red_o[((size_t)w * 16 + r) * D + d] * f;
+            red_f[w * 16 + r] = f;
             ll += red_ml[((size_t)w * 16 + r) * 2 + 1] * f;
         }
-        po[(size_t)r * n_splits * D + d] = acc;
-        if (d == 0) {
-            pml[(size_t)r * n_splits * 2] = mm;
-            pml[(size_t)r * n_splits * 2 + 1] = ll;
+        pml[(size_t)r * n_splits * 2] = mm;
+        pml[(size_t)r * n_splits * 2 + 1] = ll;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < valid * (D / 4); idx += TD_THREADS) {
+        const int r = idx / (D / 4), d = (idx - r * (D / 4)) * 4;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int w = 0; w < TD_WARPS; ++w) {
+            const float f = red_f[w * 16 + r];
+            const float4 v = *reinterpret_cast<const float4*>(red_o + ((size_t)w * 16 + r) * D + d);
+            acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
         }
+        *reinterpret_cast<float4*>(po + (size_t)r * n_splits * D + d) = acc;
     }
     if (counters)                                      // (its first barrier also ends the reads of red_o above)
         merge_if_last<D>(counters + (size_t)ti * gridDim.y + blockIdx.y, reinterpret_cast<float*>(smem),
