@@ -62,12 +62,16 @@ __device__ __forceinline__ void store4(bf16* p, const float* v) {
 // delta may come as several 32-bit partial sums (the split-K products of the few-token
 // matrix kernel), split_stride elements apart.  VEC = 4 needs d % 4 == 0.
 template <typename TD, typename TO, int VEC>
-__global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int splits,
+__global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int splits,
                                    long long split_stride, const void* __restrict__ dbias, int dbias_dtype,
                                    const void* __restrict__ w, int wdtype, float eps,
                                    TO* __restrict__ out, const int* __restrict__ rows, int d) {
     __shared__ float red[32];
     pdl_launch_dependents();
+    // the norm's weights do not come from the kernel in front: the thread's first vector of them
+    // is fetched before the wait
+    float w_first[4] = {0.f, 0.f, 0.f, 0.f};
+    if (VEC == 4 && (int)threadIdx.x * 4 < d) load4_any(w, wdtype, threadIdx.x * 4, w_first);
     pdl_wait();
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
@@ -79,16 +83,20 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
     // first loop: loads only (global stores wait for the second loop, so that the loads of all
     // of a thread's vectors can be in flight together)
     if (VEC == 4) {
-#pragma unroll 4
+#pragma unroll 2
         for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
             float v[4];
             load4(xr + i, v);
             if (dr) {
-#pragma unroll 4
-                for (int s = 0; s < splits; ++s) {
-                    float t[4];
-                    load4(dr + (size_t)s * split_stride + i, t);
-                    v[0] += t[0]; v[1] += t[1]; v[2] += t[2]; v[3] += t[3];
+                // eight partial sums' loads in flight at a time; added in ascending order
+                for (int s0 = 0; s0 < splits; s0 += 8) {
+                    float t[8][4];
+#pragma unroll
+                    for (int k = 0; k < 8; ++k)
+                        if (s0 + k < splits) load4(dr + (size_t)(s0 + k) * split_stride + i, t[k]);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k)
+                        if (s0 + k < splits) { v[0] += t[k][0]; v[1] += t[k][1]; v[2] += t[k][2]; v[3] += t[k][3]; }
                 }
                 if (dbias) {
                     float t[4];
@@ -119,7 +127,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
             float v[4], ww[4];
             load4(vbuf + i, v);
             if (write_x) store4(xr + i, v);
-            load4_any(w, wdtype, i, ww);
+            if (i == (int)threadIdx.x * 4) { ww[0] = w_first[0]; ww[1] = w_first[1]; ww[2] = w_first[2]; ww[3] = w_first[3]; }
+            else load4_any(w, wdtype, i, ww);
             v[0] = v[0] * sc * ww[0]; v[1] = v[1] * sc * ww[1]; v[2] = v[2] * sc * ww[2]; v[3] = v[3] * sc * ww[3];
             store4(orow + i, v);
         }
