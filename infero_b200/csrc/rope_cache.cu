@@ -211,10 +211,15 @@ rope_cache_partials_vec_kernel(const float* __restrict__ partial, int splits, lo
     const size_t in_page = (size_t)(pos % page_size) * head_dim;
     auto sum4 = [&](size_t col, float* v) {
         v[0] = v[1] = v[2] = v[3] = 0.f;
-#pragma unroll 4
-        for (int s = 0; s < splits; ++s) {
-            const float4 f = *reinterpret_cast<const float4*>(src_row + (size_t)s * split_stride + col);
-            v[0] += f.x; v[1] += f.y; v[2] += f.z; v[3] += f.w;
+        // eight splits' loads in flight at a time; added in ascending order
+        for (int s0 = 0; s0 < splits; s0 += 8) {
+            float4 f[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                if (s0 + k < splits) f[k] = *reinterpret_cast<const float4*>(src_row + (size_t)(s0 + k) * split_stride + col);
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                if (s0 + k < splits) { v[0] += f[k].x; v[1] += f[k].y; v[2] += f[k].z; v[3] += f[k].w; }
         }
         if (bias) {
 #pragma unroll
