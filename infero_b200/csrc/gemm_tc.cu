@@ -44,7 +44,10 @@ constexpr int A_STAGE_BYTES = TILE_A * TILE_K * 2;
 
 // The SWIGLU epilogues take a weight matrix whose rows alternate gate_j, up_j and write
 // silu(gate_j) * up_j to column j of a bf16 result half as wide.
-enum : int { EPI_ROW = 0, EPI_COL = 1, EPI_PARTIAL = 2, EPI_ROW_SWIGLU = 3, EPI_COL_SWIGLU = 4 };
+// EPI_CLUSTER: the CTAs that share a tile and differ in their split of K form a cluster; each leaves its
+// 32-bit tile in its own shared memory and the cluster adds the tiles up through distributed shared
+// memory, in ascending order of the splits, each CTA a share of the token columns: out[token, feature].
+enum : int { EPI_ROW = 0, EPI_COL = 1, EPI_PARTIAL = 2, EPI_ROW_SWIGLU = 3, EPI_COL_SWIGLU = 4, EPI_CLUSTER = 5 };
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
 
@@ -232,6 +235,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 float v[16];
                 tmem_ld16(lane_addr + (uint32_t)c0, v);
                 const int rb = b0 + c0;
+                if (EPI == EPI_CLUSTER) {
+                    // the ring is free (every load was consumed and every MMA has finished): the tile goes
+                    // there, token-major, so that the threads of a warp touch consecutive words
+                    float* stage = reinterpret_cast<float*>(smem);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) stage[(c0 + i) * TILE_A + q * 32 + lane] = v[i];
+                    continue;
+                }
                 if (EPI == EPI_COL_SWIGLU) {
                     // lanes 2j, 2j+1 hold gate_j and up_j of the same tokens: out[rb + i, ra / 2]
 #pragma unroll
@@ -297,6 +308,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             *abort_flag = 1;
             atomicExch(err_flag, 3);
         }
+    }
+    if (EPI == EPI_CLUSTER) {
+        // every thread of every CTA of the cluster comes here, also after a wait that ran out
+        __syncwarp();
+        cluster_sync_all();                                  // all tiles are in shared memory
+        if (warp >= 2 && !*abort_flag) {
+            const int S = (int)gridDim.z;                    // = the cluster's size: one CTA per split
+            const int rank = (int)cluster_ctarank();
+            const int n_cols = min(BN, RB - b0);
+            const int per_rank = (n_cols + S - 1) / S;
+            const int c_lo = rank * per_rank, c_hi = min(n_cols, c_lo + per_rank);
+            const int row = (warp & 3) * 32 + lane, ra = a0 + row;
+            uint32_t remote[8];
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp) remote[sp] = cluster_addr_of(smem, (uint32_t)(sp < S ? sp : 0));
+            for (int c = c_lo; c < c_hi; ++c) {
+                const uint32_t off = (uint32_t)(c * TILE_A + row) * 4u;
+                float v[8];
+#pragma unroll
+                for (int sp = 0; sp < 8; ++sp)
+                    if (sp < S) v[sp] = ld_cluster_f32(remote[sp] + off);
+                float acc = v[0];
+#pragma unroll
+                for (int sp = 1; sp < 8; ++sp)
+                    if (sp < S) acc += v[sp];
+                if (ra < RA) out[(size_t)(b0 + c) * (size_t)RA + ra] = from_f32<OutT>(acc);
+            }
+        }
+        cluster_sync_all();                                  // nobody leaves while its tile is still being read
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -774,6 +814,55 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, const void* 
     return infero_check_launch("gemm_tc");
 }
 
+// The few-token kernel with the splits of a tile as one cluster (at most 8 CTAs).
+template <int BN, int STAGES>
+int launch_cluster(const CUtensorMap& ma, const CUtensorMap& mb, float* out, int RA, int RB, int K,
+                   int ktiles_per_split, int splits, int* err, cudaStream_t stream) {
+    using Plan = SmemPlan<BN, STAGES>;
+    auto kern = gemm_tc_kernel<BN, STAGES, EPI_CLUSTER, float>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::TOTAL);
+        if (e != cudaSuccess) {
+            infero_set_error("gemm_tc: cannot get %d bytes of shared memory: %s", Plan::TOTAL, cudaGetErrorString(e));
+            return 1;
+        }
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((RA + TILE_A - 1) / TILE_A, (RB + BN - 1) / BN, splits);
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = Plan::TOTAL;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = splits;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = infero_pdl_enabled() ? 2 : 1;
+    cudaLaunchKernelEx(&cfg, kern, ma, mb, out, (const void*)nullptr, 0, RA, RB, K, ktiles_per_split, (long long)0, 1, err);
+    return infero_check_launch("gemm_tc_cluster");
+}
+
+// Splits of a tile add up inside a cluster when INFERO_GEMM_CLUSTER=1 (or infero_gemm_set_cluster(1)).
+// Off by default: measured on whole decode steps it gains nothing at batch 1 and 64 and loses 1.6 % at
+// batch 8 (a cluster starts only when all of its CTAs find room at once, which costs more of the early
+// weight prefetch than the partial sums' trip through L2 did).
+constexpr int MAX_CLUSTER = 8;
+std::atomic<int> g_cluster{-1};
+bool cluster_sum() {
+    int v = g_cluster.load(std::memory_order_relaxed);
+    if (v < 0) {
+        const char* e = getenv("INFERO_GEMM_CLUSTER");
+        v = (e && e[0] == '1') ? 1 : 0;
+        g_cluster.store(v, std::memory_order_relaxed);
+    }
+    return v != 0;
+}
+
 // Tile width for the persistent kernel: the multiple of 16 (64..256) with the shortest schedule.
 // A tile's time does not shrink in proportion to its width (the token operand is read from
 // shared memory for every MMA whatever the width): measured at K = 18944 a tile of width bn
@@ -936,6 +1025,7 @@ int infero_gemm_tc_plan(int M, int N, int K, int sm_count, int* splits, int* kti
         s = target / tiles;
         if (s < 1) s = 1;
         if (s > 16) s = 16;
+        if (cluster_sum() && s > MAX_CLUSTER) s = MAX_CLUSTER;     // the splits of a tile form one cluster
         const int min_kt = 4;                              // a split shorter than this is all start-up
         if (s > total_kt / min_kt) s = total_kt / min_kt > 0 ? total_kt / min_kt : 1;
         per = (total_kt + s - 1) / s;
@@ -972,6 +1062,35 @@ int infero_gemm_tc_partials(const void* x, const void* w, float* partial, int M,
 #undef GO
 }
 
+// The same product added up over the splits inside the kernel (a cluster per tile, at most 8 splits):
+// out[t, n], 32-bit, no bias.
+int infero_gemm_tc_summed(const void* x, const void* w, float* out, int M, int N, int K, int ldx, int splits,
+                          int ktiles_per_split, cudaStream_t stream) {
+    INFERO_REQUIRE(infero_gemm_tc_supported(x, w, M, N, K, ldx), "gemm_tc: shape M=%d N=%d K=%d ldx=%d not supported", M, N, K, ldx);
+    INFERO_REQUIRE(M <= 256, "gemm_tc_summed: M=%d above 256", M);
+    INFERO_REQUIRE(splits >= 2 && splits <= MAX_CLUSTER && ktiles_per_split >= 1 &&
+                       (long long)(splits - 1) * ktiles_per_split * TILE_K < K,
+                   "gemm_tc_summed: %d splits of %d k-tiles do not fit K=%d (2..%d splits)", splits, ktiles_per_split, K, MAX_CLUSTER);
+    int* err;
+    if (err_flag_ptr(&err)) return 1;
+    const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+    CUtensorMap mw, mx;
+    if (get_map(w, N, K, K, TILE_A, &mw)) return 1;
+    if (get_map(x, M, K, ldx, bn, &mx)) return 1;
+#define GO(BN_, ST_) return launch_cluster<BN_, ST_>(mw, mx, out, N, M, K, ktiles_per_split, splits, err, stream)
+    switch (bn) {
+        case 16: GO(16, 6);
+        case 32: GO(32, 5);
+        case 64: GO(64, 4);
+        case 128: GO(128, 3);
+        default: GO(256, 4);
+    }
+#undef GO
+}
+
+int infero_gemm_cluster_enabled() { return cluster_sum() ? 1 : 0; }
+void infero_gemm_set_cluster(int on) { g_cluster.store(on ? 1 : 0, std::memory_order_relaxed); }
+
 int infero_reduce_partials(const float* partial, int splits, const void* bias, int bias_dtype, void* out,
                            int out_dtype, int M, int N, int ldc, cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
@@ -1001,6 +1120,10 @@ int infero_gemm_tc(const void* x, const void* w, const void* bias, int bias_dtyp
         infero_gemm_tc_plan(M, N, K, sm_count, &splits, &per, &need);
         if (splits > 1) {
             INFERO_REQUIRE(workspace && workspace_bytes >= need, "gemm_tc: workspace of %lld bytes needed, %lld given", need, workspace_bytes);
+            if (cluster_sum() && splits <= MAX_CLUSTER) {
+                if (infero_gemm_tc_summed(x, w, (float*)workspace, M, N, K, ldx, splits, per, stream)) return 1;
+                return infero_reduce_partials((const float*)workspace, 1, bias, bias_dtype, out, out_dtype, M, N, ldc, stream);
+            }
             if (infero_gemm_tc_partials(x, w, (float*)workspace, M, N, K, ldx, splits, per, stream)) return 1;
             return infero_reduce_partials((const float*)workspace, splits, bias, bias_dtype, out, out_dtype, M, N, ldc, stream);
         }

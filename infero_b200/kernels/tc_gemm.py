@@ -57,6 +57,13 @@ def gemm(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: to
                                 c_int(tile_n), _stream()))
 
 
+def set_cluster(on: bool) -> None:
+    """Few-row products whose K is cut into splits: add the splits up inside the kernel (a cluster
+    per tile, through distributed shared memory) or return them as partial sums (the default;
+    ``INFERO_GEMM_CLUSTER=1`` turns the cluster on)."""
+    lib().infero_gemm_set_cluster(c_int(1 if on else 0))
+
+
 def set_pairs(on: bool) -> None:
     """Many-token products on pairs of CTAs (cta_group::2) or on single CTAs; on unless
     ``INFERO_GEMM_PAIR=0``."""
@@ -82,6 +89,12 @@ def partials(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     M, K = a.shape
     N = w.shape[0]
     s, per, _ = plan(M, N, K, a.device)
+    if 2 <= s <= 8 and lib().infero_gemm_cluster_enabled():
+        # the splits of a tile add up inside the kernel (a cluster per tile): one array comes back
+        out = torch.empty((1, M, N), dtype=torch.float32, device=a.device)
+        _check(lib().infero_gemm_tc_summed(_ptr(a), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K),
+                                           c_int(a.stride(0)), c_int(s), c_int(per), _stream()))
+        return out
     out = torch.empty((s, M, N), dtype=torch.float32, device=a.device)
     _check(lib().infero_gemm_tc_partials(_ptr(a), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K),
                                          c_int(a.stride(0)), c_int(s), c_int(per), _stream()))

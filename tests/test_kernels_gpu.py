@@ -96,6 +96,41 @@ def test_gemm_tensor_core_partials_sum_in_fixed_order():
     assert tc_gemm.error_flag() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(8, 3584, 18944), (64, 4608, 3584), (1, 3584, 3584), (200, 1000, 2048), (33, 130, 1024),
+                                   (256, 896, 4864)])
+def test_gemm_tensor_core_splits_added_inside_a_cluster(M, N, K):
+    """The splits of a tile as one cluster, added up through distributed shared memory: the same
+    sums in the same order as the partial sums added up afterwards, bit for bit."""
+    import ctypes
+    from infero_b200.kernels import tc_gemm
+    a = _rand((M, K), torch.bfloat16, 8)
+    w = _rand((N, K), torch.bfloat16, 9, 0.02)
+    tc_gemm.set_cluster(True)
+    try:
+        s, per, _ = tc_gemm.plan(M, N, K, DEV)
+        assert 2 <= s <= 8, "this shape was meant to be cut along K"
+        summed = tc_gemm.partials(a, w)
+        assert summed.shape == (1, M, N)
+        again = tc_gemm.partials(a, w)
+        assert torch.equal(summed, again)
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=DEV)
+        tc_gemm.gemm(a, w, None, out)                      # the whole product through the same kernel
+        assert _rel_err(out, _gemm_ref(a, w, None)) <= 6e-3
+    finally:
+        tc_gemm.set_cluster(False)
+    parts = torch.full((s, M, N), float("nan"), dtype=torch.float32, device=DEV)
+    L = tc_gemm.lib()
+    rc = L.infero_gemm_tc_partials(ctypes.c_void_p(a.data_ptr()), ctypes.c_void_p(w.data_ptr()),
+                                   ctypes.c_void_p(parts.data_ptr()), M, N, K, a.stride(0), s, per,
+                                   ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    ref = torch.empty((M, N), dtype=torch.float32, device=DEV)
+    tc_gemm.reduce_partials(parts, None, ref)
+    assert torch.equal(summed[0], ref)
+    assert _rel_err(ref, _gemm_ref(a, w, None)) <= 1e-5
+    assert tc_gemm.error_flag() == 0
+
+
 @pytest.mark.parametrize("M,N,K", [(8, 37888, 3584), (64, 1024, 512), (300, 400, 264), (2048, 1280, 512), (5, 354, 64),
                                    (2048, 7168, 192), (700, 3000, 72)])
 def test_gemm_tensor_core_with_swiglu_epilogue(M, N, K, cta_pairs):
