@@ -16,6 +16,7 @@ from typing import Dict, Hashable, List, Optional, Sequence
 import numpy as np
 import torch
 
+from .. import kernels as K
 from ..cache import CacheManager, CacheStorage, OutOfPages, RequestCache
 from ..config.engine_config import EngineConfig
 from ..models.decoder import DecoderModel
@@ -182,7 +183,8 @@ class ModelRunner:
                 logits = self._graph_step(key, entries, rcs)
             if key is None or logits is None:
                 ctx, rows = self._build_context(entries, rcs)
-                logits = self.model.forward(ctx, ctx.token_ids, rows)
+                with K.stream_scope():
+                    logits = self.model.forward(ctx, ctx.token_ids, rows)
                 n_tokens = ctx.n_tokens
             else:
                 n_tokens = len(entries)
@@ -320,13 +322,14 @@ class _DecodeGraph:
         self.graph = torch.cuda.CUDAGraph()
         # No garbage collection while the stream is capturing: an old CUDA graph that is freed in
         # the middle of a capture (runners sit in reference cycles, so they go when the collector
-        # gets to them) invalidates the capture.  Collect first, then hold the collector off.
-        gc.collect()
+        # gets to them) invalidates the capture.  The collector is held off meanwhile (a full
+        # collection first would cost more than the capture itself).
         was_enabled = gc.isenabled()
         gc.disable()
         try:
             with torch.cuda.graph(self.graph):
-                self.logits = runner.model.forward(ctx, ctx.token_ids, rows)
+                with K.stream_scope():
+                    self.logits = runner.model.forward(ctx, ctx.token_ids, rows)
         finally:
             if was_enabled:
                 gc.enable()

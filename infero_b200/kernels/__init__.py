@@ -65,8 +65,31 @@ def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
     return c_void_p(t.data_ptr())
 
 
+_SCOPED_STREAM: Optional[c_void_p] = None
+
+
 def _stream() -> c_void_p:
+    """The stream kernels are launched on: torch's current stream, looked up once per
+    ``stream_scope`` (a look-up costs about as much as a launch) or at every call outside one."""
+    if _SCOPED_STREAM is not None:
+        return _SCOPED_STREAM
     return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class stream_scope:
+    """Inside, every kernel of this module goes to the stream that was current on entry (enter it
+    inside ``torch.cuda.graph`` / ``torch.cuda.stream``, not around them)."""
+
+    def __enter__(self):
+        global _SCOPED_STREAM
+        self._prev = _SCOPED_STREAM
+        _SCOPED_STREAM = c_void_p(torch.cuda.current_stream().cuda_stream)
+        return self
+
+    def __exit__(self, *exc):
+        global _SCOPED_STREAM
+        _SCOPED_STREAM = self._prev
+        return False
 
 
 def _check(rc: int) -> None:

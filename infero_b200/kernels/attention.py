@@ -113,9 +113,24 @@ def prefill_tc(q, out, k_cache, v_cache, table, entry_q_start, entry_q_len, entr
         c_int(n_kv), c_int(head_dim), c_int(page_size), c_int(window or 0), c_float(scale), _stream()))
 
 
+def shape_of_batch(q_lens: Sequence[int], pos0: Sequence[int]):
+    """What the choice of kernels needs to know of a batch, the same for every layer of a step:
+    (single-token requests in front, most keys any of them sees, blocks of 128 query rows of the
+    others, blocks of the mma.sync kernel's height)."""
+    E = len(q_lens)
+    n_dec = 0
+    while n_dec < E and q_lens[n_dec] == 1:
+        n_dec += 1
+    vis = max((int(pos0[i]) + 1 for i in range(n_dec)), default=0)
+    tiles_128 = sum(-(-int(n) // 128) for n in q_lens[n_dec:])
+    tiles_mma = sum(-(-int(n) // PREFILL_ROWS) for n in q_lens[n_dec:])
+    return n_dec, vis, tiles_128, tiles_mma
+
+
 def attention_any(q, out, k_cache, v_cache, table, tok_entry, positions, n_heads: int, n_kv: int, head_dim: int,
                   page_size: int, window: Optional[int], scale: float, q_lens: Sequence[int], pos0: Sequence[int],
-                  entry_q_start=None, entry_q_len=None, entry_pos0=None, kv_bound: Optional[int] = None) -> None:
+                  entry_q_start=None, entry_q_len=None, entry_pos0=None, kv_bound: Optional[int] = None,
+                  batch_shape=None) -> None:
     """q: [T, >= H*D] view with rotated queries in front (row stride free); out [T, H*D].
     ``q_lens`` / ``pos0`` are the host copies of each request's new-token count and cached
     length; the device copies are made here when the caller has none.  ``kv_bound``: plan the
@@ -126,11 +141,11 @@ def attention_any(q, out, k_cache, v_cache, table, tok_entry, positions, n_heads
                           page_size, window, scale)
         return
     E = len(q_lens)
-    n_dec = 0
-    while n_dec < E and q_lens[n_dec] == 1:
-        n_dec += 1
+    if batch_shape is None:
+        batch_shape = shape_of_batch(q_lens, pos0)
+    n_dec, vis_now, tiles_128, tiles_mma = batch_shape
     if n_dec:
-        vis = max(int(pos0[i]) + 1 for i in range(n_dec)) if kv_bound is None else int(kv_bound)
+        vis = vis_now if kv_bound is None else int(kv_bound)
         if window:
             vis = min(vis, window + 15)
         chunk, splits = plan_decode(n_dec, n_kv, n_heads // n_kv, vis)
@@ -146,11 +161,11 @@ def attention_any(q, out, k_cache, v_cache, table, tok_entry, positions, n_heads
             entry_q_len = torch.tensor([int(n) for n in q_lens], dtype=torch.int32, device=dev)
             entry_pos0 = torch.tensor([int(p) for p in pos0], dtype=torch.int32, device=dev)
         if prefill_tc_supported(q, out, head_dim, page_size) and k_cache.is_contiguous() and v_cache.is_contiguous():
-            n_tiles = sum(-(-int(n) // 128) for n in q_lens[n_dec:])
+            n_tiles = tiles_128
             prefill_tc(q, out, k_cache, v_cache, table, entry_q_start, entry_q_len, entry_pos0, E, n_dec, n_tiles,
                        n_heads, n_kv, head_dim, page_size, window, scale)
             return
-        n_tiles = sum(-(-int(n) // PREFILL_ROWS) for n in q_lens[n_dec:])
+        n_tiles = tiles_mma
         prefill(q, out, k_cache, v_cache, table, entry_q_start, entry_q_len, entry_pos0, E, n_dec, n_tiles,
                 n_heads, n_kv, head_dim, page_size, window, scale)
 
@@ -159,4 +174,15 @@ def paged_attention(ctx, qkv, out, kv, table, n_heads, n_kv, head_dim, window, s
     """qkv: [T, (H + 2 Hkv) D] with rotated queries in front; out [T, H*D]."""
     attention_any(qkv, out, kv.k, kv.v, table, ctx.tok_entry, ctx.positions, n_heads, n_kv, head_dim,
                   kv.page_size, window, scale, ctx.h_q_len, ctx.h_pos0, ctx.entry_q_start, ctx.entry_q_len,
-                  ctx.entry_pos0, kv_bound=getattr(ctx, "kv_bound", None))
+                  ctx.entry_pos0, kv_bound=getattr(ctx, "kv_bound", None), batch_shape=_batch_shape(ctx))
+
+
+def _batch_shape(ctx):
+    memo = getattr(ctx, "_attn_batch_shape", None)
+    if memo is None:
+        memo = shape_of_batch(ctx.h_q_len, ctx.h_pos0)
+        try:
+            ctx._attn_batch_shape = memo
+        except AttributeError:          # a context that takes no new attributes
+            pass
+    return memo

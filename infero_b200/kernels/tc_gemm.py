@@ -18,6 +18,10 @@ from . import BF16, F32, KernelError, _check, _dt, _ptr, _stream, lib
 _SM_COUNT = {}
 
 
+_plans = {}
+_plan_epoch = [0]          # bumped when a switch that changes the plans is thrown
+
+
 def sm_count(device) -> int:
     idx = torch.device(device).index or 0
     if idx not in _SM_COUNT:
@@ -29,15 +33,21 @@ def supported(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not w.is_contiguous() or a.stride(1) != 1:
         return False
     M, K = a.shape
-    return bool(lib().infero_gemm_tc_supported(_ptr(a), _ptr(w), c_int(M), c_int(w.shape[0]), c_int(K),
-                                               c_int(a.stride(0))))
+    ld = a.stride(0)
+    # what infero_gemm_tc_supported checks, without the call: it is asked before every product
+    return (M > 0 and w.shape[0] > 0 and K >= 8 and K % 8 == 0 and ld % 8 == 0 and ld >= K
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
 def plan(M: int, N: int, K: int, device) -> Tuple[int, int, int]:
     """(splits, k-tiles per split, workspace bytes) of the few-row path."""
-    s, per, ws = c_int(0), c_int(0), c_longlong(0)
-    lib().infero_gemm_tc_plan(c_int(M), c_int(N), c_int(K), c_int(sm_count(device)), byref(s), byref(per), byref(ws))
-    return s.value, per.value, ws.value
+    key = (M, N, K, _plan_epoch[0])
+    hit = _plans.get(key)
+    if hit is None:
+        s, per, ws = c_int(0), c_int(0), c_longlong(0)
+        lib().infero_gemm_tc_plan(c_int(M), c_int(N), c_int(K), c_int(sm_count(device)), byref(s), byref(per), byref(ws))
+        hit = _plans[key] = (s.value, per.value, ws.value)
+    return hit
 
 
 def gemm(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
@@ -62,6 +72,7 @@ def set_cluster(on: bool) -> None:
     per tile, through distributed shared memory) or return them as partial sums (the default;
     ``INFERO_GEMM_CLUSTER=1`` turns the cluster on)."""
     lib().infero_gemm_set_cluster(c_int(1 if on else 0))
+    _plan_epoch[0] += 1
 
 
 def set_pairs(on: bool) -> None:
