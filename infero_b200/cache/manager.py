@@ -224,15 +224,18 @@ class CacheManager:
         return out
 
     def step_layout(self, slots: np.ndarray, n_tokens: np.ndarray, tokens: np.ndarray, want_counts: np.ndarray,
-                    wants: np.ndarray, table_width: int, out: np.ndarray) -> List[int]:
+                    wants: np.ndarray, table_width: int, out: np.ndarray, n_pad: int = 0, pad_slot: int = 0,
+                    pad_page: int = 0) -> List[int]:
         """Write a step's int32 arrays into ``out`` (see csrc/host_cache.cpp: token ids, positions,
         token -> entry, per entry first row / row count / cached length / slot, wanted rows, one
-        block table per group) and return the section sizes.  All arguments are int32 arrays."""
+        block table per group) and return the section sizes.  All arguments are int32 arrays.
+        ``n_pad`` entries of a request that does not exist follow the real ones (token 0 at position
+        0, state slot ``pad_slot``, the single page ``pad_page``)."""
         sizes = (ctypes.c_longlong * (8 + len(self.groups)))()
         as_p = lambda a: a.ctypes.data_as(ctypes.POINTER(ctypes.c_int))     # noqa: E731
         total = self._L.infero_step_layout(self._h, int(slots.size), as_p(slots), as_p(n_tokens), as_p(tokens),
                                            as_p(want_counts), as_p(wants), int(table_width), as_p(out),
-                                           ctypes.c_longlong(out.size), sizes)
+                                           ctypes.c_longlong(out.size), sizes, int(n_pad), int(pad_slot), int(pad_page))
         if total < 0:
             raise ValueError("step layout does not fit its buffer, or a request holds more pages than the table is wide")
         return [int(v) for v in sizes]

@@ -318,13 +318,17 @@ int infero_cache_check(void* h) {
 //   the rows whose logits are wanted [R], and per group the block table [E, table_width].
 // sizes[0 .. 7 + n_groups] receives the section sizes.  Returns the total, or -1 when cap is too small
 // or a request holds more than table_width pages.
+//
+// n_pad more entries follow the real ones (a captured step is replayed with fewer requests than it was
+// captured for): each feeds token 0 at position 0 of a request that does not exist, in state slot
+// pad_slot, with a block table of the single page pad_page, and wants its logits (which nobody reads).
 long long infero_step_layout(void* h, int n_entries, const int* slots, const int* n_tokens, const int* tokens,
                              const int* want_counts, const int* wants, int table_width, int* out, long long cap,
-                             long long* sizes) {
+                             long long* sizes, int n_pad, int pad_slot, int pad_page) {
     Cache* c = static_cast<Cache*>(h);
-    const int E = n_entries, G = (int)c->groups.size();
-    long long T = 0, R = 0;
-    for (int e = 0; e < E; ++e) { T += n_tokens[e]; R += want_counts[e]; }
+    const int real = n_entries, E = n_entries + n_pad, G = (int)c->groups.size();
+    long long T = n_pad, R = n_pad;
+    for (int e = 0; e < real; ++e) { T += n_tokens[e]; R += want_counts[e]; }
     const long long total = 3 * T + 4LL * E + R + (long long)G * std::max(1, E) * table_width;
     if (total > cap) return -1;
     int* tok = out;
@@ -337,7 +341,13 @@ long long infero_step_layout(void* h, int n_entries, const int* slots, const int
     int* rows = slot_out + E;
     int* tab = rows + R;
     long long t = 0, r = 0, w = 0;
-    for (int e = 0; e < E; ++e) {
+    for (int e = real; e < E; ++e) {                     // the pads' rows come after the real ones'
+        const long long tp = T - n_pad + (e - real);
+        q_start[e] = (int)tp; q_len[e] = 1; pos0[e] = 0; slot_out[e] = pad_slot;
+        rows[R - n_pad + (e - real)] = (int)tp;
+        tok[tp] = 0; pos[tp] = 0; ent[tp] = e;
+    }
+    for (int e = 0; e < real; ++e) {
         const Request& rq = c->reqs[slots[e]];
         const int base = rq.length;                  // tokens already in the cache (this step's are only reserved)
         q_start[e] = (int)t;
@@ -356,7 +366,11 @@ long long infero_step_layout(void* h, int n_entries, const int* slots, const int
     for (int g = 0; g < G; ++g) {
         int* dst = tab + (long long)g * std::max(1, E) * table_width;
         if (E == 0) std::fill(dst, dst + table_width, -1);
-        for (int e = 0; e < E; ++e) {
+        for (int e = real; e < E; ++e) {
+            std::fill(dst + (long long)e * table_width, dst + (long long)(e + 1) * table_width, -1);
+            dst[(long long)e * table_width] = pad_page;
+        }
+        for (int e = 0; e < real; ++e) {
             const Request& rq = c->reqs[slots[e]];
             if ((int)rq.tables[g].size() > table_width) return -1;
             const int* row = c->mirror[g].data() + (size_t)slots[e] * c->width;

@@ -95,8 +95,11 @@ class ModelRunner:
         self.page_size = cfg.page_size
         self.num_pages = cfg.resolved_num_pages()
         self.max_blocks = max(1, -(-cfg.ctx // cfg.page_size))
-        self.storage = CacheStorage(model.kv_specs, model.state_specs, self.num_pages, cfg.page_size,
-                                    cfg.max_seqs, self.act_dtype, self.device)
+        # one page and one state slot beyond what the manager hands out: where the entries that pad a
+        # captured step to its captured size read and write
+        self.pad_page, self.pad_slot = self.num_pages, cfg.max_seqs
+        self.storage = CacheStorage(model.kv_specs, model.state_specs, self.num_pages + 1, cfg.page_size,
+                                    cfg.max_seqs + 1, self.act_dtype, self.device)
         self.manager = CacheManager(self.storage.bookkeeping_groups(), self.num_pages, cfg.page_size,
                                     cfg.max_seqs, max_blocks=self.max_blocks)
         # the sampler's last pick per request slot, for steps launched before the host has read it
@@ -199,9 +202,10 @@ class ModelRunner:
         return logits
 
     # ---- device inputs of a step ---------------------------------------------------------------
-    def _layout_args(self, entries: Sequence[StepEntry], rcs: Sequence[RequestCache]):
+    def _layout_args(self, entries: Sequence[StepEntry], rcs: Sequence[RequestCache], pad: int = 0):
         """What the C++ layout builder takes: per entry slot, token count and wanted count, the
-        flat token ids and wanted places, and the number of ints the step's arrays need."""
+        flat token ids and wanted places, and the number of ints the step's arrays need (with
+        ``pad`` single-token entries of no request behind the real ones)."""
         E = len(entries)
         slots = np.fromiter((rc.slot for rc in rcs), dtype=np.int32, count=E)
         lens = np.fromiter((len(e.tokens) for e in entries), dtype=np.int32, count=E)
@@ -218,13 +222,13 @@ class ModelRunner:
             wants = np.concatenate([np.asarray(e.want, dtype=np.int32) for e in entries if len(e.want)])
         else:
             wants = np.zeros(1, dtype=np.int32)
-        total = 3 * T + 4 * E + R + len(self.manager.groups) * max(1, E) * self.max_blocks
-        return (slots, lens, tokens, want_counts, wants), total, T
+        total = 3 * (T + pad) + 4 * (E + pad) + R + pad + len(self.manager.groups) * max(1, E + pad) * self.max_blocks
+        return (slots, lens, tokens, want_counts, wants), total, T + pad
 
-    def _fill(self, args, out: np.ndarray):
+    def _fill(self, args, out: np.ndarray, pad: int = 0):
         """Lay the step's arrays out in ``out`` (pinned host memory); returns the section sizes and
         host copies of the per-entry arrays."""
-        sizes = self.manager.step_layout(*args, self.max_blocks, out)
+        sizes = self.manager.step_layout(*args, self.max_blocks, out, pad, self.pad_slot, self.pad_page)
         T, E = sizes[0], sizes[3]
         o = 3 * T
         host = tuple(out[o + k * E:o + (k + 1) * E].copy() for k in range(4))    # first row, rows, cached length, slot
@@ -273,9 +277,19 @@ class ModelRunner:
         bound = 256
         while bound < need:
             bound *= 2
-        return (len(entries), min(bound, self.max_blocks * self.page_size))
+        return (self._graph_size(len(entries)), min(bound, self.max_blocks * self.page_size))
 
     MAX_GRAPH_ENTRIES = 256
+    GRAPH_SIZES = (1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+
+    def _graph_size(self, n: int) -> int:
+        """A step of n single tokens runs as the captured step of the next size in GRAPH_SIZES, the
+        difference made up by entries of no request (so that a batch that shrinks request by
+        request does not capture a graph at every size), unless its logits would not fit."""
+        for size in self.GRAPH_SIZES:
+            if size >= n:
+                return size if size <= self.cfg.max_logit_rows else n
+        return n
 
     def _graph_step(self, key, entries, rcs) -> Optional[torch.Tensor]:
         seen = self._graph_seen.get(key, 0)
@@ -290,7 +304,7 @@ class ModelRunner:
         g.load(entries, rcs)
         g.graph.replay()
         self.graph_replays += 1
-        return g.logits
+        return g.logits[:len(entries)]
 
     def drop_graphs(self) -> None:
         self._graphs.clear()
@@ -304,8 +318,9 @@ class _DecodeGraph:
 
     def __init__(self, runner: ModelRunner, key, entries, rcs):
         self.runner = runner
-        E, bound = key
-        args, n, _ = runner._layout_args(entries, rcs)
+        E, bound = key                    # E: the captured size, len(entries) or the next size above it
+        self.size = E
+        args, n, _ = runner._layout_args(entries, rcs, E - len(entries))
         self.dev = torch.zeros(n, dtype=torch.int32, device=runner.device)
         self.staging = [torch.empty(n, dtype=torch.int32, pin_memory=True) for _ in range(2)]
         self.copied = [None, None]
@@ -336,13 +351,14 @@ class _DecodeGraph:
         self.n_kernels = K.launch_count() - before
 
     def load(self, entries, rcs, args=None):
+        pad = self.size - len(entries)
         if args is None:
-            args, _, _ = self.runner._layout_args(entries, rcs)
+            args, _, _ = self.runner._layout_args(entries, rcs, pad)
         i = self.turn
         self.turn ^= 1
         if self.copied[i] is not None:
             self.copied[i].synchronize()
-        filled = self.runner._fill(args, self.staging[i].numpy())
+        filled = self.runner._fill(args, self.staging[i].numpy(), pad)
         self.dev.copy_(self.staging[i], non_blocking=True)
         self.runner.last_h2d_bytes = self.dev.numel() * 4
         ev = torch.cuda.Event()

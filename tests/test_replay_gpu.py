@@ -156,6 +156,53 @@ def test_captured_decode_steps_equal_eager_ones(name, dtype):
     torch.cuda.synchronize()
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_captured_steps_padded_to_a_size(dtype):
+    """A batch of five single tokens runs as the captured step of six, of which one entry belongs
+    to no request; as requests end the batch shrinks through sizes that capture nothing new.  The
+    logits of the real entries are those of eager steps (float32: bit for bit, since a row's
+    arithmetic does not depend on the batch)."""
+    import torch
+    from infero_b200.engine import StepEntry
+    name = "B"
+    mdir = model_dir(name)
+    lens = [64, 57, 50, 43, 36]
+    reqs = make_requests(name, lens, seed=33)
+    head = 12
+
+    def run(graphs):
+        runner = make_runner(mdir, dtype, 512, cuda_graphs=graphs)
+        for rid, toks in reqs.items():
+            runner.open(rid)
+            runner.step([StepEntry(rid, toks[:head], [])])
+        out = {rid: [] for rid in reqs}
+        for p in range(head, max(lens)):
+            live = [rid for rid, toks in reqs.items() if p < len(toks)]
+            logits = runner.step([StepEntry(rid, [reqs[rid][p]], [0]) for rid in live]).float().cpu()
+            for i, rid in enumerate(live):
+                out[rid].append(logits[i].clone())
+            for rid in list(reqs):
+                if p + 1 == len(reqs[rid]):
+                    runner.close(rid)
+        runner.manager.check()
+        assert not runner.manager.requests
+        return out, runner
+
+    eager, _ = run(False)
+    captured, runner = run(True)
+    assert runner._graph_size(5) == 6 and runner._graph_size(3) == 3 and runner._graph_size(7) == 8
+    # sizes met: 5 -> 6, 4, 3, 2, 1: five graphs at most for this key bound, far fewer than steps
+    assert 2 <= runner.graph_captures <= 6 and runner.graph_replays > 30
+    worst = 0.0
+    for rid in reqs:
+        for a, b in zip(eager[rid], captured[rid]):
+            if dtype == "float32":
+                assert torch.equal(a, b), f"{rid}: a padded captured step changed a real row"
+            worst = max(worst, float((a - b).abs().max() / a.abs().max()))
+    assert worst <= TOL[dtype]
+    torch.cuda.synchronize()
+
+
 @pytest.mark.parametrize("name", ["A", "B"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_greedy_generation_through_the_entry_point(name, dtype):
