@@ -40,6 +40,14 @@ QWEN25_7B = {
     "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "use_sliding_window": False,
     "max_position_embeddings": 32768, "hidden_act": "silu",
 }
+# the other shapes the same two metrics are asked for (--shape); the default stays the 7B one
+OTHER_SHAPES = {
+    "14b": {"num_hidden_layers": 48, "hidden_size": 5120, "num_attention_heads": 40, "num_key_value_heads": 8,
+            "intermediate_size": 13824, "vocab_size": 152064, "rms_norm_eps": 1e-5, "tie_word_embeddings": False},
+    "0.5b": {"num_hidden_layers": 24, "hidden_size": 896, "num_attention_heads": 14, "num_key_value_heads": 2,
+             "head_dim": 64, "intermediate_size": 4864, "vocab_size": 151936, "rms_norm_eps": 1e-6, "tie_word_embeddings": True},
+}
+SHAPE_NAMES = {"7b": "Qwen2.5-7B shape", "14b": "Qwen2.5-14B shape", "0.5b": "Qwen2.5-0.5B shape"}
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
@@ -224,6 +232,7 @@ def main(argv=None) -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--shape", default="7b", choices=sorted(SHAPE_NAMES), help="layer sizes: Qwen2.5-7B (the headline), 14B or 0.5B")
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
     ap.add_argument("--skip-e2e", action="store_true")
@@ -245,6 +254,8 @@ def main(argv=None) -> int:
     from infero_b200.loading import random_model
     K.lib()
     cfg_json = dict(QWEN25_7B)
+    cfg_json.update(OTHER_SHAPES.get(args.shape, {}))
+    shape_name = SHAPE_NAMES[args.shape]
     full_layers = cfg_json["num_hidden_layers"]
     layers = args.layers or full_layers
     cfg_json["num_hidden_layers"] = layers
@@ -280,12 +291,12 @@ def main(argv=None) -> int:
 
     achieved = main_pt["bytes"] / (main_pt["ms_per_step"] / 1e3) / 1e9
     line = {
-        "metric": "decode tok/s at batch 8 (4K ctx), Qwen2.5-7B shape",
+        "metric": f"decode tok/s at batch {args.batch} (4K ctx), {shape_name}",
         "value": round(main_pt["tok_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": round(main_pt["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic: random weights N(0,0.02) from a seed, uniform random token ids",
         "impl": "ours",
-        "config": {"model": "Qwen2.5-7B shape", "global_batch": args.batch, "seq_len": CONTEXT,
+        "config": {"model": shape_name, "global_batch": args.batch, "seq_len": CONTEXT,
                    "parallelism": "single GPU", "layers": layers, "layers_of_configuration": full_layers,
                    "hidden": cfg_json["hidden_size"], "heads": cfg_json["num_attention_heads"],
                    "kv_heads": cfg_json["num_key_value_heads"], "head_dim": cfg_json["head_dim"],
