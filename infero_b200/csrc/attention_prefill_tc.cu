@@ -187,12 +187,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                         tma_load_2d(smem + Plan::Q_OFF + t * Plan::Q_BYTES + b * Plan::QBLOCK_BYTES, &map_q,
                                     (head0 + t) * D + b * 64, tok0 + row_first, q_full);
             }
+            // pages of up to 64 rows are fetched whole (slice == page_size): no division in the loop
+            const bool whole_pages = slice == page_size;
+            const int per_tile = KTILE / slice;
             auto row_of = [&](int j) {
-                const int key0 = (kt_begin + j) * KTILE + lane * slice;
-                const int blk = key0 / page_size;
+                int blk, in_page;
+                if (whole_pages) {
+                    blk = (kt_begin + j) * per_tile + lane;
+                    in_page = 0;
+                } else {
+                    const int key0 = (kt_begin + j) * KTILE + lane * slice;
+                    blk = key0 / page_size;
+                    in_page = key0 - blk * page_size;
+                }
                 const int page = blk < max_blocks ? table[blk] : -1;
                 // a page that is not held (beyond the request's end) is never visible; any finite rows do
-                return (page < 0 ? 0 : (page * n_kv + kvh) * page_size) + key0 % page_size;
+                return (page < 0 ? 0 : (page * n_kv + kvh) * page_size) + in_page;
             };
             bool ok = true;
             int issued = 0;
