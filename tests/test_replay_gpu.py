@@ -238,6 +238,45 @@ def test_greedy_generation_through_the_entry_point(name, dtype):
     assert not eng.runner.manager.requests
 
 
+def test_generation_under_page_pressure_equals_plain():
+    """More requests than the cache can hold at once: requests wait, the youngest is preempted and
+    recomputed, window pages come back early, captured steps are padded and run ahead; in 32-bit
+    every request still gets exactly the plain implementation's greedy continuation."""
+    import plain_qwen2
+    from engine_fixtures import plain_model
+    from infero_b200.engine import Engine
+    from infero_b200.sampling import SamplingParams
+    mdir = model_dir("B", seed=77, qk_gain=1.5)
+    cfg, w = plain_model(mdir)
+    lens = [33, 5, 48, 17, 60, 9, 26, 41, 3, 55]
+    reqs = make_requests("B", lens, seed=52)
+    n_new = 14
+    want = {rid: plain_qwen2.greedy_generate(cfg, w, toks, n_new) for rid, toks in reqs.items()}
+    eng = Engine(mdir, dtype="float32", ctx=96, max_seqs=4, kv_slots=10 * 16, max_batch_tokens=24)
+    pick = SamplingParams(temperature=0.0, repetition_penalty=1.0)
+    for rid, toks in reqs.items():
+        eng.add_request(toks, pick, max_new_tokens=n_new, ignore_eos=True, rid=rid)
+    got = {rid: [] for rid in reqs}
+    reasons = {}
+    for _ in range(5000):
+        if eng.is_idle():
+            break
+        for ev in eng.step():
+            if ev.token is not None:
+                got[ev.rid].append(ev.token)
+            if ev.finished:
+                reasons[ev.rid] = ev.reason
+        eng.runner.manager.check()
+    assert eng.is_idle()
+    assert eng.scheduler.stats["preemptions"] > 0, "the pool was meant to be too small"
+    assert set(reasons.values()) == {"length"}
+    for rid in reqs:
+        assert got[rid] == want[rid], f"request {rid}"
+    assert not eng.runner.manager.requests
+    for a in eng.runner.manager.allocators:
+        assert a.num_free == a.num_pages
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_running_ahead_changes_no_token(dtype):
     """One step in flight (tokens fed from the device, end-of-sequence seen a step late) against
