@@ -185,11 +185,24 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const int n_slices = (k_end - k_begin + KEYS16 - 1) / KEYS16;
     const int my_slices = n_slices > warp ? (n_slices - warp + TD_WARPS - 1) / TD_WARPS : 0;
     const uint64_t policy = tc::policy_evict_first();                 // the cache is read once per step
+    // The pages of the warp's slices, 32 at a time: lane l holds the page of slice base + l, so that the
+    // look-ups in the block table are one round of loads, not one dependent load in front of every issue.
+    int pages_base = 0;
+    auto load_pages = [&](int base_slice) {
+        const int i = base_slice + lane;
+        int pg = -1;
+        if (i < my_slices) pg = table[(k_begin + (warp + i * TD_WARPS) * KEYS16) / page_size];
+        pages_base = base_slice;
+        return pg;
+    };
+    int my_page = load_pages(0);
     // lane 0 issues the loads of the warp's i-th slice into stage i % STAGES
     auto issue = [&](int i) {
-        if (i < my_slices && lane == 0) {
+        if (i >= my_slices) return;                                   // (uniform over the warp)
+        if (i >= pages_base + 32) my_page = load_pages(i);
+        const int page = __shfl_sync(0xffffffffu, my_page, i - pages_base);
+        if (lane == 0) {
             const int key0 = k_begin + (warp + i * TD_WARPS) * KEYS16;
-            const int page = table[key0 / page_size];
             const int row = (page < 0 ? 0 : (page * n_kv + kvh) * page_size) + key0 % page_size;
             uint8_t* st = my + (size_t)(i % STAGES) * Plan::STAGE_BYTES;
             uint64_t* bar = &my_bar[i % STAGES];
