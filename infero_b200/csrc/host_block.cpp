@@ -1,0 +1,296 @@
+// One layer of the built-in kind (pre-norm block: RMSNorm, grouped-query attention with rotary
+// positions over the paged cache, RMSNorm, SwiGLU) launched from native code: the same kernels with
+// the same arguments, in the same order, as the Python parts launch them one by one, so the results
+// are the same bit for bit; only the host's time per layer differs (one call instead of a dozen
+// Python wrappers).  bf16 steps on the tensor-core path only; everything else stays with the parts.
+//
+// The reference runs its whole layer loop natively (crates/model/src/lib.rs:3423-4243); this is
+// the corresponding piece for the one layout of block this engine builds itself.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdint>
+#include <cstdlib>
+
+extern "C" {
+// elementwise.cu, rope_cache.cu, gemm_tc.cu, attention_*.cu, runtime.cu
+int infero_add_rmsnorm(float* x, const void* delta, int delta_dtype, int delta_splits, long long split_stride,
+                       const void* dbias, int dbias_dtype, const void* w, int w_dtype, float eps, void* out,
+                       int out_dtype, const int* rows, int n_rows, int d, cudaStream_t stream);
+int infero_swiglu(const void* gate_up, int splits, long long split_stride, void* out, int dtype, int out_bf16,
+                  int n_tokens, int ff, cudaStream_t stream);
+int infero_rope_cache(void* qkv, int dtype, int row_stride, const int* positions, const int* tok_entry,
+                      const int* block_table, int max_blocks, const float* inv_freq, int rotary_dim, void* k_cache,
+                      void* v_cache, int page_size, int n_tokens, int n_heads, int n_kv, int head_dim,
+                      int write_cache, cudaStream_t stream);
+int infero_rope_cache_partials(const float* partial, int splits, long long split_stride, const void* bias,
+                               int bias_dtype, void* q_out, int q_stride, int dtype, const int* positions,
+                               const int* tok_entry, const int* block_table, int max_blocks, const float* inv_freq,
+                               int rotary_dim, void* k_cache, void* v_cache, int page_size, int n_tokens,
+                               int n_heads, int n_kv, int head_dim, int write_cache, cudaStream_t stream);
+int infero_gemm_tc_supported(const void* x, const void* w, int M, int N, int K, int ldx);
+int infero_gemm_tc_plan(int M, int N, int K, int sm_count, int* splits, int* ktiles_per_split, long long* ws_bytes);
+int infero_gemm_tc_partials(const void* x, const void* w, float* partial, int M, int N, int K, int ldx, int splits,
+                            int ktiles_per_split, cudaStream_t stream);
+int infero_gemm_tc_summed(const void* x, const void* w, float* out, int M, int N, int K, int ldx, int splits,
+                          int ktiles_per_split, cudaStream_t stream);
+int infero_gemm_cluster_enabled();
+int infero_gemm_tc(const void* x, const void* w, const void* bias, int bias_dtype, void* out, int out_dtype, int M,
+                   int N, int K, int ldx, int ldc, void* workspace, long long workspace_bytes, int sm_count,
+                   int tile_n, cudaStream_t stream);
+int infero_gemm_tc_swiglu(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int ldc,
+                          int sm_count, cudaStream_t stream);
+long long infero_attn_decode_scratch(int n_tok, int n_heads, int head_dim, int n_splits);
+int infero_attn_decode_tma_supported(int head_dim, int page_size);
+int infero_attn_decode_tma(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
+                           const void* v_cache, int num_pages, const int* block_table, int max_blocks,
+                           const int* tok_entry, const int* positions, int tok_first, int n_tok, int n_heads,
+                           int n_kv, int head_dim, int page_size, int window, float scale, int chunk, int n_splits,
+                           void* scratch, int* counters, int n_counters, cudaStream_t stream);
+int infero_attn_prefill_tc_supported(int head_dim, int page_size, int q_stride, int out_stride);
+int infero_attn_prefill_tc(const void* q, int q_stride, int n_tokens, void* out, int out_stride, const void* k_cache,
+                           const void* v_cache, int num_pages, const int* block_table, int max_blocks,
+                           const int* entry_q_start, const int* entry_q_len, const int* entry_pos0, int n_entries,
+                           int first_entry, int n_tiles, int n_heads, int n_kv, int head_dim, int page_size,
+                           int window, float scale, cudaStream_t stream);
+}
+void infero_set_error(const char* fmt, ...);
+
+extern "C" {
+
+enum : int { F32 = 0, BF16 = 1 };
+
+// What is fixed for one execution of a block (a schedule entry): sizes, weights, its cache.
+struct InferoBlock {
+    int hidden, n_heads, n_kv, head_dim, intermediate, rotary_dim, window, write_cache;
+    float eps_mixer, eps_ffn, scale;
+    int norm_dtype, qkv_bias_dtype, o_bias_dtype;
+    const void* w_norm_mixer;
+    const void* w_norm_ffn;
+    const void* w_qkv;
+    const void* b_qkv;          // or null
+    const void* w_o;
+    const void* b_o;            // or null
+    const void* w_gate_up;      // rows alternate gate_j, up_j
+    const void* w_down;
+    const float* inv_freq;      // rotary_dim / 2 floats (rotary_dim 0: none)
+    void* k_cache;
+    void* v_cache;
+    int num_pages, page_size;
+};
+
+// What is fixed for one step: the batch and where things live.  The same for every layer.
+struct InferoStep {
+    int n_tokens, n_entries, n_decode;          // single-token requests come first
+    int decode_visible;                         // keys the decode kernel is planned for
+    int prefill_tiles;                          // blocks of 128 query rows of the other requests
+    int sm_count;
+    const int* positions;
+    const int* tok_entry;
+    const int* entry_q_start;
+    const int* entry_q_len;
+    const int* entry_pos0;
+    float* x;                                   // residual stream [n_tokens, hidden]
+    uint8_t* arena;                             // scratch of infero_block_arena_bytes
+    long long arena_bytes;
+    int* counters;                              // zeroed ints for the decode kernel
+    int n_counters;
+    cudaStream_t stream;
+};
+
+// A layer's pending output: the next norm adds it to x.
+struct InferoDelta {
+    const void* data;           // null: nothing pending
+    int dtype;                  // F32 (partial sums) or BF16 (a finished product)
+    int splits;
+    long long split_stride;
+    const void* bias;           // added with the sum (partial sums only), or null
+    int bias_dtype;
+};
+
+static long long align_up(long long v) { return (v + 255) / 256 * 256; }
+
+struct ArenaPlan {
+    long long delta[2], h, qkv, q, attn, scratch, o_delta, act, gate_up, total;
+};
+
+// Room for the product of T rows with a [N, K] matrix, which comes as partial sums (few rows) or finished.
+static long long product_bytes(int T, int N, int K, int sm_count) {
+    if (T > 256) return align_up((long long)T * N * 2);
+    int splits = 1, per = 1;
+    long long ws = 0;
+    infero_gemm_tc_plan(T, N, K, sm_count, &splits, &per, &ws);
+    return align_up((long long)std::max(1, splits) * T * N * 4);
+}
+
+static ArenaPlan plan_arena(const InferoBlock& b, int T, int sm_count) {
+    ArenaPlan p;
+    const int da = b.n_heads * b.head_dim, nqkv = (b.n_heads + 2 * b.n_kv) * b.head_dim;
+    long long off = 0;
+    auto take = [&](long long bytes) { long long at = off; off += align_up(bytes); return at; };
+    p.delta[0] = take(product_bytes(T, b.hidden, b.intermediate, sm_count));
+    p.delta[1] = take(product_bytes(T, b.hidden, b.intermediate, sm_count));
+    p.h = take((long long)T * b.hidden * 2);
+    p.qkv = take(product_bytes(T, nqkv, b.hidden, sm_count));
+    p.q = take((long long)T * da * 2);
+    p.attn = take((long long)T * da * 2);
+    // the decode kernel's splits: tokens x splits stays below about two CTAs per SM (or one split each)
+    p.scratch = take(infero_attn_decode_scratch(std::max(T, 2 * 148), b.n_heads, b.head_dim, 1));
+    p.o_delta = take(product_bytes(T, b.hidden, da, sm_count));
+    p.act = take((long long)T * b.intermediate * 2);
+    p.gate_up = take(T <= 256 ? product_bytes(T, 2 * b.intermediate, b.hidden, sm_count) : 0);
+    p.total = off;
+    return p;
+}
+
+// The most any step of up to max_tokens tokens needs (the need does not grow evenly with the tokens:
+// few rows come as partial sums).
+long long infero_block_arena_bytes(const InferoBlock* b, int max_tokens, int sm_count) {
+    long long most = 0;
+    const int probes[] = {1, 16, 32, 64, 128, 256, 257, max_tokens};
+    for (int t : probes)
+        if (t <= max_tokens || t == 1) most = std::max(most, plan_arena(*b, std::min(t, std::max(1, max_tokens)), sm_count).total);
+    return most;
+}
+
+// Can this block run here at all?  (Shapes the tensor-core kernels take, head sizes the TMA-fed
+// attention kernels take.)
+int infero_block_supported(const InferoBlock* b) {
+    const int da = b->n_heads * b->head_dim;
+    auto ok_k = [](int K) { return K >= 8 && K % 8 == 0; };
+    return (b->head_dim == 64 || b->head_dim == 128) && b->page_size % 16 == 0 && b->n_kv > 0 &&
+           b->n_heads % b->n_kv == 0 && ok_k(b->hidden) && ok_k(da) && ok_k(b->intermediate) &&
+           b->rotary_dim % 2 == 0 && b->rotary_dim <= b->head_dim;
+}
+
+// out = a[T, K] * w[N, K]^T for the caller's next kernel: partial sums for few rows, a finished bf16
+// product (bias added) for many.
+static int product(const InferoStep& s, const void* a, int K, const void* w, int N, const void* bias, int bias_dtype,
+                   void* dst, InferoDelta* out) {
+    const int T = s.n_tokens;
+    if (T <= 256) {
+        int splits = 1, per = 1;
+        long long ws = 0;
+        infero_gemm_tc_plan(T, N, K, s.sm_count, &splits, &per, &ws);
+        int rc;
+        if (splits >= 2 && splits <= 8 && infero_gemm_cluster_enabled()) {
+            rc = infero_gemm_tc_summed(a, w, (float*)dst, T, N, K, K, splits, per, s.stream);
+            splits = 1;
+        } else {
+            rc = infero_gemm_tc_partials(a, w, (float*)dst, T, N, K, K, splits, per, s.stream);
+        }
+        if (rc) return rc;
+        *out = InferoDelta{dst, F32, splits, (long long)T * N, bias, bias_dtype};
+        return 0;
+    }
+    if (int rc = infero_gemm_tc(a, w, bias, bias_dtype, dst, BF16, T, N, K, K, N, nullptr, 0, s.sm_count, 0, s.stream))
+        return rc;
+    *out = InferoDelta{dst, BF16, 1, 0, nullptr, F32};
+    return 0;
+}
+
+static void plan_decode(int n_tok, int n_kv, int group, int max_visible, int* chunk, int* splits) {
+    static int min_chunk = -1;
+    if (min_chunk < 0) {
+        const char* e = getenv("INFERO_DECODE_MIN_CHUNK");
+        min_chunk = e && atoi(e) > 0 ? atoi(e) : 256;
+    }
+    const int target = 2 * 148, max_splits = 256;
+    const int per_split = std::max(1, n_tok * n_kv * ((group + 15) / 16));
+    const int want = std::max(1, target / per_split);
+    max_visible = std::max(16, max_visible);
+    int c = (max_visible + want - 1) / want;
+    c = std::max(min_chunk, (c + 15) / 16 * 16);
+    int sp = (max_visible + c - 1) / c;
+    if (sp > max_splits) {
+        c = ((max_visible + max_splits - 1) / max_splits + 15) / 16 * 16;
+        sp = (max_visible + c - 1) / c;
+    }
+    *chunk = c;
+    *splits = sp;
+}
+
+// x += pending; the block; leaves its own feed-forward output pending in *delta.  layer_parity picks
+// which of the arena's two output areas this layer writes (the other one still holds its input).
+int infero_block_forward(const InferoBlock* b, const InferoStep* s, const int* block_table, int max_blocks,
+                         int layer_parity, InferoDelta* delta) {
+    const int T = s->n_tokens;
+    if (T == 0) return 0;
+    const ArenaPlan p = plan_arena(*b, T, s->sm_count);
+    if (p.total > s->arena_bytes) {
+        infero_set_error("block_forward: %lld bytes of scratch needed for %d tokens, %lld given", p.total, T, s->arena_bytes);
+        return 1;
+    }
+    uint8_t* A = s->arena;
+    const int H = b->n_heads, Hkv = b->n_kv, D = b->head_dim, d = b->hidden, ff = b->intermediate;
+    const int da = H * D, nqkv = (H + 2 * Hkv) * D;
+    void* h = A + p.h;
+    // ---- mixer ------------------------------------------------------------------------------------
+    if (int rc = infero_add_rmsnorm(s->x, delta->data, delta->data ? delta->dtype : F32, delta->data ? delta->splits : 1,
+                                    delta->data ? delta->split_stride : 0, delta->data ? delta->bias : nullptr,
+                                    delta->bias_dtype, b->w_norm_mixer, b->norm_dtype, b->eps_mixer, h, BF16, nullptr, T, d,
+                                    s->stream))
+        return rc;
+    InferoDelta qkv;
+    if (int rc = product(*s, h, d, b->w_qkv, nqkv, b->b_qkv, b->qkv_bias_dtype, A + p.qkv, &qkv)) return rc;
+    const void* q;
+    int q_stride;
+    if (qkv.dtype == F32) {
+        q = A + p.q;
+        q_stride = da;
+        if (int rc = infero_rope_cache_partials((const float*)qkv.data, qkv.splits, qkv.split_stride, qkv.bias, qkv.bias_dtype,
+                                                A + p.q, da, BF16, s->positions, s->tok_entry, block_table, max_blocks,
+                                                b->inv_freq, b->rotary_dim, b->k_cache, b->v_cache, b->page_size, T, H, Hkv,
+                                                D, b->write_cache, s->stream))
+            return rc;
+    } else {
+        q = qkv.data;
+        q_stride = nqkv;
+        if (int rc = infero_rope_cache(A + p.qkv, BF16, nqkv, s->positions, s->tok_entry, block_table, max_blocks,
+                                       b->inv_freq, b->rotary_dim, b->k_cache, b->v_cache, b->page_size, T, H, Hkv, D,
+                                       b->write_cache, s->stream))
+            return rc;
+    }
+    void* attn = A + p.attn;
+    if (s->n_decode > 0) {
+        int vis = s->decode_visible;
+        if (b->window > 0) vis = std::min(vis, b->window + 15);
+        int chunk, splits;
+        plan_decode(s->n_decode, Hkv, H / Hkv, vis, &chunk, &splits);
+        if (infero_attn_decode_scratch(s->n_decode, H, D, splits) > p.o_delta - p.scratch) {
+            infero_set_error("block_forward: %d decode tokens in %d splits need more scratch than was set aside", s->n_decode, splits);
+            return 1;
+        }
+        if (int rc = infero_attn_decode_tma(q, q_stride, attn, da, b->k_cache, b->v_cache, b->num_pages, block_table,
+                                            max_blocks, s->tok_entry, s->positions, 0, s->n_decode, H, Hkv, D,
+                                            b->page_size, b->window, b->scale, chunk, splits, A + p.scratch, s->counters,
+                                            s->n_counters, s->stream))
+            return rc;
+    }
+    if (s->n_decode < s->n_entries) {
+        if (int rc = infero_attn_prefill_tc(q, q_stride, T, attn, da, b->k_cache, b->v_cache, b->num_pages, block_table,
+                                            max_blocks, s->entry_q_start, s->entry_q_len, s->entry_pos0, s->n_entries,
+                                            s->n_decode, s->prefill_tiles, H, Hkv, D, b->page_size, b->window, b->scale,
+                                            s->stream))
+            return rc;
+    }
+    InferoDelta o;
+    if (int rc = product(*s, attn, da, b->w_o, d, b->b_o, b->o_bias_dtype, A + p.o_delta, &o)) return rc;
+    // ---- feed-forward -----------------------------------------------------------------------------
+    if (int rc = infero_add_rmsnorm(s->x, o.data, o.dtype, o.splits, o.split_stride, o.bias, o.bias_dtype, b->w_norm_ffn,
+                                    b->norm_dtype, b->eps_ffn, h, BF16, nullptr, T, d, s->stream))
+        return rc;
+    void* act = A + p.act;
+    int rc = infero_gemm_tc_swiglu(h, b->w_gate_up, act, T, 2 * ff, d, d, ff, s->sm_count, s->stream);
+    if (rc == 2) {
+        // few rows and K cut into splits: the activation is not linear, so the product comes as
+        // partial sums and the SwiGLU kernel adds them up
+        InferoDelta gu;
+        if (int rc2 = product(*s, h, d, b->w_gate_up, 2 * ff, nullptr, F32, A + p.gate_up, &gu)) return rc2;
+        rc = infero_swiglu(gu.data, gu.splits, gu.split_stride, act, F32, 1, T, ff, s->stream);
+    }
+    if (rc) return rc;
+    return product(*s, act, ff, b->w_down, d, nullptr, F32, A + p.delta[layer_parity & 1], delta);
+}
+
+}  // extern "C"

@@ -13,6 +13,8 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
+import ctypes
+
 import numpy as np
 import torch
 
@@ -67,6 +69,10 @@ class StepContext:
         self.kv_bound: Optional[int] = None     # plan decode attention for this many keys (captured steps)
         self.device_tokens: torch.Tensor = runner.device_tokens
         self._empty_f32 = None
+        # the native block launcher's view of the step (made at the first layer that uses it)
+        self._native_step = None
+        self.native_parity = 0
+        self.native_arena: Optional[torch.Tensor] = None
 
     def kv_cache(self, slot: int):
         return self._runner.storage.layer_kv(slot)
@@ -77,6 +83,33 @@ class StepContext:
 
     def block_table(self, group: int) -> torch.Tensor:
         return self._tables[group]
+
+    def native_step(self, x: torch.Tensor, block_desc):
+        """The step as ``infero_block_forward`` takes it (see parts/native_block.py); None when this
+        step cannot go that way."""
+        from ..kernels import attention as A
+        from ..kernels import tc_gemm
+        from ..parts import native_block as NB
+        r = self._runner
+        arena = r.native_arena(block_desc)
+        if arena is None or self.h_q_len is None:
+            return None
+        st = self._native_step
+        if st is None:
+            n_dec, vis_now, tiles_128, _ = A._batch_shape(self)
+            vis = vis_now if self.kv_bound is None else int(self.kv_bound)
+            counters = A._arrival_counters(self.device)
+            ptr = lambda t: t.data_ptr()                       # noqa: E731
+            st = NB._Step(self.n_tokens, self.n_entries, n_dec, vis, tiles_128, tc_gemm.sm_count(self.device),
+                          ptr(self.positions), ptr(self.tok_entry), ptr(self.entry_q_start), ptr(self.entry_q_len),
+                          ptr(self.entry_pos0), ptr(x), ptr(arena), arena.numel(), ptr(counters), A.N_COUNTERS,
+                          K._stream().value)
+            self._native_step = st
+            self._native_keep = (x, counters)
+        elif st.arena != arena.data_ptr():
+            st.arena, st.arena_bytes = arena.data_ptr(), arena.numel()
+        self.native_arena = arena
+        return st
 
     def zero_inv_freq(self, device) -> torch.Tensor:
         if self._empty_f32 is None:
@@ -110,6 +143,9 @@ class ModelRunner:
         # first time it is seen, captured the second time and replayed from then on (the
         # reference does the same per (pool, tokens, kv bucket), crates/model/src/lib.rs:3887-3981)
         self._graphs: Dict[tuple, "_DecodeGraph"] = {}
+        self._arena: Optional[torch.Tensor] = None         # scratch of the native block launcher
+        self._old_arenas: List[torch.Tensor] = []
+        self._arena_need: Dict[tuple, int] = {}
         self._graph_seen: Dict[tuple, int] = {}
         self.graph_replays = 0
         self.graph_captures = 0
@@ -200,6 +236,26 @@ class ModelRunner:
         self.steps_run += 1
         self.tokens_run += n_tokens
         return logits
+
+    # ---- scratch of the native block launcher -----------------------------------------------------
+    def native_arena(self, block_desc) -> Optional[torch.Tensor]:
+        """Device scratch large enough for any step of this runner through the given block
+        (``infero_block_arena_bytes``).  It only ever grows; captured graphs keep the arenas they
+        were captured with alive."""
+        from ..kernels import tc_gemm
+        from ..parts import native_block as NB
+        key = (ctypes.addressof(block_desc), tc_gemm._plan_epoch[0])
+        need = self._arena_need.get(key)
+        if need is None:
+            # (a captured step may be padded past max_batch_tokens, up to the largest captured size)
+            need = int(NB._lib().infero_block_arena_bytes(ctypes.byref(block_desc), max(int(self.cfg.max_batch_tokens), self.MAX_GRAPH_ENTRIES),
+                                                          tc_gemm.sm_count(self.device)))
+            self._arena_need[key] = need
+        if self._arena is None or self._arena.numel() < need:
+            if self._arena is not None:
+                self._old_arenas.append(self._arena)
+            self._arena = torch.empty(need, dtype=torch.uint8, device=self.device)
+        return self._arena
 
     # ---- device inputs of a step ---------------------------------------------------------------
     def _layout_args(self, entries: Sequence[StepEntry], rcs: Sequence[RequestCache], pad: int = 0):

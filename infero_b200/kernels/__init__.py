@@ -151,6 +151,8 @@ def add_rmsnorm(x: torch.Tensor, delta, weight: torch.Tensor, eps: float,
     """x += delta (if given; 32-bit), out = rmsnorm(x) * weight.  ``delta`` is a tensor or
     ``Partials``.  With ``rows`` only those rows are normalised (out has len(rows) rows) and x
     is left as it is."""
+    if hasattr(delta, "as_partials"):          # left by the native block launcher in its scratch arena
+        delta = delta.as_partials()
     d = x.shape[1]
     assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous()
     assert weight.numel() == d and out.shape[1] == d

@@ -25,6 +25,7 @@ class PreNormBlock(Part):
         self.mixer = part_class("mixer", spec.mixer.kind)(spec.mixer, p)
         self.ffn_norm = part_class("norm", spec.ffn_norm.kind)(spec.ffn_norm, f"{p}.post_attention_layernorm.weight")
         self.ffn = part_class("feed_forward", spec.ffn.kind)(spec.ffn, p)
+        self._native = None                  # the native launcher of this block, made at first use
 
     def parts(self):
         return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]
@@ -40,6 +41,18 @@ class PreNormBlock(Part):
             part.bind(tensors)
 
     def forward(self, ctx, x, delta, slot):
+        native = self._native
+        if native is None:
+            from .native_block import NativeBlock
+            native = self._native = NativeBlock(self)
+        if native.wants(ctx):
+            # the package's own parts in a bf16 step: the whole layer in one native call (same kernels,
+            # same arguments, same order as below)
+            out = native.run(ctx, x, delta, slot)
+            if out is not None:
+                return out
+        if hasattr(delta, "as_partials"):
+            delta = delta.as_partials()
         h = self.mixer_norm.forward(ctx, x, delta)
         a = self.mixer.forward(ctx, h, slot)
         h = self.ffn_norm.forward(ctx, x, a)

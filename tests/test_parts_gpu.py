@@ -242,6 +242,40 @@ def _layer_reading_cache(x, x_keys, w, cfg, i, pos):
                             w[p + "mlp.down_proj.weight"])
 
 
+
+@pytest.mark.parametrize("window", [None, 24])
+def test_native_block_launcher_changes_nothing(window):
+    """The block launched by one native call per layer gives, bit for bit, what its parts give when
+    they launch their kernels one by one: prompts in portions, mixed batches, single tokens."""
+    from infero_b200.engine import StepEntry
+    from infero_b200.parts import native_block as NB
+    spec = _spec(layers=3, window=window, H=4, Hkv=2, D=64, d=128, ff=320, V=400)
+    toks = {r: [int(t) for t in torch.randint(0, 400, (n,), generator=torch.Generator().manual_seed(s))]
+            for r, n, s in (("a", 300, 1), ("b", 41, 2), ("c", 7, 3))}
+
+    def run(native):
+        NB.set_enabled(native)
+        try:
+            model, runner, _ = _build(spec, torch.bfloat16, pages=40)
+            before = NB.CALLS[0]
+            for r in toks:
+                runner.open(r)
+            out = [runner.step([StepEntry("a", toks["a"][:280], [279])]),                       # many rows
+                   runner.step([StepEntry("b", toks["b"][:40], [5, 39]), StepEntry("a", toks["a"][280:290], [9])]),
+                   runner.step([StepEntry("a", toks["a"][290:291], [0]), StepEntry("b", toks["b"][40:], [0]),
+                                StepEntry("c", toks["c"], [6])]),                                # decodes beside a prompt
+                   runner.step([StepEntry("a", toks["a"][291:292], [0])])]
+            return [o.float().cpu() for o in out], NB.CALLS[0] - before
+        finally:
+            NB.set_enabled(True)
+
+    plain, n_plain = run(False)
+    native, n_native = run(True)
+    assert n_plain == 0 and n_native == 4 * 3, "every layer of every step should have gone the native way"
+    for a, b in zip(plain, native):
+        assert torch.equal(a, b)
+
+
 # ---- a toy mixer with state of its own, from outside the package ------------------------------------
 def _register_toy():
     """A mixer that keeps a running, decaying sum of its projected inputs per request:
