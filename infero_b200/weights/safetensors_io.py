@@ -5,13 +5,14 @@ File = 8-byte little-endian header length, a JSON header mapping each tensor nam
 header), then the raw little-endian payload.  The checks mirror the reference's
 (crates/safetensors/src/lib.rs:390-436): header inside the file, offsets inside the
 payload, byte count == prod(shape) * element size; a name present in two shards is an
-error (:477-514).
+error (:477-514).  Reading is native code (``csrc/host_safetensors.cpp``); writing (the
+random-weights mode) is Python.
 """
 from __future__ import annotations
 
+import ctypes
 import glob
 import json
-import mmap
 import os
 import struct
 import warnings
@@ -45,61 +46,85 @@ class TensorEntry:
     file: "SafetensorsFile"
 
 
+def _lib():
+    from ..kernels import lib
+    L = lib()
+    if not getattr(L, "_st_api_ready", False):
+        L.infero_st_open.restype = ctypes.c_void_p
+        L.infero_st_open.argtypes = [ctypes.c_char_p]
+        for fn in ("infero_st_error", "infero_st_name"):
+            getattr(L, fn).restype = ctypes.c_char_p
+        for fn in ("infero_st_nbytes", "infero_st_offset"):
+            getattr(L, fn).restype = ctypes.c_longlong
+        L.infero_st_data.restype = ctypes.c_void_p
+        for fn in ("infero_st_error", "infero_st_count", "infero_st_close"):
+            getattr(L, fn).argtypes = [ctypes.c_void_p]
+        for fn in ("infero_st_name", "infero_st_dtype", "infero_st_rank", "infero_st_nbytes", "infero_st_offset",
+                   "infero_st_data"):
+            getattr(L, fn).argtypes = [ctypes.c_void_p, ctypes.c_int]
+        L.infero_st_shape.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_longlong)]
+        L._st_api_ready = True
+    return L
+
+
+_DTYPE_ORDER = ("F32", "F16", "BF16", "I32", "I64", "U8")       # the reader's dtype numbers
+
+
 class SafetensorsFile:
+    """One file, mapped and checked by the native reader (``csrc/host_safetensors.cpp``, in the
+    engine's shared library, no CUDA in it); tensors come back as views of the mapping."""
+
     def __init__(self, path: str):
         self.path = path
-        size = os.path.getsize(path)
-        if size < 8:
-            raise SafetensorsError(f"{path}: too short to hold a safetensors header")
-        self._fh = open(path, "rb")
-        (hlen,) = struct.unpack("<Q", self._fh.read(8))
-        if hlen <= 0 or 8 + hlen > size:
-            raise SafetensorsError(f"{path}: header length {hlen} does not fit the file ({size} bytes)")
-        try:
-            header = json.loads(self._fh.read(hlen).decode("utf-8"))
-        except Exception as e:
-            raise SafetensorsError(f"{path}: header is not valid JSON: {e}") from None
-        self.metadata = header.pop("__metadata__", {}) or {}
-        self._mm = mmap.mmap(self._fh.fileno(), 0, access=mmap.ACCESS_READ) if size else None
-        payload = size - 8 - hlen
+        self._L = _lib()
+        self._h = ctypes.c_void_p(self._L.infero_st_open(os.fsencode(path)))
+        if not self._h:
+            raise MemoryError("safetensors reader")
+        err = self._L.infero_st_error(self._h).decode("utf-8", "replace")
+        if err:
+            self._L.infero_st_close(self._h)
+            self._h = None
+            raise SafetensorsError(err)
+        self.metadata: Dict[str, str] = {}
         self.entries: Dict[str, TensorEntry] = {}
-        for name, info in header.items():
-            dt = info.get("dtype")
-            if dt not in _DTYPES:
-                raise SafetensorsError(f"{path}: tensor '{name}' has unsupported dtype {dt!r}")
-            tdtype, esize = _DTYPES[dt]
-            shape = tuple(int(s) for s in info["shape"])
-            b, e = (int(x) for x in info["data_offsets"])
-            n = 1
-            for s in shape:
-                n *= s
-            if b < 0 or e < b or e > payload:
-                raise SafetensorsError(f"{path}: tensor '{name}' offsets [{b}, {e}) lie outside the payload")
-            if e - b != n * esize:
-                raise SafetensorsError(
-                    f"{path}: tensor '{name}' holds {e - b} bytes but shape {list(shape)} of {dt} needs {n * esize}")
-            self.entries[name] = TensorEntry(name, tdtype, shape, 8 + hlen + b, e - b, self)
+        self._index: Dict[str, int] = {}
+        for i in range(self._L.infero_st_count(self._h)):
+            name = self._L.infero_st_name(self._h, i).decode("utf-8")
+            rank = self._L.infero_st_rank(self._h, i)
+            dims = (ctypes.c_longlong * max(1, rank))()
+            self._L.infero_st_shape(self._h, i, dims)
+            tdtype, _ = _DTYPES[_DTYPE_ORDER[self._L.infero_st_dtype(self._h, i)]]
+            self.entries[name] = TensorEntry(name, tdtype, tuple(int(dims[k]) for k in range(rank)),
+                                             int(self._L.infero_st_offset(self._h, i)),
+                                             int(self._L.infero_st_nbytes(self._h, i)), self)
+            self._index[name] = i
 
     def tensor(self, name: str) -> torch.Tensor:
-        """A CPU tensor over the mapped bytes (read-only view; copy before writing)."""
+        """A CPU tensor over the mapped bytes (read-only view; copy before writing).  The mapping
+        stays for the life of the process once a tensor has been handed out."""
         ent = self.entries[name]
         n = 1
         for s in ent.shape:
             n *= s
         if n == 0:
             return torch.empty(ent.shape, dtype=ent.dtype)
+        ptr = self._L.infero_st_data(self._h, self._index[name])
+        buf = (ctypes.c_char * ent.nbytes).from_address(ptr)
         with warnings.catch_warnings():
             warnings.simplefilter("ignore", UserWarning)     # the mapping is read-only by design
-            t = torch.frombuffer(self._mm, dtype=ent.dtype, count=n, offset=ent.begin)
+            t = torch.frombuffer(buf, dtype=ent.dtype, count=n)
         return t.view(ent.shape)
 
     def close(self):
+        h, self._h = self._h, None
+        if h:
+            self._L.infero_st_close(h)
+
+    def __del__(self):
         try:
-            if self._mm is not None:
-                self._mm.close()
-        except BufferError:
-            pass  # tensors still alias the mapping; the OS unmaps at exit
-        self._fh.close()
+            self.close()
+        except Exception:          # noqa: BLE001  (interpreter shutdown)
+            pass
 
 
 class SafetensorsDir:
@@ -154,5 +179,5 @@ def write_safetensors(path: str, decls: List[Tuple[str, torch.dtype, Tuple[int, 
                     f"write: tensor '{name}' is {t.dtype}{list(t.shape)}, declared {dtype}{list(shape)}")
             t = t.contiguous().cpu()
             if t.numel():
-                f.write(t.view(torch.uint8).numpy().tobytes() if t.dtype != torch.uint8 else t.numpy().tobytes())
+                f.write(t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.dtype != torch.uint8 else t.numpy().tobytes())
     os.replace(tmp, path)

@@ -126,3 +126,71 @@ def test_duplicate_name_across_shards(tmp_path):
     with pytest.raises(SafetensorsError) as e:
         SafetensorsDir(str(tmp_path))
     assert "both" in str(e.value)
+
+
+def _raw_file(path, header: bytes, payload: bytes = b"", hlen=None):
+    import struct
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(header) if hlen is None else hlen))
+        f.write(header)
+        f.write(payload)
+
+
+@pytest.mark.parametrize("case,needle", [
+    ("short", "too short"),
+    ("header_past_end", "does not fit"),
+    ("not_json", "not valid JSON"),
+    ("unknown_dtype", "unsupported dtype"),
+    ("offsets_outside", "outside the payload"),
+    ("size_mismatch", "needs"),
+    ("missing_key", "lacks"),
+])
+def test_damaged_containers_are_refused(tmp_path, case, needle):
+    """The native reader's checks, one damaged file each (crates/safetensors/src/lib.rs:390-436)."""
+    from infero_b200.weights.safetensors_io import SafetensorsFile
+    p = str(tmp_path / "m.safetensors")
+    good = b'{"x":{"dtype":"F32","shape":[2,3],"data_offsets":[0,24]}}'
+    if case == "short":
+        open(p, "wb").write(b"\x01\x02")
+    elif case == "header_past_end":
+        _raw_file(p, good, b"\0" * 24, hlen=10_000)
+    elif case == "not_json":
+        _raw_file(p, b'{"x":{"dtype":"F32","shape":[2,3],"data_offsets":[0,24]', b"\0" * 24)
+    elif case == "unknown_dtype":
+        _raw_file(p, good.replace(b"F32", b"F8X"), b"\0" * 24)
+    elif case == "offsets_outside":
+        _raw_file(p, good, b"\0" * 20)
+    elif case == "size_mismatch":
+        _raw_file(p, good.replace(b"[2,3]", b"[2,4]"), b"\0" * 24)
+    elif case == "missing_key":
+        _raw_file(p, b'{"x":{"dtype":"F32","shape":[2,3]}}', b"\0" * 24)
+    with pytest.raises(SafetensorsError) as e:
+        SafetensorsFile(p)
+    assert needle in str(e.value), str(e.value)
+
+
+def test_native_reader_reads_what_the_writer_wrote(tmp_path):
+    """Names with escapes and non-ASCII letters, metadata, an empty tensor, every dtype; values
+    come back bit for bit as views of the mapping."""
+    from infero_b200.weights.safetensors_io import SafetensorsFile
+    g = torch.Generator().manual_seed(0)
+    tensors = {
+        "plain.weight": torch.randn(3, 5, generator=g),
+        'quote"and\\slash': torch.randn(4, generator=g).to(torch.bfloat16),
+        "größe.层": torch.randint(-5, 5, (2, 2), generator=g, dtype=torch.int32),
+        "half": torch.randn(7, generator=g).to(torch.float16),
+        "long": torch.arange(6, dtype=torch.int64).view(2, 3),
+        "bytes": torch.arange(9, dtype=torch.uint8),
+        "empty": torch.zeros((0, 4)),
+        "scalar": torch.tensor(3.5),
+    }
+    p = str(tmp_path / "m.safetensors")
+    write_safetensors(p, [(n, t.dtype, tuple(t.shape)) for n, t in tensors.items()], lambda n: tensors[n],
+                      metadata={"format": "pt", "note": "x\ny"})
+    f = SafetensorsFile(p)
+    assert set(f.entries) == set(tensors)
+    for n, t in tensors.items():
+        got = f.tensor(n)
+        assert got.dtype == t.dtype and tuple(got.shape) == tuple(t.shape)
+        assert torch.equal(got, t)
+    f.close()
