@@ -128,8 +128,12 @@ static ArenaPlan plan_arena(const InferoBlock& b, int T, int sm_count) {
     const int da = b.n_heads * b.head_dim, nqkv = (b.n_heads + 2 * b.n_kv) * b.head_dim;
     long long off = 0;
     auto take = [&](long long bytes) { long long at = off; off += align_up(bytes); return at; };
-    p.delta[0] = take(product_bytes(T, b.hidden, b.intermediate, sm_count));
-    p.delta[1] = take(product_bytes(T, b.hidden, b.intermediate, sm_count));
+    // The two output areas lie at places that depend on the step and the residual width only, not on the
+    // block (up to 16 splits of up to 256 rows, or a finished product): the layer that reads one as its
+    // input may be built to other sizes and must not have its own areas overlap it.
+    const long long delta_bytes = std::max(16LL * std::min(T, 256) * b.hidden * 4, (long long)T * b.hidden * 2);
+    p.delta[0] = take(delta_bytes);
+    p.delta[1] = take(delta_bytes);
     p.h = take((long long)T * b.hidden * 2);
     p.qkv = take(product_bytes(T, nqkv, b.hidden, sm_count));
     p.q = take((long long)T * da * 2);
