@@ -182,12 +182,12 @@ class ModelRunner:
             rc = self.manager.get(e.rid)
             if rc.length + n > self.cfg.ctx:
                 raise StepError(f"request {e.rid!r} would reach {rc.length + n} tokens, context is {self.cfg.ctx}")
-            for w in e.want:
-                if not (0 <= int(w) < n):
-                    raise StepError(f"request {e.rid!r}: wanted place {w} outside its {n} tokens")
-            for tkn in e.tokens:
-                if not (0 <= int(tkn) < vocab) and not (n == 1 and int(tkn) == FROM_DEVICE):
-                    raise StepError(f"request {e.rid!r}: token id {tkn} outside the vocabulary of {vocab}")
+            if len(e.want) and not (0 <= min(e.want) and max(e.want) < n):
+                raise StepError(f"request {e.rid!r}: wanted places {list(e.want)} outside its {n} tokens")
+            lo, hi = (e.tokens[0], e.tokens[0]) if n == 1 else (min(e.tokens), max(e.tokens))
+            if not (0 <= lo and hi < vocab) and not (n == 1 and int(lo) == FROM_DEVICE):
+                bad = next(t for t in e.tokens if not 0 <= int(t) < vocab)
+                raise StepError(f"request {e.rid!r}: token id {bad} outside the vocabulary of {vocab}")
             total += n
             rows += len(e.want)
             rcs.append(rc)
