@@ -10,10 +10,12 @@
 // row, as in the reference (crates/server/src/scheduler.rs:1279-1299), so a host sampler
 // fed the same u picks the same token.
 //
-// One block per row.  The selection is a 4-pass radix select over order-preserving 32-bit
-// keys with integer histograms, ties at the threshold taken in ascending index, so the
-// result is a deterministic function of the row.  At most SAMPLE_MAX_K candidates survive
-// the top-k stage; a larger (or disabled) top_k is clamped to that.
+// The selection is a 4-pass radix select over order-preserving 32-bit keys with integer
+// histograms, ties at the threshold taken in ascending index, so the result is a deterministic
+// function of the row.  At most SAMPLE_MAX_K candidates survive the top-k stage; a larger (or
+// disabled) top_k is clamped to that.  Small vocabularies: one block per row.  Large ones (a
+// block alone takes hundreds of microseconds over 150,000 logits): blocks over chunks of 8,192
+// logits each keep their chunk's k largest, then one block per row selects among those.
 #include "common.cuh"
 #include <math_constants.h>
 
@@ -136,7 +138,7 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* total, int* warp
     if (lane == 31) warp_sums[warp] = inc;
     __syncthreads();
     if (warp == 0) {
-        int w = warp_sums[lane];
+        int w = lane < (int)((blockDim.x + 31) >> 5) ? warp_sums[lane] : 0;
         int winc = w;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -151,55 +153,75 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* total, int* warp
     return warp_sums[warp] + inc - v;
 }
 
-__global__ void __launch_bounds__(SAMPLE_THREADS)
-sample_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
-              const int* __restrict__ top_k, const float* __restrict__ top_p,
-              const double* __restrict__ draw, int* __restrict__ out) {
-    __shared__ int hist[256];
-    __shared__ int scan_ws[33];
-    __shared__ unsigned long long cand[SAMPLE_MAX_K];   // (key << 32) | ~index : descending sort = value desc, index asc
-    __shared__ uint32_t s_prefix;
-    __shared__ int s_need;
-    const int row = blockIdx.x;
-    const float* z = logits + (size_t)row * vocab;
-    int k = top_k[row];
-    if (k <= 0 || k > SAMPLE_MAX_K) k = SAMPLE_MAX_K;
-    if (k > vocab) k = vocab;
+// Where a selection reads its (key, token) pairs: a stretch of a row of logits, or the survivors
+// that the chunks of a row left in scratch (SAMPLE_MAX_K slots per chunk, each chunk's in token order).
+struct FromLogits {
+    const float* z;
+    int first;                                           // token of element 0
+    __device__ __forceinline__ uint32_t key(int i) const { return order_key(z[i]); }
+    __device__ __forceinline__ uint32_t token(int i) const { return (uint32_t)(first + i); }
+};
+struct FromChunks {
+    const unsigned long long* list;                      // [chunks][SAMPLE_MAX_K]: (key << 32) | ~token
+    int per_chunk;                                       // survivors of every chunk but perhaps the last
+    __device__ __forceinline__ unsigned long long at(int i) const {
+        return list[(size_t)(i / per_chunk) * SAMPLE_MAX_K + (i % per_chunk)];
+    }
+    __device__ __forceinline__ uint32_t key(int i) const { return (uint32_t)(at(i) >> 32); }
+    __device__ __forceinline__ uint32_t token(int i) const { return ~(uint32_t)(at(i) & 0xffffffffull); }
+};
 
-    // ---- radix select: the key of the k-th largest element ----------------------------------
-    if (threadIdx.x == 0) { s_prefix = 0u; s_need = k; }
+constexpr int HIST_COPIES = 8;                           // warps spread over copies: fewer colliding atomics
+
+// The k largest of src's n elements (ties at the threshold: lowest tokens first), written to cand[]
+// in the order of the source (ascending token) as (key << 32) | ~token.  Returns how many (k, or n).
+// A 4-pass radix select over order-preserving 32-bit keys with integer histograms: a deterministic
+// function of the elements.  Every thread of the block calls it.
+template <class Src>
+__device__ int select_largest(const Src& src, int n, int k, unsigned long long* cand, int (*hist)[256], int* scan_ws,
+                              uint32_t* s_prefix, int* s_need) {
+    if (k > n) k = n;
+    if (threadIdx.x == 0) { *s_prefix = 0u; *s_need = k; }
     __syncthreads();
+    int* my_hist = hist[(threadIdx.x >> 5) % HIST_COPIES];
     for (int pass = 0; pass < 4; ++pass) {
         const int shift = 24 - 8 * pass;
         const uint32_t mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
-        for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
+        for (int i = threadIdx.x; i < HIST_COPIES * 256; i += blockDim.x) hist[0][i] = 0;
         __syncthreads();
-        const uint32_t prefix = s_prefix;
-        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-            const uint32_t key = order_key(z[i]);
-            if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255], 1);
+        const uint32_t prefix = *s_prefix;
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const uint32_t key = src.key(i);
+            if ((key & mask) == prefix) atomicAdd(&my_hist[(key >> shift) & 255], 1);
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+            int t = 0;
+#pragma unroll
+            for (int c = 0; c < HIST_COPIES; ++c) t += hist[c][i];
+            hist[0][i] = t;
         }
         __syncthreads();
         if (threadIdx.x == 0) {
-            int need = s_need, b = 255;
+            int need = *s_need, b = 255;
             for (; b > 0; --b) {
-                if (hist[b] >= need) break;
-                need -= hist[b];
+                if (hist[0][b] >= need) break;
+                need -= hist[0][b];
             }
-            s_prefix = prefix | ((uint32_t)b << shift);
-            s_need = need;
+            *s_prefix = prefix | ((uint32_t)b << shift);
+            *s_need = need;
         }
         __syncthreads();
     }
-    const uint32_t thr = s_prefix;     // key of the k-th largest
-    const int need_eq = s_need;        // how many elements equal to thr are taken (lowest indices)
+    const uint32_t thr = *s_prefix;    // key of the k-th largest
+    const int need_eq = *s_need;       // how many elements equal to thr are taken (lowest tokens)
 
-    // ---- collect survivors in index order (contiguous range per thread) -----------------------
-    const int per = (vocab + blockDim.x - 1) / blockDim.x;
-    const int lo = threadIdx.x * per, hi = min(vocab, lo + per);
+    // survivors in source order (a contiguous range per thread)
+    const int per = (n + blockDim.x - 1) / blockDim.x;
+    const int lo = min(n, (int)threadIdx.x * per), hi = min(n, lo + per);
     int n_gt = 0, n_eq = 0;
     for (int i = lo; i < hi; ++i) {
-        const uint32_t key = order_key(z[i]);
+        const uint32_t key = src.key(i);
         n_gt += key > thr;
         n_eq += key == thr;
     }
@@ -209,23 +231,84 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
     for (int i = threadIdx.x; i < SAMPLE_MAX_K; i += blockDim.x) cand[i] = 0ull;   // sorts last
     __syncthreads();
     for (int i = lo; i < hi; ++i) {
-        const uint32_t key = order_key(z[i]);
+        const uint32_t key = src.key(i);
+        const unsigned long long e = ((unsigned long long)key << 32) | (uint32_t)(~src.token(i));
         if (key > thr) {
-            cand[off_gt++] = ((unsigned long long)key << 32) | (uint32_t)(~(uint32_t)i);
+            cand[off_gt++] = e;
         } else if (key == thr) {
-            if (off_eq < need_eq) cand[tot_gt + off_eq] = ((unsigned long long)key << 32) | (uint32_t)(~(uint32_t)i);
+            if (off_eq < need_eq) cand[tot_gt + off_eq] = e;
             ++off_eq;
         }
     }
     __syncthreads();
-    const int n_cand = tot_gt + min(need_eq, tot_eq);    // == k
+    return tot_gt + min(need_eq, tot_eq);                // == k
+}
 
-    // ---- bitonic sort, descending, over SAMPLE_MAX_K slots ------------------------------------
-    for (int size = 2; size <= SAMPLE_MAX_K; size <<= 1) {
+__device__ __forceinline__ int effective_k(int k, int vocab) {
+    if (k <= 0 || k > SAMPLE_MAX_K) k = SAMPLE_MAX_K;
+    return k > vocab ? vocab : k;
+}
+
+// Stage 1 for large vocabularies: block (chunk, row) leaves the k largest of its chunk in scratch.
+// The k largest of the row are among them, and the chunks' survivors, chunk after chunk, are in
+// token order, so stage 2 selects from them exactly what it would select from the whole row.
+constexpr int SAMPLE_CHUNK = 8192;
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_chunk_kernel(const float* __restrict__ logits, int vocab, const int* __restrict__ top_k,
+                    unsigned long long* __restrict__ scratch) {
+    __shared__ int hist[HIST_COPIES][256];
+    __shared__ int scan_ws[33];
+    __shared__ unsigned long long cand[SAMPLE_MAX_K];
+    __shared__ uint32_t s_prefix;
+    __shared__ int s_need;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.y, chunk = blockIdx.x;
+    const int lo = chunk * SAMPLE_CHUNK, n = min(SAMPLE_CHUNK, vocab - lo);
+    const int k = effective_k(top_k[row], vocab);
+    const FromLogits src{logits + (size_t)row * vocab + lo, lo};
+    const int n_cand = select_largest(src, n, k, cand, hist, scan_ws, &s_prefix, &s_need);
+    unsigned long long* dst = scratch + ((size_t)row * gridDim.x + chunk) * SAMPLE_MAX_K;
+    for (int i = threadIdx.x; i < n_cand; i += blockDim.x) dst[i] = cand[i];
+}
+
+// The pick.  chunks == 0: the candidates are selected from the row of logits itself (small
+// vocabularies); else from what sample_chunk_kernel left in scratch.
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
+              const int* __restrict__ top_k, const float* __restrict__ top_p,
+              const double* __restrict__ draw, int* __restrict__ out, const unsigned long long* __restrict__ scratch,
+              int chunks) {
+    __shared__ int hist[HIST_COPIES][256];
+    __shared__ int scan_ws[33];
+    __shared__ unsigned long long cand[SAMPLE_MAX_K];   // (key << 32) | ~token : descending sort = value desc, token asc
+    __shared__ uint32_t s_prefix;
+    __shared__ int s_need;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.x;
+    const int k = effective_k(top_k[row], vocab);
+    int n_cand;
+    if (chunks == 0) {
+        const FromLogits src{logits + (size_t)row * vocab, 0};
+        n_cand = select_largest(src, vocab, k, cand, hist, scan_ws, &s_prefix, &s_need);
+    } else {
+        const int last = vocab - (chunks - 1) * SAMPLE_CHUNK;
+        const int per_chunk = min(k, SAMPLE_CHUNK);
+        const FromChunks src{scratch + (size_t)row * chunks * SAMPLE_MAX_K, per_chunk};
+        n_cand = select_largest(src, (chunks - 1) * per_chunk + min(k, last), k, cand, hist, scan_ws, &s_prefix, &s_need);
+    }
+
+    // ---- bitonic sort, descending, over the smallest power of two of slots that holds the candidates
+    // (the slots past them hold 0, which sorts last) ---------------------------------------------------
+    int sort_n = 2;
+    while (sort_n < n_cand) sort_n <<= 1;
+    for (int size = 2; size <= sort_n; size <<= 1) {
         for (int stride = size >> 1; stride > 0; stride >>= 1) {
             const int i = threadIdx.x;
             const int j = i ^ stride;
-            if (i < SAMPLE_MAX_K && j > i) {
+            if (i < sort_n && j > i) {
                 const bool desc = (i & size) == 0;
                 const unsigned long long a = cand[i], b = cand[j];
                 if ((a < b) == desc) { cand[i] = b; cand[j] = a; }
@@ -306,11 +389,29 @@ int infero_argmax(const float* logits, int n_rows, int vocab, int* out, void* sc
     return infero_check_launch("argmax_final");
 }
 
+// Bytes of scratch infero_sample needs (0 for vocabularies small enough for one block per row).
+static int sample_chunks(int vocab) { return vocab > 2 * SAMPLE_CHUNK ? (vocab + SAMPLE_CHUNK - 1) / SAMPLE_CHUNK : 0; }
+long long infero_sample_scratch(int n_rows, int vocab) {
+    return (long long)n_rows * sample_chunks(vocab) * SAMPLE_MAX_K * 8;
+}
+
 int infero_sample(const float* logits, int n_rows, int vocab, const float* temperature, const int* top_k,
-                  const float* top_p, const double* draw, int* out, cudaStream_t stream) {
+                  const float* top_p, const double* draw, int* out, void* scratch, long long scratch_bytes,
+                  cudaStream_t stream) {
     if (n_rows == 0) return 0;
-    INFERO_REQUIRE(vocab > 0, "sample: empty vocabulary");
-    sample_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, vocab, temperature, top_k, top_p, draw, out);
+    INFERO_REQUIRE(vocab > 0 && n_rows <= 65535, "sample: bad sizes rows=%d vocab=%d", n_rows, vocab);
+    const int chunks = sample_chunks(vocab);
+    if (chunks) {
+        INFERO_REQUIRE(scratch && scratch_bytes >= infero_sample_scratch(n_rows, vocab),
+                       "sample: %lld bytes of scratch needed, %lld given", infero_sample_scratch(n_rows, vocab), scratch_bytes);
+        // few blocks: large ones finish sooner; many: small ones, eight to an SM, finish in one round
+        const int chunk_threads = (long long)chunks * n_rows <= 2 * 148 ? SAMPLE_THREADS : 256;
+        launch_pdl(sample_chunk_kernel, dim3(chunks, n_rows), dim3(chunk_threads), 0, stream, logits, vocab, top_k,
+                   (unsigned long long*)scratch);
+        if (infero_check_launch("sample_chunk")) return 1;
+    }
+    launch_pdl(sample_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, stream, logits, vocab, temperature, top_k, top_p, draw,
+               out, (const unsigned long long*)scratch, chunks);
     return infero_check_launch("sample");
 }
 

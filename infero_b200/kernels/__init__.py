@@ -297,8 +297,13 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
     R, V = logits.shape
     assert logits.dtype == torch.float32 and logits.is_contiguous()
     assert temperature.dtype == torch.float32 and top_p.dtype == torch.float32 and draw.dtype == torch.float64
-    _check(lib().infero_sample(_ptr(logits), c_int(R), c_int(V), _ptr(temperature), _ptr(_i32(top_k, "top_k")),
-                               _ptr(top_p), _ptr(draw), _ptr(_i32(out, "out")), _stream()))
+    L = lib()
+    L.infero_sample_scratch.restype = ctypes.c_longlong
+    need = int(L.infero_sample_scratch(c_int(R), c_int(V)))
+    scratch = torch.empty(need // 8, dtype=torch.int64, device=logits.device) if need else None
+    _check(L.infero_sample(_ptr(logits), c_int(R), c_int(V), _ptr(temperature), _ptr(_i32(top_k, "top_k")),
+                           _ptr(top_p), _ptr(draw), _ptr(_i32(out, "out")), _ptr(scratch), ctypes.c_longlong(need),
+                           _stream()))
 
 
 def keep_tokens(greedy: torch.Tensor, sampled: Optional[torch.Tensor], rows_info: torch.Tensor,

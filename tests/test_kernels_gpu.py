@@ -597,11 +597,18 @@ def _host_sample(z, temp, top_k, top_p, u):
     return int(idx[keep - 1])
 
 
-def test_sample_matches_host_statement():
+@pytest.mark.parametrize("V,ties", [(5003, False), (152064, False), (40001, True)])
+def test_sample_matches_host_statement(V, ties):
+    """Small vocabularies take one block per row; large ones go through blocks per chunk of 8,192
+    logits first.  With ties: values from a handful of levels, so that the k-th largest is shared by
+    many tokens in many chunks and the lowest tokens must win."""
     from infero_b200 import kernels as Kn
-    V, R = 5003, 24
+    R = 24
     rng = np.random.default_rng(5)
-    z = torch.from_numpy(rng.normal(size=(R, V)).astype(np.float32) * 3).to(DEV)
+    zn = rng.normal(size=(R, V)).astype(np.float32) * 3
+    if ties:
+        zn = np.round(zn * 2) / 2
+    z = torch.from_numpy(zn).to(DEV)
     temp = torch.tensor([0.7, 1.0, 0.3] * 8, dtype=torch.float32, device=DEV)
     top_k = torch.tensor([20, 50, 5, 1000] * 6, dtype=torch.int32, device=DEV)
     top_p = torch.tensor([0.8, 1.0, 0.5, 0.95, 0.9, 0.3] * 4, dtype=torch.float32, device=DEV)
