@@ -81,23 +81,30 @@ def sample_rows_async(logits: torch.Tensor, samplers: Sequence[RowSampler], hist
     greedy = [s.params.is_greedy() for s in samplers]
     out = torch.empty(3 * R, dtype=torch.int32, device=dev)      # argmax | sampled | final
     K.argmax(logits, out[:R])
-    sampled = None
-    if not all(greedy):
-        temp = np.array([max(s.params.temperature, 0.0) for s in samplers], dtype=np.float32)
-        topk = np.array([s.params.top_k for s in samplers], dtype=np.int32)
-        topp = np.array([s.params.top_p for s in samplers], dtype=np.float32)
-        # a draw is taken for every row, greedy or not, as the reference does (sampling.rs:113-121)
-        draw = np.array([s.next_draw() for s in samplers], dtype=np.float64)
-        sampled = out[R:2 * R]
-        K.sample(logits, torch.from_numpy(temp).to(dev), torch.from_numpy(topk).to(dev),
-                 torch.from_numpy(topp).to(dev), torch.from_numpy(draw).to(dev), sampled)
-    info = np.empty(2 * R, dtype=np.int32)
+    # everything the device needs from the host this step, in one pinned buffer and one copy:
+    # draws (64-bit) | slot per row, use-the-sample flag per row | temperature, top_p, top_k
+    sampling = not all(greedy)
+    n_bytes = 8 * R + 8 * R + (12 * R if sampling else 0)
+    staged = torch.empty(n_bytes, dtype=torch.uint8, pin_memory=(dev.type == "cuda"))
+    h = staged.numpy()
+    info = h[8 * R:16 * R].view(np.int32)
     info[:R] = -1 if slots is None or device_tokens is None else np.asarray(slots, dtype=np.int32)
     info[R:] = [0 if g else 1 for g in greedy]
-    info_pinned = torch.empty(2 * R, dtype=torch.int32, pin_memory=True)
-    info_pinned.numpy()[:] = info
+    if sampling:
+        # a draw is taken for every row, greedy or not, as the reference does (sampling.rs:113-121)
+        h[:8 * R].view(np.float64)[:] = [s.next_draw() for s in samplers]
+        h[16 * R:20 * R].view(np.float32)[:] = [max(s.params.temperature, 0.0) for s in samplers]
+        h[20 * R:24 * R].view(np.float32)[:] = [s.params.top_p for s in samplers]
+        h[24 * R:28 * R].view(np.int32)[:] = [s.params.top_k for s in samplers]
+    on_dev = staged.to(dev, non_blocking=True)
+    sampled = None
+    if sampling:
+        sampled = out[R:2 * R]
+        K.sample(logits, on_dev[16 * R:20 * R].view(torch.float32), on_dev[24 * R:28 * R].view(torch.int32),
+                 on_dev[20 * R:24 * R].view(torch.float32), on_dev[:8 * R].view(torch.float64), sampled)
     keep = device_tokens if device_tokens is not None else out[2 * R:]      # slot -1: nothing is kept
-    K.keep_tokens(out[:R], sampled, info_pinned.to(dev, non_blocking=True), out[2 * R:], keep)
+    K.keep_tokens(out[:R], sampled, on_dev[8 * R:16 * R].view(torch.int32), out[2 * R:], keep)
+    info_pinned = staged
     host = torch.empty(R, dtype=torch.int32, pin_memory=True)
     host.copy_(out[2 * R:], non_blocking=True)
     ready = torch.cuda.Event()
