@@ -54,6 +54,52 @@ __global__ void apply_penalty_kernel(float* __restrict__ logits, int vocab, cons
     }
 }
 
+// The same penalty from a history kept on the device: ring[slot][0 .. ring_width) holds a request's
+// generated tokens (position n % ring_width for the n-th), ring_len[slot] how many there have been.
+// The last min(len, window) of them count: a token seen c times is penalised c times in a sampled
+// row and once in a greedy one (crates/model/src/sampling.rs:240-310).  One block per row; entry i of
+// the window is thread i's; the first occurrence of a token does the work for all of them.
+constexpr int PENALTY_RING_THREADS = 256;
+
+__global__ void __launch_bounds__(PENALTY_RING_THREADS)
+apply_penalty_ring_kernel(float* __restrict__ logits, int vocab, const int* __restrict__ slot,
+                          const float* __restrict__ penalty, const int* __restrict__ window,
+                          const int* __restrict__ use_sample, const int* __restrict__ ring,
+                          const int* __restrict__ ring_len, int ring_width) {
+    extern __shared__ int recent[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.x;
+    const float p = penalty[row];
+    const int s = slot[row];
+    if (p == 1.0f || s < 0) return;
+    const int len = ring_len[s];
+    int n = min(len, min(window[row], ring_width));
+    if (n <= 0) return;
+    const int* r = ring + (size_t)s * ring_width;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) recent[i] = r[(len - n + i) % ring_width];
+    __syncthreads();
+    const bool every = use_sample[row] != 0;             // sampled rows: once per occurrence
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int tok = recent[i];
+        if (tok < 0 || tok >= vocab) continue;
+        int count = 0;
+        bool first = true;
+        for (int j = 0; j < n; ++j) {
+            if (recent[j] == tok) {
+                if (j < i) { first = false; break; }
+                ++count;
+            }
+        }
+        if (!first) continue;
+        float* z = logits + (size_t)row * vocab + tok;
+        float v = *z;
+        const int times = every ? count : 1;
+        for (int k = 0; k < times; ++k) v = v > 0.f ? v / p : v * p;
+        *z = v;
+    }
+}
+
 // Greedy pick in two passes: every block scans one chunk of one row for its best (value, index),
 // then one warp per row merges the chunks.  "Best" is the larger value, and among equal values
 // the lower index, at every stage, so the result is the row's first maximum.
@@ -113,16 +159,25 @@ argmax_final_kernel(const float* __restrict__ pv, const int* __restrict__ pi, in
 
 // final[r] = use_sample[r] ? sampled[r] : greedy[r];  device_tokens[slot[r]] = final[r]: the
 // sampler's picks, left on the device for a step that is launched before the host reads them.
+// With a ring (see apply_penalty_ring_kernel) the pick is also appended to its request's history.
 __global__ void keep_tokens_kernel(const int* __restrict__ greedy, const int* __restrict__ sampled,
                                    const int* __restrict__ use_sample, const int* __restrict__ slot,
-                                   int* __restrict__ final_tok, int* __restrict__ device_tokens, int n_rows) {
+                                   int* __restrict__ final_tok, int* __restrict__ device_tokens, int n_rows,
+                                   int* __restrict__ ring, int* __restrict__ ring_len, int ring_width) {
     pdl_launch_dependents();
     pdl_wait();
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= n_rows) return;
     const int tok = (sampled && use_sample[r]) ? sampled[r] : greedy[r];
     final_tok[r] = tok;
-    if (slot[r] >= 0) device_tokens[slot[r]] = tok;
+    const int s = slot[r];
+    if (s < 0) return;
+    device_tokens[s] = tok;
+    if (ring) {
+        const int len = ring_len[s];
+        ring[(size_t)s * ring_width + len % ring_width] = tok;
+        ring_len[s] = len + 1;
+    }
 }
 
 // Exclusive prefix sum of one int per thread over the block; returns the total too.
@@ -416,12 +471,24 @@ int infero_sample(const float* logits, int n_rows, int vocab, const float* tempe
 }
 
 // rows_info: [n_rows] slot per row, then [n_rows] use_sample flags.  final_tok [n_rows].
+// ring [slots, ring_width] and ring_len [slots], or both null: the requests' generated tokens on the device.
 int infero_keep_tokens(const int* greedy, const int* sampled, const int* rows_info, int* final_tok,
-                       int* device_tokens, int n_rows, cudaStream_t stream) {
+                       int* device_tokens, int n_rows, int* ring, int* ring_len, int ring_width, cudaStream_t stream) {
     if (n_rows == 0) return 0;
     launch_pdl(keep_tokens_kernel, dim3((n_rows + 127) / 128), dim3(128), 0, stream, greedy, sampled,
-               rows_info + n_rows, rows_info, final_tok, device_tokens, n_rows);
+               rows_info + n_rows, rows_info, final_tok, device_tokens, n_rows, ring, ring_len, ring_width);
     return infero_check_launch("keep_tokens");
+}
+
+// rows_info as for infero_keep_tokens (slot per row, then the use-the-sample flag per row).
+int infero_apply_penalty_ring(float* logits, int n_rows, int vocab, const int* rows_info, const float* penalty,
+                              const int* window, const int* ring, const int* ring_len, int ring_width,
+                              cudaStream_t stream) {
+    if (n_rows == 0) return 0;
+    INFERO_REQUIRE(ring_width > 0 && ring_width <= 8192, "apply_penalty_ring: ring of %d tokens", ring_width);
+    launch_pdl(apply_penalty_ring_kernel, dim3(n_rows), dim3(PENALTY_RING_THREADS), (size_t)ring_width * sizeof(int), stream,
+               logits, vocab, rows_info, penalty, window, rows_info + n_rows, ring, ring_len, ring_width);
+    return infero_check_launch("apply_penalty_ring");
 }
 
 int infero_sample_max_k() { return SAMPLE_MAX_K; }

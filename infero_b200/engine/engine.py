@@ -68,7 +68,8 @@ class Engine:
                                 seed=seed, cuda_graphs=cuda_graphs, device=device)
         self.runner = ModelRunner(self.model, self.cfg)
         self.scheduler = Scheduler(self.runner.manager, self._execute, max_seqs, max_batch_tokens, ctx,
-                                   max_prefill_chunk=max_prefill_chunk, launch=self._launch, run_ahead=run_ahead)
+                                   max_prefill_chunk=max_prefill_chunk, launch=self._launch, run_ahead=run_ahead,
+                                   device_penalty_window=self.runner.HISTORY_WIDTH)
         self._ids = itertools.count()
         self.eos_token_ids = tuple(self.model.spec.eos_token_ids)
 
@@ -134,12 +135,16 @@ class Engine:
         launched before they are read."""
         entries = [StepEntry(it.run.req.rid, it.tokens, [len(it.tokens) - 1] if it.samples else [])
                    for it in items]
+        for it in items:
+            if it.run.rc.fresh:                          # its first step in this slot (new, or recomputed)
+                self.runner.reset_history(it.run.rc.slot, it.run.generated)
         logits = self.runner.step(entries)
         rows = [it for it in items if it.samples]
         if not rows:
             return ReadyTokens([])
         return sample_rows_async(logits, [it.run.sampler for it in rows], [it.run.generated for it in rows],
-                                 [it.run.rc.slot for it in rows], self.runner.device_tokens)
+                                 [it.run.rc.slot for it in rows], self.runner.device_tokens,
+                                 self.runner.history, self.runner.history_len)
 
     def _execute(self, items: List[PlanItem]) -> List[int]:
         return self._launch(items).result()

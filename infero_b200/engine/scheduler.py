@@ -24,7 +24,8 @@ host) the scheduler keeps one step in flight: while step k runs it launches step
 same requests, feeding each the token step k is about to pick, which the sampler leaves on the
 device.  It does so only when nothing can change the batch behind its back: every running
 request is decoding, none reaches its length limit at step k, none samples with a repetition
-penalty (that needs the token on the host), nobody waits for admission, and pages for one more
+penalty over a window longer than the device keeps (that would need the token on the host), nobody
+waits for admission, and pages for one more
 token each are free.  A request that ends at step k on an end-of-sequence token has then run
 one token too far; that token is dropped.  (The reference's scheduler reads every step's tokens
 before it plans the next, crates/server/src/scheduler.rs:1268-1429.)
@@ -122,11 +123,15 @@ class Scheduler:
 
     def __init__(self, manager: CacheManager, execute: Callable[[List[PlanItem]], List[int]],
                  max_seqs: int, max_batch_tokens: int, ctx: int, max_prefill_chunk: Optional[int] = None,
-                 launch: Optional[Callable[[List[PlanItem]], object]] = None, run_ahead: bool = True):
+                 launch: Optional[Callable[[List[PlanItem]], object]] = None, run_ahead: bool = True,
+                 device_penalty_window: int = 0):
         self.manager = manager
         self.execute = execute
         self.launch = launch                   # like execute, but returns an object with .result()
         self.run_ahead = run_ahead and launch is not None
+        # the longest repetition window whose penalty the launcher works out on the device (0: none);
+        # a request with a longer one needs every token on the host before the next step
+        self.device_penalty_window = device_penalty_window
         self._inflight: Optional[_InFlight] = None
         self.max_seqs = max_seqs
         self.max_batch_tokens = max_batch_tokens
@@ -176,7 +181,9 @@ class Scheduler:
 
     # ---- queue ------------------------------------------------------------------------------
     def enqueue(self, req: Request) -> None:
-        needs_host = req.params.repetition_penalty != 1.0        # the penalty needs every token on the host
+        p = req.params
+        needs_host = (p.repetition_penalty != 1.0 and p.repetition_window > 0
+                      and p.repetition_window > self.device_penalty_window)
         sid = self._L.infero_sched_enqueue(self._h, len(req.prompt), int(req.max_new_tokens), int(needs_host))
         if sid == -1:
             self._events.append(Event(req.rid, None, True, "error", "empty prompt"))

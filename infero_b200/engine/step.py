@@ -137,6 +137,10 @@ class ModelRunner:
                                     cfg.max_seqs, max_blocks=self.max_blocks)
         # the sampler's last pick per request slot, for steps launched before the host has read it
         self.device_tokens = torch.zeros(max(1, cfg.max_seqs), dtype=torch.int32, device=self.device)
+        # the requests' generated tokens, per slot, for a repetition penalty worked out on the device:
+        # the n-th token of a request sits at history[slot, n % HISTORY_WIDTH]
+        self.history = torch.zeros((max(1, cfg.max_seqs), self.HISTORY_WIDTH), dtype=torch.int32, device=self.device)
+        self.history_len = torch.zeros(max(1, cfg.max_seqs), dtype=torch.int32, device=self.device)
         self.steps_run = 0
         self.tokens_run = 0
         # captured decode steps: (entries, key bound) -> _DecodeGraph; a shape is run eagerly the
@@ -334,6 +338,20 @@ class ModelRunner:
         while bound < need:
             bound *= 2
         return (self._graph_size(len(entries)), min(bound, self.max_blocks * self.page_size))
+
+    HISTORY_WIDTH = 1024          # the longest repetition window the device-side penalty covers
+
+    def reset_history(self, slot: int, generated: Sequence[int]) -> None:
+        """A request starts (or starts again after a preemption) in ``slot``: its history on the
+        device becomes what it has generated so far."""
+        n = len(generated)
+        self.history_len[slot] = n
+        if n:
+            W = self.HISTORY_WIDTH
+            tail = list(generated[-W:])
+            first = n - len(tail)
+            idx = torch.tensor([(first + i) % W for i in range(len(tail))], dtype=torch.long, device=self.device)
+            self.history[slot].index_copy_(0, idx, torch.tensor(tail, dtype=torch.int32, device=self.device))
 
     MAX_GRAPH_ENTRIES = 256
     GRAPH_SIZES = (1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256)

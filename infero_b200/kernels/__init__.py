@@ -307,13 +307,30 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
 
 
 def keep_tokens(greedy: torch.Tensor, sampled: Optional[torch.Tensor], rows_info: torch.Tensor,
-                final_tok: torch.Tensor, device_tokens: torch.Tensor) -> None:
-    """final_tok[r] = sampled[r] if rows_info[R + r] else greedy[r]; device_tokens[rows_info[r]] = final_tok[r]."""
+                final_tok: torch.Tensor, device_tokens: torch.Tensor, ring: Optional[torch.Tensor] = None,
+                ring_len: Optional[torch.Tensor] = None) -> None:
+    """final_tok[r] = sampled[r] if rows_info[R + r] else greedy[r]; device_tokens[rows_info[r]] = final_tok[r];
+    with ``ring`` [slots, width] / ``ring_len`` [slots] the pick is appended to its request's history."""
     R = final_tok.numel()
-    assert rows_info.numel() == 2 * R
+    assert rows_info.numel() == 2 * R and (ring is None) == (ring_len is None)
     _check(lib().infero_keep_tokens(_ptr(_i32(greedy, "greedy")), _ptr(None if sampled is None else _i32(sampled, "sampled")),
                                     _ptr(_i32(rows_info, "rows_info")), _ptr(_i32(final_tok, "final_tok")),
-                                    _ptr(_i32(device_tokens, "device_tokens")), c_int(R), _stream()))
+                                    _ptr(_i32(device_tokens, "device_tokens")), c_int(R),
+                                    _ptr(None if ring is None else _i32(ring, "ring")),
+                                    _ptr(None if ring_len is None else _i32(ring_len, "ring_len")),
+                                    c_int(ring.shape[1] if ring is not None else 0), _stream()))
+
+
+def apply_penalty_ring(logits: torch.Tensor, rows_info: torch.Tensor, penalty: torch.Tensor, window: torch.Tensor,
+                       ring: torch.Tensor, ring_len: torch.Tensor) -> None:
+    """The repetition penalty from the histories kept on the device (``keep_tokens`` appends to them):
+    row r looks at the last ``window[r]`` tokens of request slot ``rows_info[r]``."""
+    R, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.is_contiguous() and penalty.dtype == torch.float32
+    assert rows_info.numel() == 2 * R and ring.dim() == 2 and ring.is_contiguous()
+    _check(lib().infero_apply_penalty_ring(_ptr(logits), c_int(R), c_int(V), _ptr(_i32(rows_info, "rows_info")),
+                                           _ptr(penalty), _ptr(_i32(window, "window")), _ptr(_i32(ring, "ring")),
+                                           _ptr(_i32(ring_len, "ring_len")), c_int(ring.shape[1]), _stream()))
 
 
 def sample_max_k() -> int:

@@ -60,57 +60,78 @@ class ReadyTokens:
 
 def sample_rows_async(logits: torch.Tensor, samplers: Sequence[RowSampler], histories: Sequence[Sequence[int]],
                       slots: Optional[Sequence[int]] = None,
-                      device_tokens: Optional[torch.Tensor] = None) -> PendingTokens:
+                      device_tokens: Optional[torch.Tensor] = None,
+                      ring: Optional[torch.Tensor] = None, ring_len: Optional[torch.Tensor] = None) -> PendingTokens:
     """As ``sample_rows``, without waiting: the picks go to pinned host memory by an asynchronous
     copy, and (when ``slots`` and ``device_tokens`` are given) stay on the device in
-    ``device_tokens[slot]`` so that the next step can be launched before the host has them."""
+    ``device_tokens[slot]`` so that the next step can be launched before the host has them.
+    With ``ring`` / ``ring_len`` (the requests' generated tokens kept on the device, per slot) the
+    repetition penalty is worked out there too and the picks are appended to the histories, so not
+    even the penalty needs the tokens on the host; ``histories`` is then only the fallback for a
+    window longer than the ring."""
     R, V = logits.shape
     assert len(samplers) == R and len(histories) == R
     dev = logits.device
-    pairs = [s.penalty_pairs(h) for s, h in zip(samplers, histories)]
-    width = max((len(p) for p in pairs), default=0)
-    if width:
-        toks = np.full((R, width), -1, dtype=np.int32)
-        cnts = np.zeros((R, width), dtype=np.int32)
-        for r, p in enumerate(pairs):
-            for i, (t, c) in enumerate(p):
-                toks[r, i], cnts[r, i] = t, c
-        pen = np.array([s.params.repetition_penalty for s in samplers], dtype=np.float32)
-        K.apply_penalty(logits, torch.from_numpy(toks).to(dev), torch.from_numpy(cnts).to(dev),
-                        torch.from_numpy(pen).to(dev))
     greedy = [s.params.is_greedy() for s in samplers]
-    out = torch.empty(3 * R, dtype=torch.int32, device=dev)      # argmax | sampled | final
-    K.argmax(logits, out[:R])
-    # everything the device needs from the host this step, in one pinned buffer and one copy:
-    # draws (64-bit) | slot per row, use-the-sample flag per row | temperature, top_p, top_k
     sampling = not all(greedy)
-    n_bytes = 8 * R + 8 * R + (12 * R if sampling else 0)
+    penalised = [s.params.repetition_penalty != 1.0 and s.params.repetition_window > 0 for s in samplers]
+    on_ring = (ring is not None and slots is not None and any(penalised)
+               and all(s.params.repetition_window <= ring.shape[1] for s, p in zip(samplers, penalised) if p))
+    # everything the device needs from the host this step, in one pinned buffer and one copy:
+    # draws (64-bit) | slot per row, use-the-sample flag per row | temperature, top_p, top_k | penalty, window
+    n_bytes = 16 * R + (12 * R if sampling else 0) + (8 * R if on_ring else 0)
     staged = torch.empty(n_bytes, dtype=torch.uint8, pin_memory=(dev.type == "cuda"))
     h = staged.numpy()
     info = h[8 * R:16 * R].view(np.int32)
     info[:R] = -1 if slots is None or device_tokens is None else np.asarray(slots, dtype=np.int32)
     info[R:] = [0 if g else 1 for g in greedy]
+    o = 16 * R
     if sampling:
         # a draw is taken for every row, greedy or not, as the reference does (sampling.rs:113-121)
         h[:8 * R].view(np.float64)[:] = [s.next_draw() for s in samplers]
-        h[16 * R:20 * R].view(np.float32)[:] = [max(s.params.temperature, 0.0) for s in samplers]
-        h[20 * R:24 * R].view(np.float32)[:] = [s.params.top_p for s in samplers]
-        h[24 * R:28 * R].view(np.int32)[:] = [s.params.top_k for s in samplers]
+        h[o:o + 4 * R].view(np.float32)[:] = [max(s.params.temperature, 0.0) for s in samplers]
+        h[o + 4 * R:o + 8 * R].view(np.float32)[:] = [s.params.top_p for s in samplers]
+        h[o + 8 * R:o + 12 * R].view(np.int32)[:] = [s.params.top_k for s in samplers]
+        o_pen = o + 12 * R
+    else:
+        o_pen = o
+    if on_ring:
+        h[o_pen:o_pen + 4 * R].view(np.float32)[:] = [s.params.repetition_penalty if p else 1.0
+                                                     for s, p in zip(samplers, penalised)]
+        h[o_pen + 4 * R:o_pen + 8 * R].view(np.int32)[:] = [s.params.repetition_window for s in samplers]
     on_dev = staged.to(dev, non_blocking=True)
+    d_info = on_dev[8 * R:16 * R].view(torch.int32)
+    if on_ring:
+        K.apply_penalty_ring(logits, d_info, on_dev[o_pen:o_pen + 4 * R].view(torch.float32),
+                             on_dev[o_pen + 4 * R:o_pen + 8 * R].view(torch.int32), ring, ring_len)
+    elif any(penalised):
+        pairs = [s.penalty_pairs(hh) for s, hh in zip(samplers, histories)]
+        width = max((len(p) for p in pairs), default=0)
+        if width:
+            toks = np.full((R, width), -1, dtype=np.int32)
+            cnts = np.zeros((R, width), dtype=np.int32)
+            for r, p in enumerate(pairs):
+                for i, (t, c) in enumerate(p):
+                    toks[r, i], cnts[r, i] = t, c
+            pen = np.array([s.params.repetition_penalty for s in samplers], dtype=np.float32)
+            K.apply_penalty(logits, torch.from_numpy(toks).to(dev), torch.from_numpy(cnts).to(dev),
+                            torch.from_numpy(pen).to(dev))
+    out = torch.empty(3 * R, dtype=torch.int32, device=dev)      # argmax | sampled | final
+    K.argmax(logits, out[:R])
     sampled = None
     if sampling:
         sampled = out[R:2 * R]
-        K.sample(logits, on_dev[16 * R:20 * R].view(torch.float32), on_dev[24 * R:28 * R].view(torch.int32),
-                 on_dev[20 * R:24 * R].view(torch.float32), on_dev[:8 * R].view(torch.float64), sampled)
+        K.sample(logits, on_dev[o:o + 4 * R].view(torch.float32), on_dev[o + 8 * R:o + 12 * R].view(torch.int32),
+                 on_dev[o + 4 * R:o + 8 * R].view(torch.float32), on_dev[:8 * R].view(torch.float64), sampled)
     keep = device_tokens if device_tokens is not None else out[2 * R:]      # slot -1: nothing is kept
-    K.keep_tokens(out[:R], sampled, on_dev[8 * R:16 * R].view(torch.int32), out[2 * R:], keep)
-    info_pinned = staged
+    use_ring = ring is not None and slots is not None and device_tokens is not None
+    K.keep_tokens(out[:R], sampled, d_info, out[2 * R:], keep, ring if use_ring else None, ring_len if use_ring else None)
     host = torch.empty(R, dtype=torch.int32, pin_memory=True)
     host.copy_(out[2 * R:], non_blocking=True)
     ready = torch.cuda.Event()
     ready.record()
     pending = PendingTokens(host, ready, R)
-    pending._keep = (out, info_pinned)          # alive until the copies have run
+    pending._keep = (out, staged, on_dev)          # alive until the copies have run
     return pending
 
 

@@ -619,3 +619,51 @@ def test_sample_matches_host_statement(V, ties):
     for r in range(R):
         want = _host_sample(zh[r], float(temp[r]), int(top_k[r]), float(top_p[r]), float(draw[r]))
         assert int(out[r]) == want, f"row {r}"
+
+
+def test_penalty_from_the_device_history_equals_the_host_statement():
+    """Rows whose generated tokens live in a ring on the device (appended by keep_tokens) against the
+    pairs the host works out from the same histories: windows shorter and longer than the history, a
+    ring that has wrapped, greedy rows (once per distinct token) beside sampled ones (once per
+    occurrence), a row without a penalty."""
+    from infero_b200 import kernels as Kn
+    from infero_b200.sampling import SamplingParams
+    from infero_b200.sampling.sampler import RowSampler
+    V, W, slots_n = 777, 32, 6
+    rng = np.random.default_rng(11)
+    lens = [0, 5, 31, 32, 50, 200]                       # tokens generated so far, per slot
+    hists = [[int(t) for t in rng.integers(0, 40, size=n)] for n in lens]      # few distinct tokens: many repeats
+    ring = torch.zeros((slots_n, W), dtype=torch.int32, device=DEV)
+    ring_len = torch.zeros(slots_n, dtype=torch.int32, device=DEV)
+    # fill the rings the way the engine does: one keep_tokens per step
+    for step in range(max(lens)):
+        rows = [s for s in range(slots_n) if step < lens[s]]
+        g = torch.tensor([hists[s][step] for s in rows], dtype=torch.int32, device=DEV)
+        info = torch.tensor(rows + [0] * len(rows), dtype=torch.int32, device=DEV)
+        Kn.keep_tokens(g, None, info, torch.empty(len(rows), dtype=torch.int32, device=DEV),
+                       torch.zeros(slots_n, dtype=torch.int32, device=DEV), ring, ring_len)
+    assert ring_len.tolist() == lens
+    params = [SamplingParams(temperature=0.0, repetition_penalty=1.3, repetition_window=8),
+              SamplingParams(temperature=0.7, repetition_penalty=1.1, repetition_window=16),
+              SamplingParams(temperature=0.0, repetition_penalty=1.0),
+              SamplingParams(temperature=0.9, repetition_penalty=1.25, repetition_window=32),
+              SamplingParams(temperature=0.0, repetition_penalty=1.05, repetition_window=20),
+              SamplingParams(temperature=0.5, repetition_penalty=1.2, repetition_window=32)]
+    z0 = torch.from_numpy(rng.normal(size=(slots_n, V)).astype(np.float32) * 2).to(DEV)
+    # host statement: pairs from the last `window` tokens
+    want = z0.clone()
+    pairs = [RowSampler(p).penalty_pairs(h) for p, h in zip(params, hists)]
+    width = max(len(p) for p in pairs)
+    toks = np.full((slots_n, width), -1, dtype=np.int32)
+    cnts = np.zeros((slots_n, width), dtype=np.int32)
+    for r, p in enumerate(pairs):
+        for i, (t, c) in enumerate(p):
+            toks[r, i], cnts[r, i] = t, c
+    Kn.apply_penalty(want, torch.from_numpy(toks).to(DEV), torch.from_numpy(cnts).to(DEV),
+                     torch.tensor([p.repetition_penalty for p in params], dtype=torch.float32, device=DEV))
+    got = z0.clone()
+    info = torch.tensor(list(range(slots_n)) + [0 if p.is_greedy() else 1 for p in params], dtype=torch.int32, device=DEV)
+    Kn.apply_penalty_ring(got, info, torch.tensor([p.repetition_penalty for p in params], dtype=torch.float32, device=DEV),
+                          torch.tensor([p.repetition_window for p in params], dtype=torch.int32, device=DEV), ring, ring_len)
+    assert torch.equal(got, want)
+    assert not torch.equal(got, z0)

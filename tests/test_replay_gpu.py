@@ -306,3 +306,37 @@ def test_running_ahead_changes_no_token(dtype):
             assert eng.scheduler.stats["steps_ahead"] > 0
     assert results[0] == results[1]
     assert "stop" in results[0][1].values() or "length" in results[0][1].values()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_default_sampling_runs_ahead_and_changes_no_token(dtype):
+    """The reference's default sampling (temperature, top-k, top-p and a repetition penalty over the
+    last 256 tokens): the penalty is worked out from histories kept on the device, so steps run
+    ahead; the tokens are those of an engine that waits for every step, and of one that is preempted."""
+    from infero_b200.engine import Engine
+    from infero_b200.sampling import SamplingParams
+    mdir = model_dir("B", seed=77, qk_gain=1.5)
+    reqs = make_requests("B", [9, 30, 3, 21, 14], seed=43)
+    results = []
+    # (a recomputed request sees its tokens again in other portions: the same logits bit for bit only in 32-bit)
+    runs = [(False, 400), (True, 400)] + ([(True, 7 * 16)] if dtype == "float32" else [])
+    for ahead, slots in runs:
+        eng = Engine(mdir, dtype=dtype, ctx=128, max_seqs=3, kv_slots=slots, max_batch_tokens=32, run_ahead=ahead)
+        for i, toks in enumerate(reqs.values()):
+            p = SamplingParams(seed=7 + i) if i % 2 == 0 else SamplingParams(temperature=0.0, repetition_penalty=1.3,
+                                                                               repetition_window=5)
+            eng.add_request(toks, p, max_new_tokens=40, ignore_eos=True, rid=i)
+        out = {}
+        while not eng.is_idle():
+            for ev in eng.step():
+                if ev.token is not None:
+                    out.setdefault(ev.rid, []).append(ev.token)
+        results.append(out)
+        if ahead:
+            assert eng.scheduler.stats["steps_ahead"] > 0
+        if slots < 400:
+            assert eng.scheduler.stats["preemptions"] > 0, "the pool was meant to be too small"
+        assert not eng.runner.manager.requests
+    assert results[0] == results[1], "running ahead changed a token"
+    if len(results) > 2:
+        assert results[0] == results[2], "a preempted request did not continue with its history"
