@@ -52,6 +52,11 @@ class CacheStorage:
             n = sum(1 for s in self._where.values() if s[0] == g)
             self.arrays.append(torch.zeros((n, 2, num_pages, spec.num_kv_heads, page_size, spec.head_dim),
                                            dtype=dtype, device=device))
+        # one object per cache slot for the life of the pool: what points into a pool (a descriptor kept
+        # by native code) is valid exactly as long as it meets the same object
+        self._layer_kv: Dict[int, LayerKv] = {
+            slot: LayerKv(k=self.arrays[g][i, 0], v=self.arrays[g][i, 1], group=g, page_size=page_size)
+            for slot, (g, i) in self._where.items()}
         self.states: Dict[int, torch.Tensor] = {
             slot: torch.zeros((max_requests,) + tuple(s.shape), dtype=s.dtype, device=device)
             for slot, s in state_specs.items()}
@@ -60,9 +65,7 @@ class CacheStorage:
         return [GroupSpec(window=s.window) for s in self.group_specs]
 
     def layer_kv(self, slot: int) -> LayerKv:
-        g, i = self._where[slot]
-        arr = self.arrays[g]
-        return LayerKv(k=arr[i, 0], v=arr[i, 1], group=g, page_size=self.page_size)
+        return self._layer_kv[slot]
 
     def state(self, slot: int) -> torch.Tensor:
         return self.states[slot]

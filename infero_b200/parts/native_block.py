@@ -107,7 +107,7 @@ class NativeBlock:
 
     def __init__(self, block):
         self.block = block
-        self._descs = {}                   # (cache slot, write_cache) -> (_Block, things kept alive)
+        self._descs = {}                   # (cache slot, write_cache) -> (_Block, the pool it points into, inv_freq)
         self.ok = self._parts_qualify()
 
     # ---- which blocks -----------------------------------------------------------------------
@@ -146,13 +146,13 @@ class NativeBlock:
     # ---- descriptors -------------------------------------------------------------------------
     def _desc(self, ctx, slot):
         key = (slot.cache, bool(slot.write_cache))
+        kv = ctx.kv_cache(slot.cache)
         hit = self._descs.get(key)
-        if hit is not None:
+        if hit is not None and hit[1] is kv:       # the same pool as last time (a model may serve several runners)
             return hit[0]
         b, m = self.block, self.block.mixer.spec
-        kv = ctx.kv_cache(slot.cache)
         if kv.k.dtype != torch.bfloat16 or not kv.k.is_contiguous() or not kv.v.is_contiguous():
-            self._descs[key] = (None, None)
+            self._descs[key] = (None, kv, None)
             return None
         rope = self.block.mixer.rope
         inv = rope.inv_freq(kv.k.device) if rope is not None else None
@@ -167,7 +167,7 @@ class NativeBlock:
                    int(kv.k.shape[0]), int(kv.page_size))
         if not _lib().infero_block_supported(ctypes.byref(d)):
             d = None
-        self._descs[key] = (d, (inv, kv))
+        self._descs[key] = (d, kv, inv)
         return d
 
     # ---- the layer -----------------------------------------------------------------------------

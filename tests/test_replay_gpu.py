@@ -60,6 +60,37 @@ def test_mixed_batches_with_page_reuse(name, dtype, seed):
         assert runner.manager.pages_reclaimed > 0, "no page of the window group came back early"
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_one_model_serves_several_pools(dtype):
+    """Runners made one after the other over the same model object, each with a pool of its own
+    (other addresses, other sizes): every one computes in its own cache.  The pool of the runner
+    before is poisoned, so a layer that kept a pointer into it would read NaN or leave the new
+    pool untouched."""
+    import torch
+    from infero_b200.config import EngineConfig
+    from infero_b200.engine import ModelRunner
+    from infero_b200.loading import load_model
+    mdir = model_dir("B", seed=31, qk_gain=1.5)
+    model, _ = load_model(mdir, dtype, "cuda:0")
+    reqs = make_requests("B", [70, 45, 100], seed=8)
+    plain = plain_logits(mdir, reqs)
+    steps = R.steps_tail_decode(reqs, 6)
+    earlier = None
+    for pages in (8, 40, 11):
+        cfg = EngineConfig(dtype=dtype, page_size=16, num_pages=pages, max_seqs=2, ctx=128, max_batch_tokens=128,
+                           max_logit_rows=128, cuda_graphs=False)
+        runner = ModelRunner(model, cfg)
+        got = R.replay_inprocess(runner, steps)
+        err, where = R.compare(got, plain)
+        assert err <= TOL[dtype], f"pool of {pages} pages, {dtype}: relative error {err:.3e} at {where}"
+        assert all(bool((a != 0).any()) for a in runner.storage.arrays), "this runner's own pool was never written"
+        if earlier is not None:
+            assert all(bool(torch.isnan(a).all()) for a in earlier.storage.arrays), "the pool before was written to"
+        for a in runner.storage.arrays:
+            a.fill_(float("nan"))
+        earlier = runner
+
+
 @pytest.mark.parametrize("name,dtype", CASES)
 def test_sharp_attention(name, dtype):
     """Scaled q/k projections make single keys dominate, so a wrong or missing key shows."""
