@@ -26,7 +26,6 @@ import json
 import os
 import random
 import sys
-import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))

@@ -9,7 +9,7 @@ per layer, crates/model/src/cache.rs:171-189.)  Per state slot one array
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, List, Tuple
 
 import torch
 

@@ -15,8 +15,7 @@ from __future__ import annotations
 
 import json
 import math
-import os
-from dataclasses import dataclass, field, asdict
+from dataclasses import dataclass
 from typing import Any, Dict, List, Optional, Tuple
 
 from .spec import (BlockSpec, FeedForwardSpec, MixerSpec, ModelSpec, NormSpec,

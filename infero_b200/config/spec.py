@@ -12,7 +12,7 @@ present (crates/model/src/weights.rs:810).  Here the block kind is explicit data
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Optional, Tuple
 
 

@@ -111,7 +111,7 @@ template <int D, typename Layout = PaddedRows<D>>
 __device__ __forceinline__ void slice16(const uint32_t (*qf)[4], const bf16* k_tile, const bf16* v_tile, int row0,
                                         int key_base, int lo0, int hi0, int lo1, int hi1, float scale_log2,
                                         float* m, float* l, float (*o)[4], int lane) {
-    const int g = lane >> 2, c = lane & 3;
+    const int c = lane & 3;
     float s[2][4];
 #pragma unroll
     for (int i = 0; i < 2; ++i)

@@ -1202,7 +1202,6 @@ int infero_gemm_tc_swiglu(const void* x, const void* w, void* out, int M, int N,
         }
 #undef GO
     }
-    const int total_kt = (K + TILE_K - 1) / TILE_K;
     CUtensorMap mx, mw;
     if (get_map(x, M, K, ldx, TILE_A, &mx)) return 1;
     if (get_map(w, N, K, K, 256, &mw)) return 1;

@@ -43,7 +43,7 @@ from typing import Callable, Dict, Hashable, List, Optional, Tuple
 
 from ..cache import CacheManager, RequestCache
 from ..sampling import RowSampler, SamplingParams
-from .step import FROM_DEVICE, StepEntry
+from .step import FROM_DEVICE
 
 
 @dataclass

@@ -10,7 +10,7 @@ where this step takes arbitrary positions.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence
 
 import ctypes

@@ -9,12 +9,12 @@ tiled prefill kernel.  The scheduler puts decodes first, as the reference's does
 """
 from __future__ import annotations
 
-from ctypes import c_float, c_int, c_longlong, c_void_p
-from typing import List, Optional, Sequence, Tuple
+from ctypes import c_float, c_int, c_longlong
+from typing import Optional, Sequence, Tuple
 
 import torch
 
-from . import KernelError, _check, _dt, _i32, _ptr, _stream, attention_generic, lib
+from . import _check, _i32, _ptr, _stream, attention_generic, lib
 
 PREFILL_ROWS = 64          # query rows per CTA of the prefill kernel
 import os as _os

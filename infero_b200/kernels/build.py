@@ -15,8 +15,8 @@ import subprocess
 import sys
 import tempfile
 import time
-from concurrent.futures import ThreadPoolExecutor, as_completed
-from typing import List, Optional
+from concurrent.futures import ThreadPoolExecutor
+from typing import List
 
 CSRC = os.path.normpath(os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "csrc"))
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]

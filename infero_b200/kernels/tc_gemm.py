@@ -8,12 +8,12 @@ pass (norm, activation, rotary + cache append).
 """
 from __future__ import annotations
 
-from ctypes import POINTER, byref, c_int, c_longlong, c_void_p
+from ctypes import byref, c_int, c_longlong
 from typing import Optional, Tuple
 
 import torch
 
-from . import BF16, F32, KernelError, _check, _dt, _ptr, _stream, lib
+from . import F32, _check, _dt, _ptr, _stream, lib
 
 _SM_COUNT = {}
 

@@ -1,9 +1,7 @@
 """From a model folder (or a configuration and a seed) to a bound model on the device."""
 from __future__ import annotations
 
-import json
-import os
-from typing import Any, Dict, Optional, Tuple
+from typing import Any, Dict, Tuple
 
 import torch
 

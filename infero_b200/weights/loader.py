@@ -12,7 +12,7 @@ tables become int32.  ``float32``: every floating tensor becomes float32.
 """
 from __future__ import annotations
 
-from typing import Dict, Iterable, List, Optional
+from typing import Dict, Iterable, List
 
 import torch
 

@@ -17,7 +17,7 @@ import os
 import struct
 import warnings
 from dataclasses import dataclass
-from typing import Dict, Iterable, Iterator, List, Tuple
+from typing import Dict, List, Tuple
 
 import torch
 

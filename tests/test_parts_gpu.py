@@ -7,7 +7,6 @@ import os
 import tempfile
 from types import SimpleNamespace
 
-import numpy as np
 import pytest
 import torch
 

@@ -6,7 +6,6 @@ import torch
 
 import plain_qwen2 as P
 from engine_fixtures import model_dir, plain_model
-from tiny_configs import CONFIGS
 
 
 def test_rms_norm_by_hand():
