@@ -146,7 +146,7 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ x
 // owns elements 4t .. 4t+3 of every row and the block size is the same as in the kernel above,
 // so each row is computed by exactly the same operations in the same order.
 template <typename TD, typename TO>
-__global__ void add_rmsnorm_rows_kernel(float* __restrict__ x, const TD* __restrict__ delta,
+__global__ void __launch_bounds__(1024, 2) add_rmsnorm_rows_kernel(float* __restrict__ x, const TD* __restrict__ delta,
                                         const void* __restrict__ dbias, int dbias_dtype,
                                         const void* __restrict__ w, int wdtype, float eps,
                                         TO* __restrict__ out, int n_rows, int d) {

@@ -126,6 +126,22 @@ def main(argv=None) -> int:
             out = torch.empty((T, ff), dtype=bf, device=dev)
             runs.append(lambda gu=gu, out=out: K.swiglu(gu, out))
         bytes_ = T * ff * 6
+    elif name == "rope":
+        # rotary on q and k in place and the append of k and v to the cache, T tokens of one request
+        P = args.page_size
+        blocks = -(-T // P)
+        n = _copies(T * (H + 2 * Hkv) * D * 2 + 2 * blocks * Hkv * P * D * 2, args.reps)
+        inv = (1e6 ** (-torch.arange(0, D, 2, dtype=torch.float64) / D)).to(torch.float32).to(dev)
+        pos = torch.arange(T, dtype=torch.int32, device=dev)
+        ent = torch.zeros(T, dtype=torch.int32, device=dev)
+        for c in range(n):
+            qkv = rnd(T, (H + 2 * Hkv) * D)
+            kc = torch.zeros((blocks, Hkv, P, D), dtype=bf, device=dev)
+            vc = torch.zeros_like(kc)
+            table = torch.randperm(blocks, generator=torch.Generator().manual_seed(c)).to(torch.int32).view(1, blocks).to(dev)
+            runs.append(lambda qkv=qkv, kc=kc, vc=vc, table=table:
+                        K.rope_cache(qkv, pos, ent, table, inv, kc, vc, H, Hkv, D, P))
+        bytes_ = 2.0 * T * D * (2 * (H + Hkv) + 3 * Hkv)       # q and k read and written, v read, k and v appended
     else:
         print(f"kernel_bench: unknown kernel {name!r}", file=sys.stderr)
         return 2
