@@ -1,7 +1,8 @@
 // Prompt-portion attention over the paged cache on the 5th-generation tensor cores.
 //
 // One CTA = 128 consecutive query tokens of one request and TWO heads that share a kv head (the
-// last head of an odd group works alone).  Both heads see the same keys, so every key and value
+// last head of an odd group works alone; when a grid of pairs would not fill the SMs, every head
+// does).  Both heads see the same keys, so every key and value
 // tile is fetched from L2 once for 256 query rows: with one head per CTA the kernel was bound by
 // L2 bandwidth (128 flops per byte fetched; measured 665 TFLOP/s with the softmax taken out).
 // The CTA walks the visible keys in tiles of 64; per head:
@@ -85,8 +86,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, int out_stride,
                        const int* __restrict__ block_table, int max_blocks, const int* __restrict__ entry_q_start,
                        const int* __restrict__ entry_q_len, const int* __restrict__ entry_pos0, int n_entries,
-                       int first_entry, int n_tiles, int n_heads, int n_kv, int page_size, int slice, int window,
-                       float scale_log2, int* __restrict__ err_flag) {
+                       int first_entry, int n_tiles, int n_heads, int n_kv, int heads_per_cta, int page_size, int slice,
+                       int window, float scale_log2, int* __restrict__ err_flag) {
     using Plan = PfPlan<D>;
     constexpr int DB = Plan::DB, ST = Plan::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -141,10 +142,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
     // ---- which kv head and pair of heads, which request and which block of 128 query rows? ------
     const int group = n_heads / n_kv;
-    const int pairs = (group + 1) >> 1;
+    const int pairs = (group + heads_per_cta - 1) / heads_per_cta;
     const int kvh = (int)blockIdx.x / pairs;
-    const int head0 = kvh * group + 2 * ((int)blockIdx.x % pairs);
-    const int n_q = (head0 + 1 < (kvh + 1) * group) ? 2 : 1;            // heads of this CTA
+    const int head0 = kvh * group + heads_per_cta * ((int)blockIdx.x % pairs);
+    const int n_q = min(heads_per_cta, (kvh + 1) * group - head0);      // heads of this CTA
     int e = -1, tile_in_e = 0;
     {
         int left = n_tiles - 1 - (int)blockIdx.y;                           // longest first
@@ -424,6 +425,17 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
            const int* entry_pos0, int n_entries, int first_entry, int n_tiles, int n_heads, int n_kv, int page_size,
            int slice, int window, float scale_log2, int* err, cudaStream_t stream) {
     using Plan = PfPlan<D>;
+    // Two heads per CTA halve the key and value traffic, but a grid that does not fill the SMs that way
+    // runs faster with one head per CTA: measured at 7B sizes 25 against 35 us at 1,024 tokens (128
+    // CTAs in pairs) and 45 against 37 us at 1,536 (192 CTAs in pairs); the same at 0.5B sizes.
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    const int group = n_heads / n_kv;
+    const int hpc = (long long)n_kv * ((group + 1) / 2) * n_tiles <= sms ? 1 : 2;
     auto kern = attn_prefill_tc_kernel<D>;
     static bool configured = false;
     if (!configured) {
@@ -434,10 +446,9 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
         }
         configured = true;
     }
-    const int group = n_heads / n_kv;
-    launch_pdl(kern, dim3(n_kv * ((group + 1) / 2), n_tiles), dim3(PFT_THREADS), Plan::TOTAL, stream, mq, mk, mv, (bf16*)out, out_stride,
+    launch_pdl(kern, dim3(n_kv * ((group + hpc - 1) / hpc), n_tiles), dim3(PFT_THREADS), Plan::TOTAL, stream, mq, mk, mv, (bf16*)out, out_stride,
                block_table, max_blocks, entry_q_start, entry_q_len, entry_pos0, n_entries, first_entry, n_tiles, n_heads,
-               n_kv, page_size, slice, window, scale_log2, err);
+               n_kv, hpc, page_size, slice, window, scale_log2, err);
     return infero_check_launch("attn_prefill_tc");
 }
 
