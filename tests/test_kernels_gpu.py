@@ -400,15 +400,22 @@ def test_attention_over_pages(H, Hkv, D, dt, window):
     assert worst <= (3e-6 if dt == torch.float32 else 1.5e-2), f"{worst:.3e}"
 
 
-@pytest.mark.parametrize("H,Hkv,D", [(7, 1, 128), (4, 2, 64)])
+SMALL_PORTIONS = [(0, 300), (300, 260), (77, 2), (129, 1)]        # 8 blocks of 128 rows
+LARGE_PORTIONS = [(0, 700), (300, 500), (77, 2), (129, 1)]        # 12 blocks
+
+
+@pytest.mark.parametrize("H,Hkv,D,P,lens", [
+    (7, 1, 128, 16, SMALL_PORTIONS), (7, 1, 128, 64, SMALL_PORTIONS),
+    (4, 2, 64, 16, SMALL_PORTIONS), (4, 2, 64, 64, SMALL_PORTIONS),
+    # enough (kv head, pair of heads, block) CTAs to fill the SMs: the kernel then gives a CTA two heads
+    (28, 4, 128, 16, LARGE_PORTIONS), (28, 4, 64, 32, LARGE_PORTIONS)])
 @pytest.mark.parametrize("window", [None, 200])
-@pytest.mark.parametrize("P", [16, 64])
-def test_prefill_attention_on_tensor_memory(H, Hkv, D, window, P):
+def test_prefill_attention_on_tensor_memory(H, Hkv, D, window, P, lens):
     """Prompt portions that span several blocks of 128 rows and several tiles of 128 keys: a
-    request from its start, one that continues 300 cached tokens, and a two-token portion."""
+    request from its start, one that continues 300 cached tokens, and a two-token portion; with
+    one head per CTA (small grids) and with two."""
     from infero_b200.kernels import attention as A
     dt = torch.bfloat16
-    lens = [(0, 300), (300, 260), (77, 2), (129, 1)]
     pages = sum(-(-(o + n) // P) for o, n in lens) + 4
     rng = np.random.default_rng(3)
     perm = rng.permutation(pages)
