@@ -35,23 +35,25 @@ def test_serving_sizes_bfloat16_against_32_bit(name):
     out = {}
     for dtype in ("float32", "bfloat16"):
         model, _ = random_model(cfg, seed=3, dtype=dtype, device="cuda:0", generate_on_device=True)
-        r = ModelRunner(model, EngineConfig(dtype=dtype, page_size=16, num_pages=256, max_seqs=4, ctx=1024,
-                                            max_batch_tokens=1024, max_logit_rows=64,
+        r = ModelRunner(model, EngineConfig(dtype=dtype, page_size=16, num_pages=256, max_seqs=4, ctx=2048,
+                                            max_batch_tokens=2048, max_logit_rows=64,
                                             cuda_graphs=(dtype == "bfloat16")))
         # poison what the allocator hands out next: scratch must not be read before it is written
         junk = torch.full((8 << 20,), float("nan"), dtype=torch.float32, device="cuda:0")
         del junk
         rng = random.Random(5)
-        toks = {i: [rng.randrange(c["vocab_size"]) for _ in range(n)] for i, n in enumerate((700, 300, 33))}
+        toks = {i: [rng.randrange(c["vocab_size"]) for _ in range(n)] for i, n in enumerate((1200, 300, 33))}
         rows = []
         for i in toks:
             r.open(i)
         # (a captured step returns its graph's own output tensor, which the next replay overwrites:
         # every result is copied out at once)
-        rows.append(r.step([StepEntry(0, toks[0][:600], [0, 599]), StepEntry(1, toks[1][:290], [289])]).float().cpu())
-        rows.append(r.step([StepEntry(2, toks[2][:32], [31]), StepEntry(0, toks[0][600:690], [89])]).float().cpu())
+        # (eleven blocks of 128 query rows: at the larger shapes the prompt attention then gives a CTA
+        # two heads; the second step's four blocks run with one head per CTA)
+        rows.append(r.step([StepEntry(0, toks[0][:1100], [0, 1099]), StepEntry(1, toks[1][:290], [289])]).float().cpu())
+        rows.append(r.step([StepEntry(2, toks[2][:32], [31]), StepEntry(0, toks[0][1100:1190], [89])]).float().cpu())
         for k in range(10):                 # first eager, then captured and replayed
-            rows.append(r.step([StepEntry(0, [toks[0][690 + k]], [0]),
+            rows.append(r.step([StepEntry(0, [toks[0][1190 + k]], [0]),
                                 StepEntry(1, [toks[1][290 + k]], [0])]).float().cpu())
         out[dtype] = torch.cat(rows)
         if dtype == "bfloat16":
