@@ -396,8 +396,8 @@ int infero_attn_decode_tma_supported(int head_dim, int page_size) {
 // The same contract as infero_attn_decode (attention_mma.cu), plus num_pages: the caches are
 // [num_pages, n_kv, page_size, head_dim] bf16, contiguous and 16-byte aligned.  n_splits is
 // at most 256.  scratch: infero_attn_decode_scratch bytes.  counters: n_counters ints, zero before the
-// first call (each launch leaves them zero again), at least n_tok * n_kv * ceil(group / 16); with
-// them the last CTA of every group of splits merges the group; without (null) a second kernel does.
+// first call (each launch leaves them zero again); with n_tok * n_kv * ceil(group / 16) of them or more
+// the last CTA of every group of splits merges the group; with fewer, or none (null), a second kernel does.
 int infero_attn_decode_tma(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
                            const void* v_cache, int num_pages, const int* block_table, int max_blocks,
                            const int* tok_entry, const int* positions, int tok_first, int n_tok, int n_heads,
@@ -419,8 +419,9 @@ int infero_attn_decode_tma(const void* q, int q_stride, void* out, int out_strid
     int* err;
     if (infero_tc_err_flag(&err)) return 1;
     if (counters) {
-        const int groups = n_tok * n_kv * ((n_heads / n_kv + 15) / 16);
-        INFERO_REQUIRE(groups <= n_counters, "attn_decode_tma: %d arrival counters needed, %d given", groups, n_counters);
+        // more groups of splits than counters: the separate merge kernel does it
+        const long long groups = (long long)n_tok * n_kv * ((n_heads / n_kv + 15) / 16);
+        if (groups > n_counters) counters = nullptr;
     }
     const float sl2 = scale * 1.4426950408889634f;
     float* po = (float*)scratch;

@@ -248,7 +248,8 @@ class ModelRunner:
         were captured with alive."""
         from ..kernels import tc_gemm
         from ..parts import native_block as NB
-        key = (ctypes.addressof(block_desc), tc_gemm._plan_epoch[0])
+        d = block_desc                       # (the need depends on the block's sizes, not on which block it is)
+        key = (d.hidden, d.n_heads, d.n_kv, d.head_dim, d.intermediate, tc_gemm._plan_epoch[0])
         need = self._arena_need.get(key)
         if need is None:
             # (a captured step may be padded past max_batch_tokens, up to the largest captured size)
