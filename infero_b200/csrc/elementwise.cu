@@ -7,7 +7,8 @@
 // Formulas as in the reference: crates/kernels/src/cu/quant.cu:138-150 (gather),
 // crates/kernels/src/cu/ops.cu:44-62 (x * rsqrt(mean(x^2)+eps) * w; multiply by the
 // scale first, then by w), ops.cu:111-133 (g / (1 + exp(-g)) * u).
-#include "common.cuh"
+#include "tc_common.cuh"
+#include <cstdlib>
 
 namespace {
 
@@ -191,6 +192,109 @@ __global__ void __launch_bounds__(1024, 2) add_rmsnorm_rows_kernel(float* __rest
     }
 }
 
+// The same rows through a ring in shared memory: one thread asks for whole rows (x and delta, one
+// bulk copy each, RING rows ahead), so a block has RING rows on their way instead of two and the
+// loads no longer wait on the block-wide sum of the row before.  The arithmetic per row is the
+// kernel's above, operation for operation.  Needs rows that are multiples of 16 bytes.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(tc::smem_u32(smem_dst)), "l"(src), "r"(bytes), "r"(tc::smem_u32(bar))
+                 : "memory");
+}
+
+template <typename TD, typename TO>
+__global__ void __launch_bounds__(1024, 2) add_rmsnorm_ring_kernel(float* __restrict__ x, const TD* __restrict__ delta,
+                                                                   const void* __restrict__ dbias, int dbias_dtype,
+                                                                   const void* __restrict__ w, int wdtype, float eps,
+                                                                   TO* __restrict__ out, int n_rows, int d, int ring,
+                                                                   int* __restrict__ err_flag) {
+    extern __shared__ __align__(16) uint8_t ring_mem[];
+    __shared__ float red[32];
+    __shared__ uint64_t full[8];
+    __shared__ int abort_flag;
+    const uint32_t x_bytes = (uint32_t)d * 4u, d_bytes = delta ? (uint32_t)d * (uint32_t)sizeof(TD) : 0u;
+    const uint32_t row_bytes = x_bytes + d_bytes;
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < ring; ++s) tc::mbar_init(&full[s], 1);
+        abort_flag = 0;
+        tc::fence_barrier_init();
+        tc::fence_proxy_async();
+    }
+    const int i = threadIdx.x * 4;
+    const bool mine = i < d;
+    float ww[4] = {0.f, 0.f, 0.f, 0.f}, bb[4] = {0.f, 0.f, 0.f, 0.f};
+    if (mine) {
+        load4_any(w, wdtype, i, ww);
+        if (dbias) load4_any(dbias, dbias_dtype, i, bb);
+    }
+    __syncthreads();
+    pdl_wait();
+    auto ask = [&](int r, int s) {                  // (thread 0) row r into stage s
+        uint8_t* st = ring_mem + (size_t)s * row_bytes;
+        tc::mbar_expect_tx(&full[s], row_bytes);
+        bulk_load(st, x + (size_t)r * d, x_bytes, &full[s]);
+        if (delta) bulk_load(st + x_bytes, delta + (size_t)r * d, d_bytes, &full[s]);
+    };
+    if (threadIdx.x == 0)
+        for (int s = 0; s < ring; ++s) {
+            const int r = (int)blockIdx.x + s * (int)gridDim.x;
+            if (r < n_rows) ask(r, s);
+        }
+    int k = 0;
+    bool ok = true;
+    for (int r = blockIdx.x; r < n_rows; r += gridDim.x, ++k) {
+        const int s = k % ring;
+        // (every thread watches the barrier itself, and the block agrees on the outcome before it goes on)
+        ok = __syncthreads_and(tc::mbar_wait(&full[s], (uint32_t)(k / ring) & 1u, &abort_flag) ? 1 : 0) != 0;
+        if (!ok) break;
+        const uint8_t* st = ring_mem + (size_t)s * row_bytes;
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (mine) {
+            load4(reinterpret_cast<const float*>(st) + i, v);
+            if (delta) {
+                float dv[4];
+                load4(reinterpret_cast<const TD*>(st + x_bytes) + i, dv);
+                v[0] += dv[0]; v[1] += dv[1]; v[2] += dv[2]; v[3] += dv[3];
+                if (dbias) { v[0] += bb[0]; v[1] += bb[1]; v[2] += bb[2]; v[3] += bb[3]; }
+            }
+        }
+        float ss = 0.f;
+        if (mine) {
+            ss = fmaf(v[0], v[0], ss); ss = fmaf(v[1], v[1], ss); ss = fmaf(v[2], v[2], ss); ss = fmaf(v[3], v[3], ss);
+        }
+        ss = block_sum(ss, red);                    // (its barriers: every thread has read the stage by now)
+        if (threadIdx.x == 0) {
+            const int rn = r + ring * (int)gridDim.x;
+            if (rn < n_rows) {
+                tc::fence_proxy_async();            // the stage was read through ordinary loads
+                ask(rn, s);
+            }
+        }
+        const float sc = 1.0f / sqrtf(ss / (float)d + eps);
+        if (mine) {
+            if (delta) store4(x + (size_t)r * d + i, v);
+            v[0] = v[0] * sc * ww[0]; v[1] = v[1] * sc * ww[1]; v[2] = v[2] * sc * ww[2]; v[3] = v[3] * sc * ww[3];
+            store4(out + (size_t)r * d + i, v);
+        }
+    }
+    if (!ok) {
+        // a row never arrived (the wait is bounded): report it; what thread 0 asked for and has not been
+        // waited for is given the same bounded time to land before the block's shared memory goes away
+        if (threadIdx.x == 0) {
+            abort_flag = 1;
+            atomicExch(err_flag, 8);
+        }
+    }
+    __syncthreads();
+    if (!ok && threadIdx.x == 0) {
+        int never = 0;
+        int kk = k;
+        for (int r = (int)blockIdx.x + k * (int)gridDim.x, n = 0; r < n_rows && n < ring; r += gridDim.x, ++n, ++kk)
+            tc::mbar_wait(&full[kk % ring], (uint32_t)(kk / ring) & 1u, &never);
+    }
+}
+
 // out[t, j] = silu(g) * u with g = sum_s gu[s][t, 2j], u = sum_s gu[s][t, 2j + 1] (s ascending):
 // gate and up alternate along a row, as the stacked weight's rows do.  VEC = 4 outputs per thread.
 template <typename T, int VEC>
@@ -287,6 +391,31 @@ int infero_add_rmsnorm(float* x, const void* delta, int delta_dtype, int delta_s
         if (per_sm < 1) per_sm = 1;
         int blocks = sms * per_sm;
         if (blocks > n_rows) blocks = n_rows;
+        // rows through a ring of bulk copies where a row is a multiple of 16 bytes and two or more fit
+        const size_t delta_row = delta ? (size_t)d * (delta_dtype == INFERO_F32 ? 4 : 2) : 0;
+        const size_t row_bytes = (size_t)d * 4 + delta_row;
+        int ring = (int)((96 * 1024) / row_bytes);
+        if (ring > 4) ring = 4;
+        static const bool ring_off = getenv("INFERO_NORM_RING") && atoi(getenv("INFERO_NORM_RING")) == 0;
+        if (!ring_off && ring >= 2 && delta_row % 16 == 0 && ((size_t)d * 4) % 16 == 0) {
+            int* err;
+            if (infero_tc_err_flag(&err)) return 1;
+            const size_t ring_bytes = (size_t)ring * row_bytes;
+#define LAUNCH_RING(TD, TO)                                                                      \
+            do {                                                                                 \
+                auto k = add_rmsnorm_ring_kernel<TD, TO>;                                        \
+                if (ring_bytes > 48 * 1024)                                                      \
+                    cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring_bytes); \
+                launch_pdl(k, dim3(blocks), dim3(threads), ring_bytes, stream, x, (const TD*)delta, dbias, dbias_dtype, \
+                           w, w_dtype, eps, (TO*)out, n_rows, d, ring, err);                      \
+            } while (0)
+            if (delta_dtype == INFERO_F32 && out_dtype == INFERO_F32) LAUNCH_RING(float, float);
+            else if (delta_dtype == INFERO_BF16 && out_dtype == INFERO_BF16) LAUNCH_RING(bf16, bf16);
+            else if (delta_dtype == INFERO_F32 && out_dtype == INFERO_BF16) LAUNCH_RING(float, bf16);
+            else LAUNCH_RING(bf16, float);
+#undef LAUNCH_RING
+            return infero_check_launch("add_rmsnorm_ring");
+        }
 #define LAUNCH_ROWS(TD, TO)                                                                      \
         launch_pdl(add_rmsnorm_rows_kernel<TD, TO>, dim3(blocks), dim3(threads), 0, stream, x, (const TD*)delta, dbias, \
                    dbias_dtype, w, w_dtype, eps, (TO*)out, n_rows, d)

@@ -230,11 +230,13 @@ def test_add_rmsnorm(d, eps, act):
 
 
 @pytest.mark.parametrize("act", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("d", [96, 3584])
-def test_add_rmsnorm_many_rows_equal_few_rows_bit_for_bit(act, d):
-    """300 rows at once (the pipelined kernel) against the same rows 100 at a time."""
+@pytest.mark.parametrize("d", [96, 100, 3584, 5120])
+@pytest.mark.parametrize("T", [300, 3000])
+def test_add_rmsnorm_many_rows_equal_few_rows_bit_for_bit(act, d, T):
+    """Many rows at once (the kernels that keep several rows on their way: through a ring in shared
+    memory where a row is a multiple of 16 bytes, from registers where it is not, as with 100 bf16
+    values; 3,000 rows make every block refill its ring) against the same rows 100 at a time."""
     from infero_b200 import kernels as Kn
-    T = 300
     x = _rand((T, d), torch.float32, 1)
     delta = _rand((T, d), act, 2)
     w = _rand((d,), act, 3) + 1
