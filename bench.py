@@ -216,7 +216,7 @@ def time_e2e(model, cfg_json, batch, steps, warmup, clocks, page_size):
     dt = time.perf_counter() - t0
     clocks.on = False
     h2d = eng.runner.last_h2d_bytes + 2 * batch * 4     # the step's arrays, and the sampler's (slot, flag) per row
-    d2h = batch * 4                          # one picked token per row
+    d2h = (batch + 1) * 4                    # one picked token per row, and the device's fault flag
     eng.abort_all("bench done")
     del eng
     torch.cuda.empty_cache()

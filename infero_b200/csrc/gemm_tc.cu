@@ -1227,4 +1227,17 @@ int infero_tc_error_flag() {
     return v;
 }
 
+// Writes the flag from the host (0 clears it).  For tests of what the host does when a wait has run
+// out: no kernel has to miss a wait for that.  Synchronises the device.
+int infero_tc_set_error_flag(int value) {
+    int* err;
+    if (err_flag_ptr(&err)) return -1;
+    cudaError_t e = cudaMemcpy(err, &value, sizeof(int), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        infero_set_error("tc_set_error_flag: %s", cudaGetErrorString(e));
+        return -1;
+    }
+    return 0;
+}
+
 }  // extern "C"

@@ -19,6 +19,8 @@
 #include "common.cuh"
 #include <math_constants.h>
 
+int infero_tc_err_flag(int** out);      // tc_host.cu: the flag that kernels with bounded waits raise
+
 namespace {
 
 constexpr int SAMPLE_THREADS = 1024;
@@ -160,13 +162,17 @@ argmax_final_kernel(const float* __restrict__ pv, const int* __restrict__ pi, in
 // final[r] = use_sample[r] ? sampled[r] : greedy[r];  device_tokens[slot[r]] = final[r]: the
 // sampler's picks, left on the device for a step that is launched before the host reads them.
 // With a ring (see apply_penalty_ring_kernel) the pick is also appended to its request's history.
+// With fault_flag, final_tok[n_rows] receives the flag the kernels with bounded waits raise when a wait
+// ran out, so that the host learns of it in the same copy that brings the picks.
 __global__ void keep_tokens_kernel(const int* __restrict__ greedy, const int* __restrict__ sampled,
                                    const int* __restrict__ use_sample, const int* __restrict__ slot,
                                    int* __restrict__ final_tok, int* __restrict__ device_tokens, int n_rows,
-                                   int* __restrict__ ring, int* __restrict__ ring_len, int ring_width) {
+                                   int* __restrict__ ring, int* __restrict__ ring_len, int ring_width,
+                                   const int* __restrict__ fault_flag) {
     pdl_launch_dependents();
     pdl_wait();
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r == 0 && fault_flag) final_tok[n_rows] = *(const volatile int*)fault_flag;
     if (r >= n_rows) return;
     const int tok = (sampled && use_sample[r]) ? sampled[r] : greedy[r];
     final_tok[r] = tok;
@@ -472,11 +478,16 @@ int infero_sample(const float* logits, int n_rows, int vocab, const float* tempe
 
 // rows_info: [n_rows] slot per row, then [n_rows] use_sample flags.  final_tok [n_rows].
 // ring [slots, ring_width] and ring_len [slots], or both null: the requests' generated tokens on the device.
+// with_fault: final_tok has n_rows + 1 ints, the last one receives the device's fault flag (0: all waits were met).
 int infero_keep_tokens(const int* greedy, const int* sampled, const int* rows_info, int* final_tok,
-                       int* device_tokens, int n_rows, int* ring, int* ring_len, int ring_width, cudaStream_t stream) {
+                       int* device_tokens, int n_rows, int* ring, int* ring_len, int ring_width, int with_fault,
+                       cudaStream_t stream) {
     if (n_rows == 0) return 0;
+    int* fault = nullptr;
+    if (with_fault && infero_tc_err_flag(&fault)) return 1;
     launch_pdl(keep_tokens_kernel, dim3((n_rows + 127) / 128), dim3(128), 0, stream, greedy, sampled,
-               rows_info + n_rows, rows_info, final_tok, device_tokens, n_rows, ring, ring_len, ring_width);
+               rows_info + n_rows, rows_info, final_tok, device_tokens, n_rows, ring, ring_len, ring_width,
+               (const int*)fault);
     return infero_check_launch("keep_tokens");
 }
 

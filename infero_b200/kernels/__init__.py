@@ -308,17 +308,20 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
 
 def keep_tokens(greedy: torch.Tensor, sampled: Optional[torch.Tensor], rows_info: torch.Tensor,
                 final_tok: torch.Tensor, device_tokens: torch.Tensor, ring: Optional[torch.Tensor] = None,
-                ring_len: Optional[torch.Tensor] = None) -> None:
+                ring_len: Optional[torch.Tensor] = None, with_fault: bool = False) -> None:
     """final_tok[r] = sampled[r] if rows_info[R + r] else greedy[r]; device_tokens[rows_info[r]] = final_tok[r];
-    with ``ring`` [slots, width] / ``ring_len`` [slots] the pick is appended to its request's history."""
-    R = final_tok.numel()
+    with ``ring`` [slots, width] / ``ring_len`` [slots] the pick is appended to its request's history.
+    ``with_fault``: final_tok has one more element, which receives the device's fault flag (the one the
+    kernels with bounded waits raise), so the host reads it with the picks."""
+    R = final_tok.numel() - (1 if with_fault else 0)
     assert rows_info.numel() == 2 * R and (ring is None) == (ring_len is None)
     _check(lib().infero_keep_tokens(_ptr(_i32(greedy, "greedy")), _ptr(None if sampled is None else _i32(sampled, "sampled")),
                                     _ptr(_i32(rows_info, "rows_info")), _ptr(_i32(final_tok, "final_tok")),
                                     _ptr(_i32(device_tokens, "device_tokens")), c_int(R),
                                     _ptr(None if ring is None else _i32(ring, "ring")),
                                     _ptr(None if ring_len is None else _i32(ring_len, "ring_len")),
-                                    c_int(ring.shape[1] if ring is not None else 0), _stream()))
+                                    c_int(ring.shape[1] if ring is not None else 0), c_int(1 if with_fault else 0),
+                                    _stream()))
 
 
 def apply_penalty_ring(logits: torch.Tensor, rows_info: torch.Tensor, penalty: torch.Tensor, window: torch.Tensor,

@@ -121,5 +121,18 @@ def reduce_partials(partial: torch.Tensor, bias: Optional[torch.Tensor], out: to
 
 
 def error_flag() -> int:
-    """Synchronises; non-zero if a tensor-core kernel gave up on one of its waits."""
+    """Synchronises; non-zero if a kernel gave up on one of its bounded waits since the flag was last
+    read (reading clears it).  1-3: a product kernel, 4: decode attention, 5-7: prompt attention,
+    8: the many-row norm."""
     return int(lib().infero_tc_error_flag())
+
+
+def clear_error_flag() -> None:
+    error_flag()
+
+
+def set_error_flag(value: int) -> None:
+    """Write the flag from the host: how tests exercise what the engine does after a wait ran out,
+    without any kernel missing one."""
+    if lib().infero_tc_set_error_flag(c_int(int(value))):
+        raise RuntimeError("cannot write the device's fault flag")

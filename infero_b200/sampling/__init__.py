@@ -1,4 +1,4 @@
 from .params import SamplingParams
-from .sampler import PendingTokens, ReadyTokens, RowSampler, sample_rows, sample_rows_async
+from .sampler import DeviceFault, PendingTokens, ReadyTokens, RowSampler, sample_rows, sample_rows_async
 
-__all__ = ["SamplingParams", "RowSampler", "sample_rows", "sample_rows_async", "PendingTokens", "ReadyTokens"]
+__all__ = ["SamplingParams", "RowSampler", "sample_rows", "sample_rows_async", "PendingTokens", "ReadyTokens", "DeviceFault"]

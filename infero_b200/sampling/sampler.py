@@ -39,15 +39,28 @@ class RowSampler:
         return sorted(Counter(recent).items())
 
 
+class DeviceFault(RuntimeError):
+    """A kernel of the step gave up on one of its bounded waits: its output is not to be trusted."""
+
+
 class PendingTokens:
-    """Tokens picked on the device, on their way to the host."""
+    """Tokens picked on the device, on their way to the host.  Behind the picks travels the device's
+    fault flag; ``result`` raises ``DeviceFault`` (and clears the flag) when a kernel of this step, or
+    of any step since the flag was last read, ran out of patience, so that the tokens of such a step
+    are never handed on."""
 
     def __init__(self, host: torch.Tensor, ready: "torch.cuda.Event", n: int):
         self._host, self._ready, self._n = host, ready, n
 
     def result(self) -> List[int]:
         self._ready.synchronize()
-        return [int(t) for t in self._host[:self._n].numpy()]
+        h = self._host.numpy()
+        if h.size > self._n and h[self._n] != 0:
+            from ..kernels import tc_gemm
+            code = int(h[self._n])
+            tc_gemm.clear_error_flag()
+            raise DeviceFault(f"a kernel's bounded wait ran out (code {code}); the step's output is discarded")
+        return [int(t) for t in h[:self._n]]
 
 
 class ReadyTokens:
@@ -116,17 +129,18 @@ def sample_rows_async(logits: torch.Tensor, samplers: Sequence[RowSampler], hist
             pen = np.array([s.params.repetition_penalty for s in samplers], dtype=np.float32)
             K.apply_penalty(logits, torch.from_numpy(toks).to(dev), torch.from_numpy(cnts).to(dev),
                             torch.from_numpy(pen).to(dev))
-    out = torch.empty(3 * R, dtype=torch.int32, device=dev)      # argmax | sampled | final
+    out = torch.empty(3 * R + 1, dtype=torch.int32, device=dev)  # argmax | sampled | final | the fault flag
     K.argmax(logits, out[:R])
     sampled = None
     if sampling:
         sampled = out[R:2 * R]
         K.sample(logits, on_dev[o:o + 4 * R].view(torch.float32), on_dev[o + 8 * R:o + 12 * R].view(torch.int32),
                  on_dev[o + 4 * R:o + 8 * R].view(torch.float32), on_dev[:8 * R].view(torch.float64), sampled)
-    keep = device_tokens if device_tokens is not None else out[2 * R:]      # slot -1: nothing is kept
+    keep = device_tokens if device_tokens is not None else out[2 * R:3 * R]      # slot -1: nothing is kept
     use_ring = ring is not None and slots is not None and device_tokens is not None
-    K.keep_tokens(out[:R], sampled, d_info, out[2 * R:], keep, ring if use_ring else None, ring_len if use_ring else None)
-    host = torch.empty(R, dtype=torch.int32, pin_memory=True)
+    K.keep_tokens(out[:R], sampled, d_info, out[2 * R:], keep, ring if use_ring else None, ring_len if use_ring else None,
+                  with_fault=True)
+    host = torch.empty(R + 1, dtype=torch.int32, pin_memory=True)
     host.copy_(out[2 * R:], non_blocking=True)
     ready = torch.cuda.Event()
     ready.record()

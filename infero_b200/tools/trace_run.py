@@ -41,6 +41,7 @@ def main(argv=None) -> int:
     from infero_b200 import kernels
     from infero_b200.config import EngineConfig
     from infero_b200.engine import ModelRunner, StepEntry
+    from infero_b200.kernels import tc_gemm
     from infero_b200.loading import load_model
 
     kernels.lib()
@@ -75,6 +76,11 @@ def main(argv=None) -> int:
                 arr.astype("<f4", copy=False).tofile(os.path.join(args.out, f"{step}.f32"))
             else:
                 torch.cuda.current_stream().synchronize()
+            fault = tc_gemm.error_flag()
+            if fault:
+                print(f"trace_run: step {step}: a kernel's bounded wait ran out (code {fault}); "
+                      "its logits are not to be trusted", file=sys.stderr, flush=True)
+                return 4
         for rid in rec.get("end", []):
             if rid in runner.manager.requests:
                 runner.close(rid)

@@ -7,8 +7,13 @@ and checks shapes separately, crates/model/src/weights.rs:1348-1460.)
 
 Precision policy.  ``bfloat16``: a tensor stored as BF16 stays bf16, F16 is widened through
 float32 and rounded to bf16 (the reference narrows BF16 to F16 instead,
-crates/safetensors/src/lib.rs:197-254), a tensor stored in 32-bit stays 32-bit, integer
-tables become int32.  ``float32``: every floating tensor becomes float32.
+crates/safetensors/src/lib.rs:197-254), integer tables become int32.  A tensor stored in
+32-bit stays 32-bit where the arithmetic is 32-bit anyway (norm weights, biases, and any role a
+part invents for itself); the operands of matrix products (roles ``matrix`` and ``embedding``)
+are rounded to bf16 once, here, because that is what the tensor-core kernels of a bfloat16
+engine multiply: a checkpoint stored in float32 then runs the same kernels as one stored in
+bf16 (the reference likewise narrows matrices and widens norms and biases to f32,
+crates/model/src/weights.rs:2063-2077).  ``float32``: every floating tensor becomes float32.
 """
 from __future__ import annotations
 
@@ -49,14 +54,17 @@ def check_names(decls: Iterable[TensorDecl], found: Dict[str, tuple], where: str
     raise WeightsError("\n".join(lines), missing, unexpected, wrong)
 
 
-def convert(t: torch.Tensor, mode: str) -> torch.Tensor:
+PRODUCT_ROLES = ("matrix", "embedding")
+
+
+def convert(t: torch.Tensor, mode: str, role: str = "matrix") -> torch.Tensor:
     """Apply the precision policy to one CPU tensor."""
     if not t.is_floating_point():
         return t.to(torch.int32)
     if mode == "float32":
         return t.to(torch.float32)
-    if t.dtype == torch.float32:
-        return t
+    if t.dtype in (torch.float32, torch.float64):
+        return t.to(torch.bfloat16) if role in PRODUCT_ROLES else t.to(torch.float32)
     if t.dtype == torch.float16:
         return t.to(torch.float32).to(torch.bfloat16)
     return t
@@ -72,5 +80,5 @@ def load_tensors(model_dir: str, decls: List[TensorDecl], mode: str, device) -> 
     for d in decls:
         if d.name not in files.entries:
             continue
-        out[d.name] = convert(files.tensor(d.name), mode).to(device)
+        out[d.name] = convert(files.tensor(d.name), mode, d.role).to(device)
     return out

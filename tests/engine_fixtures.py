@@ -11,7 +11,7 @@ import numpy as np
 import torch
 
 import plain_qwen2
-from tiny_configs import CONFIGS, NORM_STD
+from tiny_configs import CONFIGS, NORM_STD, STORE
 
 _TMP = tempfile.mkdtemp(prefix="infero_b200_tests_")
 
@@ -24,9 +24,11 @@ TOL = {"float32": 2e-5, "bfloat16": 3e-2}
 
 
 @functools.lru_cache(maxsize=None)
-def model_dir(name: str, store: str = "float32", seed: int = 1234, qk_gain: float = 1.0) -> str:
-    """A random model folder (made once per process, in a temporary folder)."""
+def model_dir(name: str, store: str = None, seed: int = 1234, qk_gain: float = 1.0) -> str:
+    """A random model folder (made once per process, in a temporary folder).  ``store``: the dtype
+    the tensors are written in (by default A, B, C in float32, D and E in bfloat16)."""
     from infero_b200.loading import write_random_model_dir
+    store = store or STORE[name]
     d = os.path.join(_TMP, f"tiny_{name}_{store}_{seed}_{qk_gain}")
     write_random_model_dir(d, CONFIGS[name], seed=seed, dtype=store, std=0.02 if qk_gain == 1.0 else 0.05,
                            norm_std=NORM_STD[name])

@@ -533,6 +533,122 @@ def test_decode_attention_fed_by_tma(H, Hkv, D, window, P, monkeypatch):
     assert tc_gemm.error_flag() == 0
 
 
+def _paged_requests(totals, Hkv, D, P, dt, seed, dead_before):
+    """Keys and values of requests of ``totals`` tokens on scattered pages.  Pages that lie wholly
+    before position ``dead_before[e]`` are not held any more (table entry -1), as after the cache
+    manager has taken back what a window passed.  Unused rows hold finite junk, as reused pages do."""
+    pages = sum(-(-L // P) for L in totals) + 5
+    rng = np.random.default_rng(seed)
+    perm = rng.permutation(pages)
+    table = torch.full((len(totals), max(-(-L // P) for L in totals) + 2), -1, dtype=torch.int32)
+    kc, vc = _rand((pages, Hkv, P, D), dt, 50 + seed), _rand((pages, Hkv, P, D), dt, 51 + seed)
+    Ks, Vs, nxt = [], [], 0
+    for e, L in enumerate(totals):
+        k, v = _rand((L, Hkv, D), dt, 60 + e), _rand((L, Hkv, D), dt, 80 + e)
+        Ks.append(k); Vs.append(v)
+        for b in range(-(-L // P)):
+            page = int(perm[nxt]); nxt += 1
+            m = min(P, L - b * P)
+            kc[page, :, :m] = k[b * P:b * P + m].transpose(0, 1)
+            vc[page, :, :m] = v[b * P:b * P + m].transpose(0, 1)
+            if b * P + P - 1 >= dead_before[e]:
+                table[e, b] = page
+    return table, kc, vc, Ks, Vs
+
+
+@pytest.mark.parametrize("H,Hkv,D", [(4, 2, 64), (7, 1, 128)])
+@pytest.mark.parametrize("window", [48, 100])
+@pytest.mark.parametrize("P", [16, 64])
+def test_window_edge_in_decode_attention_fed_by_tma(H, Hkv, D, window, P):
+    """The edge of the window, to the key.  From position p the keys p - W + 1 .. p are seen.  Requests
+    come in pairs of equal length: in the first of a pair key p - W + 1 (the oldest one inside) is given
+    a score that dominates head 0, so losing it shows; in the second key p - W (the youngest one
+    outside) gets that score, so seeing it shows.  Pages the window has passed are not held (-1)."""
+    from infero_b200.kernels import attention as A
+    assert A.lib().infero_attn_decode_tma_supported(D, P)
+    dt = torch.bfloat16
+    lengths = [L for L in (window + 1, window + 2, 129, 333, 700) for _ in (0, 1)]
+    n = len(lengths)
+    table, kc, vc, Ks, Vs = _paged_requests(lengths, Hkv, D, P, dt, 1, [L - window for L in lengths])
+    assert int((table == -1).sum(1).max()) > 2
+    scale = 1.0 / math.sqrt(D)
+    q = _rand((n, H * D), dt, 7)
+    q3 = q.view(n, H, D)
+    for e, L in enumerate(lengths):
+        p = L - 1
+        j = p - window + 1 if e % 2 == 0 else p - window
+        kk = Ks[e][j, 0].float()
+        q3[e, 0] = (kk * (7.0 / scale / float(kk @ kk))).to(dt)
+    positions = torch.tensor([L - 1 for L in lengths], dtype=torch.int32, device=DEV)
+    entry = torch.arange(n, dtype=torch.int32, device=DEV)
+    out = torch.zeros((n, H * D), dtype=dt, device=DEV)
+    A.attention_any(q, out, kc, vc, table.to(DEV), entry, positions, H, Hkv, D, P, window, scale,
+                    q_lens=[1] * n, pos0=[L - 1 for L in lengths])
+    for e, L in enumerate(lengths):
+        ref = _attention_ref(q3[e].double().cpu(), Ks[e].double().cpu(), Vs[e].double().cpu(), scale, window)
+        err = float((out[e].double().cpu().view(H, D) - ref).abs().max() / ref.abs().max())
+        what = "the oldest key inside the window was lost" if e % 2 == 0 else "the key just outside the window was seen"
+        assert err <= 1.5e-2, f"request {e} of {L} tokens: {err:.3e} ({what}?)"
+    from infero_b200.kernels import tc_gemm
+    assert tc_gemm.error_flag() == 0
+
+
+@pytest.mark.parametrize("H,Hkv,D", [(4, 2, 64), (7, 1, 128), (28, 4, 128)])
+@pytest.mark.parametrize("window", [64, 200])
+@pytest.mark.parametrize("P", [16, 64])
+def test_window_edge_in_prefill_attention_on_tensor_memory(H, Hkv, D, window, P):
+    """The same for prompt portions, at the rows where an off-by-one would hide: the first row after a
+    cut, the last row of a block of 128 rows, the first row of the next block, the last row of the
+    portion.  Requests come in pairs: key p - W + 1 dominant (must be seen) and key p - W dominant
+    (must not).  Pages that lie wholly before the portion's window are not held (-1)."""
+    from infero_b200.kernels import attention as A
+    dt = torch.bfloat16
+    portions = [(0, 300), (300, 260), (window + 13, 2), (511, 130)]
+    if H >= 28:
+        portions = [(0, 700), (300, 500), (window + 13, 2), (511, 130)]      # enough blocks for two heads per CTA
+    lens = [pn for pn in portions for _ in (0, 1)]
+    totals = [o + n for o, n in lens]
+    table, kc, vc, Ks, Vs = _paged_requests(totals, Hkv, D, P, dt, 3, [o - window + 1 for o, _ in lens])
+    T = sum(n for _, n in lens)
+    scale = 1.0 / math.sqrt(D)
+    qkv = _rand((T, (H + 2 * Hkv) * D), dt, 7)             # q sits in front of a wider row, as in the model
+    q = qkv[:, :H * D]
+    checked = []
+    t0 = 0
+    for e, (o, n) in enumerate(lens):
+        for i in sorted({0, 127, 128, 255, 256, n - 1}):
+            p = o + i
+            j = p - window + 1 if e % 2 == 0 else p - window
+            if i >= n or j < 0:
+                continue
+            kk = Ks[e][j, 0].float()
+            qkv[t0 + i, :D] = (kk * (7.0 / scale / float(kk @ kk))).to(dt)
+            checked.append((e, i, t0 + i))
+        t0 += n
+    assert len(checked) >= 20
+    positions = torch.tensor([o + i for o, n in lens for i in range(n)], dtype=torch.int32, device=DEV)
+    entry = torch.tensor([e for e, (_, n) in enumerate(lens) for _ in range(n)], dtype=torch.int32, device=DEV)
+    out = torch.zeros((T, H * D), dtype=dt, device=DEV)
+    assert A.prefill_tc_supported(q, out, D, P)
+    A.attention_any(q, out, kc, vc, table.to(DEV), entry, positions, H, Hkv, D, P, window, scale,
+                    q_lens=[n for _, n in lens], pos0=[o for o, _ in lens])
+    rows = {t for _, _, t in checked}
+    t = 0
+    for e, (o, n) in enumerate(lens):
+        for i in range(n):
+            if t in rows or i % 37 == 0:
+                L = o + i + 1
+                ref = _attention_ref(qkv[t, :H * D].double().cpu().view(H, D), Ks[e][:L].double().cpu(),
+                                     Vs[e][:L].double().cpu(), scale, window)
+                err = float((out[t].double().cpu().view(H, D) - ref).abs().max() / ref.abs().max())
+                what = "" if t not in rows else (" (the oldest key inside the window was lost?)" if e % 2 == 0
+                                                 else " (the key just outside the window was seen?)")
+                assert err <= 1.5e-2, f"request {e} (cached {o}), row {i}: {err:.3e}{what}"
+            t += 1
+    from infero_b200.kernels import tc_gemm
+    assert tc_gemm.error_flag() == 0
+
+
 def test_consumers_add_up_partial_products():
     """The fused consumers of split-K partial sums against the plain sum."""
     from infero_b200 import kernels as Kn
@@ -633,9 +749,76 @@ def test_sample_matches_host_statement(V, ties):
         assert int(out[r]) == want, f"row {r}"
 
 
+def _host_penalty(logits: np.ndarray, history, penalty: float, window: int, greedy: bool) -> np.ndarray:
+    """The reference's repetition penalty in NumPy, float32 like its logits
+    (crates/model/src/sampling.rs:249-298): over the last ``window`` tokens of the history a positive
+    logit is divided by the penalty and any other multiplied by it; the greedy scan marks tokens in a
+    bitset (:256-271), so each distinct token is penalised once, while the sampling path walks the
+    history (:284-297) and penalises once per occurrence."""
+    out = logits.astype(np.float32).copy()
+    pen = np.float32(penalty)
+    if penalty == 1.0 or not len(history):
+        return out
+    recent = list(history[max(0, len(history) - window):])
+    for t in (sorted(set(recent)) if greedy else recent):
+        if t < out.size:
+            out[t] = out[t] / pen if out[t] > 0 else out[t] * pen
+    return out
+
+
+def test_the_references_own_sampler_cases():
+    """The inputs and expected picks of the reference's sampler tests
+    (crates/model/src/sampling.rs:350-433), through the device sampler."""
+    from infero_b200.sampling import SamplingParams, sample_rows
+    from infero_b200.sampling.sampler import RowSampler
+
+    def pick(logits, params, history=()):
+        z = torch.tensor([logits], dtype=torch.float32, device=DEV)
+        return sample_rows(z, [RowSampler(params)], [list(history)])[0]
+
+    # greedy_takes_the_argmax (:350-355)
+    assert pick([0.1, 5.0, -2.0, 4.9], SamplingParams.greedy()) == 1
+    # top_k_1_is_greedy_even_at_temperature (:357-368)
+    s = RowSampler(SamplingParams(temperature=2.0, top_k=1))
+    for _ in range(20):
+        z = torch.tensor([[0.1, 5.0, -2.0]], dtype=torch.float32, device=DEV)
+        assert sample_rows(z, [s], [[]])[0] == 1
+    # top_p_confines_sampling_to_the_nucleus (:388-405): one token holds nearly all the mass
+    logits = [0.0] * 100
+    logits[7] = 20.0
+    s = RowSampler(SamplingParams(temperature=1.0, top_p=0.9, top_k=100, repetition_penalty=1.0, seed=1))
+    for _ in range(50):
+        z = torch.tensor([logits], dtype=torch.float32, device=DEV)
+        assert sample_rows(z, [s], [[]])[0] == 7
+    # repetition_penalty_demotes_recent_tokens (:407-419)
+    p = SamplingParams(temperature=0.0, repetition_penalty=2.0, repetition_window=8)
+    assert pick([1.0, 1.1, 1.0], p) == 1
+    assert pick([1.0, 1.1, 1.0], p, [1]) != 1
+    assert pick([1.0, 1.1, 1.0], p, [1]) == 0           # the tie goes to the lowest index (:302-310)
+    # negative_logits_are_penalised_downward (:421-433)
+    p = SamplingParams(temperature=0.0, repetition_penalty=2.0)
+    assert pick([-1.0, -1.5], p) == 0
+    assert pick([-1.0, -1.5], p, [0]) == 1
+    # selection_picks_the_same_top_k_as_a_sort (:326-348): 200 draws stay inside the true top 20
+    logits = [((i * 7919) % 5000) * 0.01 for i in range(5000)]
+    allowed = set(np.argsort(-np.asarray(logits, dtype=np.float32), kind="stable")[:20].tolist())
+    s = RowSampler(SamplingParams(temperature=1.0, top_k=20, top_p=1.0, repetition_penalty=1.0, seed=9))
+    z = torch.tensor([logits], dtype=torch.float32, device=DEV)
+    for _ in range(200):
+        assert sample_rows(z.clone(), [s], [[]])[0] in allowed
+    # a_seed_makes_sampling_reproducible (:370-386)
+    logits = [i * 0.1 for i in range(64)]
+    runs = []
+    for _ in range(2):
+        s = RowSampler(SamplingParams(seed=42, temperature=1.0, top_k=64, top_p=1.0, repetition_penalty=1.0))
+        z = torch.tensor([logits], dtype=torch.float32, device=DEV)
+        runs.append([sample_rows(z.clone(), [s], [[]])[0] for _ in range(32)])
+    assert runs[0] == runs[1] and len(set(runs[0])) > 4
+
+
 def test_penalty_from_the_device_history_equals_the_host_statement():
-    """Rows whose generated tokens live in a ring on the device (appended by keep_tokens) against the
-    pairs the host works out from the same histories: windows shorter and longer than the history, a
+    """Rows whose generated tokens live in a ring on the device (appended by keep_tokens) against a
+    NumPy statement of the reference's rule over the same histories: windows shorter and longer than the history, a
     ring that has wrapped, greedy rows (once per distinct token) beside sampled ones (once per
     occurrence), a row without a penalty."""
     from infero_b200 import kernels as Kn
@@ -662,8 +845,11 @@ def test_penalty_from_the_device_history_equals_the_host_statement():
               SamplingParams(temperature=0.0, repetition_penalty=1.05, repetition_window=20),
               SamplingParams(temperature=0.5, repetition_penalty=1.2, repetition_window=32)]
     z0 = torch.from_numpy(rng.normal(size=(slots_n, V)).astype(np.float32) * 2).to(DEV)
-    # host statement: pairs from the last `window` tokens
-    want = z0.clone()
+    want = torch.from_numpy(np.stack([_host_penalty(z0[r].cpu().numpy(), hists[r], params[r].repetition_penalty,
+                                                    params[r].repetition_window, params[r].is_greedy())
+                                      for r in range(slots_n)])).to(DEV)
+    # the other route of the product (pairs worked out on the host, applied by apply_penalty) gives the same
+    via_pairs = z0.clone()
     pairs = [RowSampler(p).penalty_pairs(h) for p, h in zip(params, hists)]
     width = max(len(p) for p in pairs)
     toks = np.full((slots_n, width), -1, dtype=np.int32)
@@ -671,8 +857,9 @@ def test_penalty_from_the_device_history_equals_the_host_statement():
     for r, p in enumerate(pairs):
         for i, (t, c) in enumerate(p):
             toks[r, i], cnts[r, i] = t, c
-    Kn.apply_penalty(want, torch.from_numpy(toks).to(DEV), torch.from_numpy(cnts).to(DEV),
+    Kn.apply_penalty(via_pairs, torch.from_numpy(toks).to(DEV), torch.from_numpy(cnts).to(DEV),
                      torch.tensor([p.repetition_penalty for p in params], dtype=torch.float32, device=DEV))
+    assert torch.equal(via_pairs, want)
     got = z0.clone()
     info = torch.tensor(list(range(slots_n)) + [0 if p.is_greedy() else 1 for p in params], dtype=torch.int32, device=DEV)
     Kn.apply_penalty_ring(got, info, torch.tensor([p.repetition_penalty for p in params], dtype=torch.float32, device=DEV),

@@ -8,15 +8,45 @@ from tiny_configs import CONFIGS
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [40, 1, 17, 33, 64, 90], "B": [120, 3, 70, 49, 97, 130], "C": [150, 31, 66]}
-CASES = [(n, d) for n in ("A", "B", "C") for d in ("float32", "bfloat16")]
+LENGTHS = {"A": [40, 1, 17, 33, 64, 90], "B": [120, 3, 70, 49, 97, 130], "C": [150, 31, 66],
+           "D": [150, 3, 70, 49, 97, 300], "E": [290, 31, 66, 130]}
+CASES = [(n, d) for n in ("A", "B", "C", "D", "E") for d in ("float32", "bfloat16")]
+# configurations whose bfloat16 steps must go through the kernels serving uses (head sizes 64 and 128)
+SERVING_PATH = ("D", "E")
+
+
+class ServingPath:
+    """Around a bfloat16 run of a SERVING_PATH configuration: proves which path ran.  Layers went
+    through the native launcher of the built-in block (which launches the tensor-core products, the
+    TMA-fed decode attention and the tcgen05 prompt attention, and nothing else), and no bounded
+    wait of those kernels ran out."""
+
+    def __init__(self, name, dtype):
+        self.on = name in SERVING_PATH and dtype == "bfloat16"
+
+    def __enter__(self):
+        if self.on:
+            from infero_b200.kernels import tc_gemm
+            from infero_b200.parts import native_block
+            tc_gemm.clear_error_flag()
+            self.calls = native_block.CALLS[0]
+        return self
+
+    def __exit__(self, *exc):
+        if self.on and exc[0] is None:
+            from infero_b200.kernels import tc_gemm
+            from infero_b200.parts import native_block
+            assert native_block.CALLS[0] > self.calls, "no layer went through the native launcher"
+            assert tc_gemm.error_flag() == 0, "a bounded wait of a tensor-core kernel ran out"
+        return False
 
 
 def _check(name, dtype, steps, reqs, mdir, max_tokens=None, page_size=16):
     plain = plain_logits(mdir, reqs)
     n = max_tokens or R.max_live_tokens(steps, reqs)
     runner = make_runner(mdir, dtype, n, page_size=page_size)
-    got = R.replay_inprocess(runner, steps)
+    with ServingPath(name, dtype):
+        got = R.replay_inprocess(runner, steps)
     assert got, "the trace asked for no logits"
     err, where = R.compare(got, plain)
     assert err <= TOL[dtype], f"{name} {dtype}: relative error {err:.3e} at {where}"
@@ -99,27 +129,29 @@ def test_sharp_attention(name, dtype):
     # score s carries an error near |s| * 2^-8 that the softmax turns into the same relative
     # error of a weight; the gain is set so that scores spread by about +-2 (max near 9),
     # which keeps single keys dominant (weights differ by e^4) and the rounding inside TOL.
-    gain = {"A": 6.0, "B": 4.5, "C": 3.0}[name] if dtype == "float32" else {"A": 3.6, "B": 2.8, "C": 1.9}[name]
+    gain = ({"A": 6.0, "B": 4.5, "C": 3.0, "D": 3.9, "E": 2.4}[name] if dtype == "float32" else
+            {"A": 3.6, "B": 2.8, "C": 1.9, "D": 2.5, "E": 1.75}[name])
     mdir = model_dir(name, qk_gain=gain)
     reqs = make_requests(name, LENGTHS[name][:4], seed=7)
     _check(name, dtype, R.steps_mixed(reqs, seed=3, max_live=3), reqs, mdir)
     _check(name, dtype, R.steps_tail_decode(reqs, 32), reqs, mdir)
 
 
+@pytest.mark.parametrize("name", ["B", "D"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("page_size", [32, 64])
-def test_other_page_sizes(dtype, page_size):
-    mdir = model_dir("B")
-    reqs = make_requests("B", [130, 70, 65, 100, 127], seed=4)
+def test_other_page_sizes(name, dtype, page_size):
+    mdir = model_dir(name)
+    reqs = make_requests(name, [130, 70, 65, 100, 127], seed=4)
     steps = R.steps_mixed(reqs, seed=9, max_live=3)
-    _check("B", dtype, steps, reqs, mdir, page_size=page_size)
+    _check(name, dtype, steps, reqs, mdir, page_size=page_size)
 
 
 @pytest.mark.parametrize("name,dtype", CASES)
 def test_long_decoding(name, dtype):
     """One prompt token, then every further token alone: hundreds of single-token steps."""
     mdir = model_dir(name)
-    n = {"A": 250, "B": 400, "C": 300}[name]
+    n = {"A": 250, "B": 400, "C": 300, "D": 400, "E": 600}[name]
     reqs = make_requests(name, [n], seed=11)
     steps = R.steps_tail_decode(reqs, tail=n - 1)
     _check(name, dtype, steps, reqs, mdir)
@@ -160,7 +192,8 @@ def test_trace_run_program(tmp_path, dtype):
     assert err <= TOL[dtype], f"trace_run {dtype}: relative error {err:.3e} at {where}"
 
 
-@pytest.mark.parametrize("name,dtype", [("B", "bfloat16"), ("C", "bfloat16"), ("B", "float32")])
+@pytest.mark.parametrize("name,dtype", [("B", "bfloat16"), ("C", "bfloat16"), ("B", "float32"), ("D", "bfloat16"),
+                                        ("E", "bfloat16")])
 def test_captured_decode_steps_equal_eager_ones(name, dtype):
     """Decode steps replayed from a captured CUDA graph give the logits of eager steps, while
     requests grow across pages and the batch changes size."""
@@ -175,13 +208,14 @@ def test_captured_decode_steps_equal_eager_ones(name, dtype):
         runner.open(rid)
         runner.step([StepEntry(rid, toks[:head], [])])
     worst = 0.0
-    for p in range(head, 70):
-        live = [rid for rid, toks in reqs.items() if p < len(toks)]
-        logits = runner.step([StepEntry(rid, [reqs[rid][p]], [0]) for rid in live])
-        got = logits.float().cpu().numpy()
-        for i, rid in enumerate(live):
-            ref = plain[rid][p]
-            worst = max(worst, float(np.abs(got[i] - ref).max() / np.abs(plain[rid]).max()))
+    with ServingPath(name, dtype):
+        for p in range(head, 70):
+            live = [rid for rid, toks in reqs.items() if p < len(toks)]
+            logits = runner.step([StepEntry(rid, [reqs[rid][p]], [0]) for rid in live])
+            got = logits.float().cpu().numpy()
+            for i, rid in enumerate(live):
+                ref = plain[rid][p]
+                worst = max(worst, float(np.abs(got[i] - ref).max() / np.abs(plain[rid]).max()))
     assert runner.graph_captures >= 2 and runner.graph_replays > 40
     assert worst <= TOL[dtype], f"{name} {dtype}: relative error {worst:.3e}"
     torch.cuda.synchronize()
@@ -371,3 +405,51 @@ def test_default_sampling_runs_ahead_and_changes_no_token(dtype):
     assert results[0] == results[1], "running ahead changed a token"
     if len(results) > 2:
         assert results[0] == results[2], "a preempted request did not continue with its history"
+
+
+def test_a_missed_wait_fails_the_step_and_leaves_the_engine_usable():
+    """The flag that kernels raise when one of their bounded waits runs out travels to the host with
+    the picked tokens.  Here the host sets it (no kernel has to miss a wait): the next step's tokens are
+    not handed on, every request ends with an error, nothing stays in the cache, and the same engine
+    then serves a new request as if nothing had happened."""
+    import plain_qwen2
+    from engine_fixtures import plain_model
+    from infero_b200.engine import Engine
+    from infero_b200.kernels import tc_gemm
+    from infero_b200.sampling import SamplingParams
+    mdir = model_dir("D", seed=77, qk_gain=1.5)
+    reqs = make_requests("D", [20, 9, 33], seed=5)
+    pick = SamplingParams(temperature=0.0, repetition_penalty=1.0)
+    eng = Engine(mdir, dtype="bfloat16", ctx=128, max_seqs=4, kv_slots=512, max_batch_tokens=64)
+    tc_gemm.clear_error_flag()
+    for rid, toks in reqs.items():
+        eng.add_request(toks, pick, max_new_tokens=30, ignore_eos=True, rid=rid)
+    seen = []
+    for _ in range(4):
+        seen += eng.step()
+    assert seen and all(ev.reason != "error" for ev in seen)
+    tc_gemm.set_error_flag(4)
+    events = []
+    for _ in range(3):                       # (a step that ran ahead may still deliver the step before)
+        events += eng.step()
+        if any(ev.reason == "error" for ev in events):
+            break
+    failed = {ev.rid for ev in events if ev.finished and ev.reason == "error"}
+    assert failed == set(reqs), f"requests that ended with an error: {failed}"
+    assert any("bounded wait" in (ev.message or "") for ev in events)
+    assert eng.is_idle() and not eng.runner.manager.requests
+    eng.runner.manager.check()
+    for a in eng.runner.manager.allocators:
+        assert a.num_free == a.num_pages
+    assert tc_gemm.error_flag() == 0, "the flag was not cleared"
+    # the engine is still good
+    cfg, w = plain_model(mdir)
+    prompt = make_requests("D", [17], seed=6)["r0"]
+    got = eng.generate([prompt], pick, max_new_tokens=6, ignore_eos=True)[0]
+    want = plain_qwen2.greedy_generate(cfg, w, prompt, 6)
+    assert len(got) == 6
+    for i in range(6):
+        if got[i] != want[i]:
+            row = plain_qwen2.forward(cfg, w, list(prompt) + want[:i])[-1]
+            assert float(row.max() - row[got[i]]) / float(row.abs().max()) <= TOL["bfloat16"]
+            break

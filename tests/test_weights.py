@@ -58,10 +58,14 @@ def test_precision_policy(tmp_path):
             "c": torch.tensor([0.5, 1.5], dtype=torch.float16), "d": torch.tensor([1, 2, 3])}
     write_safetensors(p, decls, lambda n: vals[n])
     from infero_b200.parts.base import TensorDecl
-    ds = [TensorDecl(n, s) for n, _, s in decls]
+    ds = [TensorDecl(n, s, role="norm" if n == "b" else "matrix") for n, _, s in decls]
     bf = load_tensors(str(tmp_path), ds, "bfloat16", "cpu")
     assert bf["a"].dtype == torch.bfloat16      # stored bf16 stays bf16
-    assert bf["b"].dtype == torch.float32       # stored in 32-bit stays so
+    assert bf["b"].dtype == torch.float32       # a norm weight stored in 32-bit stays so
+    as_matrix = load_tensors(str(tmp_path), [TensorDecl(n, s) for n, _, s in decls], "bfloat16", "cpu")
+    assert as_matrix["b"].dtype == torch.bfloat16   # an operand of a matrix product is rounded once
+    as_own = load_tensors(str(tmp_path), [TensorDecl(n, s, role="decay") for n, _, s in decls], "bfloat16", "cpu")
+    assert as_own["b"].dtype == torch.float32       # a role a part invents keeps what was stored
     assert bf["c"].dtype == torch.bfloat16      # f16 becomes bf16
     assert bf["d"].dtype == torch.int32         # integer tables as int32
     f32 = load_tensors(str(tmp_path), ds, "float32", "cpu")

@@ -5,7 +5,8 @@ their own start-up code, or a late allocation could stall or fail), so
 ``infero_attn_decode_static`` keeps the scratch for its context splits in a fixed array
 inside the library.  This test calls it through its exported C symbol, twice in a row (the
 second call finds the first one's leftovers in the shared array), and compares each result
-with what ``infero_attn_decode`` gives with scratch from the caller.  It is collected last
+with what ``infero_attn_decode`` gives with scratch from the caller, and both with a float64
+statement of the same attention over the same pages.  It is collected last
 so that a run that stops at the first failure has already run every other test.
 """
 import ctypes
@@ -37,6 +38,26 @@ def _case(seed, n_tok, H, Hkv, D, lengths, page=16):
     positions = torch.tensor([L - 1 for L in lengths], dtype=torch.int32)
     entry = torch.arange(n_tok, dtype=torch.int32)
     return [t.to(DEV) for t in (q, kc, vc, table, entry, positions)]
+
+
+def _reference(q, kc, vc, table, positions, H, Hkv, D, window, page=16):
+    """softmax(q K^T / sqrt(D)) V per token and head in float64, keys gathered through the block
+    table: key j is seen from position p iff j <= p and (no window or p - j < window)."""
+    q, kc, vc = q.double().cpu(), kc.double().cpu(), vc.double().cpu()
+    table, positions = table.cpu(), positions.cpu()
+    n_tok, g = q.shape[0], H // Hkv
+    out = torch.zeros((n_tok, H, D), dtype=torch.float64)
+    for t in range(n_tok):
+        p = int(positions[t])
+        lo = max(0, p - window + 1) if window else 0
+        js = torch.arange(lo, p + 1)
+        pages = table[t, js // page].long()
+        for h in range(H):
+            keys = kc[pages, h // g, js % page]               # [n, D]
+            vals = vc[pages, h // g, js % page]
+            w = torch.softmax(keys @ q[t, h * D:(h + 1) * D] / math.sqrt(D), dim=0)
+            out[t, h] = w @ vals
+    return out.reshape(n_tok, H * D).numpy()
 
 
 def _args(q, out, kc, vc, table, entry, positions, n_tok, H, Hkv, D, page, window, chunk, splits):
@@ -78,6 +99,10 @@ def test_static_scratch_decode_matches_the_allocating_entry_point():
         worst = float(np.abs(got - ref).max() / np.abs(ref).max())
         assert worst <= 1.5e-2, f"call {seed}: relative difference {worst:.3e}"   # the kernel tests' bf16 bound
         assert np.abs(ref).max() > 0
+        exact = _reference(q, kc, vc, table, positions, H, Hkv, D, window)
+        for name, arr in (("the static entry point", got), ("the allocating entry point", ref)):
+            worst = float(np.abs(arr - exact).max() / np.abs(exact).max())
+            assert worst <= 1.5e-2, f"call {seed}: {name} is {worst:.3e} from the float64 statement"
 
 
 def test_static_scratch_refuses_what_does_not_fit():

@@ -25,8 +25,29 @@ TINY_C = {
     "max_position_embeddings": 1024, "hidden_act": "silu",
 }
 
-NORM_STD = {"A": 0.0, "B": 0.1, "C": 0.1}
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# Two shapes with the head sizes real checkpoints have (64 and 128), stored in bf16: a bfloat16 engine
+# runs them through the kernels serving uses (tensor-core products, TMA-fed decode attention,
+# tcgen05 prompt attention, the native launcher of the built-in block).
+TINY_D = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 3, "hidden_size": 128, "num_attention_heads": 4, "num_key_value_heads": 2,
+    "head_dim": 64, "intermediate_size": 320, "vocab_size": 408, "rope_theta": 20000.0,
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "use_sliding_window": True,
+    "sliding_window": 48, "max_window_layers": 1, "max_position_embeddings": 512, "hidden_act": "silu",
+}
+
+TINY_E = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 2, "hidden_size": 256, "num_attention_heads": 2, "num_key_value_heads": 1,
+    "head_dim": 128, "intermediate_size": 616, "vocab_size": 650, "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "use_sliding_window": False,
+    "max_position_embeddings": 1024, "hidden_act": "silu",
+}
+
+NORM_STD = {"A": 0.0, "B": 0.1, "C": 0.1, "D": 0.1, "E": 0.05}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
+# how the test folders of a configuration are stored
+STORE = {"A": "float32", "B": "float32", "C": "float32", "D": "bfloat16", "E": "bfloat16"}
 
 
 def write_model(tmpdir, name, seed=1234, dtype="float32"):
