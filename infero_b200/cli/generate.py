@@ -1,12 +1,17 @@
 """generate: run one prompt through a model and report prefill and decode speed.
 
-    python -m infero_b200.cli.generate <model_dir> [token ids...] [--greedy] [-n N]
+    generate <model_dir> [token ids...] [--greedy] [-n N]
+    generate --model <model_dir> --prompt-ids 5,17,3 -n 32 --temperature 0.7 --top-k 20 --top-p 0.8
+    generate --config <config.json> --random-weights --seed 3 --prompt-len 64 --dtype float32
+             --max-seq-len 512 --page-size 16 --num-pages 40
 
 After the reference's example (crates/model/examples/generate.rs:26-161): the positional
 words after the model are the prompt, ``--greedy`` fixes the sampler, ``-n`` caps the
 generation (128), ``GEN_CTX`` sets the context (4096), and the report lines have its form.
 There is no tokenizer in this engine, so the prompt is token ids (``--raw`` is accepted and
 changes nothing); ``--prompt-len L`` makes a seeded random prompt instead.
+``--max-seq-len`` is the context (it wins over ``GEN_CTX``), ``--page-size`` and ``--num-pages``
+the geometry of the cache pool (by default one context's worth of pages).
 ``--kv-quant`` only takes the unquantised cache and ``--gpu-layers`` is not taken at all:
 quantised caches and host offload are not built.
 """
@@ -21,13 +26,21 @@ import time
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="generate")
-    ap.add_argument("model", help="model folder (config.json + model.safetensors), or a config.json with --random-weights")
+    ap.add_argument("model", nargs="?", default=None,
+                    help="model folder (config.json + model.safetensors), or a config.json with --random-weights")
     ap.add_argument("prompt", nargs="*", help="prompt token ids")
+    ap.add_argument("--model", dest="model_opt", default=None, help="the model folder, as an option")
+    ap.add_argument("--config", default=None, help="a config.json (with --random-weights)")
+    ap.add_argument("--prompt-ids", default=None, help="prompt token ids, comma-separated")
     ap.add_argument("--raw", action="store_true", help="accepted for compatibility; prompts are always raw ids")
     ap.add_argument("--greedy", action="store_true")
     ap.add_argument("-n", type=int, default=128, dest="max_new")
     ap.add_argument("--kv-quant", default="f16")
-    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32", "bf16", "fp32"])
+    ap.add_argument("--max-seq-len", type=int, default=None, help="context length (default: GEN_CTX, else 4096)")
+    ap.add_argument("--page-size", type=int, default=16, choices=[16, 32, 64])
+    ap.add_argument("--num-pages", type=int, default=None, help="pages in the cache pool (default: one context's worth)")
+    ap.add_argument("--repetition-penalty", type=float, default=None)
     ap.add_argument("--prompt-len", type=int, default=None)
     ap.add_argument("--random-weights", action="store_true", help="MODEL is a config.json; weights are drawn from --seed")
     ap.add_argument("--seed", type=int, default=0)
@@ -38,6 +51,18 @@ def main(argv=None) -> int:
     ap.add_argument("--no-warmup", action="store_true",
                     help="time the very first run (kernel loading and graph capture included)")
     args = ap.parse_args(argv)
+    if args.model_opt is not None or args.config is not None:
+        if args.model is not None:               # with --model / --config every positional word is the prompt
+            args.prompt = [args.model] + list(args.prompt)
+        args.model = args.model_opt if args.model_opt is not None else args.config
+        if args.config is not None and not args.random_weights:
+            print("generate: --config needs --random-weights (a configuration alone has no weights)", file=sys.stderr)
+            return 2
+    if args.model is None:
+        ap.print_usage(sys.stderr)
+        print("generate: no model given", file=sys.stderr)
+        return 2
+    args.dtype = {"bf16": "bfloat16", "fp32": "float32"}.get(args.dtype, args.dtype)
     if args.kv_quant not in ("f16", "bf16", "none"):
         print(f"generate: --kv-quant {args.kv_quant}: quantised caches are not built (f16 only)", file=sys.stderr)
         return 2
@@ -47,15 +72,19 @@ def main(argv=None) -> int:
     from infero_b200.engine import Engine
     from infero_b200.sampling import SamplingParams
 
-    ctx = int(os.environ.get("GEN_CTX", "4096"))
-    kw = dict(dtype=args.dtype, ctx=ctx, max_seqs=1, kv_slots=ctx, max_batch_tokens=min(ctx, 2048))
+    ctx = args.max_seq_len if args.max_seq_len is not None else int(os.environ.get("GEN_CTX", "4096"))
+    slots = args.num_pages * args.page_size if args.num_pages is not None else ctx
+    kw = dict(dtype=args.dtype, ctx=ctx, max_seqs=1, kv_slots=slots, page_size=args.page_size,
+              max_batch_tokens=min(ctx, 2048))
     if args.random_weights:
         with open(args.model) as f:
             eng = Engine(config=json.load(f), seed=args.seed, **kw)
     else:
         eng = Engine(args.model, **kw)
     vocab = eng.model.spec.vocab_size
-    if args.prompt:
+    if args.prompt_ids is not None:
+        tokens = [int(t) for t in args.prompt_ids.split(",") if t.strip()]
+    elif args.prompt:
         tokens = [int(t) for word in args.prompt for t in word.split(",") if t]
     else:
         rng = random.Random(args.seed)
@@ -67,6 +96,8 @@ def main(argv=None) -> int:
         params.top_k = args.top_k
     if args.top_p is not None:
         params.top_p = args.top_p
+    if args.repetition_penalty is not None:
+        params.repetition_penalty = args.repetition_penalty
 
     print(f"--- prompt ({len(tokens)} tokens) ---")
     print(" ".join(map(str, tokens)) + "\n")

@@ -140,13 +140,22 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], token_ids: List[int]) -> torc
     return x @ head.T
 
 
-def greedy_generate(cfg: dict, w: Dict[str, torch.Tensor], prompt: List[int], n: int) -> List[int]:
+def greedy_generate(cfg: dict, w: Dict[str, torch.Tensor], prompt: List[int], n: int,
+                    repetition_penalty: float = 1.0, repetition_window: int = 256) -> List[int]:
     """Argmax continuation, recomputing the whole sequence each step; ties -> lowest index
-    (crates/model/src/sampling.rs:302-310)."""
+    (crates/model/src/sampling.rs:302-310).  With a repetition penalty, the logit of every distinct
+    token among the last ``repetition_window`` generated ones is divided by it when positive and
+    multiplied by it otherwise before the argmax (crates/model/src/sampling.rs:249-277; the logits are
+    32-bit there, so the penalised values are rounded to 32-bit here too)."""
     seq = list(prompt)
     out = []
     for _ in range(n):
         logits = forward(cfg, w, seq)[-1]
+        if repetition_penalty != 1.0 and out:
+            logits = logits.to(torch.float32)
+            pen = torch.tensor(repetition_penalty, dtype=torch.float32)
+            for t in set(out[-repetition_window:]):
+                logits[t] = logits[t] / pen if logits[t] > 0 else logits[t] * pen
         nxt = int(torch.argmax(logits))          # torch.argmax returns the first maximum
         out.append(nxt)
         seq.append(nxt)
