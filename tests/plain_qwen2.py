@@ -44,7 +44,7 @@ def rope_neox(x: torch.Tensor, positions: torch.Tensor, theta: float, rotary_dim
     """crates/metal/examples/qwen2_f16.rs:803-817; crates/kernels/src/cpu/mod.rs:275-314.
     x [T, heads, d]; pairs (i, i + rotary_dim/2); inv = theta^(-2i/rotary_dim)."""
     half = rotary_dim // 2
-    i = torch.arange(half, dtype=torch.float64)
+    i = torch.arange(half, dtype=torch.float64, device=x.device)
     inv = (theta ** (-2.0 * i / rotary_dim)).to(x.dtype)
     ang = positions.to(x.dtype)[:, None] * inv[None, :]            # [T, half]
     c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
@@ -64,7 +64,7 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
     Hkv = k.shape[1]
     group = H // Hkv
     out = torch.zeros_like(q)
-    pos = torch.arange(T)
+    pos = torch.arange(T, device=q.device)
     visible = pos[None, :] <= pos[:, None]
     if window is not None:
         visible &= (pos[:, None] - pos[None, :]) < window
@@ -130,9 +130,10 @@ def decoder_layer(x: torch.Tensor, w: Dict[str, torch.Tensor], cfg: dict, i: int
 def forward(cfg: dict, w: Dict[str, torch.Tensor], token_ids: List[int]) -> torch.Tensor:
     """Logits [T, vocab] for one whole sequence (crates/metal/examples/qwen2_f16.rs:819-939:
     embedding row, layers, final norm, head = lm_head or the embedding when tied)."""
-    ids = torch.as_tensor(token_ids, dtype=torch.long)
+    dev = w["model.embed_tokens.weight"].device       # (a test may hold the weights on a GPU to save time)
+    ids = torch.as_tensor(token_ids, dtype=torch.long, device=dev)
     x = w["model.embed_tokens.weight"][ids]
-    positions = torch.arange(len(token_ids))
+    positions = torch.arange(len(token_ids), device=dev)
     for i in range(cfg["num_hidden_layers"]):
         x = decoder_layer(x, w, cfg, i, positions)
     x = rms_norm(x, w["model.norm.weight"], cfg.get("rms_norm_eps", 1e-5))

@@ -65,3 +65,57 @@ def test_serving_sizes_bfloat16_against_32_bit(name):
     err = float((a - b).abs().max() / a.abs().max())
     assert err <= 3e-2, f"{name}: bfloat16 differs from the 32-bit path by {err:.3e} of the largest logit"
     assert tc_gemm.error_flag() == 0
+
+
+# ---- the measured model's layer widths against the plain implementation ------------------------------
+WIDTHS_7B = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", hidden_act="silu", num_hidden_layers=2,
+                 hidden_size=3584, num_attention_heads=28, num_key_value_heads=4, head_dim=128,
+                 intermediate_size=18944, vocab_size=2999, rms_norm_eps=1e-6, rope_theta=1e6,
+                 tie_word_embeddings=False, max_position_embeddings=4096)
+_WIDE = {}
+
+
+def _wide_model():
+    """Two layers of the measured 7B widths (group 7, hidden 3584, feed-forward 18944) with the
+    vocabulary cut to 2,999 rows so that the head stays cheap: a folder of bf16 tensors, and the plain
+    implementation's float64 copy of it on the GPU (torch is the oracle's arithmetic, not the engine's)."""
+    if not _WIDE:
+        import os
+        import tempfile
+        import plain_qwen2
+        from infero_b200.loading import write_random_model_dir
+        d = os.path.join(tempfile.mkdtemp(prefix="infero_b200_wide_"), "m")
+        write_random_model_dir(d, WIDTHS_7B, seed=11, dtype="bfloat16", std=0.02, norm_std=0.1)
+        cfg, w = plain_qwen2.read_model(d, torch.float64)
+        _WIDE.update(dir=d, cfg=cfg, w={k: v.to("cuda:0") for k, v in w.items()})
+    return _WIDE
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_measured_widths_equal_the_plain_implementation(dtype):
+    """The four cuts (whole, last 32 one by one, changing portions, mixed with page reuse) at the widths
+    the benchmark runs, in true 32-bit against the plain implementation (2e-5 of the largest logit) and
+    in bfloat16 through the serving kernels."""
+    import plain_qwen2
+    import replay_util as R
+    from engine_fixtures import TOL, make_runner
+    from infero_b200.kernels import tc_gemm
+    from infero_b200.parts import native_block
+    m = _wide_model()
+    rng = random.Random(2)
+    reqs = {f"r{i}": [rng.randrange(WIDTHS_7B["vocab_size"]) for _ in range(n)]
+            for i, n in enumerate([300, 40, 129, 70, 205])}
+    plain = {rid: plain_qwen2.forward(m["cfg"], m["w"], toks).cpu().numpy() for rid, toks in reqs.items()}
+    cuts = {"whole": R.steps_whole(reqs), "last 32 one by one": R.steps_tail_decode(reqs, 32),
+            "changing portions": R.steps_chunked(reqs, seed=1), "mixed": R.steps_mixed(reqs, seed=2, max_live=3)}
+    calls = native_block.CALLS[0]
+    for what, steps in cuts.items():
+        runner = make_runner(m["dir"], dtype, R.max_live_tokens(steps, reqs))
+        got = R.replay_inprocess(runner, steps)
+        err, where = R.compare(got, plain)
+        assert err <= TOL[dtype], f"{what}, {dtype}: relative error {err:.3e} at {where}"
+        if what == "mixed":
+            assert runner.manager.pages_reused > 0
+        del runner
+    if dtype == "bfloat16":
+        assert native_block.CALLS[0] > calls and tc_gemm.error_flag() == 0
