@@ -1,6 +1,5 @@
-from .manager import CacheManager, GroupSpec, OutOfSlots, RequestCache
-from .pages import OutOfPages, PageAllocator
-from .storage import CacheStorage, LayerKv, group_cache_slots
+from .manager import CacheManager, GroupSpec, OutOfPages, OutOfSlots, RequestCache
+from .storage import CacheStorage, LayerKv, group_cache_slots, plan_group_pages
 
-__all__ = ["CacheManager", "GroupSpec", "OutOfSlots", "RequestCache", "OutOfPages", "PageAllocator",
-           "CacheStorage", "LayerKv", "group_cache_slots"]
+__all__ = ["CacheManager", "GroupSpec", "OutOfSlots", "RequestCache", "OutOfPages",
+           "CacheStorage", "LayerKv", "group_cache_slots", "plan_group_pages"]

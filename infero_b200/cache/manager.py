@@ -24,7 +24,13 @@ from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
 import numpy as np
 
-from .pages import OutOfPages
+
+class OutOfPages(RuntimeError):
+    """The pool of a group cannot supply the pages asked for.  Nothing was taken."""
+
+    def __init__(self, group: int, wanted: int, free: int):
+        super().__init__(f"cache group {group}: {wanted} pages wanted, {free} free")
+        self.group, self.wanted, self.free = group, wanted, free
 
 
 class OutOfSlots(RuntimeError):
@@ -89,7 +95,7 @@ class _AllocatorView:
 
     def __init__(self, manager: "CacheManager", group: int):
         self._m, self.group = manager, group
-        self.num_pages = manager.num_pages
+        self.num_pages = manager.pages_per_group[group]
 
     @property
     def num_free(self) -> int:
@@ -102,18 +108,25 @@ class _AllocatorView:
 
 
 class CacheManager:
-    def __init__(self, groups: Sequence[GroupSpec], num_pages: int, page_size: int, max_requests: int,
+    def __init__(self, groups: Sequence[GroupSpec], num_pages, page_size: int, max_requests: int,
                  max_blocks: Optional[int] = None):
-        if num_pages <= 0:
-            raise ValueError("a page pool needs at least one page")
+        """``num_pages``: the pool size of every group, or one size per group (each group has a pool of
+        its own; a window group gets by with far fewer pages than a group that keeps every key)."""
         self.groups = list(groups)
+        per_group = [int(num_pages)] * len(self.groups) if isinstance(num_pages, int) else [int(n) for n in num_pages]
+        if len(per_group) != len(self.groups):
+            raise ValueError(f"{len(per_group)} pool sizes for {len(self.groups)} groups")
+        if any(n <= 0 for n in per_group) or (isinstance(num_pages, int) and num_pages <= 0):
+            raise ValueError("a page pool needs at least one page")
         self.page_size = page_size
-        self.num_pages = num_pages
+        self.pages_per_group = per_group
+        self.num_pages = max(per_group, default=int(num_pages) if isinstance(num_pages, int) else 0)
         self.max_requests = max_requests
         self.max_blocks = max_blocks
         self._L = _lib()
         windows = (ctypes.c_int * max(1, len(self.groups)))(*[int(g.window or 0) for g in self.groups])
-        self._h = ctypes.c_void_p(self._L.infero_cache_new(len(self.groups), windows, num_pages, page_size,
+        pages = (ctypes.c_int * max(1, len(self.groups)))(*per_group)
+        self._h = ctypes.c_void_p(self._L.infero_cache_new(len(self.groups), windows, pages, page_size,
                                                            max_requests, int(max_blocks or 0)))
         if not self._h:
             raise ValueError("bad cache geometry")
@@ -177,18 +190,8 @@ class CacheManager:
         self._L.infero_cache_pages_needed(self._h, rc.slot, int(n_new), self._need)
         return [int(self._need[g]) for g in range(len(self.groups))]
 
-    def can_reserve(self, items: Sequence[Tuple[RequestCache, int]]) -> bool:
-        need = [0] * len(self.groups)
-        for rc, n in items:
-            for g, k in enumerate(self.pages_needed(rc, n)):
-                need[g] += k
-        return all(need[g] <= self.free_pages(g) for g in range(len(self.groups)))
-
     def free_pages(self, group: int = 0) -> int:
         return self._L.infero_cache_num_free(self._h, group)
-
-    def min_free_pages(self) -> int:
-        return min((self.free_pages(g) for g in range(len(self.groups))), default=self.num_pages)
 
     def reserve(self, rc: RequestCache, n_new: int) -> None:
         """Take the pages n_new more tokens need, in every group, or none at all."""
@@ -208,34 +211,18 @@ class CacheManager:
         self._L.infero_cache_abort(self._h, rc.slot)
 
     # ---- tables for the device -----------------------------------------------------------
-    def block_table_array(self, group: int, rcs: Sequence[RequestCache], width: int) -> np.ndarray:
-        """[len(rcs), width] int32: logical page -> page id (-1 where none is held)."""
-        t = self._mirror(group)
-        if not rcs:
-            return np.full((1, width), -1, dtype=np.int32)
-        for rc in rcs:
-            if rc.table_len(group) > width:
-                raise ValueError(f"request {rc.rid!r} holds {rc.table_len(group)} pages, table width is {width}")
-        slots = np.fromiter((rc.slot for rc in rcs), dtype=np.intp, count=len(rcs))
-        if width <= t.shape[1]:
-            return t[slots, :width].copy()
-        out = np.full((len(rcs), width), -1, dtype=np.int32)
-        out[:, :t.shape[1]] = t[slots]
-        return out
-
     def step_layout(self, slots: np.ndarray, n_tokens: np.ndarray, tokens: np.ndarray, want_counts: np.ndarray,
-                    wants: np.ndarray, table_width: int, out: np.ndarray, n_pad: int = 0, pad_slot: int = 0,
-                    pad_page: int = 0) -> List[int]:
+                    wants: np.ndarray, table_width: int, out: np.ndarray, n_pad: int = 0, pad_slot: int = 0) -> List[int]:
         """Write a step's int32 arrays into ``out`` (see csrc/host_cache.cpp: token ids, positions,
         token -> entry, per entry first row / row count / cached length / slot, wanted rows, one
         block table per group) and return the section sizes.  All arguments are int32 arrays.
         ``n_pad`` entries of a request that does not exist follow the real ones (token 0 at position
-        0, state slot ``pad_slot``, the single page ``pad_page``)."""
+        0, state slot ``pad_slot``, and in every group the single page past the group's pool)."""
         sizes = (ctypes.c_longlong * (8 + len(self.groups)))()
         as_p = lambda a: a.ctypes.data_as(ctypes.POINTER(ctypes.c_int))     # noqa: E731
         total = self._L.infero_step_layout(self._h, int(slots.size), as_p(slots), as_p(n_tokens), as_p(tokens),
                                            as_p(want_counts), as_p(wants), int(table_width), as_p(out),
-                                           ctypes.c_longlong(out.size), sizes, int(n_pad), int(pad_slot), int(pad_page))
+                                           ctypes.c_longlong(out.size), sizes, int(n_pad), int(pad_slot))
         if total < 0:
             raise ValueError("step layout does not fit its buffer, or a request holds more pages than the table is wide")
         return [int(v) for v in sizes]

@@ -14,7 +14,8 @@ from typing import Optional
 class EngineConfig:
     dtype: str = "bfloat16"            # "bfloat16" | "float32"
     page_size: int = 16                # tokens per cache page (16, 32 or 64)
-    num_pages: Optional[int] = None    # pages per cache group; None = from max_tokens
+    num_pages: Optional[int] = None    # pages of a cache group that keeps every key (a window group gets
+                                       # what its live requests can hold at once); None = from max_tokens
     max_tokens: Optional[int] = None   # tokens the cache can hold (rounded up to pages)
     max_seqs: int = 32                 # live requests (--max-seqs)
     ctx: int = 4096                    # longest sequence (--ctx)

@@ -23,6 +23,7 @@ namespace {
 
 struct Group {
     int window = 0;                          // 0: every key is kept
+    int num_pages = 0;                       // this group's own pool
     std::vector<int> free_stack;             // lowest page on top, so the first request gets page 0 upward
     std::vector<uint8_t> held, ever_held;
 };
@@ -35,7 +36,7 @@ struct Request {
 };
 
 struct Cache {
-    int num_pages = 0, page_size = 0, max_requests = 0, max_blocks = 0;   // max_blocks 0: no limit
+    int page_size = 0, max_requests = 0, max_blocks = 0;   // max_blocks 0: no limit
     std::vector<Group> groups;
     std::vector<Request> reqs;
     std::vector<int> free_slots;             // lowest slot on top
@@ -70,14 +71,21 @@ bool valid_slot(const Cache* c, int slot) { return slot >= 0 && slot < c->max_re
 
 extern "C" {
 
-void* infero_cache_new(int n_groups, const int* windows, int num_pages, int page_size, int max_requests, int max_blocks) {
-    if (n_groups < 0 || num_pages <= 0 || page_size <= 0 || max_requests <= 0) return nullptr;
+// Every group has a pool of its own, of num_pages[g] pages: a group that keeps a window of keys needs
+// far fewer than one that keeps them all.
+void* infero_cache_new(int n_groups, const int* windows, const int* pages_per_group, int page_size, int max_requests,
+                       int max_blocks) {
+    if (n_groups < 0 || page_size <= 0 || max_requests <= 0) return nullptr;
+    for (int g = 0; g < n_groups; ++g)
+        if (pages_per_group[g] <= 0) return nullptr;
     Cache* c = new Cache();
-    c->num_pages = num_pages; c->page_size = page_size; c->max_requests = max_requests; c->max_blocks = max_blocks;
+    c->page_size = page_size; c->max_requests = max_requests; c->max_blocks = max_blocks;
     c->groups.resize(n_groups);
     for (int g = 0; g < n_groups; ++g) {
         Group& G = c->groups[g];
         G.window = windows[g];
+        G.num_pages = pages_per_group[g];
+        const int num_pages = G.num_pages;
         G.free_stack.resize(num_pages);
         for (int p = 0; p < num_pages; ++p) G.free_stack[p] = num_pages - 1 - p;
         G.held.assign(num_pages, 0);
@@ -127,10 +135,29 @@ int infero_cache_fresh(void* h, int slot) { return static_cast<Cache*>(h)->reqs[
 int infero_cache_num_free(void* h, int group) { return (int)static_cast<Cache*>(h)->groups[group].free_stack.size(); }
 int infero_cache_table_len(void* h, int group, int slot) { return (int)static_cast<Cache*>(h)->reqs[slot].tables[group].size(); }
 int infero_cache_first_live(void* h, int group, int slot) { return static_cast<Cache*>(h)->reqs[slot].first_live[group]; }
-// n_groups, num_pages, page_size, max_requests
+// n_groups, pages of the largest pool, page_size, max_requests
 void infero_cache_geometry(void* h, int* out) {
     Cache* c = static_cast<Cache*>(h);
-    out[0] = (int)c->groups.size(); out[1] = c->num_pages; out[2] = c->page_size; out[3] = c->max_requests;
+    int most = 0;
+    for (const Group& G : c->groups) most = std::max(most, G.num_pages);
+    out[0] = (int)c->groups.size(); out[1] = most; out[2] = c->page_size; out[3] = c->max_requests;
+}
+int infero_cache_group_pages(void* h, int group) { return static_cast<Cache*>(h)->groups[group].num_pages; }
+int infero_cache_group_window(void* h, int group) { return static_cast<Cache*>(h)->groups[group].window; }
+// Pages of group g that the request in `slot` holds now (a window group's table also lists, as -1, what it gave back).
+int infero_cache_held_by(void* h, int group, int slot) {
+    Cache* c = static_cast<Cache*>(h);
+    const Request& r = c->reqs[slot];
+    return (int)r.tables[group].size() - r.first_live[group];
+}
+// The most pages of group g a request of n_tokens ever holds at once when it is fed in portions of at
+// most max_chunk tokens: all of them in a group that keeps every key; in a group with window W what
+// covers the W - 1 keys before a portion and the portion itself.
+int infero_cache_most_pages(void* h, int group, int n_tokens, int max_chunk) {
+    Cache* c = static_cast<Cache*>(h);
+    const int all = c->pages_for(n_tokens), W = c->groups[group].window;
+    if (W <= 0) return all;
+    return std::min(all, c->pages_for(W - 1 + std::max(1, max_chunk)) + 1);
 }
 int infero_cache_width(void* h) { return static_cast<Cache*>(h)->width; }
 const int* infero_cache_mirror(void* h, int group) { return static_cast<Cache*>(h)->mirror[group].data(); }
@@ -237,7 +264,7 @@ void infero_cache_abort(void* h, int slot) {
 int infero_cache_held(void* h, int group, int* out, int cap) {
     Cache* c = static_cast<Cache*>(h);
     int n = 0;
-    for (int p = 0; p < c->num_pages; ++p)
+    for (int p = 0; p < c->groups[group].num_pages; ++p)
         if (c->groups[group].held[p]) {
             if (out && n < cap) out[n] = p;
             ++n;
@@ -251,7 +278,8 @@ int infero_cache_check(void* h) {
     char buf[256];
     for (size_t g = 0; g < c->groups.size(); ++g) {
         const Group& G = c->groups[g];
-        std::vector<uint8_t> seen(c->num_pages, 0);
+        const int num_pages = G.num_pages;
+        std::vector<uint8_t> seen(num_pages, 0);
         int held = 0;
         for (int s = 0; s < c->max_requests; ++s) {
             const Request& r = c->reqs[s];
@@ -265,7 +293,7 @@ int infero_cache_check(void* h) {
                     return 1;
                 }
                 if (p < 0) continue;
-                if (p >= c->num_pages || seen[p]) {
+                if (p >= num_pages || seen[p]) {
                     snprintf(buf, sizeof buf, "group %zu: page %d is held twice", g, p);
                     c->error = buf;
                     return 1;
@@ -280,18 +308,18 @@ int infero_cache_check(void* h) {
                     return 1;
                 }
         }
-        for (int p = 0; p < c->num_pages; ++p)
+        for (int p = 0; p < num_pages; ++p)
             if ((seen[p] != 0) != (G.held[p] != 0)) {
                 snprintf(buf, sizeof buf, "group %zu: page %d lost or leaked (tables and allocator disagree)", g, p);
                 c->error = buf;
                 return 1;
             }
-        if (held + (int)G.free_stack.size() != c->num_pages) {
-            snprintf(buf, sizeof buf, "group %zu: %d held + %zu free != %d", g, held, G.free_stack.size(), c->num_pages);
+        if (held + (int)G.free_stack.size() != num_pages) {
+            snprintf(buf, sizeof buf, "group %zu: %d held + %zu free != %d", g, held, G.free_stack.size(), num_pages);
             c->error = buf;
             return 1;
         }
-        std::vector<uint8_t> on_free(c->num_pages, 0);
+        std::vector<uint8_t> on_free(num_pages, 0);
         for (int p : G.free_stack) {
             if (on_free[p] || G.held[p]) {
                 snprintf(buf, sizeof buf, "group %zu: page %d is on the free list twice, or free and held", g, p);
@@ -321,10 +349,12 @@ int infero_cache_check(void* h) {
 //
 // n_pad more entries follow the real ones (a captured step is replayed with fewer requests than it was
 // captured for): each feeds token 0 at position 0 of a request that does not exist, in state slot
-// pad_slot, with a block table of the single page pad_page, and wants its logits (which nobody reads).
+// pad_slot, with a block table of a single page, and wants its logits (which nobody reads).  That page
+// is, in every group, the one past the group's pool (id = the group's page count): the device arrays
+// hold one page more than the bookkeeping hands out.
 long long infero_step_layout(void* h, int n_entries, const int* slots, const int* n_tokens, const int* tokens,
                              const int* want_counts, const int* wants, int table_width, int* out, long long cap,
-                             long long* sizes, int n_pad, int pad_slot, int pad_page) {
+                             long long* sizes, int n_pad, int pad_slot) {
     Cache* c = static_cast<Cache*>(h);
     const int real = n_entries, E = n_entries + n_pad, G = (int)c->groups.size();
     long long T = n_pad, R = n_pad;
@@ -368,7 +398,7 @@ long long infero_step_layout(void* h, int n_entries, const int* slots, const int
         if (E == 0) std::fill(dst, dst + table_width, -1);
         for (int e = real; e < E; ++e) {
             std::fill(dst + (long long)e * table_width, dst + (long long)(e + 1) * table_width, -1);
-            dst[(long long)e * table_width] = pad_page;
+            dst[(long long)e * table_width] = c->groups[g].num_pages;
         }
         for (int e = 0; e < real; ++e) {
             const Request& rq = c->reqs[slots[e]];

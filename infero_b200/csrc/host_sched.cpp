@@ -25,6 +25,9 @@ int infero_cache_num_free(void* h, int group);
 int infero_cache_table_len(void* h, int group, int slot);
 void infero_cache_pages_needed(void* h, int slot, int n_new, int* out);
 void infero_cache_geometry(void* h, int* out);
+int infero_cache_group_pages(void* h, int group);
+int infero_cache_held_by(void* h, int group, int slot);
+int infero_cache_most_pages(void* h, int group, int n_tokens, int max_chunk);
 }
 
 namespace {
@@ -38,7 +41,7 @@ struct Req {
 struct Sched {
     void* cache;
     int max_seqs, max_batch_tokens, ctx, max_prefill_chunk;
-    int n_groups, num_pages, page_size;
+    int n_groups, page_size;
     std::vector<Req> reqs;
     std::vector<int> free_ids;
     std::deque<int> waiting;
@@ -49,19 +52,16 @@ struct Sched {
 
     int pages_for(int n_tokens) const { return (n_tokens + page_size - 1) / page_size; }
     int free_pages(int g) const { return infero_cache_num_free(cache, g); }
-    int min_free() const {
-        int m = num_pages;
-        for (int g = 0; g < n_groups; ++g) m = std::min(m, free_pages(g));
-        return m;
-    }
-    // pages the running requests still have to take to hold their tokens plus one
-    int outstanding() const {
+    // Pages of group g a request of n tokens has to hold at once, at least: all of them where every key
+    // is kept; where a window is kept, what a token-by-token feed holds (larger portions hold more for
+    // a step, and the planner cuts portions to the pages that are free).
+    int least_need(int g, int n_tokens) const { return infero_cache_most_pages(cache, g, n_tokens, 1); }
+    // pages of group g the running requests still have to take to hold their tokens plus one
+    int outstanding(int g) const {
         int total = 0;
         for (int id : running) {
             const Req& r = reqs[id];
-            int held = 0;
-            for (int g = 0; g < n_groups; ++g) held = std::max(held, infero_cache_table_len(cache, g, r.slot));
-            total += std::max(0, pages_for(r.n_tokens + 1) - held);
+            total += std::max(0, least_need(g, r.n_tokens + 1) - infero_cache_held_by(cache, g, r.slot));
         }
         return total;
     }
@@ -97,7 +97,6 @@ void* infero_sched_new(void* cache, int max_seqs, int max_batch_tokens, int ctx,
     int geo[4];
     infero_cache_geometry(cache, geo);
     s->n_groups = geo[0];
-    s->num_pages = geo[1];
     s->page_size = geo[2];
     s->need.assign(std::max(1, s->n_groups), 0);
     s->used.assign(std::max(1, s->n_groups), 0);
@@ -147,8 +146,15 @@ int infero_sched_admit(void* h, int* out, int cap) {
     while (!s->waiting.empty() && (int)s->running.size() < s->max_seqs && n < cap) {
         const int id = s->waiting.front();
         Req& r = s->reqs[id];
-        const int need = s->pages_for(r.n_tokens + 1);
-        if (need > s->num_pages) {
+        // every group has a pool of its own: the request must fit each, and each must have the room now
+        int need = 0;
+        bool never = false, not_now = false;
+        for (int g = 0; g < s->n_groups; ++g) {
+            const int need_g = s->least_need(g, r.n_tokens + 1);
+            if (need_g > infero_cache_group_pages(s->cache, g)) { never = true; need = std::max(need, need_g); }
+            else if (need_g > s->free_pages(g) - s->outstanding(g)) not_now = true;
+        }
+        if (never) {
             s->waiting.pop_front();
             const bool resumed = r.preemptions > 0;
             r.finished = true;
@@ -157,7 +163,7 @@ int infero_sched_admit(void* h, int* out, int cap) {
             ++n;
             continue;
         }
-        if (need > s->min_free() - s->outstanding()) break;      // stays at the front; tried again next step
+        if (not_now) break;                                      // stays at the front; tried again next step
         const int slot = infero_cache_open(s->cache);
         if (slot < 0) break;
         s->waiting.pop_front();

@@ -19,12 +19,20 @@ from .step import ModelRunner, StepEntry
 
 
 def _auto_pages(model, page_size: int, act_dtype, device, max_seqs: int, ctx: int,
-                fraction: Optional[float]) -> int:
-    """Pages that fit beside the weights: the reference leaves 1/8 of the card plus 512 MiB
-    free (crates/server/src/scheduler.rs:2341-2432); never more than max_seqs full contexts."""
+                fraction: Optional[float], max_batch_tokens: int) -> int:
+    """Pages (of the groups that keep every key) that fit beside the weights: the reference leaves 1/8
+    of the card plus 512 MiB free (crates/server/src/scheduler.rs:2341-2432); never more than max_seqs
+    full contexts.  A group that keeps a window has a pool of fixed size, which comes off the room first."""
+    from ..cache.storage import window_pool_pages
     esize = 2 if act_dtype == torch.bfloat16 else 4
-    per_token = sum(2 * s.num_kv_heads * s.head_dim * esize for s in model.kv_specs.values())
     want = max_seqs * (-(-ctx // page_size))
+    per_token, fixed = 0, 0
+    for s in model.kv_specs.values():
+        b = s.num_kv_heads * (s.head_dim + s.value_dim) * esize
+        if s.window and window_pool_pages(s.window, page_size, max_seqs, max_batch_tokens) < want:
+            fixed += b * page_size * (window_pool_pages(s.window, page_size, max_seqs, max_batch_tokens) + 1)
+        else:
+            per_token += b
     if per_token == 0:
         return max(1, want)
     free, total = torch.cuda.mem_get_info(device)
@@ -32,7 +40,7 @@ def _auto_pages(model, page_size: int, act_dtype, device, max_seqs: int, ctx: in
         room = int(total * fraction) - (total - free)
     else:
         room = free - total // 8 - (512 << 20)
-    fit = max(1, room // (per_token * page_size))
+    fit = max(1, (room - fixed) // (per_token * page_size))
     return int(max(1, min(want, fit)))
 
 
@@ -62,7 +70,7 @@ class Engine:
             pages = -(-kv_slots // page_size)
         else:
             pages = _auto_pages(self.model, page_size, act, torch.device(device), max_seqs, ctx,
-                                gpu_memory_fraction)
+                                gpu_memory_fraction, max_batch_tokens)
         self.cfg = EngineConfig(dtype=dtype, page_size=page_size, num_pages=pages, max_seqs=max_seqs, ctx=ctx,
                                 max_batch_tokens=max_batch_tokens, max_logit_rows=max(max_seqs, 256),
                                 seed=seed, cuda_graphs=cuda_graphs, device=device)

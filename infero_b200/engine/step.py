@@ -19,7 +19,8 @@ import numpy as np
 import torch
 
 from .. import kernels as K
-from ..cache import CacheManager, CacheStorage, OutOfPages, RequestCache
+from ..cache import CacheManager, CacheStorage, OutOfPages, RequestCache, plan_group_pages
+from ..cache.storage import group_cache_slots
 from ..config.engine_config import EngineConfig
 from ..models.decoder import DecoderModel
 
@@ -128,12 +129,17 @@ class ModelRunner:
         self.page_size = cfg.page_size
         self.num_pages = cfg.resolved_num_pages()
         self.max_blocks = max(1, -(-cfg.ctx // cfg.page_size))
-        # one page and one state slot beyond what the manager hands out: where the entries that pad a
-        # captured step to its captured size read and write
-        self.pad_page, self.pad_slot = self.num_pages, cfg.max_seqs
-        self.storage = CacheStorage(model.kv_specs, model.state_specs, self.num_pages + 1, cfg.page_size,
-                                    cfg.max_seqs + 1, self.act_dtype, self.device)
-        self.manager = CacheManager(self.storage.bookkeeping_groups(), self.num_pages, cfg.page_size,
+        # Every group of cache slots has a pool of its own: cfg.num_pages where every key is kept, what
+        # max_seqs requests under the step's token budget can ever hold where only a window is.
+        # One page (in every group) and one state slot beyond what the manager hands out: where the
+        # entries that pad a captured step to its captured size read and write.
+        groups, _ = group_cache_slots(model.kv_specs)
+        self.pages_per_group = plan_group_pages(groups, self.num_pages, cfg.page_size, cfg.max_seqs,
+                                                int(cfg.max_batch_tokens))
+        self.pad_slot = cfg.max_seqs
+        self.storage = CacheStorage(model.kv_specs, model.state_specs, [n + 1 for n in self.pages_per_group],
+                                    cfg.page_size, cfg.max_seqs + 1, self.act_dtype, self.device)
+        self.manager = CacheManager(self.storage.bookkeeping_groups(), self.pages_per_group, cfg.page_size,
                                     cfg.max_seqs, max_blocks=self.max_blocks)
         # the sampler's last pick per request slot, for steps launched before the host has read it
         self.device_tokens = torch.zeros(max(1, cfg.max_seqs), dtype=torch.int32, device=self.device)
@@ -289,7 +295,7 @@ class ModelRunner:
     def _fill(self, args, out: np.ndarray, pad: int = 0):
         """Lay the step's arrays out in ``out`` (pinned host memory); returns the section sizes and
         host copies of the per-entry arrays."""
-        sizes = self.manager.step_layout(*args, self.max_blocks, out, pad, self.pad_slot, self.pad_page)
+        sizes = self.manager.step_layout(*args, self.max_blocks, out, pad, self.pad_slot)
         T, E = sizes[0], sizes[3]
         o = 3 * T
         host = tuple(out[o + k * E:o + (k + 1) * E].copy() for k in range(4))    # first row, rows, cached length, slot

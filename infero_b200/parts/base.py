@@ -39,10 +39,17 @@ class TensorDecl:
 @dataclass(frozen=True)
 class KvCacheSpec:
     """Paged keys and values of one cache slot.  Slots with equal specs form a group that
-    shares a page allocator and block tables."""
+    shares a page allocator and block tables.  Keys and values may have different widths (a mixer
+    whose values are narrower or wider than its keys, or that caches one latent vector as the
+    "key" and a value of another size): the storage keeps them in two arrays."""
     num_kv_heads: int
-    head_dim: int
+    head_dim: int                     # width of a key
     window: Optional[int] = None      # None: every key is kept
+    v_head_dim: Optional[int] = None  # width of a value; None: the same as the key's
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
 
 @dataclass(frozen=True)

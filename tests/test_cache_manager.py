@@ -3,22 +3,62 @@ import random
 
 import pytest
 
-from infero_b200.cache import CacheManager, GroupSpec, OutOfPages, OutOfSlots, PageAllocator
+from infero_b200.cache import CacheManager, GroupSpec, OutOfPages, OutOfSlots
 
 
-def test_allocator_is_all_or_nothing_and_refuses_double_free():
-    a = PageAllocator(4)
-    got = a.alloc(3)
-    assert got == [0, 1, 2] and a.num_free == 1
-    with pytest.raises(OutOfPages):
-        a.alloc(2)
-    assert a.num_free == 1
-    a.free([1])
-    with pytest.raises(AssertionError):
-        a.free([1])
-    with pytest.raises(AssertionError):
-        a.free([3])
-    assert a.alloc(2) == [1, 3]
+def test_allocator_is_all_or_nothing_and_never_frees_twice():
+    """The allocator generation uses (csrc/host_cache.cpp) through the manager: lowest pages first, a
+    request that does not fit takes nothing, a page that came back is handed out again, and closing
+    a request twice gives nothing back twice."""
+    m = CacheManager([GroupSpec(None)], num_pages=4, page_size=16, max_requests=3)
+    a, b = m.open("a"), m.open("b")
+    m.reserve(a, 48)
+    m.commit(a, 48)
+    assert a.tables == [[0, 1, 2]] and m.free_pages(0) == 1
+    with pytest.raises(OutOfPages) as e:
+        m.reserve(b, 17)
+    assert (e.value.group, e.value.wanted, e.value.free) == (0, 2, 1)
+    assert m.free_pages(0) == 1 and b.tables == [[]]
+    m.reserve(b, 16)
+    m.commit(b, 16)
+    assert b.tables == [[3]] and m.allocators[0].held_pages() == [0, 1, 2, 3]
+    m.close("a")
+    assert m.free_pages(0) == 3 and m.allocators[0].held_pages() == [3]
+    with pytest.raises(KeyError):
+        m.close("a")
+    assert m._L.infero_cache_close(m._h, a.slot) != 0        # the native side refuses a slot that is not open
+    assert m.free_pages(0) == 3
+    m.check()
+    c = m.open("c")
+    m.reserve(c, 33)
+    assert sorted(c.tables[0]) == [0, 1, 2] and m.pages_reused == 3
+    m.check()
+
+
+def test_every_group_has_a_pool_of_its_own_size():
+    """A window group with far fewer pages than the all-keys group: long requests run in portions, the
+    window pages come back as the window passes, and only the group that is short refuses."""
+    W, P = 32, 16
+    m = CacheManager([GroupSpec(None), GroupSpec(W)], num_pages=[40, 6], page_size=P, max_requests=2)
+    assert [a.num_pages for a in m.allocators] == [40, 6] and m.num_pages == 40
+    a = m.open("a")
+    for n in [40, 40, 40, 40, 1, 1, 30, 64]:
+        m.reserve(a, n)
+        m.commit(a, n)
+        m.check()
+        assert m.allocators[1].num_pages - m.free_pages(1) <= -(-W // P) + 1
+    assert a.length == 256 and m.free_pages(0) == 40 - 16 and m.pages_reclaimed >= 13
+    with pytest.raises(OutOfPages) as e:
+        m.reserve(a, 97)                      # the window group cannot hold a portion that long
+    assert e.value.group == 1 and m.free_pages(0) == 24
+    b = m.open("b")
+    with pytest.raises(OutOfPages) as e:
+        m.reserve(b, 25 * P)                  # and here the all-keys group is the one that is short
+    assert e.value.group == 0
+    m.close("a")
+    m.close("b")
+    assert [m.free_pages(g) for g in (0, 1)] == [40, 6]
+    m.check()
 
 
 def test_pages_follow_the_length_and_come_back_on_close():
@@ -95,13 +135,15 @@ def test_abort_returns_reserved_pages_only():
     m.check()
 
 
-def test_block_table_array_marks_released_pages():
-    m = CacheManager([GroupSpec(16)], num_pages=8, page_size=16, max_requests=2)
+def test_the_table_copy_for_the_device_marks_released_pages():
+    m = CacheManager([GroupSpec(16)], num_pages=8, page_size=16, max_requests=2, max_blocks=6)
     a = m.open("a")
     m.reserve(a, 40)
     m.commit(a, 40)
-    t = m.block_table_array(0, [a], 6)
-    assert t.shape == (1, 6) and t[0, 0] == -1 and t[0, 2] >= 0 and t[0, 3] == -1
+    t = m._mirror(0)[a.slot]
+    # the next query, at position 40, sees keys 25 .. 40: page 0 (keys 0 .. 15) went back
+    assert t.shape == (6,) and t[0] == -1 and t[1] >= 0 and t[2] >= 0 and t[3] == -1
+    assert a.tables == [[-1, int(t[1]), int(t[2])]] and a.first_live == [1]
 
 
 @pytest.mark.parametrize("seed", range(12))
@@ -109,7 +151,8 @@ def test_random_orders_of_requests_keep_every_invariant(seed):
     rng = random.Random(seed)
     groups = [GroupSpec(None), GroupSpec(rng.choice([16, 24, 48, 100]))]
     P = rng.choice([16, 32, 64])
-    m = CacheManager(groups, num_pages=rng.randint(6, 24), page_size=P, max_requests=4)
+    pools = [rng.randint(6, 24), rng.randint(6, 24)] if seed % 2 else rng.randint(6, 24)
+    m = CacheManager(groups, num_pages=pools, page_size=P, max_requests=4)
     live = {}
     next_id = 0
     for _ in range(600):

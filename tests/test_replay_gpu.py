@@ -453,3 +453,36 @@ def test_a_missed_wait_fails_the_step_and_leaves_the_engine_usable():
             row = plain_qwen2.forward(cfg, w, list(prompt) + want[:i])[-1]
             assert float(row.max() - row[got[i]]) / float(row.abs().max()) <= TOL["bfloat16"]
             break
+
+
+@pytest.mark.parametrize("name,dtype", [("B", "float32"), ("D", "bfloat16"), ("D", "float32")])
+def test_the_window_group_runs_in_a_far_smaller_pool(name, dtype):
+    """Each group of layers has a pool of its own size: the layers that keep a window of 48 keys get
+    what four live requests can hold at once, a third of what the all-keys layer gets, and the mixed
+    trace (long prompts in portions, pages coming back as the window passes) still equals the plain
+    implementation.  The memory that early returns save is memory that is never allocated."""
+    from infero_b200.cache.storage import window_pool_pages
+    from infero_b200.config import EngineConfig
+    from infero_b200.engine import ModelRunner
+    from infero_b200.loading import load_model
+    mdir = model_dir(name)
+    model, _ = load_model(mdir, dtype, "cuda:0")
+    cfg = EngineConfig(dtype=dtype, page_size=16, num_pages=120, max_seqs=4, ctx=320, max_batch_tokens=256,
+                       max_logit_rows=256, cuda_graphs=False)
+    runner = ModelRunner(model, cfg)
+    small = window_pool_pages(48, 16, 4, 256)
+    assert small == 40 and runner.pages_per_group == [120, small]
+    assert [a.num_pages for a in runner.manager.allocators] == [120, small]
+    n_win = len(model.spec.schedule) - 1                     # layers from max_window_layers = 1 on
+    per_page = runner.storage.bytes_per_token(0) * 16
+    assert runner.storage.bytes_per_token(1) == n_win * runner.storage.bytes_per_token(0)
+    assert runner.storage.bytes() == per_page * 121 + n_win * per_page * (small + 1)
+    reqs = make_requests(name, [300, 150, 97, 210, 305, 60, 280], seed=17)
+    steps = R.steps_mixed(reqs, seed=5, max_live=4)
+    plain = plain_logits(mdir, reqs)
+    with ServingPath(name, dtype):
+        got = R.replay_inprocess(runner, steps)
+    err, where = R.compare(got, plain)
+    assert err <= TOL[dtype], f"{name} {dtype}: relative error {err:.3e} at {where}"
+    assert runner.manager.pages_reclaimed > 20 and runner.manager.pages_reused > 0
+    assert [runner.manager.free_pages(g) for g in (0, 1)] == [120, small] and not runner.manager.requests

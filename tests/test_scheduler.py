@@ -335,3 +335,24 @@ def test_native_records_are_handed_back():
     assert s.stats["finished"] == 21
     sid = s._L.infero_sched_enqueue(s._h, 5, 1, 0)
     assert 0 <= sid < 8, "ids of finished requests are used again"
+
+
+def test_a_small_window_pool_cuts_portions_and_never_blocks_admission():
+    """The window group's pool is far smaller than the all-keys group's: prompts longer than it run in
+    portions no longer than its free pages hold, admission looks at each group's own pool, and every
+    request still gets its tokens; a request that cannot even fit the all-keys pool is refused."""
+    W, P = 32, 16
+    s, ex, m = make(num_pages=[48, 9], page_size=P, max_seqs=3, budget=96, ctx=1024,
+                    groups=[GroupSpec(None), GroupSpec(W)])
+    prompts = {"a": list(range(1, 201)), "b": list(range(3, 150)), "c": list(range(7, 60)), "d": list(range(2, 90))}
+    for rid, p in prompts.items():
+        s.enqueue(req(rid, p, n=12))
+    s.enqueue(req("huge", range(48 * P + 5), n=2))
+    out, reasons = run_all(s)
+    for rid, p in prompts.items():
+        assert out[rid] == expected_output(p, 12), rid
+    assert reasons["huge"][0] == "error" and "pages" in reasons["huge"][1]
+    portions = [n for b in ex.batches for (_, n, is_decode, _) in b if not is_decode]
+    assert max(portions) <= 9 * P and any(n < 96 for n in portions)
+    assert m.pages_reclaimed > 0
+    assert [m.free_pages(g) for g in (0, 1)] == [48, 9] and not m.requests
