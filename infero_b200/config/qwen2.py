@@ -21,6 +21,12 @@ from typing import Any, Dict, List, Optional, Tuple
 from .spec import (BlockSpec, FeedForwardSpec, MixerSpec, ModelSpec, NormSpec,
                    PositionSpec, ScheduleEntry)
 
+# Where a Qwen2 checkpoint keeps a layer's tensors, under ``model.layers.<i>``
+# (crates/model/src/weights.rs:3165-3205, :2970-3004, :3349-3355).
+ATTENTION_TENSORS = (("q", "self_attn.q_proj"), ("k", "self_attn.k_proj"), ("v", "self_attn.v_proj"),
+                     ("o", "self_attn.o_proj"))
+MLP_TENSORS = (("gate", "mlp.gate_proj"), ("up", "mlp.up_proj"), ("down", "mlp.down_proj"))
+
 
 class ConfigError(ValueError):
     """A config.json that cannot describe a runnable model."""
@@ -234,17 +240,21 @@ class Qwen2Config:
                 num_heads=self.num_attention_heads, num_kv_heads=self.num_key_value_heads,
                 head_dim=self.head_dim, qkv_bias=self.attention_bias, out_bias=False,
                 scale=1.0 / math.sqrt(self.head_dim),   # crates/model/src/config.rs:923-925
-                window=self.layer_window(i), position=pos)
+                window=self.layer_window(i), position=pos, names=ATTENTION_TENSORS)
             ffn = FeedForwardSpec(kind="swiglu", hidden=self.hidden_size,
-                                  intermediate=self.intermediate_size)
+                                  intermediate=self.intermediate_size, names=MLP_TENSORS)
             norm = NormSpec(kind="rmsnorm", dim=self.hidden_size, eps=self.rms_norm_eps)
             blocks.append(BlockSpec(kind="prenorm", prefix=prefix, mixer=mixer, ffn=ffn,
-                                    mixer_norm=norm, ffn_norm=norm))
+                                    mixer_norm=norm, ffn_norm=norm,
+                                    mixer_norm_name="input_layernorm.weight",
+                                    ffn_norm_name="post_attention_layernorm.weight"))
         schedule = tuple(ScheduleEntry(block=i, cache=i) for i in range(self.num_hidden_layers))
         return ModelSpec(
             architecture="Qwen2ForCausalLM", vocab_size=self.vocab_size, hidden=self.hidden_size,
             blocks=tuple(blocks), schedule=schedule,
             final_norm=NormSpec(kind="rmsnorm", dim=self.hidden_size, eps=self.rms_norm_eps),
             tie_embeddings=self.tie_word_embeddings,
+            embed_name="model.embed_tokens.weight", final_norm_name="model.norm.weight",
+            head_name="lm_head.weight",
             max_positions=self.max_position_embeddings,
             eos_token_ids=self.eos_token_ids)

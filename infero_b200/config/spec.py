@@ -16,6 +16,26 @@ from dataclasses import dataclass
 from typing import Optional, Tuple
 
 
+def _name_map(given, defaults) -> dict:
+    known = dict(defaults)
+    out = dict(known)
+    for k, v in given:
+        if k not in known and k not in ("qkv", "gate_up"):
+            raise ValueError(f"unknown tensor role '{k}' (known: {sorted(known)})")
+        out[k] = v
+    return out
+
+
+# Leaf names (under the block's prefix) of the tensors the built-in parts bind, as the Hugging Face
+# checkpoints of the Llama / Qwen2 family store them (crates/model/src/weights.rs:3165-3205,
+# :2970-3004).  An architecture that stores the same arithmetic under other names passes its own in
+# ``names``; "qkv" (one [q; k; v] stacked tensor) or "gate_up" (one [gate; up] stacked tensor) may
+# stand for the separate ones.
+ATTENTION_NAMES = (("q", "self_attn.q_proj"), ("k", "self_attn.k_proj"), ("v", "self_attn.v_proj"),
+                   ("o", "self_attn.o_proj"))
+SWIGLU_NAMES = (("gate", "mlp.gate_proj"), ("up", "mlp.up_proj"), ("down", "mlp.down_proj"))
+
+
 @dataclass(frozen=True)
 class PositionSpec:
     """Rotary position encoding applied to queries and keys inside a mixer.
@@ -56,12 +76,17 @@ class MixerSpec:
     position: Optional[PositionSpec] = None
     # free-form extras for mixers defined outside the framework
     extra: Tuple[Tuple[str, object], ...] = ()
+    # role -> leaf name under the block's prefix (see ATTENTION_NAMES); roles not given keep the default
+    names: Tuple[Tuple[str, str], ...] = ()
 
     def get(self, key, default=None):
         for k, v in self.extra:
             if k == key:
                 return v
         return default
+
+    def tensor_names(self) -> dict:
+        return _name_map(self.names, ATTENTION_NAMES)
 
 
 @dataclass(frozen=True)
@@ -71,6 +96,10 @@ class FeedForwardSpec:
     hidden: int
     intermediate: int
     extra: Tuple[Tuple[str, object], ...] = ()
+    names: Tuple[Tuple[str, str], ...] = ()          # role -> leaf name (see SWIGLU_NAMES)
+
+    def tensor_names(self) -> dict:
+        return _name_map(self.names, SWIGLU_NAMES)
 
 
 @dataclass(frozen=True)
@@ -85,6 +114,9 @@ class BlockSpec:
     ffn: FeedForwardSpec
     mixer_norm: NormSpec
     ffn_norm: NormSpec
+    # leaf names of the two norm weights under the prefix
+    mixer_norm_name: str = "input_layernorm.weight"
+    ffn_norm_name: str = "post_attention_layernorm.weight"
 
 
 @dataclass(frozen=True)

@@ -18,7 +18,9 @@ class GqaAttention(Mixer):
     (crates/model/src/lib.rs:5628-5663, :5895-5913, :5979-5993, :6996-7047).
 
     q, k and v are one stacked product [H*D + 2*Hkv*D, d] with a stacked bias; the reference
-    stacks them only for its quantised formats (crates/model/src/weights.rs:2704-2735).
+    stacks them only for its quantised formats (crates/model/src/weights.rs:2704-2735).  Where the
+    tensors live under the block's prefix is data of the spec (``MixerSpec.names``): separate q, k, v
+    or one stored [q; k; v] tensor.
     """
 
     def __init__(self, spec: MixerSpec, prefix: str):
@@ -33,9 +35,11 @@ class GqaAttention(Mixer):
             self.rope = part_class("position", spec.position.kind)(spec.position)
         self.qkv: Linear = None
         self.out: Linear = None
+        self.names = spec.tensor_names()
+        self.stored_stacked = "qkv" in self.names       # the checkpoint holds one [q; k; v] tensor
 
-    def _n(self, leaf: str) -> str:
-        return f"{self.prefix}.self_attn.{leaf}"
+    def _n(self, role: str, what: str = "weight") -> str:
+        return f"{self.prefix}.{self.names[role]}.{what}"
 
     def cache_spec(self) -> Optional[KvCacheSpec]:
         return KvCacheSpec(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window)
@@ -43,16 +47,14 @@ class GqaAttention(Mixer):
     def declare(self) -> List[TensorDecl]:
         s = self.spec
         da, dkv = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
-        out = [TensorDecl(self._n("q_proj.weight"), (da, s.hidden)),
-               TensorDecl(self._n("k_proj.weight"), (dkv, s.hidden)),
-               TensorDecl(self._n("v_proj.weight"), (dkv, s.hidden)),
-               TensorDecl(self._n("o_proj.weight"), (s.hidden, da))]
+        widths = {"q": da, "k": dkv, "v": dkv, "qkv": da + 2 * dkv}
+        roles = ("qkv",) if self.stored_stacked else ("q", "k", "v")
+        out = [TensorDecl(self._n(r), (widths[r], s.hidden)) for r in roles]
+        out.append(TensorDecl(self._n("o"), (s.hidden, da)))
         if s.qkv_bias:
-            out += [TensorDecl(self._n("q_proj.bias"), (da,), role="bias"),
-                    TensorDecl(self._n("k_proj.bias"), (dkv,), role="bias"),
-                    TensorDecl(self._n("v_proj.bias"), (dkv,), role="bias")]
+            out += [TensorDecl(self._n(r, "bias"), (widths[r],), role="bias") for r in roles]
         if s.out_bias:
-            out.append(TensorDecl(self._n("o_proj.bias"), (s.hidden,), role="bias"))
+            out.append(TensorDecl(self._n("o", "bias"), (s.hidden,), role="bias"))
         return out
 
     @staticmethod
@@ -63,11 +65,12 @@ class GqaAttention(Mixer):
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         s = self.spec
-        w = self._stack([tensors[self._n(f"{p}_proj.weight")] for p in "qkv"])
-        b = self._stack([tensors[self._n(f"{p}_proj.bias")] for p in "qkv"]) if s.qkv_bias else None
-        self.qkv = Linear(w, b, self._n("qkv_proj"))
-        ob = tensors[self._n("o_proj.bias")] if s.out_bias else None
-        self.out = Linear(tensors[self._n("o_proj.weight")], ob, self._n("o_proj"))
+        roles = ("qkv",) if self.stored_stacked else ("q", "k", "v")
+        w = self._stack([tensors[self._n(r)] for r in roles])
+        b = self._stack([tensors[self._n(r, "bias")] for r in roles]) if s.qkv_bias else None
+        self.qkv = Linear(w, b, f"{self.prefix}.qkv")
+        ob = tensors[self._n("o", "bias")] if s.out_bias else None
+        self.out = Linear(tensors[self._n("o")], ob, self._n("o", "product"))
 
     def forward(self, ctx, h, slot):
         s = self.spec

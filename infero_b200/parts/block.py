@@ -21,9 +21,9 @@ class PreNormBlock(Part):
     def __init__(self, spec: BlockSpec):
         self.spec = spec
         p = spec.prefix
-        self.mixer_norm = part_class("norm", spec.mixer_norm.kind)(spec.mixer_norm, f"{p}.input_layernorm.weight")
+        self.mixer_norm = part_class("norm", spec.mixer_norm.kind)(spec.mixer_norm, f"{p}.{spec.mixer_norm_name}")
         self.mixer = part_class("mixer", spec.mixer.kind)(spec.mixer, p)
-        self.ffn_norm = part_class("norm", spec.ffn_norm.kind)(spec.ffn_norm, f"{p}.post_attention_layernorm.weight")
+        self.ffn_norm = part_class("norm", spec.ffn_norm.kind)(spec.ffn_norm, f"{p}.{spec.ffn_norm_name}")
         self.ffn = part_class("feed_forward", spec.ffn.kind)(spec.ffn, p)
         self._native = None                  # the native launcher of this block, made at first use
 

@@ -188,3 +188,23 @@ def test_random_orders_of_requests_keep_every_invariant(seed):
     m.check()
     assert all(a.num_free == a.num_pages for a in m.allocators)
     assert m.pages_reused > 0
+
+
+def test_storage_keeps_keys_and_values_at_their_own_widths_and_pools():
+    """Keys and values are two arrays per group (a mixer may cache values wider or narrower than its
+    keys), and every group's arrays have its own number of pages."""
+    import torch
+    from infero_b200.cache import CacheStorage, plan_group_pages
+    from infero_b200.cache.storage import group_cache_slots, window_pool_pages
+    from infero_b200.parts.base import KvCacheSpec
+    specs = {0: KvCacheSpec(2, 16, None), 1: KvCacheSpec(2, 16, 32), 2: KvCacheSpec(2, 16, 32),
+             3: KvCacheSpec(3, 8, None, v_head_dim=24)}
+    groups, where = group_cache_slots(specs)
+    assert len(groups) == 3 and where[2] == (1, 1)
+    pages = plan_group_pages(groups, 500, 16, max_requests=4, max_batch_tokens=64)
+    assert pages == [500, window_pool_pages(32, 16, 4, 64), 500] and pages[1] == 4 * 5 + 4
+    st = CacheStorage(specs, {}, [n + 1 for n in pages], 16, 5, torch.float32, "cpu")
+    assert st.layer_kv(0).k.shape == (501, 2, 16, 16) and st.layer_kv(2).v.shape == (25, 2, 16, 16)
+    assert st.layer_kv(3).k.shape == (501, 3, 16, 8) and st.layer_kv(3).v.shape == (501, 3, 16, 24)
+    assert st.bytes_per_token() == 4 * (2 * 2 * 16 * 3 + 3 * (8 + 24))
+    assert st.bytes() == 4 * 16 * (501 * 64 + 2 * 25 * 64 + 501 * 96)
