@@ -41,6 +41,8 @@ int infero_gemm_tc(const void* x, const void* w, const void* bias, int bias_dtyp
 int infero_gemm_tc_swiglu(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int ldc,
                           int sm_count, cudaStream_t stream);
 long long infero_attn_decode_scratch(int n_tok, int n_heads, int head_dim, int n_splits);
+int infero_sm_count();
+void infero_attn_plan_decode(int n_tok, int n_kv, int group, int max_visible, int sm_count, int* chunk, int* splits);
 int infero_attn_decode_tma_supported(int head_dim, int page_size);
 int infero_attn_decode_tma(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
                            const void* v_cache, int num_pages, const int* block_table, int max_blocks,
@@ -139,7 +141,8 @@ static ArenaPlan plan_arena(const InferoBlock& b, int T, int sm_count) {
     p.q = take((long long)T * da * 2);
     p.attn = take((long long)T * da * 2);
     // the decode kernel's splits: tokens x splits stays below about two CTAs per SM (or one split each)
-    p.scratch = take(infero_attn_decode_scratch(std::max(T, 2 * 148), b.n_heads, b.head_dim, 1));
+    p.scratch = take(infero_attn_decode_scratch(std::max(T, 2 * (sm_count > 0 ? sm_count : infero_sm_count())), b.n_heads,
+                                                b.head_dim, 1));
     p.o_delta = take(product_bytes(T, b.hidden, da, sm_count));
     p.act = take((long long)T * b.intermediate * 2);
     p.gate_up = take(T <= 256 ? product_bytes(T, 2 * b.intermediate, b.hidden, sm_count) : 0);
@@ -193,27 +196,6 @@ static int product(const InferoStep& s, const void* a, int K, const void* w, int
     return 0;
 }
 
-static void plan_decode(int n_tok, int n_kv, int group, int max_visible, int* chunk, int* splits) {
-    static int min_chunk = -1;
-    if (min_chunk < 0) {
-        const char* e = getenv("INFERO_DECODE_MIN_CHUNK");
-        min_chunk = e && atoi(e) > 0 ? atoi(e) : 256;
-    }
-    const int target = 2 * 148, max_splits = 256;
-    const int per_split = std::max(1, n_tok * n_kv * ((group + 15) / 16));
-    const int want = std::max(1, target / per_split);
-    max_visible = std::max(16, max_visible);
-    int c = (max_visible + want - 1) / want;
-    c = std::max(min_chunk, (c + 15) / 16 * 16);
-    int sp = (max_visible + c - 1) / c;
-    if (sp > max_splits) {
-        c = ((max_visible + max_splits - 1) / max_splits + 15) / 16 * 16;
-        sp = (max_visible + c - 1) / c;
-    }
-    *chunk = c;
-    *splits = sp;
-}
-
 // x += pending; the block; leaves its own feed-forward output pending in *delta.  layer_parity picks
 // which of the arena's two output areas this layer writes (the other one still holds its input).
 int infero_block_forward(const InferoBlock* b, const InferoStep* s, const int* block_table, int max_blocks,
@@ -260,7 +242,7 @@ int infero_block_forward(const InferoBlock* b, const InferoStep* s, const int* b
         int vis = s->decode_visible;
         if (b->window > 0) vis = std::min(vis, b->window + 15);
         int chunk, splits;
-        plan_decode(s->n_decode, Hkv, H / Hkv, vis, &chunk, &splits);
+        infero_attn_plan_decode(s->n_decode, Hkv, H / Hkv, vis, s->sm_count, &chunk, &splits);
         if (infero_attn_decode_scratch(s->n_decode, H, D, splits) > p.o_delta - p.scratch) {
             infero_set_error("block_forward: %d decode tokens in %d splits need more scratch than was set aside", s->n_decode, splits);
             return 1;

@@ -52,6 +52,47 @@ void infero_set_pdl(int on) { g_pdl.store(on ? 1 : 0, std::memory_order_relaxed)
 
 long long infero_launch_count() { return g_launches.load(std::memory_order_relaxed); }
 
+// Multiprocessors of the current device (asked once per device; the B200's 148 if the query fails).
+int infero_sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (!cached[dev]) {
+        int sms = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+        cached[dev] = sms;
+    }
+    return cached[dev];
+}
+
+// How decode attention cuts the keys of a step into splits: (keys per split, number of splits) such
+// that the splits cover max_visible keys and the grid of n_tok x n_kv x ceil(group / 16) x splits CTAs
+// has about two CTAs per multiprocessor; a split has at least INFERO_DECODE_MIN_CHUNK keys (256) and
+// there are at most 256 splits (the merge keeps one weight per split in shared memory).  The one
+// statement of the plan: the Python parts, the native launcher of a block and the scratch sizing all
+// call this.
+void infero_attn_plan_decode(int n_tok, int n_kv, int group, int max_visible, int sm_count, int* chunk, int* splits) {
+    static int min_chunk = -1;
+    if (min_chunk < 0) {
+        const char* e = getenv("INFERO_DECODE_MIN_CHUNK");
+        min_chunk = e && atoi(e) > 0 ? atoi(e) : 256;
+    }
+    const int target = 2 * (sm_count > 0 ? sm_count : infero_sm_count()), max_splits = 256;
+    const int per_split = n_tok * n_kv * ((group + 15) / 16) > 0 ? n_tok * n_kv * ((group + 15) / 16) : 1;
+    const int want = target / per_split > 0 ? target / per_split : 1;
+    if (max_visible < 16) max_visible = 16;
+    int c = (max_visible + want - 1) / want;
+    c = (c + 15) / 16 * 16;
+    if (c < min_chunk) c = min_chunk;
+    int sp = (max_visible + c - 1) / c;
+    if (sp > max_splits) {
+        c = ((max_visible + max_splits - 1) / max_splits + 15) / 16 * 16;
+        sp = (max_visible + c - 1) / c;
+    }
+    *chunk = c;
+    *splits = sp;
+}
+
 int infero_device_info(int device, int* sm_count, int* cc_major, int* cc_minor, int* smem_optin) {
     cudaDeviceProp p;
     cudaError_t e = cudaGetDeviceProperties(&p, device);

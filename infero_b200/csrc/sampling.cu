@@ -19,6 +19,7 @@
 #include "common.cuh"
 #include <math_constants.h>
 
+extern "C" int infero_sm_count();     // runtime.cu
 int infero_tc_err_flag(int** out);      // tc_host.cu: the flag that kernels with bounded waits raise
 
 namespace {
@@ -466,7 +467,7 @@ int infero_sample(const float* logits, int n_rows, int vocab, const float* tempe
         INFERO_REQUIRE(scratch && scratch_bytes >= infero_sample_scratch(n_rows, vocab),
                        "sample: %lld bytes of scratch needed, %lld given", infero_sample_scratch(n_rows, vocab), scratch_bytes);
         // few blocks: large ones finish sooner; many: small ones, eight to an SM, finish in one round
-        const int chunk_threads = (long long)chunks * n_rows <= 2 * 148 ? SAMPLE_THREADS : 256;
+        const int chunk_threads = (long long)chunks * n_rows <= 2 * infero_sm_count() ? SAMPLE_THREADS : 256;
         launch_pdl(sample_chunk_kernel, dim3(chunks, n_rows), dim3(chunk_threads), 0, stream, logits, vocab, top_k,
                    (unsigned long long*)scratch);
         if (infero_check_launch("sample_chunk")) return 1;

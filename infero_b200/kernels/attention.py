@@ -9,7 +9,7 @@ tiled prefill kernel.  The scheduler puts decodes first, as the reference's does
 """
 from __future__ import annotations
 
-from ctypes import c_float, c_int, c_longlong
+from ctypes import byref as _byref, c_float, c_int, c_longlong
 from typing import Optional, Sequence, Tuple
 
 import torch
@@ -17,10 +17,6 @@ import torch
 from . import _check, _i32, _ptr, _stream, attention_generic, lib
 
 PREFILL_ROWS = 64          # query rows per CTA of the prefill kernel
-import os as _os
-
-DECODE_MIN_CHUNK = int(_os.environ.get("INFERO_DECODE_MIN_CHUNK", "256"))   # keys per split, at least (a tuning knob)
-TARGET_CTAS = 2 * 148      # decode CTAs wanted in flight: two resident per SM
 MAX_SPLITS = 256           # the merge kernel keeps one weight per split in shared memory
 
 
@@ -28,19 +24,15 @@ def mma_supported(head_dim: int, page_size: int) -> bool:
     return bool(lib().infero_attn_mma_supported(c_int(head_dim), c_int(page_size)))
 
 
-def plan_decode(n_tok: int, n_kv: int, group: int, max_visible: int) -> Tuple[int, int]:
+def plan_decode(n_tok: int, n_kv: int, group: int, max_visible: int, sm_count: int = 0) -> Tuple[int, int]:
     """(keys per split, number of splits) so that the splits cover ``max_visible`` keys and the
-    grid has about TARGET_CTAS blocks."""
-    ctas_per_split = max(1, n_tok * n_kv * (-(-group // 16)))
-    want = max(1, TARGET_CTAS // ctas_per_split)
-    max_visible = max(16, max_visible)
-    chunk = -(-max_visible // want)
-    chunk = max(DECODE_MIN_CHUNK, -(-chunk // 16) * 16)
-    splits = -(-max_visible // chunk)
-    if splits > MAX_SPLITS:
-        chunk = -(-(-(-max_visible // MAX_SPLITS)) // 16) * 16
-        splits = -(-max_visible // chunk)
-    return chunk, splits
+    grid has about two blocks per multiprocessor.  The plan is stated once, in native code
+    (``infero_attn_plan_decode``), which the native launcher of a block calls too; ``sm_count`` 0
+    means the current device's."""
+    chunk, splits = c_int(0), c_int(0)
+    lib().infero_attn_plan_decode(c_int(n_tok), c_int(n_kv), c_int(group), c_int(max_visible), c_int(sm_count),
+                                  _byref(chunk), _byref(splits))
+    return chunk.value, splits.value
 
 
 _COUNTERS = {}

@@ -242,13 +242,23 @@ def _layer_reading_cache(x, x_keys, w, cfg, i, pos):
 
 
 
+@pytest.mark.parametrize("shape", [dict(H=4, Hkv=2, D=64, d=128, ff=320), dict(H=2, Hkv=1, D=128, d=256, ff=616),
+                                   # a residual width of 512 lets the few-token products cut K into splits: gate and
+                                   # up then come as partial sums and the SwiGLU kernel adds them up
+                                   dict(H=8, Hkv=2, D=64, d=512, ff=200)],
+                         ids=["head64", "head128", "split_k"])
 @pytest.mark.parametrize("window", [None, 24])
-def test_native_block_launcher_changes_nothing(window):
+def test_native_block_launcher_changes_nothing(window, shape):
     """The block launched by one native call per layer gives, bit for bit, what its parts give when
-    they launch their kernels one by one: prompts in portions, mixed batches, single tokens."""
+    they launch their kernels one by one: prompts in portions (more than 256 rows: finished products;
+    fewer: partial sums), mixed batches, single tokens; with and without a window; at both head sizes
+    of the TMA-fed attention kernels."""
     from infero_b200.engine import StepEntry
+    from infero_b200.kernels import tc_gemm
     from infero_b200.parts import native_block as NB
-    spec = _spec(layers=3, window=window, H=4, Hkv=2, D=64, d=128, ff=320, V=400)
+    spec = _spec(layers=3, window=window, V=400, **shape)
+    if shape["d"] == 512:
+        assert tc_gemm.plan(8, 2 * shape["ff"], 512, DEV)[0] >= 2, "this shape was meant to cut K into splits"
     toks = {r: [int(t) for t in torch.randint(0, 400, (n,), generator=torch.Generator().manual_seed(s))]
             for r, n, s in (("a", 300, 1), ("b", 41, 2), ("c", 7, 3))}
 

@@ -356,3 +356,21 @@ def test_a_small_window_pool_cuts_portions_and_never_blocks_admission():
     assert max(portions) <= 9 * P and any(n < 96 for n in portions)
     assert m.pages_reclaimed > 0
     assert [m.free_pages(g) for g in (0, 1)] == [48, 9] and not m.requests
+
+
+def test_decode_attention_plan_covers_the_keys():
+    """The one statement of how decode attention cuts its keys (native code; the parts and the native
+    launcher of a block both call it): the splits cover the visible keys, a split has a multiple of 16
+    keys and at least 256 unless there are fewer than that to see, there are at most 256 splits, and
+    more multiprocessors never mean fewer splits."""
+    from infero_b200.kernels.attention import plan_decode
+    for n_tok, n_kv, group, vis in [(1, 4, 7, 4096), (8, 4, 7, 4096), (64, 4, 7, 4096), (1, 1, 1, 17), (3, 2, 2, 300),
+                                    (1, 2, 7, 200000), (200, 8, 5, 32768), (1, 4, 7, 1)]:
+        for sms in (0, 148, 64, 296):
+            chunk, splits = plan_decode(n_tok, n_kv, group, vis, sms)
+            assert chunk % 16 == 0 and 1 <= splits <= 256 and chunk * splits >= vis
+            assert chunk >= 256 or splits == 256, (n_tok, vis, sms, chunk, splits)
+            assert (splits - 1) * chunk < max(vis, 16), "a split with no keys"
+        assert plan_decode(n_tok, n_kv, group, vis, 296)[1] >= plan_decode(n_tok, n_kv, group, vis, 64)[1]
+    assert plan_decode(1, 4, 7, 4096, 148) == (256, 16)
+    assert plan_decode(64, 4, 7, 4096, 148) == (4096, 1)
