@@ -7,9 +7,12 @@ One JSON line on standard output.  A "step" is one decode step of the whole batc
 host-to-device copy of the step's inputs, the model's forward pass from the cache (a
 captured CUDA graph once the shape has been seen twice) and the argmax kernel.
 
-  value     decoded tokens per second at batch 8 with about 4,096 tokens of context each,
-            timed on the device with CUDA events around exactly K steps; the tokens fed are
-            drawn beforehand, so no step waits for the host
+  value     decoded tokens per second at batch 8 with 4,096 tokens of context each, timed on
+            the device with CUDA events around exactly K steps; the tokens fed are drawn
+            beforehand, so no step waits for the host.  The K-step region is run REPEATS times
+            (every repeat cut back to the same context, so each ends at 4,096 tokens) after
+            decode steps have run for at least half a second since the cache was filled; the
+            median repeat is reported, and every repeat with its median SM clock in ``repeats``
   e2e       the same through ``Engine.add_request`` / ``Engine.step``: host token ids in,
             sampled token ids back on the host every step
   prefill   one step of 2,048 prompt tokens (flops / time / peak)
@@ -49,6 +52,8 @@ OTHER_SHAPES = {
 SHAPE_NAMES = {"7b": "Qwen2.5-7B shape", "14b": "Qwen2.5-14B shape", "0.5b": "Qwen2.5-0.5B shape"}
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
+REPEATS = 5                 # timed K-step regions; the median one is reported
+WARM_SECONDS = 0.5          # decode steps run at least this long between the cache fill and the first timed region
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
@@ -106,47 +111,73 @@ def fill_cache(runner, rids, length, vocab, rng, chunk):
             done += n
 
 
-def time_decode(model, cfg_json, layers, batch, steps, warmup, clocks, page_size):
-    """Device-timed decode steps at ``batch`` requests of about CONTEXT tokens each."""
+def time_decode(model, cfg_json, layers, batch, steps, warmup, clocks, page_size, repeats=REPEATS):
+    """Device-timed decode steps at ``batch`` requests that end at CONTEXT tokens each: ``repeats``
+    regions of exactly ``steps`` steps, every one cut back to the same starting context first."""
     import torch
     from infero_b200 import kernels as K
     from infero_b200.config import EngineConfig
     from infero_b200.engine import ModelRunner, StepEntry
     vocab = cfg_json["vocab_size"]
     rng = random.Random(1000 + batch)
-    start_len = CONTEXT - (steps + warmup) - 1
+    start_len = CONTEXT - steps
     ecfg = EngineConfig(dtype="bfloat16", page_size=page_size, num_pages=batch * (-(-CONTEXT // page_size)),
                         max_seqs=batch, ctx=CONTEXT, max_batch_tokens=PREFILL_TOKENS, max_logit_rows=max(batch, 8),
                         cuda_graphs=True)
     runner = ModelRunner(model, ecfg)
     rids = [f"b{batch}_{i}" for i in range(batch)]
     fill_cache(runner, rids, start_len, vocab, rng, PREFILL_TOKENS)
-    feed = [[rng.randrange(vocab) for _ in range(batch)] for _ in range(steps + warmup)]
+    torch.cuda.synchronize()
+    filled_at = time.perf_counter()
+    feed = [[rng.randrange(vocab) for _ in range(batch)] for _ in range(steps)]
     picked = torch.empty(batch, dtype=torch.int32, device="cuda")
 
-    def one(i):
-        logits = runner.step([StepEntry(rid, [feed[i][j]], [0]) for j, rid in enumerate(rids)])
-        K.argmax(logits, picked)
+    def region(n):
+        for rid in rids:
+            if runner.length(rid) > start_len:
+                runner.truncate(rid, start_len)
+        for i in range(n):
+            logits = runner.step([StepEntry(rid, [feed[i][j]], [0]) for j, rid in enumerate(rids)])
+            K.argmax(logits, picked)
 
-    for i in range(warmup):
-        one(i)
+    # warm-up: at least `warmup` steps, and decode steps until WARM_SECONDS have passed since the fill (the
+    # fill runs at the power limit; the first steps after it would be timed at its clocks)
+    region(min(steps, max(warmup, 3)))
     torch.cuda.synchronize()
-    launches0, replays0 = K.launch_count(), runner.graph_replays
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    clocks.on = True
-    e0.record()
-    for i in range(warmup, warmup + steps):
-        one(i)
-    e1.record()
-    torch.cuda.synchronize()
-    clocks.on = False
-    ms = e0.elapsed_time(e1) / steps
-    graph_nodes = max((g.n_kernels for g in runner._graphs.values()), default=0)
-    launches = (K.launch_count() - launches0) + (runner.graph_replays - replays0) * graph_nodes
-    kv_tokens = sum(runner.length(r) for r in rids)
-    out = {"ms_per_step": ms, "tok_s": batch / (ms / 1e3), "launches": int(launches),
+    while time.perf_counter() - filled_at < WARM_SECONDS:
+        region(steps)
+        torch.cuda.synchronize()
+    runs = []
+    for _ in range(repeats):
+        for rid in rids:
+            runner.truncate(rid, start_len)
+        launches0, replays0 = K.launch_count(), runner.graph_replays
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        clocks.on = True
+        t0 = time.perf_counter()
+        e0.record()
+        for i in range(steps):
+            logits = runner.step([StepEntry(rid, [feed[i][j]], [0]) for j, rid in enumerate(rids)])
+            K.argmax(logits, picked)
+        e1.record()
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        clocks.on = False
+        graph_nodes = max((g.n_kernels for g in runner._graphs.values()), default=0)
+        runs.append({"ms_per_step": e0.elapsed_time(e1) / steps, "t": (t0, t1),
+                     "launches": int((K.launch_count() - launches0) + (runner.graph_replays - replays0) * graph_nodes),
+                     "graph_replays": runner.graph_replays - replays0})
+    # the keys a step reads, averaged over the region: each request grows from start_len to CONTEXT - 1
+    kv_tokens = batch * (start_len + (steps - 1) / 2.0)
+    order = sorted(range(repeats), key=lambda i: runs[i]["ms_per_step"])
+    mid = runs[order[repeats // 2]]
+    out = {"ms_per_step": mid["ms_per_step"], "tok_s": batch / (mid["ms_per_step"] / 1e3), "launches": mid["launches"],
            "bytes": decode_bytes(cfg_json, layers, batch, kv_tokens), "h2d": runner.last_h2d_bytes,
-           "graph_replays": runner.graph_replays - replays0, "kv_tokens": kv_tokens}
+           "graph_replays": mid["graph_replays"], "kv_tokens": kv_tokens,
+           "repeats": [{"ms_per_step": round(r["ms_per_step"], 4),
+                        "sm_mhz": clocks.median_between(*r["t"]) if hasattr(clocks, "median_between") else None}
+                       for r in runs]}
     for r in rids:
         runner.close(r)
     del runner
@@ -186,17 +217,21 @@ def time_prefill(model, cfg_json, layers, reps, warmup, clocks, page_size):
     return {"ms": ms, "flops": prefill_flops(cfg_json, layers, PREFILL_TOKENS)}
 
 
-def time_e2e(model, cfg_json, batch, steps, warmup, clocks, page_size):
-    """Through the Engine: requests in as host token ids, sampled ids out on the host each step."""
+def time_e2e(model, cfg_json, batch, steps, warmup, clocks, page_size, repeats=REPEATS):
+    """Through the Engine: requests in as host token ids, sampled ids out on the host each step.
+    ``repeats`` regions of ``steps`` steps one after the other (generation cannot be cut back, so the
+    contexts grow through the regions and reach CONTEXT at the end of the last); the median is reported."""
     import torch
     from infero_b200.engine import Engine
     from infero_b200.sampling import SamplingParams
     vocab = cfg_json["vocab_size"]
     rng = random.Random(2000 + batch)
-    start_len = CONTEXT - (steps + warmup) - 2
+    repeats = max(1, min(repeats, 300 // steps)) if steps < 300 else 1
+    warm_steps = max(warmup, 30)
     eng = Engine(model=model, dtype="bfloat16", ctx=CONTEXT, max_seqs=batch, kv_slots=batch * CONTEXT,
                  max_batch_tokens=PREFILL_TOKENS, page_size=page_size, cuda_graphs=True)
-    start_len -= 4 * batch                   # requests that finish their prompt early decode meanwhile
+    # requests that finish their prompt early decode while the others are still fed: 4 * batch steps at most
+    start_len = CONTEXT - repeats * steps - warm_steps - 4 * batch - 2
     pure_argmax = SamplingParams(temperature=0.0, repetition_penalty=1.0)
     for _ in range(batch):
         eng.add_request(random_prompt(rng, vocab, start_len), pure_argmax,
@@ -204,23 +239,31 @@ def time_e2e(model, cfg_json, batch, steps, warmup, clocks, page_size):
     started = set()
     while len(started) < batch:              # prompts, in portions, until every request has its first token
         started.update(ev.rid for ev in eng.step() if ev.token is not None)
-    for _ in range(warmup):
+    torch.cuda.synchronize()
+    filled_at = time.perf_counter()
+    n = 0
+    while n < warmup or (n < warm_steps and time.perf_counter() - filled_at < WARM_SECONDS):
         eng.step()
-    torch.cuda.synchronize()
-    clocks.on = True
-    t0 = time.perf_counter()
-    tokens = 0
-    for _ in range(steps):
-        tokens += sum(1 for ev in eng.step() if ev.token is not None)
-    torch.cuda.synchronize()
-    dt = time.perf_counter() - t0
-    clocks.on = False
+        n += 1
+    runs = []
+    for _ in range(repeats):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        tokens = 0
+        for _ in range(steps):
+            tokens += sum(1 for ev in eng.step() if ev.token is not None)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        runs.append((dt, tokens))
+    runs.sort(key=lambda r: r[0] / max(1, r[1]))
+    dt, tokens = runs[len(runs) // 2]
     h2d = eng.runner.last_h2d_bytes + 2 * batch * 4     # the step's arrays, and the sampler's (slot, flag) per row
     d2h = (batch + 1) * 4                    # one picked token per row, and the device's fault flag
     eng.abort_all("bench done")
     del eng
     torch.cuda.empty_cache()
-    return {"tok_s": tokens / dt, "ms_per_step": dt * 1e3 / steps, "h2d": h2d, "d2h": d2h, "tokens": tokens}
+    return {"tok_s": tokens / dt, "ms_per_step": dt * 1e3 / steps, "h2d": h2d, "d2h": d2h, "tokens": tokens,
+            "repeats": len(runs)}
 
 
 def main(argv=None) -> int:
@@ -268,10 +311,11 @@ def main(argv=None) -> int:
     main_clocks = clocks.summary()
     quiet = ClockSampler.__new__(ClockSampler)
     quiet.on = False
+    quiet.median_between = lambda t0, t1: None
     points = {}
     if not args.skip_points:
         for b in (1, 64):
-            r = time_decode(model, cfg_json, layers, b, min(steps, 50), warmup, quiet, args.page_size)
+            r = time_decode(model, cfg_json, layers, b, min(steps, 50), warmup, quiet, args.page_size, repeats=3)
             points[f"decode_b{b}"] = round(r["tok_s"], 1)
             points[f"decode_b{b}_hbm_frac"] = round(r["bytes"] / (r["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"], 3)
     prefill = None
@@ -301,12 +345,14 @@ def main(argv=None) -> int:
                    "kv_heads": cfg_json["num_key_value_heads"], "head_dim": cfg_json["head_dim"],
                    "intermediate": cfg_json["intermediate_size"], "vocab": cfg_json["vocab_size"],
                    "page_size": args.page_size, "l2": "inputs larger than L2 (weights and cache)",
-                   "peaks": pk["source"], "prefill_tokens": PREFILL_TOKENS},
+                   "peaks": pk["source"], "prefill_tokens": PREFILL_TOKENS, "repeats": REPEATS,
+                   "timing": f"median of {REPEATS} regions of {steps} steps, each ending at {CONTEXT} tokens"},
         "e2e": e2e, "gpu_launches": main_pt["launches"], "clocks": main_clocks,
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
+        "repeats": main_pt["repeats"],
         "wall_s": round(time.time() - t_start, 1),
     }
     print(json.dumps(line))

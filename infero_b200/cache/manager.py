@@ -206,6 +206,16 @@ class CacheManager:
         if self._L.infero_cache_commit(self._h, rc.slot, int(n_new)):
             raise ValueError("commit of more tokens than were reserved")
 
+    def truncate(self, rc: RequestCache, length: int) -> None:
+        """Forget the request's tokens from position ``length`` on; pages wholly behind the new end go
+        back (the reference's ``KvPool::truncate``, crates/model/src/cache.rs:656-679).  A window group
+        that has already given back keys a query at ``length`` would see cannot go back that far."""
+        rcode = self._L.infero_cache_truncate(self._h, rc.slot, int(length))
+        if rcode == 2:
+            raise ValueError(f"request {rc.rid!r}: a window group no longer holds the keys position {length} sees")
+        if rcode:
+            raise ValueError(f"request {rc.rid!r} holds {rc.length} tokens (reserved {rc.reserved}); cannot cut to {length}")
+
     def abort_reservation(self, rc: RequestCache) -> None:
         """Drop pages reserved for a step that did not run."""
         self._L.infero_cache_abort(self._h, rc.slot)

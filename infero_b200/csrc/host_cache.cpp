@@ -243,6 +243,41 @@ int infero_cache_commit(void* h, int slot, int n_new) {
     return 0;
 }
 
+// Forget the tokens from position `length` on (the reference's KvPool::truncate,
+// crates/model/src/cache.rs:656-679): pages that lie wholly behind the new end go back, the rest
+// stays.  0: done.  1: nothing to cut (length above what is cached), or a step is in flight.
+// 2: a window group has already given back pages that a query at `length` would see, so the
+// request cannot go back that far.  Nothing changes unless 0 is returned.
+int infero_cache_truncate(void* h, int slot, int length) {
+    Cache* c = static_cast<Cache*>(h);
+    if (!valid_slot(c, slot)) return 1;
+    Request& r = c->reqs[slot];
+    if (length < 0 || length > r.length || r.reserved != 0) return 1;
+    const int P = c->page_size;
+    for (size_t g = 0; g < c->groups.size(); ++g) {
+        const int W = c->groups[g].window;
+        if (W <= 0) continue;
+        // at the new length, pages whose last position is <= length - W may be missing, no others
+        const int live_from = length - W + 1;
+        const int may_be_dead = live_from > 0 ? live_from / P : 0;
+        if (r.first_live[g] > may_be_dead) return 2;
+    }
+    const int keep = c->pages_for(length);
+    for (size_t g = 0; g < c->groups.size(); ++g) {
+        std::vector<int>& t = r.tables[g];
+        int* row = c->mirror[g].data() + (size_t)slot * c->width;
+        for (int k = keep; k < (int)t.size(); ++k) {
+            if (t[k] >= 0) c->give_back((int)g, t[k]);
+            row[k] = -1;
+        }
+        if ((int)t.size() > keep) t.resize(keep);
+        if (r.first_live[g] > keep) r.first_live[g] = keep;
+    }
+    r.length = length;
+    if (length == 0) r.fresh = true;
+    return 0;
+}
+
 void infero_cache_abort(void* h, int slot) {
     Cache* c = static_cast<Cache*>(h);
     Request& r = c->reqs[slot];

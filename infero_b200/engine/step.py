@@ -171,6 +171,10 @@ class ModelRunner:
     def length(self, rid: Hashable) -> int:
         return self.manager.get(rid).length
 
+    def truncate(self, rid: Hashable, length: int) -> None:
+        """Cut a request back to its first ``length`` tokens; the next step appends from there."""
+        self.manager.truncate(self.manager.get(rid), length)
+
     # ---- the step ----------------------------------------------------------------------------
     def _validate(self, entries: Sequence[StepEntry]) -> List[RequestCache]:
         if not entries:

@@ -6,13 +6,14 @@ import time
 
 
 class ClockSampler:
-    """Reads SM clock and throttle reasons through NVML every 20 ms while ``on`` is set.
+    """Reads SM clock and throttle reasons through NVML every 5 ms while ``on`` is set.
     Reading only: nothing about the GPU is changed."""
     REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
                0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting"}
 
     def __init__(self, index: int = 0):
         self.samples, self.reasons, self.on, self._stop = [], set(), False, False
+        self.times = []                    # time.perf_counter() of each sample
         self.max_mhz = None
         try:
             import pynvml
@@ -32,13 +33,19 @@ class ClockSampler:
             if self.on:
                 try:
                     self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                    self.times.append(time.perf_counter())
                     mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
                     for bit, name in self.REASONS.items():
                         if mask & bit:
                             self.reasons.add(name)
                 except Exception:       # noqa: BLE001
                     pass
-            time.sleep(0.02)
+            time.sleep(0.005)
+
+    def median_between(self, t0: float, t1: float):
+        """Median SM clock over the samples taken between two ``time.perf_counter()`` readings."""
+        s = sorted(m for m, t in zip(self.samples, self.times) if t0 <= t <= t1)
+        return s[len(s) // 2] if s else None
 
     def summary(self):
         self._stop = True

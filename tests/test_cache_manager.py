@@ -178,6 +178,13 @@ def test_random_orders_of_requests_keep_every_invariant(seed):
                 m.abort_reservation(rc)
             else:
                 m.commit(rc, n)
+        elif op < 0.92 and live:
+            rc = live[rng.choice(list(live))]
+            before = (rc.length, [a.num_free for a in m.allocators])
+            try:
+                m.truncate(rc, max(0, rc.length - rng.choice([0, 1, 5, 40])))
+            except ValueError:
+                assert (rc.length, [a.num_free for a in m.allocators]) == before
         elif live:
             rid = rng.choice(list(live))
             m.close(rid)
@@ -208,3 +215,33 @@ def test_storage_keeps_keys_and_values_at_their_own_widths_and_pools():
     assert st.layer_kv(3).k.shape == (501, 3, 16, 8) and st.layer_kv(3).v.shape == (501, 3, 16, 24)
     assert st.bytes_per_token() == 4 * (2 * 2 * 16 * 3 + 3 * (8 + 24))
     assert st.bytes() == 4 * 16 * (501 * 64 + 2 * 25 * 64 + 501 * 96)
+
+
+def test_truncate_gives_back_the_tail_and_refuses_what_a_window_lost():
+    m = CacheManager([GroupSpec(None), GroupSpec(32)], num_pages=[16, 8], page_size=16, max_requests=2)
+    a = m.open("a")
+    m.reserve(a, 70)
+    m.commit(a, 70)                                   # window pages 0 and 1 (keys 0 .. 31) went back
+    assert a.tables[1][:2] == [-1, -1] and m.free_pages(0) == 11
+    m.truncate(a, 65)                                 # a query at 65 sees keys 34 .. 65: still all held
+    assert a.length == 65 and len(a.tables[0]) == 5 and m.free_pages(0) == 11
+    m.truncate(a, 64)                                 # the fifth page is behind the end now
+    assert len(a.tables[0]) == 4 and len(a.tables[1]) == 4 and m.free_pages(0) == 12
+    m.check()
+    with pytest.raises(ValueError, match="window"):
+        m.truncate(a, 50)                             # would see keys 19 .. 50, and page 1 is gone
+    with pytest.raises(ValueError):
+        m.truncate(a, 65)                             # nothing to cut
+    assert a.length == 64
+    m.reserve(a, 3)
+    with pytest.raises(ValueError):
+        m.truncate(a, 60)                             # a step is in flight
+    m.commit(a, 3)
+    b = m.open("b")
+    m.reserve(b, 40)
+    m.commit(b, 40)
+    m.truncate(b, 0)
+    assert b.length == 0 and b.fresh and b.tables == [[], []]
+    m.check()
+    m.close("a"); m.close("b")
+    assert [m.free_pages(g) for g in (0, 1)] == [16, 8]

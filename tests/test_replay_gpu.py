@@ -486,3 +486,39 @@ def test_the_window_group_runs_in_a_far_smaller_pool(name, dtype):
     assert err <= TOL[dtype], f"{name} {dtype}: relative error {err:.3e} at {where}"
     assert runner.manager.pages_reclaimed > 20 and runner.manager.pages_reused > 0
     assert [runner.manager.free_pages(g) for g in (0, 1)] == [120, small] and not runner.manager.requests
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("E", "bfloat16"), ("E", "float32")])
+def test_a_request_cut_back_continues_with_other_tokens(name, dtype):
+    """Truncation (the reference's KvPool::truncate, crates/model/src/cache.rs:656-679): a request is
+    cut back to a prefix and continues with other tokens; the logits are those of the new sequence, and
+    the pages behind the cut were given back and used again."""
+    from infero_b200.engine import StepEntry
+    mdir = model_dir(name)
+    base = make_requests(name, [100], seed=21)["r0"]
+    other = make_requests(name, [100], seed=22)["r0"]
+    runner = make_runner(mdir, dtype, 128)
+    runner.open("x")
+    runner.step([StepEntry("x", base, [99])])
+    free_before = runner.manager.free_pages(0)
+    runner.truncate("x", 37)
+    assert runner.length("x") == 37 and runner.manager.free_pages(0) == free_before + 4
+    new = base[:37] + other[37:90]
+    rows = [runner.step([StepEntry("x", new[37:70], list(range(33)))]).float().cpu().numpy()]
+    for p in range(70, 90):
+        rows.append(runner.step([StepEntry("x", [new[p]], [0])]).float().cpu().numpy())
+    got = {("x", 37 + i): row for i, row in enumerate(np.concatenate(rows))}
+    err, where = R.compare(got, plain_logits(mdir, {"x": new}))
+    assert err <= TOL[dtype], f"{name} {dtype}: relative error {err:.3e} at {where}"
+    runner.manager.check()
+    runner.close("x")
+    assert runner.manager.free_pages(0) == runner.manager.allocators[0].num_pages
+    # where a window has passed, the keys are gone and the cut is refused
+    if name == "E":
+        wdir = model_dir("D")
+        r2 = make_runner(wdir, dtype, 128)
+        r2.open("y")
+        r2.step([StepEntry("y", make_requests("D", [100], seed=1)["r0"], [])])
+        with pytest.raises(ValueError, match="window"):
+            r2.truncate("y", 60)
+        r2.truncate("y", 99)
