@@ -137,6 +137,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + TD_WARPS * STAGES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+    TL_BEGIN();
     pdl_launch_dependents();
     if (threadIdx.x == 0) {
         tc::prefetch_tensormap(&map_k);
@@ -313,6 +314,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         merge_if_last<D>(counters + (size_t)ti * gridDim.y + blockIdx.y, reinterpret_cast<float*>(smem),
                          po - (size_t)split * D, pml - (size_t)split * 2, n_splits, valid,
                          out + (size_t)t * out_stride + (size_t)h0 * D);
+    TL_END(TL_ATTN_DECODE);
 }
 
 // out[t, h, :] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), M = max_s m_s; splits in
@@ -443,3 +445,5 @@ int infero_attn_decode_tma(const void* q, int q_stride, void* out, int out_strid
 }
 
 }  // extern "C"
+
+INFERO_TL_UNIT(attention_decode)

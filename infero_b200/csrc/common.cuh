@@ -75,6 +75,48 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// ---- timeline (only in a library built with -DINFERO_TIMELINE) -----------------------------
+// The reference times its kernels one by one with events (crates/cuda/src/profile.rs:28-130).  Under
+// programmatic dependent launch neighbours overlap, and what a kernel costs in place is not what it
+// takes alone; a library built with INFERO_TIMELINE=1 therefore lets every block of the instrumented
+// kernels leave (kind, grid size, block, multiprocessor, first and last nanosecond of the global
+// timer) in a log that tools/timeline.py attaches and reads.  The ordinary build compiles none of it.
+enum : int { TL_EMBED = 1, TL_NORM = 2, TL_GEMM = 3, TL_ROPE = 4, TL_ATTN_DECODE = 5, TL_ARGMAX = 6,
+              TL_ARGMAX_FINAL = 7, TL_KEEP = 8, TL_SWIGLU = 9, TL_ATTN_PREFILL = 10 };
+#ifdef INFERO_TIMELINE
+struct InferoTlRecord { unsigned long long t0, t1; int kind, grid, block, sm; };
+struct InferoTlLog { unsigned int cursor, capacity; unsigned long long pad; InferoTlRecord rec[1]; };
+static __device__ InferoTlLog* infero_tl_log = nullptr;          // one per translation unit
+__device__ __forceinline__ unsigned long long tl_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void tl_end(int kind, unsigned long long t0) {
+    InferoTlLog* log = infero_tl_log;
+    if (!log) return;
+    const unsigned int i = atomicAdd(&log->cursor, 1u);
+    if (i >= log->capacity) return;
+    unsigned int sm;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
+    InferoTlRecord r;
+    r.t0 = t0, r.t1 = tl_now(), r.kind = kind, r.grid = (int)(gridDim.x * gridDim.y * gridDim.z);
+    r.block = (int)((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x), r.sm = (int)sm;
+    log->rec[i] = r;
+}
+#define TL_BEGIN() const unsigned long long tl_t0 = tl_now()
+#define TL_END_IF(cond, kind) do { if (cond) tl_end(kind, tl_t0); } while (0)
+#define INFERO_TL_UNIT(name)                                                                       \
+    extern "C" int infero_tl_attach_##name(void* log) {                                            \
+        return cudaMemcpyToSymbol(infero_tl_log, &log, sizeof(log)) != cudaSuccess;                \
+    }
+#else
+#define TL_BEGIN() do { } while (0)
+#define TL_END_IF(cond, kind) do { } while (0)
+#define INFERO_TL_UNIT(name)
+#endif
+#define TL_END(kind) TL_END_IF(threadIdx.x == 0 && threadIdx.y == 0, kind)
+
 // ---- error reporting -------------------------------------------------------------------
 // Launchers return 0 on success.  On failure they return non-zero and leave a message
 // that infero_last_error() hands to the caller.

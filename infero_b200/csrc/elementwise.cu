@@ -16,6 +16,7 @@ template <typename TE>
 __global__ void embed_gather_kernel(const TE* __restrict__ table, const int* __restrict__ ids,
                                     const int* __restrict__ device_tokens, float* __restrict__ x, int d, int vocab,
                                     float scale) {
+    TL_BEGIN();
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -27,6 +28,7 @@ __global__ void embed_gather_kernel(const TE* __restrict__ table, const int* __r
     const TE* row = table + (size_t)id * d;
     float* o = x + (size_t)t * d;
     for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_f32(row[i]) * scale;
+    TL_END(TL_EMBED);
 }
 
 // 4 consecutive elements as 32-bit values (p must be aligned to 4 elements).
@@ -68,6 +70,7 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ x
                                    const void* __restrict__ w, int wdtype, float eps,
                                    TO* __restrict__ out, const int* __restrict__ rows, int d) {
     __shared__ float red[32];
+    TL_BEGIN();
     pdl_launch_dependents();
     // the norm's weights do not come from the kernel in front: the thread's first vector of them
     // is fetched before the wait
@@ -140,6 +143,7 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ x
             orow[i] = from_f32<TO>(v0 * sc * load_any(w, wdtype, i));
         }
     }
+    TL_END(TL_NORM);
 }
 
 // Many rows, one vector per thread: a block walks over rows blockIdx.x, + gridDim.x, ... and
@@ -152,6 +156,7 @@ __global__ void __launch_bounds__(1024, 2) add_rmsnorm_rows_kernel(float* __rest
                                         const void* __restrict__ w, int wdtype, float eps,
                                         TO* __restrict__ out, int n_rows, int d) {
     __shared__ float red[32];
+    TL_BEGIN();
     pdl_launch_dependents();
     pdl_wait();
     const int i = threadIdx.x * 4;
@@ -190,6 +195,7 @@ __global__ void __launch_bounds__(1024, 2) add_rmsnorm_rows_kernel(float* __rest
             store4(out + (size_t)r * d + i, v);
         }
     }
+    TL_END(TL_NORM);
 }
 
 // The same rows through a ring in shared memory: one thread asks for whole rows (x and delta, one
@@ -214,6 +220,7 @@ __global__ void __launch_bounds__(1024, 2) add_rmsnorm_ring_kernel(float* __rest
     __shared__ int abort_flag;
     const uint32_t x_bytes = (uint32_t)d * 4u, d_bytes = delta ? (uint32_t)d * (uint32_t)sizeof(TD) : 0u;
     const uint32_t row_bytes = x_bytes + d_bytes;
+    TL_BEGIN();
     pdl_launch_dependents();
     if (threadIdx.x == 0) {
         for (int s = 0; s < ring; ++s) tc::mbar_init(&full[s], 1);
@@ -293,6 +300,7 @@ __global__ void __launch_bounds__(1024, 2) add_rmsnorm_ring_kernel(float* __rest
         for (int r = (int)blockIdx.x + k * (int)gridDim.x, n = 0; r < n_rows && n < ring; r += gridDim.x, ++n, ++kk)
             tc::mbar_wait(&full[kk % ring], (uint32_t)(kk / ring) & 1u, &never);
     }
+    TL_END(TL_NORM);
 }
 
 // out[t, j] = silu(g) * u with g = sum_s gu[s][t, 2j], u = sum_s gu[s][t, 2j + 1] (s ascending):
@@ -300,6 +308,7 @@ __global__ void __launch_bounds__(1024, 2) add_rmsnorm_ring_kernel(float* __rest
 template <typename T, int VEC>
 __global__ void swiglu_kernel(const T* __restrict__ gu, int splits, long long split_stride, T* __restrict__ out_same,
                               bf16* __restrict__ out_bf16, int ff, size_t total) {
+    TL_BEGIN();
     pdl_launch_dependents();
     pdl_wait();
     size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
@@ -333,6 +342,7 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, int splits, long long sp
         if (out_bf16) out_bf16[i] = __float2bfloat16_rn(h[0]);
         else out_same[i] = from_f32<T>(h[0]);
     }
+    TL_END(TL_SWIGLU);
 }
 
 // x[t,:] += delta[t,:]   (used when no norm follows)
@@ -485,3 +495,5 @@ int infero_residual_add(float* x, const void* delta, int delta_dtype, int n_toke
 }
 
 }  // extern "C"
+
+INFERO_TL_UNIT(elementwise)

@@ -107,6 +107,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* never_flag = abort_flag + 1;           // stays 0: for waits that must not be cut short
 
+    TL_BEGIN();
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int a0 = blockIdx.x * TILE_A, b0 = blockIdx.y * BN;
@@ -344,6 +345,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, TMEM_COLS);
     }
+    TL_END(TL_GEMM);
 }
 
 // One epilogue warp's share of a finished accumulator: its 32 rows (TMEM lanes at lane_addr, result
@@ -436,6 +438,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* never_flag = abort_flag + 1;
 
+    TL_BEGIN();
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_a = (RA + TILE_A - 1) / TILE_A, tiles_b = (RB + BN - 1) / BN;
@@ -582,6 +585,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, 2 * PERS_MAX_BN);
     }
+    TL_END(TL_GEMM);
 }
 
 // ---- many tokens: a pair of CTAs per tile (cta_group::2) ---------------------------------------------
@@ -615,6 +619,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* never_flag = abort_flag + 1;
 
+    TL_BEGIN();
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
@@ -768,6 +773,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         tc_fence_after_sync();
         tmem_dealloc_pair(tmem_base, 2 * PERS_MAX_BN);
     }
+    TL_END(TL_GEMM);
 }
 
 // out[t, n] = sum_s partial[s, t, n] (+ bias[n]); the sum runs over s in ascending order.
@@ -1241,3 +1247,5 @@ int infero_tc_set_error_flag(int value) {
 }
 
 }  // extern "C"
+
+INFERO_TL_UNIT(gemm_tc)

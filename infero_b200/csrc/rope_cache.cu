@@ -21,6 +21,7 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int row_stride, const int
                                   int max_blocks, const float* __restrict__ inv_freq, int rotary_dim,
                                   T* __restrict__ k_cache, T* __restrict__ v_cache, int page_size,
                                   int n_heads, int n_kv, int head_dim, int write_cache) {
+    TL_BEGIN();
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -53,6 +54,7 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int row_stride, const int
     } else {
         for (int i = threadIdx.x; i < head_dim; i += blockDim.x) dst[i] = row[i];
     }
+    TL_END(TL_ROPE);
 }
 
 // bf16, many tokens: one block per token.  The sines and cosines of the token's position are
@@ -66,6 +68,7 @@ rope_cache_vec_kernel(bf16* __restrict__ qkv, int row_stride, const int* __restr
                       bf16* __restrict__ v_cache, int page_size, int n_heads, int n_kv, int head_dim,
                       int write_cache) {
     extern __shared__ float2 sc[];                 // [rotary_dim / 2] (sin, cos)
+    TL_BEGIN();
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -126,6 +129,7 @@ rope_cache_vec_kernel(bf16* __restrict__ qkv, int row_stride, const int* __restr
         }
         *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
     }
+    TL_END(TL_ROPE);
 }
 
 // The same, reading q, k and v as the sum of 32-bit partial products (+ bias) that the
@@ -139,6 +143,7 @@ __global__ void rope_cache_partials_kernel(const float* __restrict__ partial, in
                                            int max_blocks, const float* __restrict__ inv_freq, int rotary_dim,
                                            T* __restrict__ k_cache, T* __restrict__ v_cache, int page_size,
                                            int n_heads, int n_kv, int head_dim, int write_cache) {
+    TL_BEGIN();
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -179,6 +184,7 @@ __global__ void rope_cache_partials_kernel(const float* __restrict__ partial, in
     } else {
         for (int i = threadIdx.x; i < head_dim; i += blockDim.x) dst[i] = from_f32<T>(value(i));
     }
+    TL_END(TL_ROPE);
 }
 
 // The same for bf16 outputs with vector loads: one block per token, sines and cosines shared by
@@ -193,6 +199,7 @@ rope_cache_partials_vec_kernel(const float* __restrict__ partial, int splits, lo
                                bf16* __restrict__ v_cache, int page_size, int n_heads, int n_kv, int head_dim,
                                int write_cache) {
     extern __shared__ float2 sc[];
+    TL_BEGIN();
     pdl_launch_dependents();
     // positions and block tables are set before the step's first kernel: the sines can be worked
     // out while the product in front is still running
@@ -284,6 +291,7 @@ rope_cache_partials_vec_kernel(const float* __restrict__ partial, int splits, lo
             store4bf(v_cache + ((size_t)page * n_kv + kvh) * page_size * head_dim + in_page + c * 4, v);
         }
     }
+    TL_END(TL_ROPE);
 }
 
 }  // namespace
@@ -361,3 +369,5 @@ int infero_rope_cache_partials(const float* partial, int splits, long long split
 }
 
 }  // extern "C"
+
+INFERO_TL_UNIT(rope_cache)

@@ -117,6 +117,7 @@ argmax_partial_kernel(const float* __restrict__ logits, int vocab, int n_chunks,
                       int* __restrict__ pi) {
     __shared__ float bv[ARGMAX_THREADS / 32];
     __shared__ int bi[ARGMAX_THREADS / 32];
+    TL_BEGIN();
     pdl_launch_dependents();
     pdl_wait();
     const int row = blockIdx.y, chunk = blockIdx.x;
@@ -142,11 +143,13 @@ argmax_partial_kernel(const float* __restrict__ logits, int vocab, int n_chunks,
             argmax_merge(best, idx, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, idx, o));
         if (lane == 0) { pv[(size_t)row * n_chunks + chunk] = best; pi[(size_t)row * n_chunks + chunk] = idx; }
     }
+    TL_END(TL_ARGMAX);
 }
 
 __global__ void __launch_bounds__(128)
 argmax_final_kernel(const float* __restrict__ pv, const int* __restrict__ pi, int n_rows, int n_chunks,
                     int* __restrict__ out) {
+    TL_BEGIN();
     pdl_launch_dependents();
     pdl_wait();
     const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -158,6 +161,7 @@ argmax_final_kernel(const float* __restrict__ pv, const int* __restrict__ pi, in
     for (int o = 16; o > 0; o >>= 1)
         argmax_merge(best, idx, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, idx, o));
     if (lane == 0) out[row] = (idx == 0x7fffffff) ? 0 : idx;   // all -inf / NaN: token 0
+    TL_END(TL_ARGMAX_FINAL);
 }
 
 // final[r] = use_sample[r] ? sampled[r] : greedy[r];  device_tokens[slot[r]] = final[r]: the
@@ -170,6 +174,7 @@ __global__ void keep_tokens_kernel(const int* __restrict__ greedy, const int* __
                                    int* __restrict__ final_tok, int* __restrict__ device_tokens, int n_rows,
                                    int* __restrict__ ring, int* __restrict__ ring_len, int ring_width,
                                    const int* __restrict__ fault_flag) {
+    TL_BEGIN();
     pdl_launch_dependents();
     pdl_wait();
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
@@ -185,6 +190,7 @@ __global__ void keep_tokens_kernel(const int* __restrict__ greedy, const int* __
         ring[(size_t)s * ring_width + len % ring_width] = tok;
         ring_len[s] = len + 1;
     }
+    TL_END(TL_KEEP);
 }
 
 // Exclusive prefix sum of one int per thread over the block; returns the total too.
@@ -506,3 +512,5 @@ int infero_apply_penalty_ring(float* logits, int n_rows, int vocab, const int* r
 int infero_sample_max_k() { return SAMPLE_MAX_K; }
 
 }  // extern "C"
+
+INFERO_TL_UNIT(sampling)

@@ -61,12 +61,19 @@ def source_digest(extra: str = "") -> str:
     return h.hexdigest()[:16]
 
 
+def variant_defines() -> List[str]:
+    """INFERO_TIMELINE=1 builds the variant whose kernels log when each of their blocks ran
+    (tools/timeline.py); it lives in a build folder of its own beside the ordinary library."""
+    return ["-DINFERO_TIMELINE"] if os.environ.get("INFERO_TIMELINE", "0") == "1" else []
+
+
 def build_dir() -> str:
     """A folder this user can write: csrc/_build, else a per-user folder under the temp dir."""
     env = os.environ.get("INFERO_BUILD_DIR")
-    cands = [env] if env else []
-    cands.append(os.path.join(CSRC, "_build"))
-    cands.append(os.path.join(tempfile.gettempdir(), f"infero_b200_build_{os.getuid()}"))
+    suffix = "_timeline" if variant_defines() else ""
+    cands = [env + suffix] if env else []
+    cands.append(os.path.join(CSRC, "_build" + suffix))
+    cands.append(os.path.join(tempfile.gettempdir(), f"infero_b200_build{suffix}_{os.getuid()}"))
     for d in cands:
         try:
             os.makedirs(d, exist_ok=True)
@@ -90,7 +97,8 @@ def _compile_one(nvcc: str, src: str, obj: str, defines: List[str]) -> None:
 def ensure_built(verbose: bool = True) -> str:
     """Return the path of an up-to-date shared library, compiling what is stale."""
     d = build_dir()
-    digest = source_digest()
+    defines = variant_defines()
+    digest = source_digest(" ".join(defines))
     lib = os.path.join(d, LIB_NAME)
     stamp = os.path.join(d, "digest.txt")
     if os.path.exists(lib) and os.path.exists(stamp):
@@ -113,7 +121,7 @@ def ensure_built(verbose: bool = True) -> str:
             objs.append(obj)
             if os.path.exists(obj):
                 continue
-            jobs.append((ex.submit(_compile_one, nvcc, s, obj + f".tmp{os.getpid()}.o", []), s, obj))
+            jobs.append((ex.submit(_compile_one, nvcc, s, obj + f".tmp{os.getpid()}.o", defines), s, obj))
         done = 0
         for fut, s, obj in [(j[0], j[1], j[2]) for j in jobs]:
             fut.result()
