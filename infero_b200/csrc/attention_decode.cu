@@ -19,6 +19,8 @@
 #include "attn_common.cuh"
 #include "tc_common.cuh"
 
+extern "C" int infero_attn_decode_tma_supported(int head_dim, int page_size);
+
 namespace {
 
 using namespace attn;
@@ -32,10 +34,29 @@ struct TdPlan {
     static constexpr int STAGE_BYTES = 2 * HALF_BYTES;
     static constexpr int WARP_BYTES = STAGES * STAGE_BYTES;
     static constexpr int TILES_BYTES = TD_WARPS * WARP_BYTES;
-    static constexpr int RED_BYTES = TD_WARPS * 16 * (D + 3) * 4;
+    static constexpr int RED_STRIDE = D + 8;                        // floats; the pad keeps the warps' row stores off each other's banks
+    static constexpr int RED_BYTES = TD_WARPS * 16 * (RED_STRIDE + 3) * 4;
     static constexpr int DATA_BYTES = TILES_BYTES > RED_BYTES ? TILES_BYTES : RED_BYTES;
     static constexpr int BAR_OFFSET = DATA_BYTES;
+    // the fused kernel's own: sines and cosines, the 16 rotated query rows, the token's new key and value
+    static constexpr int Q_STRIDE = D + 8;
+    static constexpr int FUSED_OFFSET = (BAR_OFFSET + TD_WARPS * STAGES * 8 + 16 + 15) / 16 * 16;
+    static constexpr int FUSED_BYTES = (D / 2) * 8 + 16 * Q_STRIDE * 2 + 2 * D * 2;
     static constexpr int TOTAL = DATA_BYTES + TD_WARPS * STAGES * 8 + 16 + 1024;
+    static constexpr int TOTAL_FUSED = FUSED_OFFSET + FUSED_BYTES + 1024;
+};
+
+// What the fused kernel takes in place of finished queries: the q/k/v product of the step's tokens as
+// the few-token product kernel leaves it (32-bit partial sums [splits][token][(heads + 2 kv heads) * D],
+// bias not yet added), and what the rotary-and-append kernel would have needed to finish it.
+struct FusedQkv {
+    const float* partial;
+    long long split_stride;
+    const void* bias;
+    const float* inv_freq;
+    bf16* k_cache;
+    bf16* v_cache;
+    int splits, row_width, bias_dtype, rotary_dim, write_cache;
 };
 
 // The CTA that finishes last among the splits of one (token, kv head, group tile) merges them:
@@ -118,7 +139,15 @@ __device__ __forceinline__ void merge_if_last(int* counter, float* wbuf, const f
 }
 
 // partial_o [n_tok, n_heads, n_splits, D] float (unnormalised), partial_ml [n_tok, n_heads, n_splits, 2].
-template <int D>
+//
+// FUSED: the kernel also does what the rotary-and-append kernel does for a step of single tokens, so
+// that a layer has one launch (and one wait for the kernel in front) fewer.  Every CTA adds up the
+// partial sums of its own query heads, adds the bias, rotates them and keeps them in shared memory
+// (the same operations in the same order as rope_cache_partials_vec_kernel, so the same bf16 values);
+// the CTA whose split holds the token's own position does the same for the key and the value of its
+// kv head, writes them to the cache for the steps to come and puts them into the row of its own tile
+// that the bulk load filled from the cache before they were there.
+template <int D, bool FUSED>
 __global__ void __launch_bounds__(TD_THREADS)
 attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        const bf16* __restrict__ q, int q_stride, const int* __restrict__ block_table,
@@ -126,7 +155,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                        int tok_first, int n_heads, int n_kv, int page_size, int window, float scale_log2,
                        int chunk, int n_splits, float* __restrict__ partial_o, float* __restrict__ partial_ml,
                        bf16* __restrict__ out, int out_stride, int* __restrict__ counters,
-                       int* __restrict__ err_flag) {
+                       int* __restrict__ err_flag, const FusedQkv fq) {
     using Plan = TdPlan<D>;
     using Layout = Swizzled128<D, 16>;
     constexpr int STAGES = Plan::STAGES;
@@ -179,6 +208,10 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                              out + (size_t)t * out_stride + (size_t)h0 * D);
         return;
     }
+    float2* sc = reinterpret_cast<float2*>(smem + Plan::FUSED_OFFSET);            // [rotary_dim / 2] (sine, cosine)
+    bf16* q_rows = reinterpret_cast<bf16*>(sc + D / 2);                            // [16][Q_STRIDE]
+    bf16* k_new = q_rows + 16 * Plan::Q_STRIDE;                                    // [D]
+    bf16* v_new = k_new + D;                                                       // [D]
     __syncthreads();
 
     uint8_t* my = smem + (size_t)warp * Plan::WARP_BYTES;
@@ -220,13 +253,130 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 #pragma unroll
     for (int i = 0; i < STAGES - 1; ++i)
         if (old_keys_only(i)) issue(i);
+    if (FUSED) {
+        // the angles depend on the position alone: worked out while the first loads are on their way
+        // (and, if this block could start early, while the product in front still runs)
+        for (int i = threadIdx.x; i < (fq.rotary_dim >> 1); i += TD_THREADS) {
+            float sn, cs;
+            sincosf((float)pos * fq.inv_freq[i], &sn, &cs);
+            sc[i] = make_float2(sn, cs);
+        }
+        __syncthreads();
+    }
     pdl_wait();                                        // q and this step's key and value
+    TL_MARK(51);
 #pragma unroll
     for (int i = 0; i < STAGES - 1; ++i)
         if (!old_keys_only(i)) issue(i);
 
     uint32_t qf[D / 16][4];
-    load_q<D>(qf, q + (size_t)t * q_stride + (size_t)h0 * D, (size_t)D, valid, lane);
+    // does this CTA's split hold the token's own position?  Then the key and value of this step are its job.
+    const bool own = FUSED && fq.write_cache && pos >= k_begin && pos < k_end;
+    if (FUSED) {
+        const float* src_row = fq.partial + (size_t)t * fq.row_width;
+        auto sum4 = [&](size_t col, float* v) {
+            v[0] = v[1] = v[2] = v[3] = 0.f;
+            // eight splits' loads in flight at a time; added in ascending order
+            for (int s0 = 0; s0 < fq.splits; s0 += 8) {
+                float4 f[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    if (s0 + k < fq.splits) f[k] = *reinterpret_cast<const float4*>(src_row + (size_t)(s0 + k) * fq.split_stride + col);
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    if (s0 + k < fq.splits) { v[0] += f[k].x; v[1] += f[k].y; v[2] += f[k].z; v[3] += f[k].w; }
+            }
+            if (fq.bias) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) v[k] += load_any(fq.bias, fq.bias_dtype, col + k);
+            }
+        };
+        auto store4bf = [](bf16* p, const float* v) {
+            uint2 u;
+            u.x = pack_bf16(v[0], v[1]);
+            u.y = pack_bf16(v[2], v[3]);
+            *reinterpret_cast<uint2*>(p) = u;
+        };
+        // the two halves of a rotated chunk at once: all loads of both (and of their bias) are on their way
+        // before the first addition, the additions in the same order as sum4's
+        auto sum4x2 = [&](size_t col_a, size_t col_b, float* a, float* b) {
+            float bias_a[4] = {0.f, 0.f, 0.f, 0.f}, bias_b[4] = {0.f, 0.f, 0.f, 0.f};
+            if (fq.bias) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    bias_a[k] = load_any(fq.bias, fq.bias_dtype, col_a + k);
+                    bias_b[k] = load_any(fq.bias, fq.bias_dtype, col_b + k);
+                }
+            }
+            a[0] = a[1] = a[2] = a[3] = b[0] = b[1] = b[2] = b[3] = 0.f;
+            for (int s0 = 0; s0 < fq.splits; s0 += 8) {
+                float4 fa[8], fb[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    if (s0 + k < fq.splits) {
+                        fa[k] = __ldcg(reinterpret_cast<const float4*>(src_row + (size_t)(s0 + k) * fq.split_stride + col_a));
+                        fb[k] = __ldcg(reinterpret_cast<const float4*>(src_row + (size_t)(s0 + k) * fq.split_stride + col_b));
+                    }
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    if (s0 + k < fq.splits) {
+                        a[0] += fa[k].x; a[1] += fa[k].y; a[2] += fa[k].z; a[3] += fa[k].w;
+                        b[0] += fb[k].x; b[1] += fb[k].y; b[2] += fb[k].z; b[3] += fb[k].w;
+                    }
+            }
+            if (fq.bias) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) { a[k] += bias_a[k]; b[k] += bias_b[k]; }
+            }
+        };
+        const int half = fq.rotary_dim >> 1, hc = half >> 2, tail = (D - fq.rotary_dim) >> 2, per_head = hc + tail;
+        const int n_q = valid * per_head, n_k = own ? per_head : 0, n_v = own ? D / 4 : 0;
+        const int page = own ? table[pos / page_size] : -1;
+        // (only one of the CTAs that share a kv head writes the cache; all of them need the values)
+        const size_t cache_row = ((size_t)(page < 0 ? 0 : page) * n_kv + kvh) * page_size * D + (size_t)(pos % page_size) * D;
+        const bool to_cache = own && page >= 0 && gt == 0;
+        for (int it = threadIdx.x; it < n_q + n_k + n_v; it += TD_THREADS) {
+            if (it < n_q + n_k) {
+                const bool is_q = it < n_q;
+                const int r = is_q ? it / per_head : 0, c = (is_q ? it : it - n_q) - r * per_head;
+                const size_t col0 = (size_t)(is_q ? h0 + r : n_heads + kvh) * D;
+                bf16* dst = is_q ? q_rows + r * Plan::Q_STRIDE : k_new;
+                if (c < hc) {
+                    float a[4], b[4], ra[4], rb[4];
+                    sum4x2(col0 + c * 4, col0 + half + c * 4, a, b);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const float2 s1 = sc[c * 4 + k];
+                        ra[k] = a[k] * s1.y - b[k] * s1.x;
+                        rb[k] = a[k] * s1.x + b[k] * s1.y;
+                    }
+                    store4bf(dst + c * 4, ra);
+                    store4bf(dst + half + c * 4, rb);
+                    if (!is_q && to_cache) {
+                        store4bf(fq.k_cache + cache_row + c * 4, ra);
+                        store4bf(fq.k_cache + cache_row + half + c * 4, rb);
+                    }
+                } else {
+                    float v[4];
+                    const int d0 = fq.rotary_dim + (c - hc) * 4;
+                    sum4(col0 + d0, v);
+                    store4bf(dst + d0, v);
+                    if (!is_q && to_cache) store4bf(fq.k_cache + cache_row + d0, v);
+                }
+            } else {
+                const int c = it - n_q - n_k;
+                float v[4];
+                sum4((size_t)(n_heads + n_kv + kvh) * D + c * 4, v);
+                store4bf(v_new + c * 4, v);
+                if (to_cache) store4bf(fq.v_cache + cache_row + c * 4, v);
+            }
+        }
+        __syncthreads();
+        TL_MARK(52);
+        load_q<D>(qf, q_rows, (size_t)Plan::Q_STRIDE, valid, lane);
+    } else {
+        load_q<D>(qf, q + (size_t)t * q_stride + (size_t)h0 * D, (size_t)D, valid, lane);
+    }
     float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
     float o[D / 8][4];
 #pragma unroll
@@ -241,6 +391,18 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         const bf16* kt = reinterpret_cast<const bf16*>(my + (size_t)(i % STAGES) * Plan::STAGE_BYTES);
         const bf16* vt = kt + 16 * D;
         const int kb = k_begin + (warp + i * TD_WARPS) * KEYS16;
+        if (own && pos >= kb && pos < kb + KEYS16) {
+            // the slice with the token's own position came from the cache before this step's key and
+            // value were there: put them into its row (the layout the bulk load leaves, 16 bytes per lane)
+            const int row = pos - kb;
+            if (lane < D / 8) {
+                *reinterpret_cast<uint4*>(const_cast<bf16*>(kt) + (size_t)Layout::chunk(row, lane) * 8) =
+                    *reinterpret_cast<const uint4*>(k_new + lane * 8);
+                *reinterpret_cast<uint4*>(const_cast<bf16*>(vt) + (size_t)Layout::chunk(row, lane) * 8) =
+                    *reinterpret_cast<const uint4*>(v_new + lane * 8);
+            }
+            __syncwarp();
+        }
         slice16<D, Layout>(qf, kt, vt, 0, kb, lo, pos, lo, pos, scale_log2, m, l, o, lane);
         __syncwarp();
     }
@@ -256,6 +418,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         for (int i = waited; i < issued; ++i)
             tc::mbar_wait(&my_bar[i % STAGES], (uint32_t)(i / STAGES) & 1u, &never);
     }
+    TL_MARK(53);
     // ---- merge the four warps ----------------------------------------------------------------------
     float l0 = l[0], l1 = l[1];
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
@@ -263,15 +426,16 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     __syncthreads();                                   // every warp is done with its stages
-    float* red_o = reinterpret_cast<float*>(smem);                    // [4 warps][16 rows][D]
-    float* red_ml = red_o + TD_WARPS * 16 * D;                        // [4 warps][16 rows][2]
+    constexpr int RS = Plan::RED_STRIDE;
+    float* red_o = reinterpret_cast<float*>(smem);                    // [4 warps][16 rows][RS]
+    float* red_ml = red_o + TD_WARPS * 16 * RS;                       // [4 warps][16 rows][2]
 #pragma unroll
     for (int nt = 0; nt < D / 8; ++nt) {
         const int d = nt * 8 + c * 2;
-        float* r0 = red_o + ((size_t)warp * 16 + g) * D + d;
-        float* r1 = red_o + ((size_t)warp * 16 + g + 8) * D + d;
-        r0[0] = o[nt][0]; r0[1] = o[nt][1];
-        r1[0] = o[nt][2]; r1[1] = o[nt][3];
+        float* r0 = red_o + ((size_t)warp * 16 + g) * RS + d;
+        float* r1 = red_o + ((size_t)warp * 16 + g + 8) * RS + d;
+        *reinterpret_cast<float2*>(r0) = make_float2(o[nt][0], o[nt][1]);
+        *reinterpret_cast<float2*>(r1) = make_float2(o[nt][2], o[nt][3]);
     }
     if (c == 0) {
         red_ml[((size_t)warp * 16 + g) * 2] = m[0];
@@ -305,11 +469,12 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 #pragma unroll
         for (int w = 0; w < TD_WARPS; ++w) {
             const float f = red_f[w * 16 + r];
-            const float4 v = *reinterpret_cast<const float4*>(red_o + ((size_t)w * 16 + r) * D + d);
+            const float4 v = *reinterpret_cast<const float4*>(red_o + ((size_t)w * 16 + r) * RS + d);
             acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
         }
         *reinterpret_cast<float4*>(po + (size_t)r * n_splits * D + d) = acc;
     }
+    TL_MARK(54);
     if (counters)                                      // (its first barrier also ends the reads of red_o above)
         merge_if_last<D>(counters + (size_t)ti * gridDim.y + blockIdx.y, reinterpret_cast<float*>(smem),
                          po - (size_t)split * D, pml - (size_t)split * 2, n_splits, valid,
@@ -363,48 +528,37 @@ attn_combine_kernel(const float* __restrict__ partial_o, const float* __restrict
     }
 }
 
-template <int D>
+template <int D, bool FUSED>
 int launch_tma(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, int q_stride, const int* block_table,
                int max_blocks, const int* tok_entry, const int* positions, int tok_first, int n_tok, int n_heads,
                int n_kv, int page_size, int window, float scale_log2, int chunk, int n_splits, float* po, float* pml,
-               void* out, int out_stride, int* counters, int* err, cudaStream_t stream) {
+               void* out, int out_stride, int* counters, int* err, const FusedQkv& fq, cudaStream_t stream) {
     using Plan = TdPlan<D>;
-    auto kern = attn_decode_tma_kernel<D>;
+    constexpr int SMEM = FUSED ? Plan::TOTAL_FUSED : Plan::TOTAL;
+    auto kern = attn_decode_tma_kernel<D, FUSED>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::TOTAL);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) {
-            infero_set_error("attn_decode_tma: cannot get %d bytes of shared memory: %s", Plan::TOTAL, cudaGetErrorString(e));
+            infero_set_error("attn_decode_tma: cannot get %d bytes of shared memory: %s", SMEM, cudaGetErrorString(e));
             return 1;
         }
         configured = true;
     }
     const int group = n_heads / n_kv;
     dim3 grid(n_splits, n_kv * ((group + 15) / 16), n_tok);
-    launch_pdl(kern, grid, dim3(TD_THREADS), Plan::TOTAL, stream, mk, mv, (const bf16*)q, q_stride, block_table,
+    launch_pdl(kern, grid, dim3(TD_THREADS), SMEM, stream, mk, mv, (const bf16*)q, q_stride, block_table,
                max_blocks, tok_entry, positions, tok_first, n_heads, n_kv, page_size, window, scale_log2, chunk,
-               n_splits, po, pml, (bf16*)out, out_stride, counters, err);
-    return infero_check_launch("attn_decode_tma");
+               n_splits, po, pml, (bf16*)out, out_stride, counters, err, fq);
+    return infero_check_launch(FUSED ? "attn_decode_tma_fused" : "attn_decode_tma");
 }
 
-}  // namespace
-
-extern "C" {
-
-int infero_attn_decode_tma_supported(int head_dim, int page_size) {
-    return (head_dim == 64 || head_dim == 128) && page_size % 16 == 0;
-}
-
-// The same contract as infero_attn_decode (attention_mma.cu), plus num_pages: the caches are
-// [num_pages, n_kv, page_size, head_dim] bf16, contiguous and 16-byte aligned.  n_splits is
-// at most 256.  scratch: infero_attn_decode_scratch bytes.  counters: n_counters ints, zero before the
-// first call (each launch leaves them zero again); with n_tok * n_kv * ceil(group / 16) of them or more
-// the last CTA of every group of splits merges the group; with fewer, or none (null), a second kernel does.
-int infero_attn_decode_tma(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
-                           const void* v_cache, int num_pages, const int* block_table, int max_blocks,
-                           const int* tok_entry, const int* positions, int tok_first, int n_tok, int n_heads,
-                           int n_kv, int head_dim, int page_size, int window, float scale, int chunk, int n_splits,
-                           void* scratch, int* counters, int n_counters, cudaStream_t stream) {
+// Checks, maps and the launch shared by the two entry points below (fq.partial null: finished queries in q).
+int decode_tma(const void* q, int q_stride, const FusedQkv& fq, void* out, int out_stride, const void* k_cache,
+               const void* v_cache, int num_pages, const int* block_table, int max_blocks, const int* tok_entry,
+               const int* positions, int tok_first, int n_tok, int n_heads, int n_kv, int head_dim, int page_size,
+               int window, float scale, int chunk, int n_splits, void* scratch, int* counters, int n_counters,
+               cudaStream_t stream) {
     if (n_tok == 0) return 0;
     INFERO_REQUIRE(infero_attn_decode_tma_supported(head_dim, page_size),
                    "attn_decode_tma: head_dim %d / page_size %d not supported", head_dim, page_size);
@@ -429,19 +583,82 @@ int infero_attn_decode_tma(const void* q, int q_stride, void* out, int out_strid
     float* po = (float*)scratch;
     float* pml = po + (size_t)n_tok * n_heads * n_splits * head_dim;
     int rc;
-    if (head_dim == 128)
-        rc = launch_tma<128>(mk, mv, q, q_stride, block_table, max_blocks, tok_entry, positions, tok_first, n_tok,
-                             n_heads, n_kv, page_size, window, sl2, chunk, n_splits, po, pml, out, out_stride, counters,
-                             err, stream);
-    else
-        rc = launch_tma<64>(mk, mv, q, q_stride, block_table, max_blocks, tok_entry, positions, tok_first, n_tok,
-                            n_heads, n_kv, page_size, window, sl2, chunk, n_splits, po, pml, out, out_stride, counters,
-                            err, stream);
+#define GO(D_, F_)                                                                                                   \
+    rc = launch_tma<D_, F_>(mk, mv, q, q_stride, block_table, max_blocks, tok_entry, positions, tok_first, n_tok,   \
+                            n_heads, n_kv, page_size, window, sl2, chunk, n_splits, po, pml, out, out_stride,       \
+                            counters, err, fq, stream)
+    if (head_dim == 128) {
+        if (fq.partial) GO(128, true); else GO(128, false);
+    } else {
+        if (fq.partial) GO(64, true); else GO(64, false);
+    }
+#undef GO
     if (rc || counters) return rc;                     // merged by the last CTA of every group
     const int warps = n_tok * n_heads;
     launch_pdl(attn_combine_kernel, dim3((warps + 3) / 4), dim3(128), 0, stream, (const float*)po, (const float*)pml,
                (bf16*)out, out_stride, tok_first, n_tok, n_heads, n_splits, head_dim);
     return infero_check_launch("attn_combine");
+}
+
+}  // namespace
+
+extern "C" {
+
+int infero_attn_decode_tma_supported(int head_dim, int page_size) {
+    return (head_dim == 64 || head_dim == 128) && page_size % 16 == 0;
+}
+
+// The same contract as infero_attn_decode (attention_mma.cu), plus num_pages: the caches are
+// [num_pages, n_kv, page_size, head_dim] bf16, contiguous and 16-byte aligned.  n_splits is
+// at most 256.  scratch: infero_attn_decode_scratch bytes.  counters: n_counters ints, zero before the
+// first call (each launch leaves them zero again); with n_tok * n_kv * ceil(group / 16) of them or more
+// the last CTA of every group of splits merges the group; with fewer, or none (null), a second kernel does.
+int infero_attn_decode_tma(const void* q, int q_stride, void* out, int out_stride, const void* k_cache,
+                           const void* v_cache, int num_pages, const int* block_table, int max_blocks,
+                           const int* tok_entry, const int* positions, int tok_first, int n_tok, int n_heads,
+                           int n_kv, int head_dim, int page_size, int window, float scale, int chunk, int n_splits,
+                           void* scratch, int* counters, int n_counters, cudaStream_t stream) {
+    FusedQkv none = {};
+    return decode_tma(q, q_stride, none, out, out_stride, k_cache, v_cache, num_pages, block_table, max_blocks, tok_entry,
+                      positions, tok_first, n_tok, n_heads, n_kv, head_dim, page_size, window, scale, chunk, n_splits,
+                      scratch, counters, n_counters, stream);
+}
+
+// Can the kernel below finish the q/k/v product itself?  (The vector widths its loads and stores use.)
+int infero_attn_decode_fused_supported(const float* partial, long long split_stride, int n_heads, int n_kv,
+                                       int head_dim, int page_size, int rotary_dim, const void* k_cache,
+                                       const void* v_cache) {
+    auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    return infero_attn_decode_tma_supported(head_dim, page_size) && rotary_dim >= 0 && rotary_dim % 8 == 0 &&
+           rotary_dim <= head_dim && split_stride % 4 == 0 && al16(partial) && al16(k_cache) && al16(v_cache) &&
+           n_kv > 0 && n_heads % n_kv == 0;
+}
+
+// Rotary positions, cache append and decode attention of a step's single tokens in one launch.  Takes
+// the q/k/v product as the few-token product kernel leaves it: partial[s][t][(n_heads + 2 n_kv) * head_dim]
+// 32-bit, s < splits, split_stride elements apart, rows indexed by the token's place in the step; bias
+// (bias_dtype) may be null.  The queries are rotated and used, never written; with write_cache the keys
+// and values of the tokens are appended to the cache as infero_rope_cache_partials appends them (the same
+// bf16 values).  Everything else as infero_attn_decode_tma.
+int infero_attn_decode_tma_fused(const float* partial, int splits, long long split_stride, const void* bias,
+                                 int bias_dtype, const float* inv_freq, int rotary_dim, int write_cache, void* out,
+                                 int out_stride, void* k_cache, void* v_cache, int num_pages, const int* block_table,
+                                 int max_blocks, const int* tok_entry, const int* positions, int tok_first, int n_tok,
+                                 int n_heads, int n_kv, int head_dim, int page_size, int window, float scale, int chunk,
+                                 int n_splits, void* scratch, int* counters, int n_counters, cudaStream_t stream) {
+    INFERO_REQUIRE(partial && splits >= 1, "attn_decode_tma_fused: no partial sums (%d splits)", splits);
+    INFERO_REQUIRE(infero_attn_decode_fused_supported(partial, split_stride, n_heads, n_kv, head_dim, page_size, rotary_dim,
+                                                      k_cache, v_cache),
+                   "attn_decode_tma_fused: head_dim %d / rotary_dim %d / split stride %lld not supported", head_dim,
+                   rotary_dim, split_stride);
+    FusedQkv fq;
+    fq.partial = partial, fq.split_stride = split_stride, fq.bias = bias, fq.inv_freq = inv_freq;
+    fq.k_cache = (bf16*)k_cache, fq.v_cache = (bf16*)v_cache, fq.splits = splits;
+    fq.row_width = (n_heads + 2 * n_kv) * head_dim, fq.bias_dtype = bias_dtype, fq.rotary_dim = rotary_dim;
+    fq.write_cache = write_cache;
+    return decode_tma(nullptr, 0, fq, out, out_stride, k_cache, v_cache, num_pages, block_table, max_blocks, tok_entry,
+                      positions, tok_first, n_tok, n_heads, n_kv, head_dim, page_size, window, scale, chunk, n_splits,
+                      scratch, counters, n_counters, stream);
 }
 
 }  // extern "C"

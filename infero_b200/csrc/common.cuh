@@ -116,6 +116,8 @@ __device__ __forceinline__ void tl_end(int kind, unsigned long long t0) {
 #define INFERO_TL_UNIT(name)
 #endif
 #define TL_END(kind) TL_END_IF(threadIdx.x == 0 && threadIdx.y == 0, kind)
+// a mark inside a kernel: a record of its own kind (50 and above) that ends where the mark stands
+#define TL_MARK(kind) TL_END(kind)
 
 // ---- error reporting -------------------------------------------------------------------
 // Launchers return 0 on success.  On failure they return non-zero and leave a message

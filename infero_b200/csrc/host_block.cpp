@@ -49,6 +49,15 @@ int infero_attn_decode_tma(const void* q, int q_stride, void* out, int out_strid
                            const int* tok_entry, const int* positions, int tok_first, int n_tok, int n_heads,
                            int n_kv, int head_dim, int page_size, int window, float scale, int chunk, int n_splits,
                            void* scratch, int* counters, int n_counters, cudaStream_t stream);
+int infero_attn_decode_fused_supported(const float* partial, long long split_stride, int n_heads, int n_kv,
+                                       int head_dim, int page_size, int rotary_dim, const void* k_cache,
+                                       const void* v_cache);
+int infero_attn_decode_tma_fused(const float* partial, int splits, long long split_stride, const void* bias,
+                                 int bias_dtype, const float* inv_freq, int rotary_dim, int write_cache, void* out,
+                                 int out_stride, void* k_cache, void* v_cache, int num_pages, const int* block_table,
+                                 int max_blocks, const int* tok_entry, const int* positions, int tok_first, int n_tok,
+                                 int n_heads, int n_kv, int head_dim, int page_size, int window, float scale, int chunk,
+                                 int n_splits, void* scratch, int* counters, int n_counters, cudaStream_t stream);
 int infero_attn_prefill_tc_supported(int head_dim, int page_size, int q_stride, int out_stride);
 int infero_attn_prefill_tc(const void* q, int q_stride, int n_tokens, void* out, int out_stride, const void* k_cache,
                            const void* v_cache, int num_pages, const int* block_table, int max_blocks,
@@ -219,9 +228,17 @@ int infero_block_forward(const InferoBlock* b, const InferoStep* s, const int* b
         return rc;
     InferoDelta qkv;
     if (int rc = product(*s, h, d, b->w_qkv, nqkv, b->b_qkv, b->qkv_bias_dtype, A + p.qkv, &qkv)) return rc;
-    const void* q;
-    int q_stride;
-    if (qkv.dtype == F32) {
+    const void* q = nullptr;
+    int q_stride = 0;
+    // A step of single tokens whose q/k/v product came as partial sums: decode attention finishes the
+    // product itself (bias, rotary positions, cache append), one launch instead of two.
+    // INFERO_FUSED_DECODE=0 keeps the two kernels apart.
+    static const bool fuse_wanted = !(getenv("INFERO_FUSED_DECODE") && getenv("INFERO_FUSED_DECODE")[0] == '0');
+    const bool fused = fuse_wanted && qkv.dtype == F32 && s->n_decode == s->n_entries && s->n_decode == T &&
+                       infero_attn_decode_fused_supported((const float*)qkv.data, qkv.split_stride, H, Hkv, D, b->page_size,
+                                                          b->rotary_dim, b->k_cache, b->v_cache);
+    if (fused) {
+    } else if (qkv.dtype == F32) {
         q = A + p.q;
         q_stride = da;
         if (int rc = infero_rope_cache_partials((const float*)qkv.data, qkv.splits, qkv.split_stride, qkv.bias, qkv.bias_dtype,
@@ -247,11 +264,19 @@ int infero_block_forward(const InferoBlock* b, const InferoStep* s, const int* b
             infero_set_error("block_forward: %d decode tokens in %d splits need more scratch than was set aside", s->n_decode, splits);
             return 1;
         }
-        if (int rc = infero_attn_decode_tma(q, q_stride, attn, da, b->k_cache, b->v_cache, b->num_pages, block_table,
-                                            max_blocks, s->tok_entry, s->positions, 0, s->n_decode, H, Hkv, D,
-                                            b->page_size, b->window, b->scale, chunk, splits, A + p.scratch, s->counters,
-                                            s->n_counters, s->stream))
-            return rc;
+        int rc;
+        if (fused)
+            rc = infero_attn_decode_tma_fused((const float*)qkv.data, qkv.splits, qkv.split_stride, qkv.bias, qkv.bias_dtype,
+                                              b->inv_freq, b->rotary_dim, b->write_cache, attn, da, b->k_cache, b->v_cache,
+                                              b->num_pages, block_table, max_blocks, s->tok_entry, s->positions, 0,
+                                              s->n_decode, H, Hkv, D, b->page_size, b->window, b->scale, chunk, splits,
+                                              A + p.scratch, s->counters, s->n_counters, s->stream);
+        else
+            rc = infero_attn_decode_tma(q, q_stride, attn, da, b->k_cache, b->v_cache, b->num_pages, block_table,
+                                        max_blocks, s->tok_entry, s->positions, 0, s->n_decode, H, Hkv, D,
+                                        b->page_size, b->window, b->scale, chunk, splits, A + p.scratch, s->counters,
+                                        s->n_counters, s->stream);
+        if (rc) return rc;
     }
     if (s->n_decode < s->n_entries) {
         if (int rc = infero_attn_prefill_tc(q, q_stride, T, attn, da, b->k_cache, b->v_cache, b->num_pages, block_table,

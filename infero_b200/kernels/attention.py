@@ -70,6 +70,25 @@ def decode(q, out, k_cache, v_cache, table, tok_entry, positions, tok_first: int
                                     c_int(n_splits), _ptr(scratch), _stream()))
 
 
+def decode_fused(qkv, out, k_cache, v_cache, table, tok_entry, positions, inv_freq, n_heads: int, n_kv: int,
+                 head_dim: int, page_size: int, window: Optional[int], scale: float, chunk: int, n_splits: int,
+                 write_cache: bool = True) -> None:
+    """Rotary positions, cache append and decode attention of single tokens in one launch, from the
+    q/k/v product as partial sums (``kernels.Partials`` [T, (H + 2 Hkv) * D], bias not yet added)."""
+    n_tok = out.shape[0]
+    need = int(lib_scratch(n_tok, n_heads, head_dim, n_splits))
+    scratch = torch.empty(need // 4, dtype=torch.float32, device=out.device)
+    bias = qkv.bias
+    _check(lib().infero_attn_decode_tma_fused(
+        _ptr(qkv.data), c_int(qkv.splits), c_longlong(qkv.split_stride), _ptr(bias),
+        c_int((1 if bias.dtype == torch.bfloat16 else 0) if bias is not None else 0), _ptr(inv_freq),
+        c_int(2 * inv_freq.numel()), c_int(1 if write_cache else 0), _ptr(out), c_int(out.stride(0)), _ptr(k_cache),
+        _ptr(v_cache), c_int(k_cache.shape[0]), _ptr(_i32(table, "block_table")), c_int(table.shape[1]),
+        _ptr(_i32(tok_entry, "tok_entry")), _ptr(_i32(positions, "positions")), c_int(0), c_int(n_tok), c_int(n_heads),
+        c_int(n_kv), c_int(head_dim), c_int(page_size), c_int(window or 0), c_float(scale), c_int(chunk),
+        c_int(n_splits), _ptr(scratch), _ptr(_arrival_counters(out.device)), c_int(N_COUNTERS), _stream()))
+
+
 def lib_scratch(n_tok, n_heads, head_dim, n_splits) -> int:
     f = lib().infero_attn_decode_scratch
     f.restype = c_longlong

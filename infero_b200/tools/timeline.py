@@ -130,9 +130,11 @@ def main(argv=None) -> int:
           f"{e0.elapsed_time(e1) * 1e3:.0f} us by events, {total_us:.0f} us from the first block's start to the last block's end; "
           f"{n} blocks in {len(rows)} launches")
 
-    # a layer = the launches from one norm that is followed by a product and a rotary kernel up to the next such norm
+    marks = [r for r in rows if r["kind"] >= 50]
+    rows = [r for r in rows if r["kind"] < 50]
+    # a layer = from one norm that is followed by a product and then by the rotary kernel or decode attention
     norm_idx = [i for i, r in enumerate(rows) if r["kind"] == 2]
-    layer_starts = [i for i in norm_idx if i + 2 < len(rows) and rows[i + 1]["kind"] == 3 and rows[i + 2]["kind"] == 4]
+    layer_starts = [i for i in norm_idx if i + 2 < len(rows) and rows[i + 1]["kind"] == 3 and rows[i + 2]["kind"] in (4, 5)]
     per_layer = [rows[a:b] for a, b in zip(layer_starts, layer_starts[1:])]
     if len(per_layer) >= 3:
         shape = [(r["kind"], r["grid"]) for r in per_layer[1]]
@@ -146,6 +148,19 @@ def main(argv=None) -> int:
             print(f"{KINDS.get(kind, kind):<22}{grid:>7}{same[0][j]['sms']:>5}{fs:>13.1f}{ls:>13.1f}{fe:>11.1f}{le:>10.1f}{le - fs:>8.1f}")
         span = sum(b[0]["first_start"] - a[0]["first_start"] for a, b in zip(same, same[1:])) / max(1, len(same) - 1) / 1e3
         print(f"a layer every {span:.1f} us")
+    if marks:
+        # marks inside kernels: how long after its own start each block passed the mark
+        print("\nmarks inside kernels (microseconds after the block's own start: least, median, most), per launch:")
+        by_kind = {}
+        for (kind, grid), rs in launches:
+            if kind >= 50:
+                by_kind.setdefault(kind, []).append(sorted((int(r["t1"]) - int(r["t0"])) / 1e3 for r in rs))
+        for kind in sorted(by_kind):
+            ls = by_kind[kind][1:] or by_kind[kind]
+            lo = sum(v[0] for v in ls) / len(ls)
+            mid = sum(v[len(v) // 2] for v in ls) / len(ls)
+            hi = sum(v[-1] for v in ls) / len(ls)
+            print(f"mark {kind}: {lo:8.1f}{mid:8.1f}{hi:8.1f}   ({len(ls)} launches)")
     print("\nall launches of the step (microseconds from the first block of the step):")
     for r in rows:
         print(f"{KINDS.get(r['kind'], r['kind']):<22}{r['grid']:>7}{r['first_start'] / 1e3:>11.1f}{r['last_start'] / 1e3:>11.1f}"

@@ -533,6 +533,78 @@ def test_decode_attention_fed_by_tma(H, Hkv, D, window, P, monkeypatch):
     assert tc_gemm.error_flag() == 0
 
 
+@pytest.mark.parametrize("H,Hkv,D,rotary", [(28, 4, 128, 128), (14, 2, 64, 64), (20, 1, 128, 64), (3, 3, 64, 0)])
+@pytest.mark.parametrize("window", [None, 100])
+@pytest.mark.parametrize("splits_in", [1, 10])
+def test_decode_attention_that_finishes_the_qkv_product_itself(H, Hkv, D, rotary, window, splits_in):
+    """The fused launch (bias, rotary positions, cache append, attention from 32-bit partial sums) against
+    the two kernels it replaces, bit for bit in the output and in the cache, and against float64."""
+    from infero_b200 import kernels as Kn
+    from infero_b200.kernels import attention as A, tc_gemm
+    P, dt = 16, torch.bfloat16
+    lengths = [1, 16, 17, 64, 333, 700, 129, 257]
+    n = len(lengths)
+    pages = sum(-(-L // P) for L in lengths) + 5
+    perm = np.random.default_rng(3).permutation(pages)
+    table = torch.full((n, max(-(-L // P) for L in lengths) + 2), -1, dtype=torch.int32)
+    kc = _rand((pages, Hkv, P, D), dt, 50)
+    vc = _rand((pages, Hkv, P, D), dt, 51)
+    Ks, Vs = [], []
+    nxt = 0
+    for e, L in enumerate(lengths):
+        k, v = _rand((L, Hkv, D), dt, 60 + e), _rand((L, Hkv, D), dt, 80 + e)      # the last row is replaced below
+        Ks.append(k); Vs.append(v)
+        for b in range(-(-L // P)):
+            table[e, b] = int(perm[nxt]); nxt += 1
+            m = min(P, L - b * P)
+            kc[table[e, b], :, :m] = k[b * P:b * P + m].transpose(0, 1)
+            vc[table[e, b], :, :m] = v[b * P:b * P + m].transpose(0, 1)
+    table = table.to(DEV)
+    width = (H + 2 * Hkv) * D
+    parts = _rand((splits_in, n, width), torch.float32, 9, scale=1.0 / math.sqrt(splits_in))
+    bias = _rand((width,), torch.float32, 10, scale=0.3)
+    qkv = Kn.Partials(parts, bias)
+    theta = 10000.0
+    inv = (theta ** (-torch.arange(0, rotary, 2, dtype=torch.float64) / max(rotary, 1))).to(torch.float32).to(DEV)
+    positions = torch.tensor([L - 1 for L in lengths], dtype=torch.int32, device=DEV)
+    entry = torch.arange(n, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(D)
+    vis = min(max(lengths), window + 15) if window else max(lengths)
+    for plan in (A.plan_decode(n, Hkv, H // Hkv, vis), (64, -(-vis // 64)), (16, -(-vis // 16))):
+        chunk, splits = plan
+        if splits > A.MAX_SPLITS:
+            continue
+        # the two kernels
+        k1, v1 = kc.clone(), vc.clone()
+        q1 = torch.empty((n, H * D), dtype=dt, device=DEV)
+        Kn.rope_cache_partials(qkv, q1, positions, entry, table, inv, k1, v1, H, Hkv, D, P)
+        out1 = torch.zeros((n, H * D), dtype=dt, device=DEV)
+        A.decode(q1, out1, k1, v1, table, entry, positions, 0, n, H, Hkv, D, P, window, scale, chunk, splits)
+        # the one kernel
+        k2, v2 = kc.clone(), vc.clone()
+        out2 = torch.zeros_like(out1)
+        A.decode_fused(qkv, out2, k2, v2, table, entry, positions, inv, H, Hkv, D, P, window, scale, chunk, splits)
+        torch.cuda.synchronize()
+        assert torch.equal(k1, k2) and torch.equal(v1, v2), f"plan {plan}: the caches differ"
+        assert torch.equal(out1, out2), f"plan {plan}: outputs differ by {(out1.float() - out2.float()).abs().max()}"
+        # float64: the token's own q, k, v from the summed product, rotated
+        full = (parts.double().sum(0) + bias.double()).cpu()
+        worst = 0.0
+        for e, L in enumerate(lengths):
+            row = full[e]
+            pos = torch.tensor([L - 1])
+            qe = _rope_ref(row[:H * D].view(1, H, D), pos, theta, rotary)[0] if rotary else row[:H * D].view(H, D)
+            ke = row[H * D:(H + Hkv) * D].view(1, Hkv, D)
+            ke = _rope_ref(ke, pos, theta, rotary)[0] if rotary else ke[0]
+            ve = row[(H + Hkv) * D:].view(Hkv, D)
+            keys, vals = Ks[e].double().cpu().clone(), Vs[e].double().cpu().clone()
+            keys[L - 1], vals[L - 1] = ke, ve
+            ref = _attention_ref(qe, keys, vals, scale, window)
+            worst = max(worst, float((out2[e].double().cpu().view(H, D) - ref).abs().max() / ref.abs().max()))
+        assert worst <= 2e-2, f"plan {plan}: {worst:.3e} from the float64 statement"
+    assert tc_gemm.error_flag() == 0
+
+
 def _paged_requests(totals, Hkv, D, P, dt, seed, dead_before):
     """Keys and values of requests of ``totals`` tokens on scattered pages.  Pages that lie wholly
     before position ``dead_before[e]`` are not held any more (table entry -1), as after the cache
