@@ -57,6 +57,12 @@ struct FusedQkv {
     bf16* k_cache;
     bf16* v_cache;
     int splits, row_width, bias_dtype, rotary_dim, write_cache;
+    // The product's input may still lack its norm's scalar (the norm folded into the products around it,
+    // gemm_tc.cu): then every summed value of token t is multiplied by
+    // rsqrt(sum_{tile < in_tiles} sumsq_in[tile * 256 + t] * inv_d + eps) before the bias is added.
+    const float* sumsq_in;
+    int in_tiles;
+    float inv_d, eps;
 };
 
 // The CTA that finishes last among the splits of one (token, kv head, group tile) merges them:
@@ -274,6 +280,12 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const bool own = FUSED && fq.write_cache && pos >= k_begin && pos < k_end;
     if (FUSED) {
         const float* src_row = fq.partial + (size_t)t * fq.row_width;
+        float rstd = 1.0f;
+        if (fq.sumsq_in) {
+            float ss = 0.f;
+            for (int tl = 0; tl < fq.in_tiles; ++tl) ss += __ldcg(fq.sumsq_in + (size_t)tl * 256 + t);
+            rstd = 1.0f / sqrtf(ss * fq.inv_d + fq.eps);
+        }
         auto sum4 = [&](size_t col, float* v) {
             v[0] = v[1] = v[2] = v[3] = 0.f;
             // eight splits' loads in flight at a time; added in ascending order
@@ -286,6 +298,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 for (int k = 0; k < 8; ++k)
                     if (s0 + k < fq.splits) { v[0] += f[k].x; v[1] += f[k].y; v[2] += f[k].z; v[3] += f[k].w; }
             }
+            if (fq.sumsq_in) { v[0] *= rstd; v[1] *= rstd; v[2] *= rstd; v[3] *= rstd; }
             if (fq.bias) {
 #pragma unroll
                 for (int k = 0; k < 4; ++k) v[k] += load_any(fq.bias, fq.bias_dtype, col + k);
@@ -323,6 +336,10 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                         a[0] += fa[k].x; a[1] += fa[k].y; a[2] += fa[k].z; a[3] += fa[k].w;
                         b[0] += fb[k].x; b[1] += fb[k].y; b[2] += fb[k].z; b[3] += fb[k].w;
                     }
+            }
+            if (fq.sumsq_in) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) { a[k] *= rstd; b[k] *= rstd; }
             }
             if (fq.bias) {
 #pragma unroll
@@ -639,13 +656,15 @@ int infero_attn_decode_fused_supported(const float* partial, long long split_str
 // 32-bit, s < splits, split_stride elements apart, rows indexed by the token's place in the step; bias
 // (bias_dtype) may be null.  The queries are rotated and used, never written; with write_cache the keys
 // and values of the tokens are appended to the cache as infero_rope_cache_partials appends them (the same
-// bf16 values).  Everything else as infero_attn_decode_tma.
+// bf16 values).  sumsq (may be null): the product's input lacked its norm's scalar, see FusedQkv.
+// Everything else as infero_attn_decode_tma.
 int infero_attn_decode_tma_fused(const float* partial, int splits, long long split_stride, const void* bias,
                                  int bias_dtype, const float* inv_freq, int rotary_dim, int write_cache, void* out,
                                  int out_stride, void* k_cache, void* v_cache, int num_pages, const int* block_table,
                                  int max_blocks, const int* tok_entry, const int* positions, int tok_first, int n_tok,
                                  int n_heads, int n_kv, int head_dim, int page_size, int window, float scale, int chunk,
-                                 int n_splits, void* scratch, int* counters, int n_counters, cudaStream_t stream) {
+                                 int n_splits, void* scratch, int* counters, int n_counters, const float* sumsq,
+                                 int sumsq_tiles, float inv_d, float eps, cudaStream_t stream) {
     INFERO_REQUIRE(partial && splits >= 1, "attn_decode_tma_fused: no partial sums (%d splits)", splits);
     INFERO_REQUIRE(infero_attn_decode_fused_supported(partial, split_stride, n_heads, n_kv, head_dim, page_size, rotary_dim,
                                                       k_cache, v_cache),
@@ -656,6 +675,7 @@ int infero_attn_decode_tma_fused(const float* partial, int splits, long long spl
     fq.k_cache = (bf16*)k_cache, fq.v_cache = (bf16*)v_cache, fq.splits = splits;
     fq.row_width = (n_heads + 2 * n_kv) * head_dim, fq.bias_dtype = bias_dtype, fq.rotary_dim = rotary_dim;
     fq.write_cache = write_cache;
+    fq.sumsq_in = sumsq, fq.in_tiles = sumsq_tiles, fq.inv_d = inv_d, fq.eps = eps;
     return decode_tma(nullptr, 0, fq, out, out_stride, k_cache, v_cache, num_pages, block_table, max_blocks, tok_entry,
                       positions, tok_first, n_tok, n_heads, n_kv, head_dim, page_size, window, scale, chunk, n_splits,
                       scratch, counters, n_counters, stream);

@@ -56,7 +56,29 @@ struct SmemPlan {
     static constexpr int B_STAGE_BYTES = BN * TILE_K * 2;
     static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-    static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;      // barriers + slack for 1024-byte alignment
+    static constexpr int SCALE_OFFSET = BAR_OFFSET + 256;      // one float per token column (GemmFuse::sumsq_in)
+    static constexpr int TOTAL = SCALE_OFFSET + BN * 4 + 1024; // barriers + scales + slack for 1024-byte alignment
+};
+
+// A layer's residual-add-and-norm kernels folded into the few-token products around them (steps of
+// single tokens, where every launch costs more than its work).  RMSNorm is x * rsqrt(mean(x^2) + eps) * w
+// and the product that follows is linear in its input, so the scalar rsqrt(...) of a token can be
+// applied after the product; what is left of the norm is the residual sum, the weight and a sum of
+// squares, which the product in front can do on its own output once its splits are added up:
+//   producer (EPI_CLUSTER, x given): the summed tile is a residual update.  x[t, f] += sum (+ bias[f]);
+//     h[t, f] = bf16(x[t, f] * norm_w[f]); sumsq_out[tile][t] = sum of x[t, f]^2 over the tile's features.
+//   consumer (sumsq_in given): token t's column is scaled by rsqrt(sum_tiles sumsq_in[tile][t] * inv_d + eps)
+//     (SwiGLU epilogue here; the fused decode attention does the same to the q/k/v partial sums).
+constexpr int SUMSQ_STRIDE = 256;                              // floats between the tiles' rows of sums
+struct GemmFuse {
+    float* x;
+    const void* bias;
+    const void* norm_w;
+    bf16* h;
+    float* sumsq_out;
+    const float* sumsq_in;
+    int bias_dtype, norm_w_dtype, in_tiles;
+    float inv_d, eps;
 };
 
 template <typename OutT>
@@ -94,7 +116,7 @@ __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                OutT* __restrict__ out, const void* __restrict__ bias, int bias_dtype,
                int RA, int RB, int K, int ktiles_per_split, long long ldc, int a_evict_first,
-               int* __restrict__ err_flag) {
+               int* __restrict__ err_flag, const GemmFuse fuse) {
     using Plan = SmemPlan<BN, STAGES>;
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
     extern __shared__ uint8_t smem_raw[];
@@ -225,6 +247,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // ---- epilogue ------------------------------------------------------------------------
         const int q = warp & 3;                              // the TMEM lane quarter this warp may read
         const int ra = a0 + q * 32 + lane;
+        float* col_scale = reinterpret_cast<float*>(smem + Plan::SCALE_OFFSET);
+        if (EPI == EPI_COL_SWIGLU && fuse.sumsq_in) {
+            // the tokens' scales, while the product runs: the sums of squares come from the kernel in front
+            pdl_wait();
+            for (int c = (warp - 2) * 32 + lane; c < BN; c += 128) {
+                float ss = 0.f;
+                if (b0 + c < RB)
+                    for (int tl = 0; tl < fuse.in_tiles; ++tl) ss += __ldcg(fuse.sumsq_in + (size_t)tl * SUMSQ_STRIDE + b0 + c);
+                col_scale[c] = 1.0f / sqrtf(ss * fuse.inv_d + fuse.eps);
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
         const bool ok = mbar_wait(accum_bar, 0, abort_flag);
         tc_fence_after_sync();
         if (ok) {
@@ -248,6 +282,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     // lanes 2j, 2j+1 hold gate_j and up_j of the same tokens: out[rb + i, ra / 2]
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
+                        if (fuse.sumsq_in) v[i] *= col_scale[c0 + i];
                         const float other = __shfl_xor_sync(0xffffffffu, v[i], 1);
                         if (!(lane & 1) && ra + 1 < RA && rb + i < RB)
                             out[(size_t)(rb + i) * ldc + (ra >> 1)] = from_f32<OutT>(silu_mul(v[i], other));
@@ -324,6 +359,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint32_t remote[8];
 #pragma unroll
             for (int sp = 0; sp < 8; ++sp) remote[sp] = cluster_addr_of(smem, (uint32_t)(sp < S ? sp : 0));
+            // (behind the tile this CTA staged for the cluster: one float per epilogue warp and token)
+            float* warp_sq = reinterpret_cast<float*>(smem) + BN * TILE_A;
+            float bias_v = 0.f, norm_w_v = 0.f;
+            if (fuse.x && ra < RA) {
+                if (fuse.bias) bias_v = load_any(fuse.bias, fuse.bias_dtype, ra);
+                norm_w_v = load_any(fuse.norm_w, fuse.norm_w_dtype, ra);
+            }
             for (int c = c_lo; c < c_hi; ++c) {
                 const uint32_t off = (uint32_t)(c * TILE_A + row) * 4u;
                 float v[8];
@@ -334,7 +376,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                 for (int sp = 1; sp < 8; ++sp)
                     if (sp < S) acc += v[sp];
-                if (ra < RA) out[(size_t)(b0 + c) * (size_t)RA + ra] = from_f32<OutT>(acc);
+                if (fuse.x) {
+                    float sq = 0.f;
+                    if (ra < RA) {
+                        const size_t at = (size_t)(b0 + c) * (size_t)RA + ra;
+                        const float xv = fuse.x[at] + (acc + bias_v);
+                        fuse.x[at] = xv;
+                        fuse.h[at] = __float2bfloat16_rn(xv * norm_w_v);
+                        sq = xv * xv;
+                    }
+                    sq = warp_sum(sq);
+                    if (lane == 0) warp_sq[(warp & 3) * BN + (c - c_lo)] = sq;
+                } else if (ra < RA) {
+                    out[(size_t)(b0 + c) * (size_t)RA + ra] = from_f32<OutT>(acc);
+                }
+            }
+            if (fuse.x) {
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                // the four warps' sums in the order of their rows: warps 2, 3 hold rows 64..127, warps 4, 5 rows 0..63
+                for (int j = (warp - 2) * 32 + lane; j < c_hi - c_lo; j += 128)
+                    fuse.sumsq_out[(size_t)blockIdx.x * SUMSQ_STRIDE + b0 + c_lo + j] =
+                        (warp_sq[0 * BN + j] + warp_sq[1 * BN + j]) + (warp_sq[2 * BN + j] + warp_sq[3 * BN + j]);
             }
         }
         cluster_sync_all();                                  // nobody leaves while its tile is still being read
@@ -802,7 +864,7 @@ int err_flag_ptr(int** out) { return infero_tc_err_flag(out); }
 template <int BN, int STAGES, int EPI, typename OutT>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, const void* bias, int bias_dtype, int RA,
            int RB, int K, int ktiles_per_split, int splits, long long ldc, int a_evict_first, int* err,
-           cudaStream_t stream) {
+           cudaStream_t stream, const GemmFuse& fuse = GemmFuse{}) {
     using Plan = SmemPlan<BN, STAGES>;
     auto kern = gemm_tc_kernel<BN, STAGES, EPI, OutT>;
     static bool configured = false;
@@ -816,14 +878,14 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, const void* 
     }
     dim3 grid((RA + TILE_A - 1) / TILE_A, (RB + BN - 1) / BN, splits);
     launch_pdl(kern, grid, dim3(GEMM_THREADS), Plan::TOTAL, stream, ma, mb, (OutT*)out, bias, bias_dtype, RA, RB, K,
-               ktiles_per_split, ldc, a_evict_first, err);
+               ktiles_per_split, ldc, a_evict_first, err, fuse);
     return infero_check_launch("gemm_tc");
 }
 
 // The few-token kernel with the splits of a tile as one cluster (at most 8 CTAs).
 template <int BN, int STAGES>
 int launch_cluster(const CUtensorMap& ma, const CUtensorMap& mb, float* out, int RA, int RB, int K,
-                   int ktiles_per_split, int splits, int* err, cudaStream_t stream) {
+                   int ktiles_per_split, int splits, int* err, cudaStream_t stream, const GemmFuse& fuse = GemmFuse{}) {
     using Plan = SmemPlan<BN, STAGES>;
     auto kern = gemm_tc_kernel<BN, STAGES, EPI_CLUSTER, float>;
     static bool configured = false;
@@ -849,7 +911,7 @@ int launch_cluster(const CUtensorMap& ma, const CUtensorMap& mb, float* out, int
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = infero_pdl_enabled() ? 2 : 1;
-    cudaLaunchKernelEx(&cfg, kern, ma, mb, out, (const void*)nullptr, 0, RA, RB, K, ktiles_per_split, (long long)0, 1, err);
+    cudaLaunchKernelEx(&cfg, kern, ma, mb, out, (const void*)nullptr, 0, RA, RB, K, ktiles_per_split, (long long)0, 1, err, fuse);
     return infero_check_launch("gemm_tc_cluster");
 }
 
@@ -1094,6 +1156,52 @@ int infero_gemm_tc_summed(const void* x, const void* w, float* out, int M, int N
 #undef GO
 }
 
+// How the kernels below cut K: as infero_gemm_tc_plan, with at most 8 splits (the splits of a tile are one cluster).
+int infero_gemm_tc_plan_cluster(int M, int N, int K, int sm_count, int* splits, int* ktiles_per_split) {
+    long long ws = 0;
+    infero_gemm_tc_plan(M, N, K, sm_count, splits, ktiles_per_split, &ws);
+    if (*splits > MAX_CLUSTER) {
+        const int total_kt = (K + TILE_K - 1) / TILE_K;
+        *ktiles_per_split = (total_kt + MAX_CLUSTER - 1) / MAX_CLUSTER;
+        *splits = (total_kt + *ktiles_per_split - 1) / *ktiles_per_split;
+    }
+    return 0;
+}
+
+// A product whose result is a residual update, with what the RMSNorm behind it needs (see GemmFuse):
+//   resid[t, n] += sum_k x[t, k] w[n, k] (+ bias[n]);  h[t, n] = bf16(resid[t, n] * norm_w[n]);
+//   sumsq[tile * 256 + t] = sum over the 128 features n of tile of resid[t, n]^2.
+// x [M, K] bf16 (row stride ldx), w [N, K] bf16, resid [M, N] float and h [M, N] bf16 contiguous; M <= 256;
+// 1..8 splits of K as infero_gemm_tc_plan_cluster says; sumsq holds ceil(N / 128) * 256 floats.
+int infero_gemm_tc_residual_norm(const void* x, const void* w, int M, int N, int K, int ldx, int splits,
+                                 int ktiles_per_split, float* resid, const void* bias, int bias_dtype,
+                                 const void* norm_w, int norm_w_dtype, void* h, float* sumsq, cudaStream_t stream) {
+    INFERO_REQUIRE(infero_gemm_tc_supported(x, w, M, N, K, ldx), "gemm_tc: shape M=%d N=%d K=%d ldx=%d not supported", M, N, K, ldx);
+    INFERO_REQUIRE(M <= 256, "gemm_tc_residual_norm: M=%d above 256", M);
+    INFERO_REQUIRE(splits >= 1 && splits <= MAX_CLUSTER && ktiles_per_split >= 1 &&
+                       (long long)(splits - 1) * ktiles_per_split * TILE_K < K,
+                   "gemm_tc_residual_norm: %d splits of %d k-tiles do not fit K=%d (1..%d splits)", splits, ktiles_per_split, K, MAX_CLUSTER);
+    INFERO_REQUIRE(resid && norm_w && h && sumsq, "gemm_tc_residual_norm: a null output");
+    int* err;
+    if (err_flag_ptr(&err)) return 1;
+    const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+    CUtensorMap mw, mx;
+    if (get_map(w, N, K, K, TILE_A, &mw)) return 1;
+    if (get_map(x, M, K, ldx, bn, &mx)) return 1;
+    GemmFuse f = {};
+    f.x = resid, f.bias = bias, f.bias_dtype = bias_dtype, f.norm_w = norm_w, f.norm_w_dtype = norm_w_dtype;
+    f.h = (bf16*)h, f.sumsq_out = sumsq;
+#define GO(BN_, ST_) return launch_cluster<BN_, ST_>(mw, mx, nullptr, N, M, K, ktiles_per_split, splits, err, stream, f)
+    switch (bn) {
+        case 16: GO(16, 6);
+        case 32: GO(32, 5);
+        case 64: GO(64, 4);
+        case 128: GO(128, 3);
+        default: GO(256, 4);
+    }
+#undef GO
+}
+
 int infero_gemm_cluster_enabled() { return cluster_sum() ? 1 : 0; }
 void infero_gemm_set_cluster(int on) { g_cluster.store(on ? 1 : 0, std::memory_order_relaxed); }
 
@@ -1216,6 +1324,40 @@ int infero_gemm_tc_swiglu(const void* x, const void* w, void* out, int M, int N,
         if (r >= 0) return r;
     }
     return launch_persistent<EPI_ROW_SWIGLU, bf16>(x, w, out, nullptr, 0, M, N, K, ldx, ldc, sm_count, err, stream);
+}
+
+// The few-token, one-split case of infero_gemm_tc_swiglu on an input that still lacks its norm's scalar:
+// token t's products are multiplied by rsqrt(sum_{tile < n_tiles} sumsq[tile * 256 + t] * inv_d + eps) before
+// the activation.  Returns 2, with nothing launched, when the plan has more than one split or M > 256.
+int infero_gemm_tc_swiglu_scaled(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int ldc,
+                                 const float* sumsq, int n_tiles, float inv_d, float eps, int sm_count,
+                                 cudaStream_t stream) {
+    if (M == 0 || N == 0) return 0;
+    INFERO_REQUIRE(infero_gemm_tc_supported(x, w, M, N, K, ldx), "gemm_tc_swiglu: shape M=%d N=%d K=%d ldx=%d not supported", M, N, K, ldx);
+    INFERO_REQUIRE(N % 2 == 0 && ldc >= N / 2, "gemm_tc_swiglu: N=%d must be even and ldc=%d at least N/2", N, ldc);
+    INFERO_REQUIRE(sumsq && n_tiles >= 1, "gemm_tc_swiglu_scaled: no sums of squares");
+    if (M > 256) return 2;
+    int splits, per;
+    long long need;
+    infero_gemm_tc_plan(M, N, K, sm_count, &splits, &per, &need);
+    if (splits > 1) return 2;
+    int* err;
+    if (err_flag_ptr(&err)) return 1;
+    const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+    CUtensorMap mw, mx;
+    if (get_map(w, N, K, K, TILE_A, &mw)) return 1;
+    if (get_map(x, M, K, ldx, bn, &mx)) return 1;
+    GemmFuse f = {};
+    f.sumsq_in = sumsq, f.in_tiles = n_tiles, f.inv_d = inv_d, f.eps = eps;
+#define GO(BN_, ST_) return launch<BN_, ST_, EPI_COL_SWIGLU, bf16>(mw, mx, out, nullptr, 0, N, M, K, per, 1, ldc, 1, err, stream, f)
+    switch (bn) {
+        case 16: GO(16, 6);
+        case 32: GO(32, 5);
+        case 64: GO(64, 4);
+        case 128: GO(128, 3);
+        default: GO(256, 4);
+    }
+#undef GO
 }
 
 // Reads (and clears) the flag a tensor-core kernel raises when one of its waits ran out.

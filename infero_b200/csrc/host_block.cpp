@@ -57,7 +57,15 @@ int infero_attn_decode_tma_fused(const float* partial, int splits, long long spl
                                  int out_stride, void* k_cache, void* v_cache, int num_pages, const int* block_table,
                                  int max_blocks, const int* tok_entry, const int* positions, int tok_first, int n_tok,
                                  int n_heads, int n_kv, int head_dim, int page_size, int window, float scale, int chunk,
-                                 int n_splits, void* scratch, int* counters, int n_counters, cudaStream_t stream);
+                                 int n_splits, void* scratch, int* counters, int n_counters, const float* sumsq,
+                                 int sumsq_tiles, float inv_d, float eps, cudaStream_t stream);
+int infero_gemm_tc_plan_cluster(int M, int N, int K, int sm_count, int* splits, int* ktiles_per_split);
+int infero_gemm_tc_residual_norm(const void* x, const void* w, int M, int N, int K, int ldx, int splits,
+                                 int ktiles_per_split, float* resid, const void* bias, int bias_dtype,
+                                 const void* norm_w, int norm_w_dtype, void* h, float* sumsq, cudaStream_t stream);
+int infero_gemm_tc_swiglu_scaled(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int ldc,
+                                 const float* sumsq, int n_tiles, float inv_d, float eps, int sm_count,
+                                 cudaStream_t stream);
 int infero_attn_prefill_tc_supported(int head_dim, int page_size, int q_stride, int out_stride);
 int infero_attn_prefill_tc(const void* q, int q_stride, int n_tokens, void* out, int out_stride, const void* k_cache,
                            const void* v_cache, int num_pages, const int* block_table, int max_blocks,
@@ -69,7 +77,7 @@ void infero_set_error(const char* fmt, ...);
 
 extern "C" {
 
-enum : int { F32 = 0, BF16 = 1 };
+enum : int { F32 = 0, BF16 = 1, PRENORMED = 2 };
 
 // What is fixed for one execution of a block (a schedule entry): sizes, weights, its cache.
 struct InferoBlock {
@@ -117,12 +125,17 @@ struct InferoDelta {
     long long split_stride;
     const void* bias;           // added with the sum (partial sums only), or null
     int bias_dtype;
+    // PRENORMED: nothing is pending any more.  x already holds the sum, data is bf16(x * w) with w the
+    // weight of the next layer's first norm, and sumsq holds, per 128-feature tile and token (256 floats
+    // per tile), the sums of x^2 from which that norm's scalar follows.
+    const float* sumsq;
+    int sumsq_tiles;
 };
 
 static long long align_up(long long v) { return (v + 255) / 256 * 256; }
 
 struct ArenaPlan {
-    long long delta[2], h, qkv, q, attn, scratch, o_delta, act, gate_up, total;
+    long long sumsq[2], delta[2], h, qkv, q, attn, scratch, o_delta, act, gate_up, total;
 };
 
 // Room for the product of T rows with a [N, K] matrix, which comes as partial sums (few rows) or finished.
@@ -143,6 +156,10 @@ static ArenaPlan plan_arena(const InferoBlock& b, int T, int sm_count) {
     // block (up to 16 splits of up to 256 rows, or a finished product): the layer that reads one as its
     // input may be built to other sizes and must not have its own areas overlap it.
     const long long delta_bytes = std::max(16LL * std::min(T, 256) * b.hidden * 4, (long long)T * b.hidden * 2);
+    // sums of squares of the residual stream, per 128-feature tile and token: [0] inside a layer (for its
+    // second norm), [1] between layers (for the next layer's first)
+    p.sumsq[0] = take((long long)((b.hidden + 127) / 128) * 256 * 4);
+    p.sumsq[1] = take((long long)((b.hidden + 127) / 128) * 256 * 4);
     p.delta[0] = take(delta_bytes);
     p.delta[1] = take(delta_bytes);
     p.h = take((long long)T * b.hidden * 2);
@@ -196,19 +213,49 @@ static int product(const InferoStep& s, const void* a, int K, const void* w, int
             rc = infero_gemm_tc_partials(a, w, (float*)dst, T, N, K, K, splits, per, s.stream);
         }
         if (rc) return rc;
-        *out = InferoDelta{dst, F32, splits, (long long)T * N, bias, bias_dtype};
+        *out = InferoDelta{dst, F32, splits, (long long)T * N, bias, bias_dtype, nullptr, 0};
         return 0;
     }
     if (int rc = infero_gemm_tc(a, w, bias, bias_dtype, dst, BF16, T, N, K, K, N, nullptr, 0, s.sm_count, 0, s.stream))
         return rc;
-    *out = InferoDelta{dst, BF16, 1, 0, nullptr, F32};
+    *out = InferoDelta{dst, BF16, 1, 0, nullptr, F32, nullptr, 0};
     return 0;
+}
+
+// Can decode attention finish this block's q/k/v product itself in this step?  (A step of single tokens
+// whose product comes as partial sums; INFERO_FUSED_DECODE=0 keeps the two kernels apart.)
+static int g_fused_decode = -1, g_fused_norm = -1;       // -1: ask the environment at first use
+static bool env_on(const char* name) {
+    const char* e = getenv(name);
+    return !(e && e[0] == '0');
+}
+static bool fused_decode(const InferoBlock& b, const InferoStep& s, const ArenaPlan& p) {
+    if (g_fused_decode < 0) g_fused_decode = env_on("INFERO_FUSED_DECODE") ? 1 : 0;
+    const bool wanted = g_fused_decode != 0;
+    const int T = s.n_tokens, nqkv = (b.n_heads + 2 * b.n_kv) * b.head_dim;
+    return wanted && T <= 256 && s.n_decode == s.n_entries && s.n_decode == T &&
+           infero_attn_decode_fused_supported((const float*)(s.arena + p.qkv), (long long)T * nqkv, b.n_heads, b.n_kv,
+                                              b.head_dim, b.page_size, b.rotary_dim, b.k_cache, b.v_cache);
+}
+
+// May the residual-add-and-norm kernels of such a step be folded into the products around them?
+// (INFERO_FUSED_NORM=0 keeps them as kernels.)
+static bool fused_norm_wanted() {
+    if (g_fused_norm < 0) g_fused_norm = env_on("INFERO_FUSED_NORM") ? 1 : 0;
+    return g_fused_norm != 0;
+}
+// The two switches at run time (tests compare the folded launches with the separate ones).
+void infero_block_set_fusion(int fused_decode_on, int fused_norm_on) {
+    g_fused_decode = fused_decode_on ? 1 : 0;
+    g_fused_norm = fused_norm_on ? 1 : 0;
 }
 
 // x += pending; the block; leaves its own feed-forward output pending in *delta.  layer_parity picks
 // which of the arena's two output areas this layer writes (the other one still holds its input).
+// next: the block that runs after this one on the same residual stream, or null (then, and whenever
+// that block could not take it, the output is left pending as partial sums or a finished product).
 int infero_block_forward(const InferoBlock* b, const InferoStep* s, const int* block_table, int max_blocks,
-                         int layer_parity, InferoDelta* delta) {
+                         int layer_parity, InferoDelta* delta, const InferoBlock* next) {
     const int T = s->n_tokens;
     if (T == 0) return 0;
     const ArenaPlan p = plan_arena(*b, T, s->sm_count);
@@ -219,25 +266,32 @@ int infero_block_forward(const InferoBlock* b, const InferoStep* s, const int* b
     uint8_t* A = s->arena;
     const int H = b->n_heads, Hkv = b->n_kv, D = b->head_dim, d = b->hidden, ff = b->intermediate;
     const int da = H * D, nqkv = (H + 2 * Hkv) * D;
+    const int tiles = (d + 127) / 128;
+    const float inv_d = 1.0f / (float)d;
+    const bool fused = fused_decode(*b, *s, p);
+    const bool fold_norms = fused && fused_norm_wanted();
     void* h = A + p.h;
     // ---- mixer ------------------------------------------------------------------------------------
-    if (int rc = infero_add_rmsnorm(s->x, delta->data, delta->data ? delta->dtype : F32, delta->data ? delta->splits : 1,
-                                    delta->data ? delta->split_stride : 0, delta->data ? delta->bias : nullptr,
-                                    delta->bias_dtype, b->w_norm_mixer, b->norm_dtype, b->eps_mixer, h, BF16, nullptr, T, d,
-                                    s->stream))
-        return rc;
+    const float* ss_mixer = nullptr;                   // the first norm's scalar is still to be applied
+    if (delta->data && delta->dtype == PRENORMED && fused) {
+        h = const_cast<void*>(delta->data);
+        ss_mixer = delta->sumsq;
+    } else {
+        const bool pending = delta->data && delta->dtype != PRENORMED;
+        if (int rc = infero_add_rmsnorm(s->x, pending ? delta->data : nullptr, pending ? delta->dtype : F32,
+                                        pending ? delta->splits : 1, pending ? delta->split_stride : 0,
+                                        pending ? delta->bias : nullptr, delta->bias_dtype, b->w_norm_mixer, b->norm_dtype,
+                                        b->eps_mixer, h, BF16, nullptr, T, d, s->stream))
+            return rc;
+    }
     InferoDelta qkv;
     if (int rc = product(*s, h, d, b->w_qkv, nqkv, b->b_qkv, b->qkv_bias_dtype, A + p.qkv, &qkv)) return rc;
+    h = A + p.h;
     const void* q = nullptr;
     int q_stride = 0;
     // A step of single tokens whose q/k/v product came as partial sums: decode attention finishes the
     // product itself (bias, rotary positions, cache append), one launch instead of two.
-    // INFERO_FUSED_DECODE=0 keeps the two kernels apart.
-    static const bool fuse_wanted = !(getenv("INFERO_FUSED_DECODE") && getenv("INFERO_FUSED_DECODE")[0] == '0');
-    const bool fused = fuse_wanted && qkv.dtype == F32 && s->n_decode == s->n_entries && s->n_decode == T &&
-                       infero_attn_decode_fused_supported((const float*)qkv.data, qkv.split_stride, H, Hkv, D, b->page_size,
-                                                          b->rotary_dim, b->k_cache, b->v_cache);
-    if (fused) {
+    if (fused && qkv.dtype == F32) {
     } else if (qkv.dtype == F32) {
         q = A + p.q;
         q_stride = da;
@@ -265,12 +319,13 @@ int infero_block_forward(const InferoBlock* b, const InferoStep* s, const int* b
             return 1;
         }
         int rc;
-        if (fused)
+        if (fused && qkv.dtype == F32)
             rc = infero_attn_decode_tma_fused((const float*)qkv.data, qkv.splits, qkv.split_stride, qkv.bias, qkv.bias_dtype,
                                               b->inv_freq, b->rotary_dim, b->write_cache, attn, da, b->k_cache, b->v_cache,
                                               b->num_pages, block_table, max_blocks, s->tok_entry, s->positions, 0,
                                               s->n_decode, H, Hkv, D, b->page_size, b->window, b->scale, chunk, splits,
-                                              A + p.scratch, s->counters, s->n_counters, s->stream);
+                                              A + p.scratch, s->counters, s->n_counters, ss_mixer, tiles, inv_d,
+                                              b->eps_mixer, s->stream);
         else
             rc = infero_attn_decode_tma(q, q_stride, attn, da, b->k_cache, b->v_cache, b->num_pages, block_table,
                                         max_blocks, s->tok_entry, s->positions, 0, s->n_decode, H, Hkv, D,
@@ -285,22 +340,52 @@ int infero_block_forward(const InferoBlock* b, const InferoStep* s, const int* b
                                             s->stream))
             return rc;
     }
-    InferoDelta o;
-    if (int rc = product(*s, attn, da, b->w_o, d, b->b_o, b->o_bias_dtype, A + p.o_delta, &o)) return rc;
-    // ---- feed-forward -----------------------------------------------------------------------------
-    if (int rc = infero_add_rmsnorm(s->x, o.data, o.dtype, o.splits, o.split_stride, o.bias, o.bias_dtype, b->w_norm_ffn,
-                                    b->norm_dtype, b->eps_ffn, h, BF16, nullptr, T, d, s->stream))
-        return rc;
+    // ---- output projection, second norm, feed-forward ----------------------------------------------
     void* act = A + p.act;
-    int rc = infero_gemm_tc_swiglu(h, b->w_gate_up, act, T, 2 * ff, d, d, ff, s->sm_count, s->stream);
-    if (rc == 2) {
-        // few rows and K cut into splits: the activation is not linear, so the product comes as
-        // partial sums and the SwiGLU kernel adds them up
-        InferoDelta gu;
-        if (int rc2 = product(*s, h, d, b->w_gate_up, 2 * ff, nullptr, F32, A + p.gate_up, &gu)) return rc2;
-        rc = infero_swiglu(gu.data, gu.splits, gu.split_stride, act, F32, 1, T, ff, s->stream);
+    int gu_splits = 1, gu_per = 1;
+    long long gu_ws = 0;
+    infero_gemm_tc_plan(T, 2 * ff, d, s->sm_count, &gu_splits, &gu_per, &gu_ws);
+    int rc;
+    if (fold_norms && gu_splits == 1) {
+        // the output projection adds itself to x and leaves x * w and the sums of squares; the gate/up
+        // product applies the norm's scalar to its own result before the activation
+        float* ss_ffn = (float*)(A + p.sumsq[0]);
+        int o_splits, o_per;
+        infero_gemm_tc_plan_cluster(T, d, da, s->sm_count, &o_splits, &o_per);
+        if (int rc2 = infero_gemm_tc_residual_norm(attn, b->w_o, T, d, da, da, o_splits, o_per, s->x, b->b_o, b->o_bias_dtype,
+                                                   b->w_norm_ffn, b->norm_dtype, h, ss_ffn, s->stream))
+            return rc2;
+        rc = infero_gemm_tc_swiglu_scaled(h, b->w_gate_up, act, T, 2 * ff, d, d, ff, ss_ffn, tiles, inv_d, b->eps_ffn,
+                                          s->sm_count, s->stream);
+    } else {
+        InferoDelta o;
+        if (int rc2 = product(*s, attn, da, b->w_o, d, b->b_o, b->o_bias_dtype, A + p.o_delta, &o)) return rc2;
+        if (int rc2 = infero_add_rmsnorm(s->x, o.data, o.dtype, o.splits, o.split_stride, o.bias, o.bias_dtype, b->w_norm_ffn,
+                                         b->norm_dtype, b->eps_ffn, h, BF16, nullptr, T, d, s->stream))
+            return rc2;
+        rc = infero_gemm_tc_swiglu(h, b->w_gate_up, act, T, 2 * ff, d, d, ff, s->sm_count, s->stream);
+        if (rc == 2) {
+            // few rows and K cut into splits: the activation is not linear, so the product comes as
+            // partial sums and the SwiGLU kernel adds them up
+            InferoDelta gu;
+            if (int rc2 = product(*s, h, d, b->w_gate_up, 2 * ff, nullptr, F32, A + p.gate_up, &gu)) return rc2;
+            rc = infero_swiglu(gu.data, gu.splits, gu.split_stride, act, F32, 1, T, ff, s->stream);
+        }
     }
     if (rc) return rc;
+    // ---- down projection -----------------------------------------------------------------------------
+    if (fold_norms && next && next->hidden == d && next->norm_dtype == b->norm_dtype &&
+        fused_decode(*next, *s, plan_arena(*next, T, s->sm_count))) {
+        // the next layer is of the same kind and takes its input without its first norm's scalar
+        float* ss_next = (float*)(A + p.sumsq[1]);
+        int dn_splits, dn_per;
+        infero_gemm_tc_plan_cluster(T, d, ff, s->sm_count, &dn_splits, &dn_per);
+        if (int rc2 = infero_gemm_tc_residual_norm(act, b->w_down, T, d, ff, ff, dn_splits, dn_per, s->x, nullptr, F32,
+                                                   next->w_norm_mixer, next->norm_dtype, h, ss_next, s->stream))
+            return rc2;
+        *delta = InferoDelta{h, PRENORMED, 1, 0, nullptr, F32, ss_next, tiles};
+        return 0;
+    }
     return product(*s, act, ff, b->w_down, d, nullptr, F32, A + p.delta[layer_parity & 1], delta);
 }
 

@@ -72,7 +72,8 @@ def decode(q, out, k_cache, v_cache, table, tok_entry, positions, tok_first: int
 
 def decode_fused(qkv, out, k_cache, v_cache, table, tok_entry, positions, inv_freq, n_heads: int, n_kv: int,
                  head_dim: int, page_size: int, window: Optional[int], scale: float, chunk: int, n_splits: int,
-                 write_cache: bool = True) -> None:
+                 write_cache: bool = True, sumsq: Optional[torch.Tensor] = None, sumsq_tiles: int = 0,
+                 inv_d: float = 0.0, eps: float = 0.0) -> None:
     """Rotary positions, cache append and decode attention of single tokens in one launch, from the
     q/k/v product as partial sums (``kernels.Partials`` [T, (H + 2 Hkv) * D], bias not yet added)."""
     n_tok = out.shape[0]
@@ -86,7 +87,8 @@ def decode_fused(qkv, out, k_cache, v_cache, table, tok_entry, positions, inv_fr
         _ptr(v_cache), c_int(k_cache.shape[0]), _ptr(_i32(table, "block_table")), c_int(table.shape[1]),
         _ptr(_i32(tok_entry, "tok_entry")), _ptr(_i32(positions, "positions")), c_int(0), c_int(n_tok), c_int(n_heads),
         c_int(n_kv), c_int(head_dim), c_int(page_size), c_int(window or 0), c_float(scale), c_int(chunk),
-        c_int(n_splits), _ptr(scratch), _ptr(_arrival_counters(out.device)), c_int(N_COUNTERS), _stream()))
+        c_int(n_splits), _ptr(scratch), _ptr(_arrival_counters(out.device)), c_int(N_COUNTERS), _ptr(sumsq),
+        c_int(sumsq_tiles), c_float(inv_d), c_float(eps), _stream()))
 
 
 def lib_scratch(n_tok, n_heads, head_dim, n_splits) -> int:

@@ -112,6 +112,44 @@ def partials(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def residual_norm(a: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, bias: Optional[torch.Tensor],
+                  norm_w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """A few-row product that is a residual update, with what the RMSNorm behind it needs:
+    resid += a @ w^T (+ bias) in place (float32 [M, N]); returns (h, sumsq) with h = bf16(resid * norm_w)
+    and sumsq[tile, t] the sum of resid[t, n]^2 over the 128 features n of tile (float32 [tiles, 256]).
+    The norm's scalar for token t is rsqrt(sumsq[:, t].sum() / N + eps); ``gemm_swiglu_scaled`` and the
+    fused decode attention apply it after their own products."""
+    from ctypes import c_float  # noqa: F401
+    M, K = a.shape
+    N = w.shape[0]
+    assert M <= 256 and resid.shape == (M, N) and resid.dtype == torch.float32 and resid.is_contiguous()
+    s, per = c_int(0), c_int(0)
+    lib().infero_gemm_tc_plan_cluster(c_int(M), c_int(N), c_int(K), c_int(sm_count(a.device)), byref(s), byref(per))
+    h = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    sumsq = torch.zeros(((N + 127) // 128, 256), dtype=torch.float32, device=a.device)
+    _check(lib().infero_gemm_tc_residual_norm(_ptr(a), _ptr(w), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)), s, per,
+                                              _ptr(resid), _ptr(bias), c_int(_dt(bias) if bias is not None else F32),
+                                              _ptr(norm_w), c_int(_dt(norm_w)), _ptr(h), _ptr(sumsq), _stream()))
+    return h, sumsq
+
+
+def gemm_swiglu_scaled(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, sumsq: torch.Tensor, eps: float) -> bool:
+    """``gemm_swiglu`` on an input that lacks its norm's scalar: token t's products are multiplied by
+    rsqrt(sumsq[:, t].sum() / K + eps) before the activation.  Few rows, one split of K; else False."""
+    from ctypes import c_float
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.shape == (M, N // 2) and out.stride(1) == 1 and out.dtype == torch.bfloat16
+    assert sumsq.dtype == torch.float32 and sumsq.shape[1] == 256 and sumsq.is_contiguous()
+    rc = lib().infero_gemm_tc_swiglu_scaled(_ptr(a), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)),
+                                            c_int(out.stride(0)), _ptr(sumsq), c_int(sumsq.shape[0]), c_float(1.0 / K),
+                                            c_float(eps), c_int(sm_count(a.device)), _stream())
+    if rc == 2:
+        return False
+    _check(rc)
+    return True
+
+
 def reduce_partials(partial: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
     S, M, N = partial.shape
     assert partial.is_contiguous() and partial.dtype == torch.float32 and out.shape == (M, N)

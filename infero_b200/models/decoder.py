@@ -111,8 +111,13 @@ class DecoderModel:
         x = torch.empty((T, s.hidden), dtype=torch.float32, device=token_ids.device)
         K.embed_gather(self.embed, token_ids, x, s.embed_scale, getattr(ctx, "device_tokens", None))
         delta = None
-        for entry in s.schedule:
+        for i, entry in enumerate(s.schedule):
+            # a block may look at what runs after it (the built-in block folds the next block's first norm
+            # into its own last product when that block is of its kind)
+            nxt = s.schedule[i + 1] if i + 1 < len(s.schedule) else None
+            ctx.upcoming = (self.blocks[nxt.block], nxt) if nxt is not None else None
             delta = self.blocks[entry.block].forward(ctx, x, delta, entry)
+        ctx.upcoming = None
         if logit_rows is None or logit_rows.numel() == 0:
             return None
         h = self.final_norm.forward(ctx, x, delta, rows=logit_rows)

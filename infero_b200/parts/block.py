@@ -40,12 +40,17 @@ class PreNormBlock(Part):
         for part in self.parts():
             part.bind(tensors)
 
-    def forward(self, ctx, x, delta, slot):
+    def _native_for(self, ctx):
+        """This block's native launcher if the step ``ctx`` goes that way, else None."""
         native = self._native
         if native is None:
             from .native_block import NativeBlock
             native = self._native = NativeBlock(self)
-        if native.wants(ctx):
+        return native if native.wants(ctx) else None
+
+    def forward(self, ctx, x, delta, slot):
+        native = self._native_for(ctx)
+        if native is not None:
             # the package's own parts in a bf16 step: the whole layer in one native call (same kernels,
             # same arguments, same order as below)
             out = native.run(ctx, x, delta, slot)

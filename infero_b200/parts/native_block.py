@@ -31,7 +31,16 @@ def set_enabled(on: bool) -> None:
     ENABLED = bool(on)
 
 
+def set_fusion(decode: bool = True, norms: bool = True) -> None:
+    """Steps of single tokens: ``decode``: attention finishes the q/k/v product itself (bias, rotary
+    positions, cache append; bit for bit what the separate kernels give); ``norms``: the residual-add-and-
+    norm kernels are folded into the products around them (same arithmetic up to where bf16 rounding
+    falls).  Both on unless INFERO_FUSED_DECODE=0 / INFERO_FUSED_NORM=0."""
+    _lib().infero_block_set_fusion(c_int(1 if decode else 0), c_int(1 if norms else 0))
+
+
 F32, BF16 = K.F32, K.BF16
+PRENORMED = 2               # a pending output that is no longer pending: see InferoDelta in csrc/host_block.cpp
 
 
 class _Block(ctypes.Structure):
@@ -54,7 +63,7 @@ class _Step(ctypes.Structure):
 
 class _Delta(ctypes.Structure):
     _fields_ = [("data", c_void_p), ("dtype", c_int), ("splits", c_int), ("split_stride", c_longlong),
-                ("bias", c_void_p), ("bias_dtype", c_int)]
+                ("bias", c_void_p), ("bias_dtype", c_int), ("sumsq", c_void_p), ("sumsq_tiles", c_int)]
 
 
 def _lib():
@@ -77,6 +86,8 @@ class NativeDelta:
         self.desc, self.arena, self.rows, self.cols, self.bias_tensor = desc, arena, rows, cols, bias
 
     def as_partials(self):
+        if self.desc.dtype == PRENORMED:
+            return None                        # x holds the sum already: nothing is pending for a Python consumer
         off = int(self.desc.data) - self.arena.data_ptr()
         if self.desc.dtype == F32:
             n = self.desc.splits * self.rows * self.cols
@@ -88,18 +99,18 @@ class NativeDelta:
 def _delta_desc(delta, keep: list) -> _Delta:
     """The descriptor of whatever the layer before left pending."""
     if delta is None:
-        return _Delta(None, F32, 1, 0, None, F32)
+        return _Delta(None, F32, 1, 0, None, F32, None, 0)
     if isinstance(delta, NativeDelta):
         return delta.desc
     if isinstance(delta, K.Partials):
         keep.append(delta)
         b = delta.bias
         return _Delta(delta.data.data_ptr(), F32, delta.splits, delta.split_stride, b.data_ptr() if b is not None else None,
-                      _dt(b))
+                      _dt(b), None, 0)
     if not delta.is_contiguous():
         delta = delta.contiguous()
     keep.append(delta)
-    return _Delta(delta.data_ptr(), _dt(delta), 1, 0, None, F32)
+    return _Delta(delta.data_ptr(), _dt(delta), 1, 0, None, F32, None, 0)
 
 
 class NativeBlock:
@@ -183,10 +194,20 @@ class NativeBlock:
         table = ctx.block_table(kv.group)
         keep = []
         desc = _delta_desc(delta, keep)
-        out = _Delta(desc.data, desc.dtype, desc.splits, desc.split_stride, desc.bias, desc.bias_dtype)
+        out = _Delta(desc.data, desc.dtype, desc.splits, desc.split_stride, desc.bias, desc.bias_dtype, desc.sumsq,
+                     desc.sumsq_tiles)
         parity = ctx.native_parity
         ctx.native_parity ^= 1
+        # the block that runs next on the same residual stream, if it is one of these too: native code may
+        # then fold that block's first norm into this block's last product
+        nxt = None
+        upcoming = getattr(ctx, "upcoming", None)
+        if upcoming is not None:
+            nb = getattr(upcoming[0], "_native_for", lambda c: None)(ctx)
+            if nb is not None:
+                nxt = nb._desc(ctx, upcoming[1])
         K._check(_lib().infero_block_forward(ctypes.byref(d), ctypes.byref(step), c_void_p(table.data_ptr()),
-                                             c_int(table.shape[1]), c_int(parity), ctypes.byref(out)))
+                                             c_int(table.shape[1]), c_int(parity), ctypes.byref(out),
+                                             ctypes.byref(nxt) if nxt is not None else None))
         CALLS[0] += 1
         return NativeDelta(out, ctx.native_arena, x.shape[0], d.hidden, None)

@@ -151,6 +151,55 @@ def test_gemm_tensor_core_with_swiglu_epilogue(M, N, K, cta_pairs):
     assert tc_gemm.error_flag() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(8, 3584, 18944), (1, 3584, 3584), (64, 896, 4864), (200, 1000, 2048), (5, 128, 320),
+                                   (16, 256, 616), (33, 130, 1024)])
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_product_that_updates_the_residual_and_prepares_the_norm(M, N, K, with_bias):
+    """resid += a w^T (+ bias); h = bf16(resid * norm_w); per-tile sums of squares -- against float64,
+    and the norm that follows from (h, sums) against the norm computed in one piece."""
+    from infero_b200.kernels import tc_gemm
+    a = _rand((M, K), torch.bfloat16, 1)
+    w = _rand((N, K), torch.bfloat16, 2, scale=1.0 / math.sqrt(K))
+    bias = _rand((N,), torch.float32, 3) if with_bias else None
+    norm_w = (1.0 + _rand((N,), torch.float32, 4, scale=0.1))
+    resid0 = _rand((M, N), torch.float32, 5, scale=2.0)
+    resid = resid0.clone()
+    h, sumsq = tc_gemm.residual_norm(a, w, resid, bias, norm_w)
+    torch.cuda.synchronize()
+    ref = resid0.double() + a.double() @ w.double().T + (bias.double() if with_bias else 0)
+    assert _rel_err(resid, ref.cpu()) <= 2e-5
+    assert _rel_err(h.float(), (ref * norm_w.double()).cpu()) <= 5e-3                    # one bf16 rounding
+    tiles = (N + 127) // 128
+    pad = torch.zeros((M, tiles * 128), dtype=torch.float64, device=DEV)
+    pad[:, :N] = ref
+    ss_ref = (pad.view(M, tiles, 128) ** 2).sum(-1).T                            # [tiles, M]
+    assert _rel_err(sumsq[:, :M], ss_ref.cpu()) <= 2e-5
+    eps = 1e-6
+    rstd = torch.rsqrt(sumsq[:, :M].double().sum(0) / N + eps)
+    normed_ref = ref * torch.rsqrt((ref ** 2).mean(-1, keepdim=True) + eps) * norm_w.double()
+    assert _rel_err(h.double() * rstd[:, None], normed_ref.cpu()) <= 5e-3
+    assert tc_gemm.error_flag() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(8, 37888, 3584), (1, 1232, 256), (64, 1024, 512), (5, 640, 128), (130, 354, 64)])
+def test_swiglu_product_that_applies_the_norms_scalar(M, N, K):
+    from infero_b200.kernels import tc_gemm
+    a = _rand((M, K), torch.bfloat16, 1)
+    w = _rand((N, K), torch.bfloat16, 2, scale=1.0 / math.sqrt(K))
+    tiles = (K + 127) // 128
+    sumsq = torch.rand((tiles, 256), generator=torch.Generator().manual_seed(3)).to(DEV) * 50.0
+    eps = 1e-5
+    out = torch.zeros((M, N // 2), dtype=torch.bfloat16, device=DEV)
+    if not tc_gemm.gemm_swiglu_scaled(a, w, out, sumsq, eps):
+        pytest.skip("this shape cuts K into splits: the scaled epilogue is not used for it")
+    rstd = torch.rsqrt(sumsq[:, :M].double().sum(0) / K + eps)
+    y = (a.double() @ w.double().T) * rstd[:, None]
+    g, u = y[:, 0::2], y[:, 1::2]
+    ref = g / (1 + torch.exp(-g)) * u
+    assert _rel_err(out.float(), ref.cpu()) <= 1e-2
+    assert tc_gemm.error_flag() == 0
+
+
 def test_gemm_tensor_core_refuses_what_it_cannot_take():
     from infero_b200.kernels import tc_gemm
     a = _rand((4, 100), torch.bfloat16, 1)               # K = 100 is no multiple of 8
