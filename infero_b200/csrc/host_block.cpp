@@ -138,9 +138,10 @@ struct ArenaPlan {
     long long sumsq[2], delta[2], h, qkv, q, attn, scratch, o_delta, act, gate_up, total;
 };
 
-// Room for the product of T rows with a [N, K] matrix, which comes as partial sums (few rows) or finished.
-static long long product_bytes(int T, int N, int K, int sm_count) {
-    if (T > 256) return align_up((long long)T * N * 2);
+// Room for the product of T rows with a [N, K] matrix, which comes as partial sums (few rows) or finished
+// (bf16, or 32-bit when it is an update of the residual stream).
+static long long product_bytes(int T, int N, int K, int sm_count, bool residual = false) {
+    if (T > 256) return align_up((long long)T * N * (residual ? 4 : 2));
     int splits = 1, per = 1;
     long long ws = 0;
     infero_gemm_tc_plan(T, N, K, sm_count, &splits, &per, &ws);
@@ -155,7 +156,7 @@ static ArenaPlan plan_arena(const InferoBlock& b, int T, int sm_count) {
     // The two output areas lie at places that depend on the step and the residual width only, not on the
     // block (up to 16 splits of up to 256 rows, or a finished product): the layer that reads one as its
     // input may be built to other sizes and must not have its own areas overlap it.
-    const long long delta_bytes = std::max(16LL * std::min(T, 256) * b.hidden * 4, (long long)T * b.hidden * 2);
+    const long long delta_bytes = std::max(16LL * std::min(T, 256) * b.hidden * 4, (long long)T * b.hidden * 4);
     // sums of squares of the residual stream, per 128-feature tile and token: [0] inside a layer (for its
     // second norm), [1] between layers (for the next layer's first)
     p.sumsq[0] = take((long long)((b.hidden + 127) / 128) * 256 * 4);
@@ -169,7 +170,7 @@ static ArenaPlan plan_arena(const InferoBlock& b, int T, int sm_count) {
     // the decode kernel's splits: tokens x splits stays below about two CTAs per SM (or one split each)
     p.scratch = take(infero_attn_decode_scratch(std::max(T, 2 * (sm_count > 0 ? sm_count : infero_sm_count())), b.n_heads,
                                                 b.head_dim, 1));
-    p.o_delta = take(product_bytes(T, b.hidden, da, sm_count));
+    p.o_delta = take(product_bytes(T, b.hidden, da, sm_count, true));
     p.act = take((long long)T * b.intermediate * 2);
     p.gate_up = take(T <= 256 ? product_bytes(T, 2 * b.intermediate, b.hidden, sm_count) : 0);
     p.total = off;
@@ -196,10 +197,11 @@ int infero_block_supported(const InferoBlock* b) {
            b->rotary_dim % 2 == 0 && b->rotary_dim <= b->head_dim;
 }
 
-// out = a[T, K] * w[N, K]^T for the caller's next kernel: partial sums for few rows, a finished bf16
-// product (bias added) for many.
+// out = a[T, K] * w[N, K]^T for the caller's next kernel: partial sums for few rows, a finished
+// product (bias added) for many: bf16, or 32-bit when it updates the residual stream (a token's residual
+// then receives 32-bit sums however many rows its step has).
 static int product(const InferoStep& s, const void* a, int K, const void* w, int N, const void* bias, int bias_dtype,
-                   void* dst, InferoDelta* out) {
+                   void* dst, InferoDelta* out, bool residual = false) {
     const int T = s.n_tokens;
     if (T <= 256) {
         int splits = 1, per = 1;
@@ -216,9 +218,10 @@ static int product(const InferoStep& s, const void* a, int K, const void* w, int
         *out = InferoDelta{dst, F32, splits, (long long)T * N, bias, bias_dtype, nullptr, 0};
         return 0;
     }
-    if (int rc = infero_gemm_tc(a, w, bias, bias_dtype, dst, BF16, T, N, K, K, N, nullptr, 0, s.sm_count, 0, s.stream))
+    const int out_dtype = residual ? F32 : BF16;
+    if (int rc = infero_gemm_tc(a, w, bias, bias_dtype, dst, out_dtype, T, N, K, K, N, nullptr, 0, s.sm_count, 0, s.stream))
         return rc;
-    *out = InferoDelta{dst, BF16, 1, 0, nullptr, F32, nullptr, 0};
+    *out = InferoDelta{dst, out_dtype, 1, 0, nullptr, F32, nullptr, 0};
     return 0;
 }
 
@@ -359,7 +362,7 @@ int infero_block_forward(const InferoBlock* b, const InferoStep* s, const int* b
                                           s->sm_count, s->stream);
     } else {
         InferoDelta o;
-        if (int rc2 = product(*s, attn, da, b->w_o, d, b->b_o, b->o_bias_dtype, A + p.o_delta, &o)) return rc2;
+        if (int rc2 = product(*s, attn, da, b->w_o, d, b->b_o, b->o_bias_dtype, A + p.o_delta, &o, true)) return rc2;
         if (int rc2 = infero_add_rmsnorm(s->x, o.data, o.dtype, o.splits, o.split_stride, o.bias, o.bias_dtype, b->w_norm_ffn,
                                          b->norm_dtype, b->eps_ffn, h, BF16, nullptr, T, d, s->stream))
             return rc2;
@@ -386,7 +389,7 @@ int infero_block_forward(const InferoBlock* b, const InferoStep* s, const int* b
         *delta = InferoDelta{h, PRENORMED, 1, 0, nullptr, F32, ss_next, tiles};
         return 0;
     }
-    return product(*s, act, ff, b->w_down, d, nullptr, F32, A + p.delta[layer_parity & 1], delta);
+    return product(*s, act, ff, b->w_down, d, nullptr, F32, A + p.delta[layer_parity & 1], delta, true);
 }
 
 }  // extern "C"

@@ -101,4 +101,4 @@ class GqaAttention(Mixer):
         attn = torch.empty((T, H * D), dtype=h.dtype, device=h.device)
         from ..kernels import attention as A
         A.paged_attention(ctx, q, attn, kv, table, H, Hkv, D, s.window, s.scale)
-        return self.out.forward(attn, defer=True)
+        return self.out.forward(attn, defer=True, residual=True)

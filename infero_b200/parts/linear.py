@@ -26,16 +26,20 @@ class Linear:
         self.out_features, self.in_features = weight.shape
 
     def forward(self, a: torch.Tensor, out: Optional[torch.Tensor] = None,
-                out_dtype: Optional[torch.dtype] = None, defer: bool = False):
+                out_dtype: Optional[torch.dtype] = None, defer: bool = False, residual: bool = False):
         """``defer``: the caller's next kernel can add up partial sums itself, so for few rows on
         the tensor-core path return ``Partials`` (32-bit split-K products + bias) instead of a
-        finished tensor."""
+        finished tensor.  ``residual``: the result is an update of the 32-bit residual stream; a
+        finished bf16-path product is then written in 32-bit too, so that what a token's residual
+        receives does not lose 16 bits in steps of many rows that it keeps in steps of few."""
         M = a.shape[0]
         if defer and out is None and 0 < M <= 256 and a.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16:
             from ..kernels import tc_gemm
             if tc_gemm.supported(a, self.weight):
                 return K.Partials(tc_gemm.partials(a, self.weight), self.bias)
         if out is None:
+            if residual and out_dtype is None and a.dtype == torch.bfloat16:
+                out_dtype = torch.float32
             out = torch.empty((M, self.out_features), dtype=out_dtype or a.dtype, device=a.device)
         if M == 0:
             return out

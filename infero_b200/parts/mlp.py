@@ -54,4 +54,4 @@ class SwiGluMlp(FeedForward):
         act = torch.empty((T, self.spec.intermediate), dtype=h.dtype, device=h.device)
         if not self.gate_up.forward_swiglu(h, act):
             K.swiglu(self.gate_up.forward(h, defer=True), act)
-        return self.down.forward(act, defer=True)
+        return self.down.forward(act, defer=True, residual=True)

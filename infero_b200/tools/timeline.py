@@ -8,7 +8,7 @@ nor a profiler's serialised list says what a kernel costs in place.  This tool l
 timeline variant (built with INFERO_TIMELINE=1 into a folder of its own: every block of the
 instrumented kernels logs its kind, grid, multiprocessor and its first and last nanosecond of the
 global timer), runs captured decode steps of a random model and prints, for the last step, an
-averaged timeline of a layer: for each launch when its first block started, when all had started,
+averaged timeline of a layer (from its q/k/v product to the next layer's): for each launch when its first block started, when all had started,
 when the first and the last ended, relative to the start of the layer's first kernel.  Nothing of
 the step is replaced or left out; the log costs each block one atomic and one 32-byte store.
 The reference's counterpart times kernels one by one with events (crates/cuda/src/profile.rs:28-130).
@@ -132,9 +132,10 @@ def main(argv=None) -> int:
 
     marks = [r for r in rows if r["kind"] >= 50]
     rows = [r for r in rows if r["kind"] < 50]
-    # a layer = from one norm that is followed by a product and then by the rotary kernel or decode attention
-    norm_idx = [i for i, r in enumerate(rows) if r["kind"] == 2]
-    layer_starts = [i for i in norm_idx if i + 2 < len(rows) and rows[i + 1]["kind"] == 3 and rows[i + 2]["kind"] in (4, 5)]
+    # a layer's window = from the product in front of decode attention (q/k/v) up to the next one
+    layer_starts = [i - 1 for i, r in enumerate(rows) if r["kind"] == 5 and i >= 1 and rows[i - 1]["kind"] == 3]
+    if any(rows[i - 1]["kind"] == 4 for i, r in enumerate(rows) if r["kind"] == 5 and i >= 2):
+        layer_starts = [i - 2 for i, r in enumerate(rows) if r["kind"] == 5 and i >= 2]    # (separate rotary kernel)
     per_layer = [rows[a:b] for a, b in zip(layer_starts, layer_starts[1:])]
     if len(per_layer) >= 3:
         shape = [(r["kind"], r["grid"]) for r in per_layer[1]]

@@ -291,8 +291,13 @@ def test_native_block_launcher_changes_nothing(window, shape):
     folded, _ = run(True, fold_norms=True)
     for a, b in zip(plain[:3], folded[:3]):            # steps with a prompt portion: nothing is folded
         assert torch.equal(a, b)
+    # two bf16 paths whose roundings fall in different places (bf16(x * rstd * w) against bf16(x * w) * rstd):
+    # each is held to the bf16 bound against the plain implementation by the replay tests; against each
+    # other they are held to the same bound here
+    from engine_fixtures import TOL
     for a, b in zip(plain[3:], folded[3:]):
-        assert float((a - b).abs().max() / a.abs().max()) <= 1e-2
+        gap = float((a - b).abs().max() / a.abs().max())
+        assert gap <= TOL["bfloat16"], f"folded norms: {gap:.3e}"
 
 
 # ---- a toy mixer with state of its own, from outside the package ------------------------------------

@@ -56,6 +56,32 @@ def _check(name, dtype, steps, reqs, mdir, max_tokens=None, page_size=16):
     return runner, err
 
 
+@pytest.mark.parametrize("name", SERVING_PATH)
+def test_a_prompt_cut_at_256_and_at_257_rows(name):
+    """Products of up to 256 rows reach the residual stream as 32-bit partial sums, those of more rows as
+    finished products: 32-bit too, so a token's logits do not depend on which side of that line its
+    portion fell.  Both cuts against the plain implementation, and against each other much closer than
+    bf16 rounding of the residual updates would leave them."""
+    mdir = model_dir(name)
+    reqs = make_requests(name, [300], seed=21)
+    toks = reqs["r0"]
+    plain = plain_logits(mdir, reqs)
+    got = {}
+    for cut in (256, 257):
+        steps = [{"step": 0, "entries": [{"id": "r0", "tokens": toks[:cut], "want": list(range(cut - 8, cut))}], "end": []},
+                 {"step": 1, "entries": [{"id": "r0", "tokens": toks[cut:], "want": list(range(len(toks) - cut))}], "end": ["r0"]}]
+        runner = make_runner(mdir, "bfloat16", 320)
+        with ServingPath(name, "bfloat16"):
+            got[cut] = R.replay_inprocess(runner, steps)
+        err, where = R.compare(got[cut], plain)
+        assert err <= TOL["bfloat16"], f"{name} cut at {cut}: relative error {err:.3e} at {where}"
+    both = sorted(set(got[256]) & set(got[257]))
+    assert len(both) >= 40
+    scale = float(np.abs(plain["r0"]).max())
+    gap = max(float(np.abs(got[256][k] - got[257][k]).max()) for k in both) / scale
+    assert gap <= TOL["bfloat16"] / 3, f"{name}: the two cuts differ by {gap:.3e}"
+
+
 @pytest.mark.parametrize("name,dtype", CASES)
 def test_each_request_alone_and_whole(name, dtype):
     mdir = model_dir(name)
