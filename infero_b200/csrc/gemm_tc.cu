@@ -366,29 +366,43 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (fuse.bias) bias_v = load_any(fuse.bias, fuse.bias_dtype, ra);
                 norm_w_v = load_any(fuse.norm_w, fuse.norm_w_dtype, ra);
             }
-            for (int c = c_lo; c < c_hi; ++c) {
-                const uint32_t off = (uint32_t)(c * TILE_A + row) * 4u;
-                float v[8];
+            // four tokens at a time: the loads of all of them (the splits' tiles through distributed shared
+            // memory, the residual stream from global memory) are on their way before the first sum
+            for (int cb = c_lo; cb < c_hi; cb += 4) {
+                float v[4][8], xin[4];
 #pragma unroll
-                for (int sp = 0; sp < 8; ++sp)
-                    if (sp < S) v[sp] = ld_cluster_f32(remote[sp] + off);
-                float acc = v[0];
+                for (int u = 0; u < 4; ++u) {
+                    const int c = cb + u;
+                    if (c < c_hi) {
+                        const uint32_t off = (uint32_t)(c * TILE_A + row) * 4u;
 #pragma unroll
-                for (int sp = 1; sp < 8; ++sp)
-                    if (sp < S) acc += v[sp];
-                if (fuse.x) {
-                    float sq = 0.f;
-                    if (ra < RA) {
-                        const size_t at = (size_t)(b0 + c) * (size_t)RA + ra;
-                        const float xv = fuse.x[at] + (acc + bias_v);
-                        fuse.x[at] = xv;
-                        fuse.h[at] = __float2bfloat16_rn(xv * norm_w_v);
-                        sq = xv * xv;
+                        for (int sp = 0; sp < 8; ++sp)
+                            if (sp < S) v[u][sp] = ld_cluster_f32(remote[sp] + off);
+                        if (fuse.x && ra < RA) xin[u] = __ldcg(fuse.x + (size_t)(b0 + c) * (size_t)RA + ra);
                     }
-                    sq = warp_sum(sq);
-                    if (lane == 0) warp_sq[(warp & 3) * BN + (c - c_lo)] = sq;
-                } else if (ra < RA) {
-                    out[(size_t)(b0 + c) * (size_t)RA + ra] = from_f32<OutT>(acc);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int c = cb + u;
+                    if (c >= c_hi) break;
+                    float acc = v[u][0];
+#pragma unroll
+                    for (int sp = 1; sp < 8; ++sp)
+                        if (sp < S) acc += v[u][sp];
+                    if (fuse.x) {
+                        float sq = 0.f;
+                        if (ra < RA) {
+                            const size_t at = (size_t)(b0 + c) * (size_t)RA + ra;
+                            const float xv = xin[u] + (acc + bias_v);
+                            fuse.x[at] = xv;
+                            fuse.h[at] = __float2bfloat16_rn(xv * norm_w_v);
+                            sq = xv * xv;
+                        }
+                        sq = warp_sum(sq);
+                        if (lane == 0) warp_sq[(warp & 3) * BN + (c - c_lo)] = sq;
+                    } else if (ra < RA) {
+                        out[(size_t)(b0 + c) * (size_t)RA + ra] = from_f32<OutT>(acc);
+                    }
                 }
             }
             if (fuse.x) {
