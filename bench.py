@@ -15,7 +15,7 @@ captured CUDA graph once the shape has been seen twice) and the argmax kernel.
             median repeat is reported, and every repeat with its median SM clock in ``repeats``
   e2e       the same through ``Engine.add_request`` / ``Engine.step``: host token ids in,
             sampled token ids back on the host every step
-  prefill   one step of 2,048 prompt tokens (flops / time / peak)
+  prefill   one step of 2,048 prompt tokens (flops / time / peak); --prefill-tokens N times a step of N instead
   roofline  bytes a decode step has to read (every weight it uses once, and the cache of
             the live requests) / its time, against the measured copy bandwidth
   points    decoded tokens per second at batch 1 and 64
@@ -185,25 +185,27 @@ def time_decode(model, cfg_json, layers, batch, steps, warmup, clocks, page_size
     return out
 
 
-def time_prefill(model, cfg_json, layers, reps, warmup, clocks, page_size):
+def time_prefill(model, cfg_json, layers, reps, warmup, clocks, page_size, tokens=PREFILL_TOKENS):
+    """One step of ``tokens`` prompt tokens of one request (the whole prompt: its attention runs over
+    ``tokens`` keys), median of ``reps``."""
     import torch
     from infero_b200.config import EngineConfig
     from infero_b200.engine import ModelRunner, StepEntry
     vocab = cfg_json["vocab_size"]
     rng = random.Random(77)
-    ecfg = EngineConfig(dtype="bfloat16", page_size=page_size, num_pages=2 * (-(-PREFILL_TOKENS // page_size)),
-                        max_seqs=2, ctx=PREFILL_TOKENS, max_batch_tokens=PREFILL_TOKENS, cuda_graphs=False)
+    ecfg = EngineConfig(dtype="bfloat16", page_size=page_size, num_pages=2 * (-(-tokens // page_size)),
+                        max_seqs=2, ctx=tokens, max_batch_tokens=tokens, cuda_graphs=False)
     runner = ModelRunner(model, ecfg)
     times = []
     for i in range(warmup + reps):
-        prompt = random_prompt(rng, vocab, PREFILL_TOKENS)
+        prompt = random_prompt(rng, vocab, tokens)
         runner.open("p")
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         if i >= warmup:
             clocks.on = True
         e0.record()
-        runner.step([StepEntry("p", prompt, [PREFILL_TOKENS - 1])])
+        runner.step([StepEntry("p", prompt, [tokens - 1])])
         e1.record()
         torch.cuda.synchronize()
         clocks.on = False
@@ -214,7 +216,7 @@ def time_prefill(model, cfg_json, layers, reps, warmup, clocks, page_size):
     torch.cuda.empty_cache()
     times.sort()
     ms = times[len(times) // 2]
-    return {"ms": ms, "flops": prefill_flops(cfg_json, layers, PREFILL_TOKENS)}
+    return {"ms": ms, "flops": prefill_flops(cfg_json, layers, tokens)}
 
 
 def time_e2e(model, cfg_json, batch, steps, warmup, clocks, page_size, repeats=REPEATS):
@@ -279,6 +281,8 @@ def main(argv=None) -> int:
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
+                    help="size of the timed prompt step (the contract's 2,048; 8,192 and more show attention over long contexts)")
     args = ap.parse_args(argv)
 
     if args.impl == "reference":
@@ -320,8 +324,8 @@ def main(argv=None) -> int:
             points[f"decode_b{b}_hbm_frac"] = round(r["bytes"] / (r["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"], 3)
     prefill = None
     if not args.skip_prefill:
-        r = time_prefill(model, cfg_json, layers, 5, 3, quiet, args.page_size)
-        prefill = {"value": round(PREFILL_TOKENS / (r["ms"] / 1e3), 1), "tokens": PREFILL_TOKENS,
+        r = time_prefill(model, cfg_json, layers, 5, 3, quiet, args.page_size, args.prefill_tokens)
+        prefill = {"value": round(args.prefill_tokens / (r["ms"] / 1e3), 1), "tokens": args.prefill_tokens,
                    "ms": round(r["ms"], 3),
                    "frac": round(r["flops"] / (r["ms"] / 1e3) / 1e12 / pk["bf16_tflops"], 4),
                    # frac is against the burst GEMM peak; the same against the sustained (power-capped) one
@@ -345,7 +349,7 @@ def main(argv=None) -> int:
                    "kv_heads": cfg_json["num_key_value_heads"], "head_dim": cfg_json["head_dim"],
                    "intermediate": cfg_json["intermediate_size"], "vocab": cfg_json["vocab_size"],
                    "page_size": args.page_size, "l2": "inputs larger than L2 (weights and cache)",
-                   "peaks": pk["source"], "prefill_tokens": PREFILL_TOKENS, "repeats": REPEATS,
+                   "peaks": pk["source"], "prefill_tokens": args.prefill_tokens, "repeats": REPEATS,
                    "timing": f"median of {REPEATS} regions of {steps} steps, each ending at {CONTEXT} tokens"},
         "e2e": e2e, "gpu_launches": main_pt["launches"], "clocks": main_clocks,
         "prefill": prefill,

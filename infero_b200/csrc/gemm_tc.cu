@@ -1170,13 +1170,27 @@ int infero_gemm_tc_summed(const void* x, const void* w, float* out, int M, int N
 #undef GO
 }
 
-// How the kernels below cut K: as infero_gemm_tc_plan, with at most 8 splits (the splits of a tile are one cluster).
+// How the kernels below cut K: as infero_gemm_tc_plan, but the splits of a tile are one cluster, so there
+// are at most 8, and no more than leave about a fifth of the multiprocessors' block slots free: a cluster
+// starts only when all of its blocks find room in one group of multiprocessors at once, and a grid that
+// fills the slots to the brim starts late, behind the blocks of the kernel in front as they drain
+// (measured at hidden 5120, 40 tiles: 7 splits = 280 blocks 6.58 ms per step, 6 splits = 240 blocks
+// 6.04 ms; at hidden 3584, 28 tiles, 8 splits = 224 blocks are the best).
 int infero_gemm_tc_plan_cluster(int M, int N, int K, int sm_count, int* splits, int* ktiles_per_split) {
     long long ws = 0;
     infero_gemm_tc_plan(M, N, K, sm_count, splits, ktiles_per_split, &ws);
-    if (*splits > MAX_CLUSTER) {
-        const int total_kt = (K + TILE_K - 1) / TILE_K;
-        *ktiles_per_split = (total_kt + MAX_CLUSTER - 1) / MAX_CLUSTER;
+    const int total_kt = (K + TILE_K - 1) / TILE_K;
+    const int tiles = (N + TILE_A - 1) / TILE_A;
+    const int slots = 2 * (sm_count > 0 ? sm_count : 148);
+    int cap = (int)(0.82 * slots) / tiles;
+    if (cap > MAX_CLUSTER) cap = MAX_CLUSTER;
+    if (cap < 1) cap = 1;
+    if (const char* e = getenv("INFERO_CLUSTER_SPLITS")) {        // tuning knob
+        const int want = atoi(e);
+        if (want >= 1 && want <= MAX_CLUSTER) cap = want;
+    }
+    if (*splits > cap) {
+        *ktiles_per_split = (total_kt + cap - 1) / cap;
         *splits = (total_kt + *ktiles_per_split - 1) / *ktiles_per_split;
     }
     return 0;

@@ -247,6 +247,18 @@ static bool fused_norm_wanted() {
     if (g_fused_norm < 0) g_fused_norm = env_on("INFERO_FUSED_NORM") ? 1 : 0;
     return g_fused_norm != 0;
 }
+// A product whose splits add up inside a cluster has at most 8 of them.  Where the plan without that limit
+// would cut K into many more (small matrices, whose products are bound by latency, not by bandwidth), the
+// cluster's blocks each stream twice as long and the norm kernel saved does not make up for it (measured at
+// hidden 896: 0.82 against 0.77 ms per step): the norm is then left as a kernel.
+static bool cluster_plan_ok(int T, int N, int K, int sm_count, int* splits, int* per) {
+    int ps = 1, pp = 1;
+    long long ws = 0;
+    infero_gemm_tc_plan(T, N, K, sm_count, &ps, &pp, &ws);
+    infero_gemm_tc_plan_cluster(T, N, K, sm_count, splits, per);
+    return *splits * 4 >= ps * 3;
+}
+
 // The two switches at run time (tests compare the folded launches with the separate ones).
 void infero_block_set_fusion(int fused_decode_on, int fused_norm_on) {
     g_fused_decode = fused_decode_on ? 1 : 0;
@@ -349,12 +361,11 @@ int infero_block_forward(const InferoBlock* b, const InferoStep* s, const int* b
     long long gu_ws = 0;
     infero_gemm_tc_plan(T, 2 * ff, d, s->sm_count, &gu_splits, &gu_per, &gu_ws);
     int rc;
-    if (fold_norms && gu_splits == 1) {
+    int o_splits = 1, o_per = 1;
+    if (fold_norms && gu_splits == 1 && cluster_plan_ok(T, d, da, s->sm_count, &o_splits, &o_per)) {
         // the output projection adds itself to x and leaves x * w and the sums of squares; the gate/up
         // product applies the norm's scalar to its own result before the activation
         float* ss_ffn = (float*)(A + p.sumsq[0]);
-        int o_splits, o_per;
-        infero_gemm_tc_plan_cluster(T, d, da, s->sm_count, &o_splits, &o_per);
         if (int rc2 = infero_gemm_tc_residual_norm(attn, b->w_o, T, d, da, da, o_splits, o_per, s->x, b->b_o, b->o_bias_dtype,
                                                    b->w_norm_ffn, b->norm_dtype, h, ss_ffn, s->stream))
             return rc2;
@@ -377,12 +388,12 @@ int infero_block_forward(const InferoBlock* b, const InferoStep* s, const int* b
     }
     if (rc) return rc;
     // ---- down projection -----------------------------------------------------------------------------
+    int dn_splits = 1, dn_per = 1;
     if (fold_norms && next && next->hidden == d && next->norm_dtype == b->norm_dtype &&
-        fused_decode(*next, *s, plan_arena(*next, T, s->sm_count))) {
+        fused_decode(*next, *s, plan_arena(*next, T, s->sm_count)) &&
+        cluster_plan_ok(T, d, ff, s->sm_count, &dn_splits, &dn_per)) {
         // the next layer is of the same kind and takes its input without its first norm's scalar
         float* ss_next = (float*)(A + p.sumsq[1]);
-        int dn_splits, dn_per;
-        infero_gemm_tc_plan_cluster(T, d, ff, s->sm_count, &dn_splits, &dn_per);
         if (int rc2 = infero_gemm_tc_residual_norm(act, b->w_down, T, d, ff, ff, dn_splits, dn_per, s->x, nullptr, F32,
                                                    next->w_norm_mixer, next->norm_dtype, h, ss_next, s->stream))
             return rc2;

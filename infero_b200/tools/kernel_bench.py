@@ -4,6 +4,8 @@
         [--reps N] [--hidden 3584 --heads 28 --kv-heads 4 --head-dim 128 --intermediate 18944]
 
 KERNEL: gemm_qkv | gemm_o | gemm_gate_up | gemm_down | gemm_head | attn_prefill | attn_decode
+        | attn_decode_fused (bias, rotary, cache append and attention from the q/k/v partial sums)
+        | gemm_o_norm | gemm_down_norm (the product adds itself to the residual stream and prepares the norm)
         | norm | rope | swiglu
 
 The kernel runs on several copies of its inputs (enough to exceed the L2 cache), back to back; a
@@ -58,7 +60,19 @@ def main(argv=None) -> int:
     name = args.kernel
     runs = []          # one callable per copy
     flops = bytes_ = 0.0
-    if name.startswith("gemm_"):
+    if name in ("gemm_o_norm", "gemm_down_norm"):
+        # few rows only: the cluster-summed product that updates the residual stream
+        T = min(T, 256) if args.tokens != 2048 else args.batch
+        N, Kd = (d, H * D) if name == "gemm_o_norm" else (d, ff)
+        n = _copies(N * Kd * 2, args.reps)
+        norm_w = rnd(d, dtype=torch.float32) + 1
+        for _ in range(n):
+            a, w = rnd(T, Kd), rnd(N, Kd, scale=0.02)
+            resid = rnd(T, N, dtype=torch.float32)
+            runs.append(lambda a=a, w=w, resid=resid: tc_gemm.residual_norm(a, w, resid, None, norm_w))
+        flops = 2.0 * T * N * Kd
+        bytes_ = 2.0 * (N * Kd + T * Kd) + 10.0 * T * N
+    elif name.startswith("gemm_"):
         N, Kd = {"gemm_qkv": ((H + 2 * Hkv) * D, d), "gemm_o": (d, H * D), "gemm_gate_up": (2 * ff, d),
                  "gemm_down": (d, ff), "gemm_head": (args.vocab, d)}[name]
         n = _copies(N * Kd * 2, args.reps)
@@ -74,10 +88,10 @@ def main(argv=None) -> int:
                 runs.append(lambda a=a, w=w, out=out: tc_gemm.gemm(a, w, None, out))
         flops = 2.0 * T * N * Kd
         bytes_ = 2.0 * (N * Kd + T * Kd + T * N)
-    elif name in ("attn_decode", "attn_prefill"):
+    elif name in ("attn_decode", "attn_prefill", "attn_decode_fused"):
         P = args.page_size
-        B = args.batch if name == "attn_decode" else 1
-        L = args.context if name == "attn_decode" else T
+        B = args.batch if name != "attn_prefill" else 1
+        L = args.context if name != "attn_prefill" else T
         blocks = -(-L // P)
         pages = B * blocks
         n = _copies(2 * pages * Hkv * P * D * 2, args.reps)
@@ -86,7 +100,18 @@ def main(argv=None) -> int:
             kc, vc = rnd(pages, Hkv, P, D), rnd(pages, Hkv, P, D)
             perm = torch.randperm(pages, generator=torch.Generator().manual_seed(c)).to(torch.int32)
             table = perm.view(B, blocks).to(dev).contiguous()
-            if name == "attn_decode":
+            if name == "attn_decode_fused":
+                width = (H + 2 * Hkv) * D
+                splits_in = tc_gemm.plan(B, width, d, dev)[0]
+                qkv = K.Partials(rnd(splits_in, B, width, dtype=torch.float32), rnd(width, dtype=torch.float32))
+                inv = (1e6 ** (-torch.arange(0, D, 2, dtype=torch.float64) / D)).to(torch.float32).to(dev)
+                out = torch.empty((B, H * D), dtype=bf, device=dev)
+                pos = torch.full((B,), L - 1, dtype=torch.int32, device=dev)
+                ent = torch.arange(B, dtype=torch.int32, device=dev)
+                chunk, splits = A.plan_decode(B, Hkv, H // Hkv, L)
+                runs.append(lambda qkv=qkv, out=out, kc=kc, vc=vc, table=table, ent=ent, pos=pos:
+                            A.decode_fused(qkv, out, kc, vc, table, ent, pos, inv, H, Hkv, D, P, None, scale, chunk, splits))
+            elif name == "attn_decode":
                 q = rnd(B, H * D)
                 out = torch.empty((B, H * D), dtype=bf, device=dev)
                 pos = torch.full((B,), L - 1, dtype=torch.int32, device=dev)
@@ -105,7 +130,7 @@ def main(argv=None) -> int:
                 runs.append(lambda q=q, out=out, kc=kc, vc=vc, table=table, ent=ent, pos=pos, a=e_start, b=e_len, c_=e_pos0:
                             A.attention_any(q, out, kc, vc, table, ent, pos, H, Hkv, D, P, None, scale,
                                             q_lens=[T], pos0=[0], entry_q_start=a, entry_q_len=b, entry_pos0=c_))
-        if name == "attn_decode":
+        if name != "attn_prefill":
             bytes_ = 2.0 * B * L * Hkv * D * 2
             flops = 4.0 * B * L * H * D
         else:
