@@ -193,21 +193,29 @@ def test_attention_mixer_alone(dt, window):
     assert worst <= TOL[dt], f"{worst:.3e}"
 
 
-@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
-def test_schedule_names_a_layer_twice_and_shares_a_cache(dt):
+@pytest.mark.parametrize("dt,sizes", [(torch.float32, dict(H=6, Hkv=2, D=48, d=80, ff=144)),
+                                      (torch.bfloat16, dict(H=6, Hkv=2, D=48, d=80, ff=144)),
+                                      # head size 64: the bf16 steps go through the native launcher, and the steps
+                                      # of single tokens through the fused decode attention (which appends nothing
+                                      # in the read-only execution) and the folded norms
+                                      (torch.bfloat16, dict(H=4, Hkv=2, D=64, d=128, ff=320))],
+                         ids=["float32", "bfloat16", "bfloat16-serving-kernels"])
+def test_schedule_names_a_layer_twice_and_shares_a_cache(dt, sizes):
     """Three executions of two blocks: block 0, block 1, block 0 again; the third execution reads
     the cache the first one filled and writes nothing."""
     from infero_b200.config.spec import ScheduleEntry
     from infero_b200.engine import StepEntry
+    from infero_b200.parts import native_block as NB
     sched = (ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(0, 0, write_cache=False))
-    spec = _spec(layers=2, schedule=sched)
+    spec = _spec(layers=2, schedule=sched, **sizes)
     model, runner, w = _build(spec, dt)
     assert model.spec.num_cache_slots() == 2
+    native_before = NB.CALLS[0]
     toks = [int(t) for t in torch.randint(0, 300, (45,), generator=torch.Generator().manual_seed(5))]
     # plain: run the layers in that order; a read-only execution attends over the keys of the
     # first execution's input
-    cfg = {"num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 48, "hidden_size": 80,
-           "rms_norm_eps": 2e-5, "rope_theta": 5000.0}
+    cfg = {"num_attention_heads": sizes["H"], "num_key_value_heads": sizes["Hkv"], "head_dim": sizes["D"],
+           "hidden_size": sizes["d"], "rms_norm_eps": 2e-5, "rope_theta": 5000.0}
     x = w["model.embed_tokens.weight"][torch.tensor(toks)]
     pos = torch.arange(len(toks))
     x1 = P.decoder_layer(x, w, cfg, 0, pos)
@@ -220,6 +228,8 @@ def test_schedule_names_a_layer_twice_and_shares_a_cache(dt):
     got += [runner.step([StepEntry("r", [t], [0])]) for t in toks[41:]]
     got = torch.cat(got)
     assert _rel(got, ref) <= TOL[dt] * 1.5
+    if sizes["D"] == 64:
+        assert NB.CALLS[0] - native_before == 3 * 6, "every execution of every step should have gone the native way"
 
 
 def _layer_reading_cache(x, x_keys, w, cfg, i, pos):
