@@ -85,6 +85,53 @@ __device__ __forceinline__ void merge_if_last(int* counter, float* wbuf, const f
     __syncthreads();
     if (!s_last) return;
     __threadfence();
+    if (n_splits <= 16 && (reinterpret_cast<uintptr_t>(out_rows) & 15u) == 0) {
+        // Up to 16 splits: one round of loads.  Every thread takes eight columns of a row and asks for the
+        // row's (m, l) of every split and for its columns of every split's partial result at once, works the
+        // weights out itself (the threads of a row all do, from the same values) and sums in ascending order.
+        for (int idx = threadIdx.x; idx < valid * (D / 8); idx += TD_THREADS) {
+            const int r = idx / (D / 8), d = (idx - r * (D / 8)) * 8;
+            const float2* ml = reinterpret_cast<const float2*>(pml_base) + (size_t)r * n_splits;
+            const float* pob = po_base + (size_t)r * n_splits * D + d;
+            float2 mls[16];
+            float4 v[16][2];
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+                if (k < n_splits) {
+                    mls[k] = __ldcg(ml + k);
+                    v[k][0] = __ldcg(reinterpret_cast<const float4*>(pob + (size_t)k * D));
+                    v[k][1] = __ldcg(reinterpret_cast<const float4*>(pob + (size_t)k * D + 4));
+                } else {
+                    mls[k] = make_float2(-CUDART_INF_F, 0.f);
+                    v[k][0] = v[k][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
+            float M = -CUDART_INF_F;
+#pragma unroll
+            for (int k = 0; k < 16; ++k) M = fmaxf(M, mls[k].x);
+            float L = 0.f, a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+                // a split without keys wrote (-inf, 0) and no result: left out, not multiplied by zero
+                const float ws = (k >= n_splits || mls[k].x == -CUDART_INF_F) ? 0.f : exp2f(mls[k].x - M);
+                if (ws != 0.f) {
+                    L = fmaf(mls[k].y, ws, L);
+                    a[0] = fmaf(v[k][0].x, ws, a[0]); a[1] = fmaf(v[k][0].y, ws, a[1]);
+                    a[2] = fmaf(v[k][0].z, ws, a[2]); a[3] = fmaf(v[k][0].w, ws, a[3]);
+                    a[4] = fmaf(v[k][1].x, ws, a[4]); a[5] = fmaf(v[k][1].y, ws, a[5]);
+                    a[6] = fmaf(v[k][1].z, ws, a[6]); a[7] = fmaf(v[k][1].w, ws, a[7]);
+                }
+            }
+            const float inv = 1.0f / L;
+            uint4 w4;
+            w4.x = pack_bf16(a[0] * inv, a[1] * inv);
+            w4.y = pack_bf16(a[2] * inv, a[3] * inv);
+            w4.z = pack_bf16(a[4] * inv, a[5] * inv);
+            w4.w = pack_bf16(a[6] * inv, a[7] * inv);
+            *reinterpret_cast<uint4*>(out_rows + (size_t)r * D + d) = w4;
+        }
+        return;
+    }
     // Everything below waits on reads from L2, so each phase issues all of its loads at once.
     // (m, l) of every row and split in one go
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
