@@ -75,16 +75,17 @@ template <int D>
 __device__ __forceinline__ void merge_if_last(int* counter, float* wbuf, const float* po_base, const float* pml_base,
                                               int n_splits, int valid, bf16* out_rows) {
     __shared__ int s_last;
-    __threadfence();                                   // this thread's partial results, before the count
-    __syncthreads();
+    __syncthreads();                                   // every thread's partial results are written ...
     if (threadIdx.x == 0) {
-        const int old = atomicAdd(counter, 1);
+        // ... and one release-and-acquire count publishes them and takes in those of the blocks before
+        // (a release by one thread after a barrier covers what the block's other threads wrote)
+        int old;
+        asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(old) : "l"(counter) : "memory");
         s_last = old == n_splits - 1;
         if (s_last) *counter = 0;
     }
     __syncthreads();
     if (!s_last) return;
-    __threadfence();
     if (n_splits <= 16 && (reinterpret_cast<uintptr_t>(out_rows) & 15u) == 0) {
         // Up to 16 splits: one round of loads.  Every thread takes eight columns of a row and asks for the
         // row's (m, l) of every split and for its columns of every split's partial result at once, works the
