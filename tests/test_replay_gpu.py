@@ -247,6 +247,35 @@ def test_captured_decode_steps_equal_eager_ones(name, dtype):
     torch.cuda.synchronize()
 
 
+@pytest.mark.parametrize("name", SERVING_PATH)
+@pytest.mark.parametrize("n_live", [20, 40])
+def test_steps_of_many_single_tokens(name, n_live):
+    """Twenty and forty requests decoding together in bfloat16 (the token-side tile of the few-token products
+    is then 32 and 64 wide, and a CTA of a cluster-summed product sums several tokens), eager and captured,
+    against the plain implementation."""
+    import torch
+    from infero_b200.engine import StepEntry
+    mdir = model_dir(name)
+    lens = [14 + (7 * i) % 23 for i in range(n_live)]
+    reqs = make_requests(name, lens, seed=55)
+    plain = plain_logits(mdir, reqs)
+    runner = make_runner(mdir, "bfloat16", 64 * n_live, max_seqs=n_live, cuda_graphs=True)
+    head = 6
+    for rid, toks in reqs.items():
+        runner.open(rid)
+        runner.step([StepEntry(rid, toks[:head], [])])
+    worst = 0.0
+    with ServingPath(name, "bfloat16"):
+        for p in range(head, 14):                       # every request is live throughout: the batch keeps its size
+            logits = runner.step([StepEntry(rid, [toks[p]], [0]) for rid, toks in reqs.items()])
+            got = logits.float().cpu().numpy()
+            for i, rid in enumerate(reqs):
+                worst = max(worst, float(np.abs(got[i] - plain[rid][p]).max() / np.abs(plain[rid]).max()))
+    assert runner.graph_replays >= 5
+    assert worst <= TOL["bfloat16"], f"{name}, {n_live} requests: relative error {worst:.3e}"
+    torch.cuda.synchronize()
+
+
 @pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
 def test_captured_steps_padded_to_a_size(dtype):
     """A batch of five single tokens runs as the captured step of six, of which one entry belongs
