@@ -509,33 +509,31 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         red_ml[((size_t)warp * 16 + g + 8) * 2 + 1] = l1;
     }
     __syncthreads();
-    // per row: the common maximum, each warp's factor 2^(m_w - max) and the row's (m, l), once
-    float* red_f = red_ml + TD_WARPS * 16 * 2;                        // [4 warps][16 rows]
-    if (threadIdx.x < valid) {
-        const int r = threadIdx.x;
-        float mm = -CUDART_INF_F;
-#pragma unroll
-        for (int w = 0; w < TD_WARPS; ++w) mm = fmaxf(mm, red_ml[((size_t)w * 16 + r) * 2]);
-        float ll = 0.f;
-#pragma unroll
-        for (int w = 0; w < TD_WARPS; ++w) {
-            const float mw = red_ml[((size_t)w * 16 + r) * 2];
-            const float f = mw == -CUDART_INF_F ? 0.f : exp2f(mw - mm);
-            red_f[w * 16 + r] = f;
-            ll += red_ml[((size_t)w * 16 + r) * 2 + 1] * f;
-        }
-        pml[(size_t)r * n_splits * 2] = mm;
-        pml[(size_t)r * n_splits * 2 + 1] = ll;
-    }
-    __syncthreads();
+    // per row: the common maximum and each warp's factor 2^(m_w - max); every thread works them out for the
+    // row of its own columns (four values from shared memory), the thread at the row's first columns also
+    // writes the row's (m, l)
     for (int idx = threadIdx.x; idx < valid * (D / 4); idx += TD_THREADS) {
         const int r = idx / (D / 4), d = (idx - r * (D / 4)) * 4;
+        float mw[TD_WARPS], f[TD_WARPS], mm = -CUDART_INF_F;
+#pragma unroll
+        for (int w = 0; w < TD_WARPS; ++w) {
+            mw[w] = red_ml[((size_t)w * 16 + r) * 2];
+            mm = fmaxf(mm, mw[w]);
+        }
+#pragma unroll
+        for (int w = 0; w < TD_WARPS; ++w) f[w] = mw[w] == -CUDART_INF_F ? 0.f : exp2f(mw[w] - mm);
+        if (d == 0) {
+            float ll = 0.f;
+#pragma unroll
+            for (int w = 0; w < TD_WARPS; ++w) ll += red_ml[((size_t)w * 16 + r) * 2 + 1] * f[w];
+            pml[(size_t)r * n_splits * 2] = mm;
+            pml[(size_t)r * n_splits * 2 + 1] = ll;
+        }
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int w = 0; w < TD_WARPS; ++w) {
-            const float f = red_f[w * 16 + r];
             const float4 v = *reinterpret_cast<const float4*>(red_o + ((size_t)w * 16 + r) * RS + d);
-            acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
+            acc.x += v.x * f[w]; acc.y += v.y * f[w]; acc.z += v.z * f[w]; acc.w += v.w * f[w];
         }
         *reinterpret_cast<float4*>(po + (size_t)r * n_splits * D + d) = acc;
     }
