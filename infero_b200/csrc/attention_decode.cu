@@ -330,8 +330,10 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         const float* src_row = fq.partial + (size_t)t * fq.row_width;
         float rstd = 1.0f;
         if (fq.sumsq_in) {
+            // the tiles' sums in one round of loads: a lane per tile, added up across the warp
             float ss = 0.f;
-            for (int tl = 0; tl < fq.in_tiles; ++tl) ss += __ldcg(fq.sumsq_in + (size_t)tl * 256 + t);
+            for (int tl = lane; tl < fq.in_tiles; tl += 32) ss += __ldcg(fq.sumsq_in + (size_t)tl * 256 + t);
+            ss = warp_sum(ss);
             rstd = 1.0f / sqrtf(ss * fq.inv_d + fq.eps);
         }
         auto sum4 = [&](size_t col, float* v) {
