@@ -9,7 +9,10 @@
 // on mma.sync (s = q k^T, p = 2^(s - m), o += p v) and refills the stage.  Nothing but the
 // TMA issue touches addresses, so the loop is a few hundred instructions per 8 KB of cache.
 // The four warps are merged in shared memory and the CTA writes an unnormalised partial
-// result (o, m, l) per query head; attn_combine merges the splits.
+// result (o, m, l) per query head; the CTA that arrives last for a (token, kv head) merges the
+// splits (attn_combine does when there are more groups of splits than arrival counters).
+// In steps of single tokens a second instance of the kernel (FUSED) also finishes the q/k/v
+// product in front of it: bias, rotary positions and the cache append (see the kernel).
 //
 // The cache of one layer is seen as a matrix [pages * kv_heads * page_size, head_dim]; a slice
 // of 16 keys is 16 consecutive rows of it (page_size is a multiple of 16).  Head sizes: 64 and

@@ -1,8 +1,11 @@
 // One layer of the built-in kind (pre-norm block: RMSNorm, grouped-query attention with rotary
-// positions over the paged cache, RMSNorm, SwiGLU) launched from native code: the same kernels with
-// the same arguments, in the same order, as the Python parts launch them one by one, so the results
-// are the same bit for bit; only the host's time per layer differs (one call instead of a dozen
-// Python wrappers).  bf16 steps on the tensor-core path only; everything else stays with the parts.
+// positions over the paged cache, RMSNorm, SwiGLU) launched from native code.  In steps with a prompt
+// portion: the same kernels with the same arguments, in the same order, as the Python parts launch
+// them one by one, so the results are the same bit for bit and only the host's time per layer
+// differs (one call instead of a dozen Python wrappers).  In steps of single tokens, where a launch
+// costs more than its work, the layer is five launches instead of eight: decode attention finishes
+// the q/k/v product itself, and the two norms are folded into the products around them (see
+// infero_block_forward).  bf16 steps on the tensor-core path only; everything else stays with the parts.
 //
 // The reference runs its whole layer loop natively (crates/model/src/lib.rs:3423-4243); this is
 // the corresponding piece for the one layout of block this engine builds itself.
