@@ -2,11 +2,14 @@
 
 ``PreNormBlock`` made of exactly the package's own parts (RMSNorm, grouped-query attention with
 NeoX rotary positions or none, SwiGLU) in a bf16 step can hand its whole layer to
-``infero_block_forward`` (``csrc/host_block.cpp``): the same kernels with the same arguments in
-the same order as the parts launch one by one, so the results are the same bit for bit; what
-changes is the host's time per layer (one call instead of a dozen wrappers), which is what bounds
-steps that are not replayed from a CUDA graph.  Any other block, dtype or part keeps to the parts'
-own ``forward``.  ``INFERO_NATIVE_BLOCK=0`` turns it off.
+``infero_block_forward`` (``csrc/host_block.cpp``).  In steps with a prompt portion that call launches
+the same kernels with the same arguments in the same order as the parts launch one by one, so the
+results are the same bit for bit; what changes is the host's time per layer (one call instead of a
+dozen wrappers), which is what bounds steps that are not replayed from a CUDA graph.  In steps of
+single tokens the native layer is made of fewer launches than the parts' (decode attention finishes
+the q/k/v product itself; the norms are folded into the products around them, see ``set_fusion``).
+Any other block, dtype or part keeps to the parts' own ``forward``.  ``INFERO_NATIVE_BLOCK=0`` turns
+it off.
 
 The reference runs its layer loop natively throughout (crates/model/src/lib.rs:3423-4243).
 """
