@@ -17,6 +17,8 @@
 
 extern "C" {
 // elementwise.cu, rope_cache.cu, gemm_tc.cu, attention_*.cu, runtime.cu
+int infero_embed_gather(const void* table, int table_dtype, const int* ids, const int* device_tokens, float* x,
+                        int n_tokens, int d, int vocab, float scale, cudaStream_t stream);
 int infero_add_rmsnorm(float* x, const void* delta, int delta_dtype, int delta_splits, long long split_stride,
                        const void* dbias, int dbias_dtype, const void* w, int w_dtype, float eps, void* out,
                        int out_dtype, const int* rows, int n_rows, int d, cudaStream_t stream);
@@ -404,6 +406,55 @@ int infero_block_forward(const InferoBlock* b, const InferoStep* s, const int* b
         return 0;
     }
     return product(*s, act, ff, b->w_down, d, nullptr, F32, A + p.delta[layer_parity & 1], delta, true);
+}
+
+// The whole model in one call: embedding, the schedule of built-in blocks, the final norm on the rows whose
+// logits are wanted, the output product.  What ``DecoderModel.forward`` does when every entry of its
+// schedule is a built-in block that goes the native way, launch for launch (the same functions with the
+// same arguments), so the logits are the same bit for bit; the host's share of a step that is not replayed
+// from a CUDA graph drops from a Python call per layer to this one call.  The reference runs its layer
+// loop natively too (crates/model/src/lib.rs:3423-4243).
+struct InferoDecoder {
+    int n_entries;                  // executions of blocks, in the order they run
+    const InferoBlock* blocks;      // one descriptor per execution (bound to its cache slot)
+    const int* entry_group;         // which block table each execution reads
+    const void* embed;              // [vocab, hidden]
+    int embed_dtype, vocab, hidden;
+    float embed_scale;
+    const void* final_norm_w;
+    int final_norm_dtype;
+    float final_eps;
+    const void* head_w;             // [vocab, hidden] bf16 (the embedding itself when tied)
+    const void* head_bias;          // or null
+    int head_bias_dtype;
+};
+
+// tables: one block table per layer group [n_entries of the step, max_blocks].  rows (n_rows of them, may be
+// none): the step's rows whose logits are wanted; h_rows: bf16 [n_rows, hidden] scratch; logits: float
+// [n_rows, vocab]; head_ws: what infero_gemm_tc_plan asks for the output product (may be null when nothing).
+int infero_decoder_forward(const InferoDecoder* m, const InferoStep* s, const int* token_ids, const int* device_tokens,
+                           const int* const* tables, int max_blocks, const int* rows, int n_rows, void* h_rows,
+                           float* logits, void* head_ws, long long head_ws_bytes) {
+    const int T = s->n_tokens;
+    if (T == 0) return 0;
+    if (int rc = infero_embed_gather(m->embed, m->embed_dtype, token_ids, device_tokens, s->x, T, m->hidden, m->vocab,
+                                     m->embed_scale, s->stream))
+        return rc;
+    InferoDelta delta = {};
+    for (int i = 0; i < m->n_entries; ++i) {
+        const InferoBlock* next = i + 1 < m->n_entries ? &m->blocks[i + 1] : nullptr;
+        if (int rc = infero_block_forward(&m->blocks[i], s, tables[m->entry_group[i]], max_blocks, i & 1, &delta, next))
+            return rc;
+    }
+    if (n_rows == 0) return 0;
+    const bool pending = delta.data && delta.dtype != PRENORMED;
+    if (int rc = infero_add_rmsnorm(s->x, pending ? delta.data : nullptr, pending ? delta.dtype : F32,
+                                    pending ? delta.splits : 1, pending ? delta.split_stride : 0,
+                                    pending ? delta.bias : nullptr, delta.bias_dtype, m->final_norm_w, m->final_norm_dtype,
+                                    m->final_eps, h_rows, BF16, rows, n_rows, m->hidden, s->stream))
+        return rc;
+    return infero_gemm_tc(h_rows, m->head_w, m->head_bias, m->head_bias_dtype, logits, F32, n_rows, m->vocab, m->hidden,
+                          m->hidden, m->vocab, head_ws, head_ws_bytes, s->sm_count, 0, s->stream);
 }
 
 }  // extern "C"

@@ -27,6 +27,7 @@ class DecoderModel:
         self.final_norm = part_class("norm", spec.final_norm.kind)(spec.final_norm, spec.final_norm_name)
         self.embed: Optional[torch.Tensor] = None
         self.head: Optional[Linear] = None
+        self._native = None                  # the native launcher of a whole step, made at first use
         for e in spec.schedule:
             if not (0 <= e.block < len(self.blocks)):
                 raise ValueError(f"schedule names block {e.block}, model has {len(self.blocks)}")
@@ -107,6 +108,13 @@ class DecoderModel:
         """token_ids int32 [T] on the device; logit_rows int32 [R] (indices into the T tokens)
         or None.  Returns float32 logits [R, vocab], or None when no row is wanted."""
         s = self.spec
+        native = self._native
+        if native is None:
+            from .native_decoder import NativeDecoder
+            native = self._native = NativeDecoder(self)
+        out = native.run(ctx, token_ids, logit_rows)      # the whole step in one native call, where it applies
+        if out is not NotImplemented:
+            return out
         T = token_ids.numel()
         x = torch.empty((T, s.hidden), dtype=torch.float32, device=token_ids.device)
         K.embed_gather(self.embed, token_ids, x, s.embed_scale, getattr(ctx, "device_tokens", None))

@@ -274,9 +274,13 @@ def test_native_block_launcher_changes_nothing(window, shape):
     toks = {r: [int(t) for t in torch.randint(0, 400, (n,), generator=torch.Generator().manual_seed(s))]
             for r, n, s in (("a", 300, 1), ("b", 41, 2), ("c", 7, 3))}
 
-    def run(native, fold_norms=False):
+    from infero_b200.models import native_decoder as ND
+
+    def run(native, fold_norms=False, whole_step=False):
         NB.set_enabled(native)
         NB.set_fusion(True, fold_norms)
+        ND.set_enabled(whole_step)
+        steps_before = ND.CALLS[0]
         try:
             model, runner, _ = _build(spec, torch.bfloat16, pages=40)
             before = NB.CALLS[0]
@@ -288,17 +292,27 @@ def test_native_block_launcher_changes_nothing(window, shape):
                                 StepEntry("c", toks["c"], [6])]),                                # decodes beside a prompt
                    runner.step([StepEntry("a", toks["a"][291:292], [0])]),
                    runner.step([StepEntry("a", toks["a"][292:293], [0]), StepEntry("b", [7], [0])])]   # single tokens only
+            assert ND.CALLS[0] - steps_before == (5 if whole_step else 0)
             return [o.float().cpu() for o in out], NB.CALLS[0] - before
         finally:
             NB.set_enabled(True)
             NB.set_fusion(True, True)
+            ND.set_enabled(True)
 
     plain, n_plain = run(False)
     native, n_native = run(True)
     assert n_plain == 0 and n_native == 5 * 3, "every layer of every step should have gone the native way"
     for a, b in zip(plain, native):
         assert torch.equal(a, b)
+    # the whole step in one native call: launch for launch what the loop over blocks does
+    whole, n_whole = run(True, whole_step=True)
+    assert n_whole == 5 * 3
+    for a, b in zip(plain, whole):
+        assert torch.equal(a, b)
+    folded_whole, _ = run(True, fold_norms=True, whole_step=True)
     folded, _ = run(True, fold_norms=True)
+    for a, b in zip(folded, folded_whole):
+        assert torch.equal(a, b)
     for a, b in zip(plain[:3], folded[:3]):            # steps with a prompt portion: nothing is folded
         assert torch.equal(a, b)
     # two bf16 paths whose roundings fall in different places (bf16(x * rstd * w) against bf16(x * w) * rstd):
