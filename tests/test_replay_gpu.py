@@ -248,11 +248,12 @@ def test_captured_decode_steps_equal_eager_ones(name, dtype):
 
 
 @pytest.mark.parametrize("name", SERVING_PATH)
-@pytest.mark.parametrize("n_live", [20, 40])
+@pytest.mark.parametrize("n_live", [20, 40, 300])
 def test_steps_of_many_single_tokens(name, n_live):
     """Twenty and forty requests decoding together in bfloat16 (the token-side tile of the few-token products
     is then 32 and 64 wide, and a CTA of a cluster-summed product sums several tokens), eager and captured,
-    against the plain implementation."""
+    against the plain implementation; and three hundred, which is more rows than the few-token kernels take
+    and more entries than a captured step holds: single tokens through the many-token products."""
     import torch
     from infero_b200.engine import StepEntry
     mdir = model_dir(name)
@@ -271,7 +272,7 @@ def test_steps_of_many_single_tokens(name, n_live):
             got = logits.float().cpu().numpy()
             for i, rid in enumerate(reqs):
                 worst = max(worst, float(np.abs(got[i] - plain[rid][p]).max() / np.abs(plain[rid]).max()))
-    assert runner.graph_replays >= 5
+    assert runner.graph_replays >= 5 or n_live > runner.MAX_GRAPH_ENTRIES
     assert worst <= TOL["bfloat16"], f"{name}, {n_live} requests: relative error {worst:.3e}"
     torch.cuda.synchronize()
 

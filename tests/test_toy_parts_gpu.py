@@ -176,6 +176,22 @@ def test_a_routed_feed_forward_and_another_position_encoding_plug_in():
     _replay(TOY, "float32", 2e-5)
 
 
+def test_toy_layers_between_layers_that_native_code_launches():
+    """bf16 at the head size the serving kernels take: layers that go through the native launcher (folded
+    norms and the fused decode attention in the steps of single tokens) around a layer with another position
+    encoding, which keeps to its parts (it rounds q and k to bf16 before it turns them, so a model of
+    several such layers drifts further from the 64-bit statement than the built-in layers do).  What a native layer leaves pending must reach a Python layer in a
+    form it can take, and the other way round.  (No routed feed-forward here: in bf16 a near-tie between two
+    experts may fall the other way, which is no fault of either path.)"""
+    from infero_b200.parts import native_block as NB
+    cfg = dict(TOY, width=128, heads=2, kv_heads=1, head=64, inner=320,
+               layers=[["rope_neox", "swiglu"], ["rope_neox", "swiglu"], ["adjacent_pairs", "swiglu"],
+                       ["rope_neox", "swiglu"]])
+    before = NB.CALLS[0]
+    _replay(cfg, "bfloat16", 3e-2)
+    assert NB.CALLS[0] > before, "no layer went through the native launcher"
+
+
 def test_another_position_encoding_in_bfloat16():
     """The in-place form of a position encoding on the bf16 path (q and k are then materialised
     from the split-K sums before the cache append)."""
